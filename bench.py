@@ -1,0 +1,386 @@
+#!/usr/bin/env python
+"""Benchmark of the int8 quantized-convolution path.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+One step = one pass of the hot path (quantize -> conv2d_quantized + add_bias + ReLU, fp32 NCHW output) over the
+batch-32 shape sweep (five layers; see tennis_b200/workloads.py CONFIG1) on synthetic seeded inputs.  With
+N > 1 every rank owns one GPU and runs the same sweep on its own shard (per-rank seed); there is no
+data-path collective, only the barrier and the max-over-ranks of the device time.
+
+Prints ONE JSON line (rank 0):
+  value        int8 TOPS of the whole job, inputs resident in HBM, device time from CUDA events
+  e2e          the same metric through the host-buffer C-ABI call (H2D of the fp32 input and D2H of the fp32
+               output inside the timed region, pinned host memory)
+  roofline     the dominant kernel (tcgen05 implicit-GEMM convolution): algorithmic ops / measured launch time
+  cpu_baseline the reference's own CPU operators (oracle/_ref) or the C port, timed on this box's host cores
+               on a bounded sample
+--impl reference times that CPU path alone and prints the same line shape.
+"""
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "int8_conv_tops"
+UNIT = "TOPS"
+WORKLOAD = "config1: int8 conv2d shape sweep, batch 32 (1x1 256->1024@14, 3x3 128->128@28, 3x3/2 256->512@28, 1x1 2048->512@7, 7x7/2 3->64@224), fp32 NCHW out, bias+ReLU"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-budget-s", type=float, default=20.0, help="host seconds the cpu_baseline sample may take")
+    return ap.parse_args()
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm_gbs=p["hbm_gbs"], bf16_tflops=p["bf16_tflops"], bf16_tflops_sustained=p["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+# -------------------------------------------------------------------------------------------------------
+# CPU arm (the reference's own operators where oracle/_ref exists, else the C port)
+# -------------------------------------------------------------------------------------------------------
+def cpu_sample(layers, images, workers, checker):
+    """Seconds for one pass of `images` samples of every layer on `workers` host threads."""
+    import numpy as np
+    from tennis_b200 import workloads
+    total = 0.0
+    for layer in layers:
+        small = dict(layer, n=images)
+        d = workloads.make_layer_data(small, seed=0)
+        pad = (layer["pad"],) * 4
+        if checker.kind == "reference":
+            sec, _ = checker.time_layer(d["x"], d["w"], pad, (layer["stride"],) * 2, (layer["dilation"],) * 2,
+                                        float(d["qscale"]), d["dq"], d["bias"], act=1, workers=workers, repeats=1)
+        else:
+            t0 = time.perf_counter()
+            xq = checker.quantize(d["x"], [float(d["qscale"])] * images)
+            checker.conv_block(xq, d["w"], pad, (layer["stride"],) * 2, (layer["dilation"],) * 2, d["dq"], d["bias"], act="relu")
+            sec = time.perf_counter() - t0
+        total += sec
+    return total
+
+
+def cpu_arm(layers):
+    from oracle import oracle as orc
+    from tennis_b200 import workloads
+    orc.build() if not os.path.exists(os.path.join(ROOT, "oracle", "liboracle.so")) else None
+    checker = orc.best()
+    cores = os.cpu_count() or 1
+    # the reference's int8 GEMM is serial inside one Workbench; all host cores are used by running one
+    # Workbench per core on its own samples.  The C port parallelises inside one call with OpenMP.
+    workers = cores if checker.kind == "reference" else 1
+    images = 1
+    ops_per_pass = sum(workloads.layer_ops(dict(l, n=images)) for l in layers) * workers
+    return checker, cores, workers, images, ops_per_pass
+
+
+def run_reference(args):
+    from tennis_b200 import workloads
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    layers = workloads.CONFIG1
+    checker, cores, workers, images, ops_per_pass = cpu_arm(layers)
+    budget = 150.0
+    for _ in range(min(args.warmup, 1)):
+        cpu_sample(layers, images, workers, checker)
+    times = []
+    t_begin = time.perf_counter()
+    for _ in range(args.steps):
+        times.append(cpu_sample(layers, images, workers, checker))
+        if time.perf_counter() - t_begin > budget:
+            break
+    sec = sum(times) / len(times)
+    value = ops_per_pass / sec / 1e12
+    sample = "%d image(s) of each of the 5 layers per worker, %d worker(s) (%s), %d of %d steps timed" % (
+        images, workers, "one Workbench with 1 computing thread per host core" if checker.kind == "reference" else "OpenMP inside the port",
+        len(times), args.steps)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "steps_timed": len(times), "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores if checker.kind == "reference" else cores,
+                         "kind": checker.kind, "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# -------------------------------------------------------------------------------------------------------
+# GPU arm
+# -------------------------------------------------------------------------------------------------------
+class ClockSampler(threading.Thread):
+    """Polls SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index = index
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+        self.stop_flag = threading.Event()
+        self.error = None
+
+    def run(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+            names = {
+                getattr(pynvml, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+                getattr(pynvml, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+                getattr(pynvml, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+                getattr(pynvml, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+            }
+            get_reasons = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+            while not self.stop_flag.is_set():
+                self.samples.append(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
+                mask = get_reasons(h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+                time.sleep(0.01)
+        except Exception as e:  # NVML missing: report it, do not fail the benchmark
+            self.error = repr(e)
+
+    def summary(self):
+        d = {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+             "reasons": sorted(self.reasons), "samples": len(self.samples)}
+        if self.error:
+            d["error"] = self.error
+        return d
+
+
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from tennis_b200 import _lib, ops, workloads
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _lib.load()
+    warmup = max(args.warmup, 3)
+    layers = workloads.CONFIG1
+    peaks = measured_peaks()
+
+    # ---- resident state: inputs, weights, plans, outputs ----
+    state = []
+    for layer in layers:
+        d = workloads.make_layer_data(layer, seed=rank)  # per-shard seed
+        x = torch.from_numpy(d["x"]).to(dev)
+        w = torch.from_numpy(d["w"]).to(dev)
+        pad = (layer["pad"],) * 4
+        plan = ops.ConvPlan(x.shape, w.shape, pad, (layer["stride"],) * 2, (layer["dilation"],) * 2, 0.0, _lib.KERNEL_AUTO, dev)
+        plan.set_weights(w)
+        tc = plan.kernel == _lib.KERNEL_TCGEN05
+        cp = ops.padded_channels(layer["c"])
+        xq = torch.empty((layer["n"], layer["h"], layer["w"], cp) if tc else x.shape, dtype=torch.int8, device=dev)
+        state.append(dict(layer=layer, d=d, x=x, w=w, plan=plan, tc=tc, xq=xq,
+                          scales=_lib.float_array([float(d["qscale"])] * layer["n"]),
+                          dq=torch.from_numpy(d["dq"]).to(dev), bias=torch.from_numpy(d["bias"]).to(dev),
+                          out=torch.empty(plan.out_shape, dtype=torch.float32, device=dev)))
+
+    def sptr():
+        return ops._stream_ptr()
+
+    def quantize(s):
+        l = s["layer"]
+        if s["tc"]:
+            _lib.check(lib.tsb_quantize_f32_nchw_to_nhwc(s["x"].data_ptr(), s["xq"].data_ptr(), l["n"], l["c"], l["h"], l["w"],
+                                                         s["scales"], l["n"], sptr()))
+        else:
+            _lib.check(lib.tsb_quantize_f32_i8(s["x"].data_ptr(), s["xq"].data_ptr(), s["x"].numel(), s["scales"], l["n"], sptr()))
+
+    def conv(s):
+        s["plan"].run(s["xq"], _lib.LAYOUT_NHWC_PAD if s["tc"] else _lib.LAYOUT_NCHW, s["dq"], bias=s["bias"],
+                      activation=_lib.ACT_RELU, out_f32=s["out"])
+
+    def step():
+        for s in state:
+            quantize(s)
+            conv(s)
+
+    flush_buf = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)  # > 126 MB of L2
+
+    def flush_l2():
+        flush_buf.fill_(1)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warmup):
+        step()
+    for s in state:
+        s["plan"].status()
+    barrier()
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+
+    # ---- timed region: exactly K steps, device time by CUDA events around each step, L2 flushed in between ----
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    launches0 = lib.tsb_kernel_launch_count()
+    barrier()
+    wall0 = time.perf_counter()
+    for k in range(args.steps):
+        flush_l2()
+        starts[k].record()
+        step()
+        ends[k].record()
+    barrier()
+    wall = time.perf_counter() - wall0
+    launches = lib.tsb_kernel_launch_count() - launches0
+    step_ms = [a.elapsed_time(b) for a, b in zip(starts, ends)]
+    total_ms = sum(step_ms)
+
+    # ---- per-kernel launch times (conv kernels only), for the roofline ----
+    reps = max(10, min(args.steps, 50))
+    per_layer = []
+    for s in state:
+        quantize(s)
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+        qevs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+        for a, b in evs:
+            flush_l2()
+            a.record()
+            conv(s)
+            b.record()
+        for a, b in qevs:
+            flush_l2()
+            a.record()
+            quantize(s)
+            b.record()
+        torch.cuda.synchronize()
+        ms = statistics.mean(a.elapsed_time(b) for a, b in evs)
+        qms = statistics.mean(a.elapsed_time(b) for a, b in qevs)
+        l = s["layer"]
+        n_in = l["n"] * l["c"] * l["h"] * l["w"]
+        per_layer.append(dict(name=l["name"], kernel="tcgen05" if s["tc"] else "direct", conv_ms=ms, quantize_ms=qms,
+                              ops=workloads.layer_ops(l), tops=workloads.layer_ops(l) / ms / 1e9,
+                              conv_bytes=workloads.layer_bytes(l), conv_gbs=workloads.layer_bytes(l) / ms / 1e6,
+                              quantize_gbs=5 * n_in / qms / 1e6))
+
+    # ---- end to end through the host-buffer C-ABI call ----
+    host = []
+    for s in state:
+        l = s["layer"]
+        nbytes = lib.tsb_conv2d_host_scratch_bytes(s["plan"].handle)
+        host.append(dict(scratch=torch.empty(nbytes, dtype=torch.uint8, device=dev), nbytes=nbytes,
+                         x=torch.from_numpy(s["d"]["x"]).pin_memory(), out=torch.empty(s["plan"].out_shape, dtype=torch.float32).pin_memory(),
+                         w=s["d"]["w"], dq=s["d"]["dq"], bias=s["d"]["bias"]))
+
+    def e2e_step(resident):
+        for s, h in zip(state, host):
+            l = s["layer"]
+            _lib.check(lib.tsb_conv2d_quantized_host(
+                s["plan"].handle, h["x"].data_ptr(), s["scales"], l["n"], h["w"].ctypes.data, h["dq"].ctypes.data,
+                h["bias"].ctypes.data, _lib.ACT_RELU, 0.0, h["out"].data_ptr(), h["scratch"].data_ptr(), h["nbytes"],
+                resident, sptr()))
+
+    e2e_step(0)
+    e2e_steps = max(3, min(args.steps, 20))
+    for _ in range(2):
+        e2e_step(1)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step(1)
+    barrier()
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    # restore the plans' weights/workspaces used by the resident path (the host call rebinds them)
+    for s in state:
+        s["plan"].set_weights(s["w"])
+    h2d = sum(h["x"].numel() * 4 for h in host)
+    d2h = sum(h["out"].numel() * 4 for h in host)
+
+    sampler.stop_flag.set()
+    sampler.join(timeout=2)
+
+    # ---- reduce over ranks: max of the device time, sum of the work ----
+    ops_per_step = sum(workloads.layer_ops(l) for l in layers)
+    t = torch.tensor([total_ms, e2e_s], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms_max, e2e_s_max = float(t[0]), float(t[1])
+    value = ops_per_step * world * args.steps / (total_ms_max / 1e3) / 1e12
+    e2e_value = ops_per_step * world / e2e_s_max / 1e12
+
+    if rank == 0:
+        tc_layers = [p for p in per_layer if p["kernel"] == "tcgen05"]
+        tc_ops = sum(p["ops"] for p in tc_layers)
+        tc_ms = sum(p["conv_ms"] for p in tc_layers)
+        int8_peak = 2.0 * peaks["bf16_tflops"]
+        achieved = tc_ops / tc_ms / 1e9 if tc_layers else 0.0
+        roofline = {"kernel": "conv_i8_tc_kernel", "bound": "tensor", "achieved": achieved, "peak": int8_peak,
+                    "unit": "TOPS", "frac": achieved / int8_peak,
+                    "peak_source": "2 x %s burst bf16 TFLOP/s (the driver's file has no int8 figure; dense int8 is nominally twice bf16)" % peaks["source"],
+                    "traffic": None,
+                    "hbm_view": {"achieved_gbs": sum(p["conv_bytes"] for p in tc_layers) / tc_ms / 1e6 if tc_layers else 0.0,
+                                 "peak_gbs": peaks["hbm_gbs"]}}
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
+            "ms_per_step": total_ms_max / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int8", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "l2": "256 MiB buffer written between timed steps", "global_batch": 32 * world,
+                       "parallelism": "replicas x%d, batch-sharded, no collective" % world},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_s_max * 1e3, "steps": e2e_steps},
+            "gpu_launches": int(launches), "wall_s_timed_region": wall,
+            "clocks": sampler.summary(), "roofline": roofline, "layers": per_layer,
+        }
+        if world == 1:
+            try:
+                checker, cores, workers, images, ops_pass = cpu_arm(layers)
+                t0 = time.perf_counter()
+                sec = cpu_sample(layers, images, workers, checker)
+                line["cpu_baseline"] = {
+                    "value": ops_pass / sec / 1e12, "unit": UNIT, "cores": cores, "kind": checker.kind,
+                    "sample": "%d image of each of the 5 layers on each of %d worker(s); %.1f s" % (images, workers, time.perf_counter() - t0)}
+            except Exception as e:
+                line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": "failed: %r" % (e,)}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

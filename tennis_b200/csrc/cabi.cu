@@ -1,0 +1,356 @@
+// extern "C" entry points of libtennis_b200.so (declared in include/tennis_b200.h) and the convolution plan.
+#include "common.cuh"
+#include "conv_common.cuh"
+#include "conv_tc.h"
+
+#include <cstring>
+#include <new>
+
+namespace tsb {
+
+std::string &last_error() {
+    static thread_local std::string e;
+    return e;
+}
+std::atomic<int64_t> g_launches{0};
+
+// quantize.cu
+int quantize_f32_i8(const float *, int8_t *, int64_t, const float *, int, cudaStream_t);
+int quantize_f32_nchw_to_nhwc(const float *, int8_t *, int, int, int, int, const float *, int, cudaStream_t);
+int repack_i8_nchw_to_nhwc(const int8_t *, int8_t *, int, int, int, int, cudaStream_t);
+int repack_i8_nhwc_to_nchw(const int8_t *, int8_t *, int, int, int, int, cudaStream_t);
+int add_bias_f32_nchw(const float *, float *, int, int, int, const float *, cudaStream_t);
+int activation_f32(const float *, float *, int64_t, int, float, cudaStream_t);
+
+namespace {
+
+size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+
+// [O][C][KH][KW] -> [O][KH][KW][Cp], padding channels zero
+__global__ void pack_weights_kernel(const int8_t *__restrict__ w, int8_t *__restrict__ wp, int O, int C, int Cp, int taps) {
+    const int64_t total = (int64_t)O * taps * Cp;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int c = (int)(i % Cp);
+        const int t = (int)((i / Cp) % taps);
+        const int o = (int)(i / ((int64_t)Cp * taps));
+        wp[i] = c < C ? w[((int64_t)o * C + c) * taps + t] : (int8_t)0;
+    }
+}
+
+}  // namespace
+}  // namespace tsb
+
+struct tsb_conv_plan {
+    tsb_conv_desc desc;
+    tsb::ConvGeom geom;
+    int kernel;                      // resolved TSB_KERNEL_*
+    const char *why_not_tc;
+    tsb::tc::Config cfg;
+    size_t off_weights, off_stage, ws_bytes;
+    // state bound by set_weights / run
+    const int8_t *weights_oihw;      // direct kernel reads the caller's tensor
+    const void *weights_ws;          // workspace the packed weights live in
+    CUtensorMap map_b;
+    const int8_t *map_a_ptr;
+    CUtensorMap map_a;
+};
+
+using namespace tsb;
+
+extern "C" {
+
+const char *tsb_last_error(void) { return last_error().c_str(); }
+
+const char *tsb_status_string(int status) {
+    switch (status) {
+        case TSB_OK: return "ok";
+        case TSB_ERR_INVALID_ARGUMENT: return "invalid argument";
+        case TSB_ERR_UNSUPPORTED: return "unsupported";
+        case TSB_ERR_WORKSPACE_TOO_SMALL: return "workspace too small";
+        case TSB_ERR_DEVICE_TIMEOUT: return "a device-side wait ran out";
+        default: return status > 0 ? cudaGetErrorString((cudaError_t)status) : "unknown status";
+    }
+}
+
+int tsb_version(void) { return 100; }
+
+int tsb_padded_channels(int channels) {
+    if (channels <= 16) return 16;
+    if (channels <= 32) return 32;
+    return round_up(channels, 64);
+}
+
+int64_t tsb_kernel_launch_count(void) { return g_launches.load(); }
+
+int tsb_quantize_f32_i8(const float *x, int8_t *y, int64_t count, const float *scales_host, int nscales, void *stream) {
+    return quantize_f32_i8(x, y, count, scales_host, nscales, (cudaStream_t)stream);
+}
+int tsb_quantize_f32_nchw_to_nhwc(const float *x, int8_t *y, int n, int c, int h, int w, const float *scales_host,
+                                  int nscales, void *stream) {
+    return quantize_f32_nchw_to_nhwc(x, y, n, c, h, w, scales_host, nscales, (cudaStream_t)stream);
+}
+int tsb_repack_i8_nchw_to_nhwc(const int8_t *x, int8_t *y, int n, int c, int h, int w, void *stream) {
+    return repack_i8_nchw_to_nhwc(x, y, n, c, h, w, (cudaStream_t)stream);
+}
+int tsb_repack_i8_nhwc_to_nchw(const int8_t *x, int8_t *y, int n, int c, int h, int w, void *stream) {
+    return repack_i8_nhwc_to_nchw(x, y, n, c, h, w, (cudaStream_t)stream);
+}
+int tsb_add_bias_f32_nchw(const float *x, float *y, int n, int c, int hw, const float *bias, void *stream) {
+    return add_bias_f32_nchw(x, y, n, c, hw, bias, (cudaStream_t)stream);
+}
+int tsb_relu_f32(const float *x, float *y, int64_t count, void *stream) {
+    return activation_f32(x, y, count, TSB_ACT_RELU, 0.0f, (cudaStream_t)stream);
+}
+int tsb_leaky_relu_f32(const float *x, float *y, int64_t count, float scale, void *stream) {
+    return activation_f32(x, y, count, TSB_ACT_LEAKY_RELU, scale, (cudaStream_t)stream);
+}
+
+int tsb_conv2d_i8_plan_create(const tsb_conv_desc *d, tsb_conv_plan **out) {
+    if (!d || !out) return fail(TSB_ERR_INVALID_ARGUMENT, "plan_create: null pointer");
+    *out = nullptr;
+    if (d->n < 1 || d->c < 1 || d->h < 1 || d->w < 1 || d->o < 1 || d->kh < 1 || d->kw < 1)
+        return fail(TSB_ERR_INVALID_ARGUMENT, "plan_create: bad extents x=[%d,%d,%d,%d] w=[%d,%d,%d,%d]", d->n, d->c, d->h,
+                    d->w, d->o, d->c, d->kh, d->kw);
+    if (d->stride_h < 1 || d->stride_w < 1 || d->dilation_h < 1 || d->dilation_w < 1)
+        return fail(TSB_ERR_INVALID_ARGUMENT, "plan_create: stride and dilation must be positive");
+    if (d->pad_top < 0 || d->pad_bottom < 0 || d->pad_left < 0 || d->pad_right < 0)
+        return fail(TSB_ERR_INVALID_ARGUMENT, "plan_create: negative padding");
+    if (d->kernel < TSB_KERNEL_AUTO || d->kernel > TSB_KERNEL_TCGEN05)
+        return fail(TSB_ERR_INVALID_ARGUMENT, "plan_create: unknown kernel selector %d", d->kernel);
+    const int OH = conv_out_dim(d->h, d->pad_top, d->pad_bottom, d->kh, d->stride_h, d->dilation_h);
+    const int OW = conv_out_dim(d->w, d->pad_left, d->pad_right, d->kw, d->stride_w, d->dilation_w);
+    if (OH < 1 || OW < 1 || d->h + d->pad_top + d->pad_bottom < d->dilation_h * (d->kh - 1) + 1 ||
+        d->w + d->pad_left + d->pad_right < d->dilation_w * (d->kw - 1) + 1)
+        return fail(TSB_ERR_INVALID_ARGUMENT, "plan_create: the filter does not fit the padded input");
+    if ((int64_t)d->n * d->o * OH * OW > INT32_MAX || (int64_t)d->n * tsb_padded_channels(d->c) * d->h * d->w > INT32_MAX)
+        return fail(TSB_ERR_UNSUPPORTED, "plan_create: tensors beyond 2^31 elements (TenniS counts are 32-bit)");
+
+    tsb_conv_plan *p = new (std::nothrow) tsb_conv_plan();
+    if (!p) return fail(TSB_ERR_INVALID_ARGUMENT, "plan_create: out of host memory");
+    p->desc = *d;
+    ConvGeom &g = p->geom;
+    g.N = d->n; g.C = d->c; g.H = d->h; g.W = d->w;
+    g.O = d->o; g.KH = d->kh; g.KW = d->kw;
+    g.OH = OH; g.OW = OW;
+    g.pad_t = d->pad_top; g.pad_l = d->pad_left;
+    g.sh = d->stride_h; g.sw = d->stride_w; g.dh = d->dilation_h; g.dw = d->dilation_w;
+    g.Cp = tsb_padded_channels(d->c);
+    g.pad_value = (int)(int8_t)d->padding_value;  // T(padding_value) of the reference's im2col call
+    p->why_not_tc = "";
+    const bool tc_ok = tc::supported(g, &p->why_not_tc);
+    if (d->kernel == TSB_KERNEL_TCGEN05 && !tc_ok) {
+        int st = fail(TSB_ERR_UNSUPPORTED, "plan_create: tcgen05 kernel not available: %s", p->why_not_tc);
+        delete p;
+        return st;
+    }
+    p->kernel = (d->kernel == TSB_KERNEL_DIRECT || !tc_ok) ? TSB_KERNEL_DIRECT : TSB_KERNEL_TCGEN05;
+    p->off_weights = 256;
+    size_t end = 256;
+    if (p->kernel == TSB_KERNEL_TCGEN05) {
+        int sms = 148, dev = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+        p->cfg = tc::choose_config(g, sms);
+        end = p->off_weights + align256((size_t)g.O * g.KH * g.KW * g.Cp);
+    }
+    p->off_stage = end;
+    // NHWC_PAD staging of an operator-visible NCHW input (either kernel can read NHWC_PAD; only the tensor-core
+    // kernel needs it)
+    if (p->kernel == TSB_KERNEL_TCGEN05) end += align256((size_t)g.N * g.H * g.W * g.Cp);
+    p->ws_bytes = end;
+    p->weights_oihw = nullptr;
+    p->weights_ws = nullptr;
+    p->map_a_ptr = nullptr;
+    *out = p;
+    return TSB_OK;
+}
+
+int tsb_conv2d_i8_plan_destroy(tsb_conv_plan *plan) {
+    delete plan;
+    return TSB_OK;
+}
+
+int tsb_conv2d_i8_output_shape(const tsb_conv_plan *plan, int shape[4]) {
+    if (!plan || !shape) return fail(TSB_ERR_INVALID_ARGUMENT, "output_shape: null pointer");
+    shape[0] = plan->geom.N; shape[1] = plan->geom.O; shape[2] = plan->geom.OH; shape[3] = plan->geom.OW;
+    return TSB_OK;
+}
+
+int tsb_conv2d_i8_kernel(const tsb_conv_plan *plan) { return plan ? plan->kernel : TSB_ERR_INVALID_ARGUMENT; }
+
+size_t tsb_conv2d_i8_workspace_bytes(const tsb_conv_plan *plan) { return plan ? plan->ws_bytes : 0; }
+
+int tsb_conv2d_i8_set_weights(tsb_conv_plan *plan, const int8_t *w_oihw, void *workspace, size_t workspace_bytes,
+                              void *stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (!plan || !w_oihw || !workspace) return fail(TSB_ERR_INVALID_ARGUMENT, "set_weights: null pointer");
+    if (workspace_bytes < plan->ws_bytes) return fail(TSB_ERR_WORKSPACE_TOO_SMALL, "set_weights: workspace %zu < %zu", workspace_bytes, plan->ws_bytes);
+    if (reinterpret_cast<uintptr_t>(workspace) % 256) return fail(TSB_ERR_INVALID_ARGUMENT, "set_weights: workspace must be 256-byte aligned");
+    TSB_CUDA(cudaMemsetAsync(workspace, 0, 256, stream));  // status word
+    plan->weights_oihw = w_oihw;
+    plan->weights_ws = workspace;
+    if (plan->kernel == TSB_KERNEL_TCGEN05) {
+        const ConvGeom &g = plan->geom;
+        int8_t *wp = static_cast<int8_t *>(workspace) + plan->off_weights;
+        const int64_t total = (int64_t)g.O * g.KH * g.KW * g.Cp;
+        const int blocks = (int)std::min<int64_t>(ceil_div64(total, 256), 148 * 8);
+        pack_weights_kernel<<<blocks, 256, 0, stream>>>(w_oihw, wp, g.O, g.C, g.Cp, g.KH * g.KW);
+        TSB_LAUNCHED("pack_weights_kernel");
+        int st = tc::encode_weight_map(g, plan->cfg, wp, &plan->map_b);
+        if (st != TSB_OK) return st;
+    }
+    return TSB_OK;
+}
+
+static int build_epilogue(const tsb_conv_plan *plan, const tsb_conv_epilogue *e, EpiParams *out) {
+    const ConvGeom &g = plan->geom;
+    if (!e->dequantize_scales) return fail(TSB_ERR_INVALID_ARGUMENT, "run: dequantize_scales is required");
+    if (!e->out_f32 && !e->out_i8 && !e->out_acc) return fail(TSB_ERR_INVALID_ARGUMENT, "run: no output requested");
+    if (e->activation < TSB_ACT_NONE || e->activation > TSB_ACT_LEAKY_RELU) return fail(TSB_ERR_INVALID_ARGUMENT, "run: unknown activation %d", e->activation);
+    if (e->out_f32_layout != TSB_LAYOUT_NCHW && e->out_f32_layout != TSB_LAYOUT_NHWC_PAD) return fail(TSB_ERR_INVALID_ARGUMENT, "run: unknown out_f32_layout");
+    if (e->out_i8_layout != TSB_LAYOUT_NCHW && e->out_i8_layout != TSB_LAYOUT_NHWC_PAD) return fail(TSB_ERR_INVALID_ARGUMENT, "run: unknown out_i8_layout");
+    EpiParams &p = *out;
+    p.dq = e->dequantize_scales;
+    p.bias = e->bias;
+    p.residual = e->residual;
+    p.out_f32 = e->out_f32;
+    p.out_i8 = e->out_i8;
+    p.out_acc = e->out_acc;
+    p.activation = e->activation;
+    p.leaky = e->leaky_scale;
+    p.f32_nhwc = e->out_f32_layout == TSB_LAYOUT_NHWC_PAD;
+    p.i8_nhwc = e->out_i8_layout == TSB_LAYOUT_NHWC_PAD;
+    p.out_cp = tsb_padded_channels(g.O);
+    p.O = g.O;
+    p.P = g.OH * g.OW;
+    p.rne_limit = 0; p.group_len = 1; p.nscales = 1;
+    p.rq_scales[0] = 1.0f;
+    if (e->out_i8) {
+        if (!e->requant_scales_host || e->n_requant_scales < 1) return fail(TSB_ERR_INVALID_ARGUMENT, "run: out_i8 needs requantize scales");
+        if (e->n_requant_scales > kMaxRequantScales) return fail(TSB_ERR_UNSUPPORTED, "run: at most %d requantize scales", kMaxRequantScales);
+        if (p.i8_nhwc && reinterpret_cast<uintptr_t>(e->out_i8) % 16) return fail(TSB_ERR_INVALID_ARGUMENT, "run: NHWC out_i8 must be 16-byte aligned");
+        QuantRule r = make_quant_rule((int64_t)g.N * g.O * g.OH * g.OW, e->n_requant_scales);
+        p.rne_limit = (uint32_t)r.rne_limit;
+        p.group_len = (uint32_t)r.group_len;
+        p.nscales = r.nscales;
+        for (int i = 0; i < e->n_requant_scales; ++i) p.rq_scales[i] = e->requant_scales_host[i];
+    }
+    return TSB_OK;
+}
+
+int tsb_conv2d_i8_run(tsb_conv_plan *plan, const int8_t *x, int x_layout, const tsb_conv_epilogue *epilogue,
+                      void *workspace, size_t workspace_bytes, void *stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (!plan || !x || !epilogue || !workspace) return fail(TSB_ERR_INVALID_ARGUMENT, "run: null pointer");
+    if (x_layout != TSB_LAYOUT_NCHW && x_layout != TSB_LAYOUT_NHWC_PAD) return fail(TSB_ERR_INVALID_ARGUMENT, "run: unknown x_layout %d", x_layout);
+    if (workspace_bytes < plan->ws_bytes) return fail(TSB_ERR_WORKSPACE_TOO_SMALL, "run: workspace %zu < %zu", workspace_bytes, plan->ws_bytes);
+    if (plan->weights_ws != workspace || !plan->weights_oihw) return fail(TSB_ERR_INVALID_ARGUMENT, "run: tsb_conv2d_i8_set_weights was not called with this workspace");
+    EpiParams epi;
+    int st = build_epilogue(plan, epilogue, &epi);
+    if (st != TSB_OK) return st;
+    const ConvGeom &g = plan->geom;
+    if (plan->kernel == TSB_KERNEL_DIRECT)
+        return launch_conv_direct(g, x, x_layout == TSB_LAYOUT_NHWC_PAD, plan->weights_oihw, epi, stream);
+
+    const int8_t *x_nhwc = x;
+    if (x_layout == TSB_LAYOUT_NCHW) {
+        int8_t *stage = static_cast<int8_t *>(workspace) + plan->off_stage;
+        st = repack_i8_nchw_to_nhwc(x, stage, g.N, g.C, g.H, g.W, stream);
+        if (st != TSB_OK) return st;
+        x_nhwc = stage;
+    }
+    if (plan->map_a_ptr != x_nhwc) {
+        st = tc::encode_activation_map(g, plan->cfg, x_nhwc, &plan->map_a);
+        if (st != TSB_OK) return st;
+        plan->map_a_ptr = x_nhwc;
+    }
+    return tc::launch_conv_tc(g, plan->cfg, plan->map_a, plan->map_b, epi, static_cast<int *>(workspace), stream);
+}
+
+int tsb_conv2d_i8_status(tsb_conv_plan *plan, void *workspace, void *stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (!plan || !workspace) return fail(TSB_ERR_INVALID_ARGUMENT, "status: null pointer");
+    int word = 0;
+    TSB_CUDA(cudaMemcpyAsync(&word, workspace, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    TSB_CUDA(cudaStreamSynchronize(stream));
+    if (word != 0) return fail(TSB_ERR_DEVICE_TIMEOUT, "conv kernel: bounded wait %d ran out (1 stage-free, 2 accumulator-free, 3 tile-loaded, 4 accumulator-ready)", word);
+    return TSB_OK;
+}
+
+// ---- host-buffer convenience --------------------------------------------------------------------------
+namespace {
+struct HostScratch {
+    size_t x_f32, x_q, w, dq, bias, out, ws, total;
+};
+HostScratch host_layout(const tsb_conv_plan *p) {
+    const ConvGeom &g = p->geom;
+    HostScratch s;
+    size_t off = 0;
+    s.x_f32 = off; off += align256((size_t)g.N * g.C * g.H * g.W * 4);
+    s.x_q = off;   off += align256((size_t)g.N * g.Cp * g.H * g.W);
+    s.w = off;     off += align256((size_t)g.O * g.C * g.KH * g.KW);
+    s.dq = off;    off += align256((size_t)g.O * 4);
+    s.bias = off;  off += align256((size_t)g.O * 4);
+    s.out = off;   off += align256((size_t)g.N * g.O * g.OH * g.OW * 4);
+    s.ws = off;    off += align256(p->ws_bytes);
+    s.total = off;
+    return s;
+}
+}  // namespace
+
+size_t tsb_conv2d_host_scratch_bytes(const tsb_conv_plan *plan) { return plan ? host_layout(plan).total : 0; }
+
+int tsb_conv2d_quantized_host(tsb_conv_plan *plan, const float *x_host, const float *qscales_host, int nq,
+                              const int8_t *w_host, const float *dq_host, const float *bias_host, int activation,
+                              float leaky, float *out_host, void *scratch, size_t scratch_bytes, int weights_resident,
+                              void *stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (!plan || !x_host || !qscales_host || !out_host || !scratch) return fail(TSB_ERR_INVALID_ARGUMENT, "conv2d_quantized_host: null pointer");
+    if (!weights_resident && (!w_host || !dq_host)) return fail(TSB_ERR_INVALID_ARGUMENT, "conv2d_quantized_host: weights and dequantize scales are required");
+    const HostScratch L = host_layout(plan);
+    if (scratch_bytes < L.total) return fail(TSB_ERR_WORKSPACE_TOO_SMALL, "conv2d_quantized_host: scratch %zu < %zu", scratch_bytes, L.total);
+    if (reinterpret_cast<uintptr_t>(scratch) % 256) return fail(TSB_ERR_INVALID_ARGUMENT, "conv2d_quantized_host: scratch must be 256-byte aligned");
+    const ConvGeom &g = plan->geom;
+    if (nq != g.N) return fail(TSB_ERR_INVALID_ARGUMENT, "conv2d_quantized_host: %d quantize scales for batch %d (one per sample, base_quantize.cpp:26)", nq, g.N);
+    char *base = static_cast<char *>(scratch);
+    float *d_x = reinterpret_cast<float *>(base + L.x_f32);
+    int8_t *d_xq = reinterpret_cast<int8_t *>(base + L.x_q);
+    int8_t *d_w = reinterpret_cast<int8_t *>(base + L.w);
+    float *d_dq = reinterpret_cast<float *>(base + L.dq);
+    float *d_bias = reinterpret_cast<float *>(base + L.bias);
+    float *d_out = reinterpret_cast<float *>(base + L.out);
+    void *ws = base + L.ws;
+    TSB_CUDA(cudaMemcpyAsync(d_x, x_host, (size_t)g.N * g.C * g.H * g.W * 4, cudaMemcpyHostToDevice, stream));
+    int st;
+    if (!weights_resident) {
+        TSB_CUDA(cudaMemcpyAsync(d_w, w_host, (size_t)g.O * g.C * g.KH * g.KW, cudaMemcpyHostToDevice, stream));
+        TSB_CUDA(cudaMemcpyAsync(d_dq, dq_host, (size_t)g.O * 4, cudaMemcpyHostToDevice, stream));
+        if (bias_host) TSB_CUDA(cudaMemcpyAsync(d_bias, bias_host, (size_t)g.O * 4, cudaMemcpyHostToDevice, stream));
+        st = tsb_conv2d_i8_set_weights(plan, d_w, ws, plan->ws_bytes, stream);
+        if (st != TSB_OK) return st;
+    }
+    int x_layout;
+    if (plan->kernel == TSB_KERNEL_TCGEN05) {
+        st = quantize_f32_nchw_to_nhwc(d_x, d_xq, g.N, g.C, g.H, g.W, qscales_host, nq, stream);
+        x_layout = TSB_LAYOUT_NHWC_PAD;
+    } else {
+        st = quantize_f32_i8(d_x, d_xq, (int64_t)g.N * g.C * g.H * g.W, qscales_host, nq, stream);
+        x_layout = TSB_LAYOUT_NCHW;
+    }
+    if (st != TSB_OK) return st;
+    tsb_conv_epilogue e;
+    std::memset(&e, 0, sizeof(e));
+    e.dequantize_scales = d_dq;
+    e.bias = bias_host ? d_bias : nullptr;
+    e.activation = activation;
+    e.leaky_scale = leaky;
+    e.out_f32 = d_out;
+    e.out_f32_layout = TSB_LAYOUT_NCHW;
+    st = tsb_conv2d_i8_run(plan, d_xq, x_layout, &e, ws, plan->ws_bytes, stream);
+    if (st != TSB_OK) return st;
+    TSB_CUDA(cudaMemcpyAsync(out_host, d_out, (size_t)g.N * g.O * g.OH * g.OW * 4, cudaMemcpyDeviceToHost, stream));
+    TSB_CUDA(cudaStreamSynchronize(stream));
+    return TSB_OK;
+}
+
+}  // extern "C"

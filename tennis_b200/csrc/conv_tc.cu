@@ -1,0 +1,520 @@
+// int8 x int8 -> int32 convolution as an implicit GEMM on the sm_100a tensor cores.
+//
+//   GEMM view   M = N*OH*OW output pixels, N = O output channels, K = KH*KW*Cp  (k ordered kh, kw, c)
+//   A operand   activations, int8 [N][H][W][Cp]; one TMA im2col load per (filter tap, channel block) brings the
+//               128 x BK tile of a 128-pixel run of output positions -- halo, stride, dilation and zero padding
+//               are resolved by the tensor map, nothing is materialised in memory
+//   B operand   weights, int8 [O][KH][KW][Cp]; plain 2-D TMA tiles of BN x BK
+//   MMA         tcgen05.mma kind::i8, 128 x BN x 32 per instruction, int32 accumulators in tensor memory,
+//               issued by one thread; two accumulator buffers so the epilogue of tile i overlaps the
+//               main loop of tile i+1
+//   epilogue    four warps read the accumulators with tcgen05.ld and apply dequantize / bias / residual /
+//               activation / requantize in registers, then store fp32 (NCHW or NHWC) and/or int8
+//
+// Warp roles in a CTA of 192 threads: warp 0 = TMA producer, warp 1 = tensor-memory owner + MMA issuer,
+// warps 2..5 = epilogue.  The kernel is persistent: gridDim.x CTAs walk the tile list with stride gridDim.x.
+//
+// Every wait on an mbarrier is bounded; a wait that runs out records a code in *status, raises a CTA-wide
+// abort flag and all roles fall through to the common exit, where tensor memory is released.
+#include "conv_common.cuh"
+#include "conv_tc.h"
+
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+namespace tsb {
+namespace tc {
+
+constexpr int kBM = 128;
+constexpr int kThreads = 192;
+constexpr int kEpiThreads = 128;
+constexpr uint32_t kSmemBudget = 200 * 1024;  // stages; the rest holds barriers and epilogue tables
+
+// ---------------------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+
+// Bounded wait.  Returns false when the CTA is aborting or ~2 s of polling went by.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t spin = 0;; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 255u) == 255u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > 4000000000LL) return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c, int w,
+                                                   int h, int n, uint16_t off_w, uint16_t off_h) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, int (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are one swizzle span (BK bytes) wide:
+// 8-row groups are 8*BK bytes apart (stride byte offset); version 1; swizzle 128B (2) or 64B (4).
+template <int BK>
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr) {
+    constexpr uint64_t layout = BK == 128 ? 2 : (BK == 64 ? 4 : 6);
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;                       // leading byte offset: unused for swizzled K-major
+    d |= (uint64_t)((8 * BK) >> 4) << 32;         // stride byte offset
+    d |= (uint64_t)1 << 46;                       // descriptor version of this architecture
+    d |= layout << 61;
+    return d;
+}
+
+// Instruction descriptor: int32 accumulate, signed 8-bit A and B, both K-major, M = 128, N = BN.
+template <int BN>
+__device__ __forceinline__ constexpr uint32_t instr_desc() {
+    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// kernel
+// ---------------------------------------------------------------------------------------------------------
+struct KernelParams {
+    int M_total;     // N*OH*OW
+    int OW, P;       // P = OH*OW
+    int KH, KW;
+    int sh, sw, dh, dw, pad_t, pad_l;
+    int Cp;          // channels of the NHWC_PAD input
+    int num_m_tiles, num_n_tiles;
+    int per_sample_scale;  // requantize: scale index = image index
+    int *status;     // device word: 0 ok, else the code of the wait that ran out
+};
+
+template <int BN, int BK>
+struct Smem {
+    static constexpr uint32_t kABytes = kBM * BK;
+    static constexpr uint32_t kBBytes = BN * BK;
+    static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+    static constexpr int kStages = (kSmemBudget / kStageBytes) > 8 ? 8 : (kSmemBudget / kStageBytes);
+    static constexpr uint32_t kTileBytes = kStages * kStageBytes;
+    // after the tiles: full[kStages], empty[kStages], tmem_full[2], tmem_empty[2], tmem base, abort flag, tables
+    static constexpr uint32_t kBarOff = kTileBytes;
+    static constexpr uint32_t kTmemSlotOff = kBarOff + 8 * (2 * kStages + 4);
+    static constexpr uint32_t kAbortOff = kTmemSlotOff + 4;
+    static constexpr uint32_t kTableOff = (kAbortOff + 4 + 15) & ~15u;
+    static constexpr uint32_t kTotal = kTableOff + 2 * 2 * BN * 4;  // dq and bias, double buffered
+    static constexpr uint32_t kDynamic = kTotal + 1024;             // slack to align the tiles to 1024 bytes
+};
+
+template <int BN, int BK>
+__global__ void __launch_bounds__(kThreads, 1)
+conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                  const __grid_constant__ KernelParams kp, const __grid_constant__ EpiParams epi) {
+    using S = Smem<BN, BK>;
+    constexpr int kStages = S::kStages;
+    constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // power of two for BN in {32,64,128,256}
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t *base_ptr = smem_raw + (base - raw);
+    const uint32_t bar_full = base + S::kBarOff;
+    const uint32_t bar_empty = bar_full + 8 * kStages;
+    const uint32_t bar_tfull = bar_empty + 8 * kStages;
+    const uint32_t bar_tempty = bar_tfull + 16;
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + S::kTmemSlotOff);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(base_ptr + S::kAbortOff);
+    float *table = reinterpret_cast<float *>(base_ptr + S::kTableOff);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total_tiles = kp.num_m_tiles * kp.num_n_tiles;
+    const int k_iters = kp.KH * kp.KW * (kp.Cp / BK);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, kEpiThreads); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int n_tile = tile % kp.num_n_tiles, m_tile = tile / kp.num_n_tiles;
+                const int m0 = m_tile * kBM;
+                const int img = m0 / kp.P, rem = m0 - img * kp.P;
+                const int oh = rem / kp.OW, ow = rem - oh * kp.OW;
+                const int wc = ow * kp.sw - kp.pad_l, hc = oh * kp.sh - kp.pad_t;
+                for (int kh = 0; kh < kp.KH && ok; ++kh)
+                    for (int kw = 0; kw < kp.KW && ok; ++kw)
+                        for (int cb = 0; cb < kp.Cp; cb += BK) {
+                            if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) {
+                                if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 1); }
+                                ok = false;
+                                break;
+                            }
+                            const uint32_t sa = base + stage * S::kStageBytes, sb = sa + S::kABytes;
+                            mbar_arrive_expect_tx(bar_full + 8 * stage, S::kStageBytes);
+                            tma_load_im2col_4d(sa, &map_a, bar_full + 8 * stage, cb, wc, hc, img,
+                                               (uint16_t)(kw * kp.dw), (uint16_t)(kh * kp.dh));
+                            tma_load_2d(sb, &map_b, bar_full + 8 * stage, (kh * kp.KW + kw) * kp.Cp + cb, n_tile * BN);
+                            if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                        }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc<BN>();
+            int stage = 0; uint32_t phase = 0;
+            bool ok = true;
+            int local = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+                const int acc = local & 1;
+                const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
+                if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag)) {
+                    if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 2); }
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                for (int it = 0; it < k_iters; ++it) {
+                    if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
+                        if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 3); }
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sa = base + stage * S::kStageBytes, sb = sa + S::kABytes;
+                    const uint64_t da = smem_desc<BK>(sa), db = smem_desc<BK>(sb);
+#pragma unroll
+                    for (int k = 0; k < BK / 32; ++k) {
+                        // +32 bytes along K inside the swizzle span = +2 in the descriptor's 16-byte address units
+                        mma_i8(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (it | k) != 0 ? 1u : 0u);
+                    }
+                    tc_commit(bar_empty + 8 * stage);  // frees the stage once these MMAs have read it
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) tc_commit(bar_tfull + 8 * acc);  // accumulator complete
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5)
+        const int quarter = warp & 3;            // the 32 tensor-memory lanes this warp may read
+        const int et = threadIdx.x - 64;         // 0..127
+        const int row = quarter * 32 + lane;     // row of the tile this thread owns
+        const EpilogueMath math{epi.activation, epi.leaky};
+        int local = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
+            const int acc = local & 1;
+            const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
+            const int n_tile = tile % kp.num_n_tiles, m_tile = tile / kp.num_n_tiles;
+            const int n0 = n_tile * BN;
+            float *t_dq = table + acc * 2 * BN, *t_bias = t_dq + BN;
+            for (int j = et; j < BN; j += kEpiThreads) {
+                const int o = n0 + j;
+                t_dq[j] = o < epi.O ? epi.dq[o] : 0.0f;
+                t_bias[j] = (o < epi.O && epi.bias) ? epi.bias[o] : 0.0f;
+            }
+            // One collective decision per tile: the wait result is AND-reduced over the 128 epilogue threads, so either
+            // all four warps go on or all four leave (the reduction is also the barrier that publishes the tables).
+            int ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag) ? 1 : 0;
+            int all_ok;
+            asm volatile(
+                "{\n\t.reg .pred p, q;\n\t"
+                "setp.ne.b32 p, %1, 0;\n\t"
+                "bar.red.and.pred q, 1, %2, p;\n\t"
+                "selp.u32 %0, 1, 0, q;\n\t}"
+                : "=r"(all_ok) : "r"(ok), "n"(kEpiThreads) : "memory");
+            if (!all_ok) {
+                if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 4); }
+                break;
+            }
+            tc_fence_after();
+            const int m = m_tile * kBM + row;
+            const bool live = m < kp.M_total;
+            const int img = live ? m / kp.P : 0;
+            const int p = live ? m - img * kp.P : 0;
+            const uint32_t nchw0 = (uint32_t)(img * epi.O) * (uint32_t)epi.P + (uint32_t)p;  // + o*P
+            const uint32_t nhwc0 = (uint32_t)m * (uint32_t)epi.O;                             // + o
+            const bool has_bias = epi.bias != nullptr, has_res = epi.residual != nullptr;
+            const float row_scale = epi.nscales == 1 ? epi.rq_scales[0] : (kp.per_sample_scale ? epi.rq_scales[img] : 0.0f);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                int v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + c * 32), v);
+                tmem_ld_wait();
+                if (live) {
+                    uint32_t q[8];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int col = c * 32 + j, o = n0 + col;
+                        int qv = 0;
+                        if (o < epi.O) {
+                            const uint32_t nchw = nchw0 + (uint32_t)o * (uint32_t)epi.P;
+                            if (epi.out_acc) epi.out_acc[nchw] = v[j];
+                            const uint32_t fidx = epi.f32_nhwc ? nhwc0 + (uint32_t)o : nchw;
+                            const float r = has_res ? epi.residual[fidx] : 0.0f;
+                            const float f = math(v[j], t_dq[col], t_bias[col], has_bias, r, has_res);
+                            if (epi.out_f32) epi.out_f32[fidx] = f;
+                            if (epi.out_i8) {
+                                float s = row_scale;
+                                bool write = true;
+                                if (epi.nscales != 1 && !kp.per_sample_scale) {
+                                    const uint32_t g = nchw / epi.group_len;
+                                    write = g < (uint32_t)epi.nscales;
+                                    s = write ? epi.rq_scales[g] : 0.0f;
+                                }
+                                qv = q8(f, s, nchw < epi.rne_limit);
+                                if (!epi.i8_nhwc && write) epi.out_i8[nchw] = (int8_t)qv;
+                            }
+                        }
+                        if ((j & 3) == 0) q[j >> 2] = 0;
+                        q[j >> 2] |= (uint32_t)(qv & 0xff) << (8 * (j & 3));
+                    }
+                    if (epi.out_i8 && epi.i8_nhwc) {
+                        int8_t *dst = epi.out_i8 + (size_t)m * epi.out_cp + n0 + c * 32;
+                        if (n0 + c * 32 < epi.out_cp) *reinterpret_cast<int4 *>(dst) = make_int4(q[0], q[1], q[2], q[3]);
+                        if (n0 + c * 32 + 16 < epi.out_cp) *reinterpret_cast<int4 *>(dst + 16) = make_int4(q[4], q[5], q[6], q[7]);
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(bar_tempty + 8 * acc);
+        }
+    }
+
+    // common exit: everybody meets here, then the allocating warp releases tensor memory
+    if (*abort_flag) {
+        // give copies that may still be in flight time to land before shared memory is released
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) { __nanosleep(1000); }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------------------
+namespace {
+
+PFN_cuTensorMapEncodeTiled_v12000 g_encode_tiled = nullptr;
+PFN_cuTensorMapEncodeIm2col_v12000 g_encode_im2col = nullptr;
+
+int load_driver() {
+    if (g_encode_tiled && g_encode_im2col) return TSB_OK;
+    cudaDriverEntryPointQueryResult q;
+    void *fn = nullptr;
+    TSB_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+    if (q != cudaDriverEntryPointSuccess || !fn) return fail(TSB_ERR_UNSUPPORTED, "driver lacks cuTensorMapEncodeTiled");
+    g_encode_tiled = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+    TSB_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &q));
+    if (q != cudaDriverEntryPointSuccess || !fn) return fail(TSB_ERR_UNSUPPORTED, "driver lacks cuTensorMapEncodeIm2col");
+    g_encode_im2col = reinterpret_cast<PFN_cuTensorMapEncodeIm2col_v12000>(fn);
+    return TSB_OK;
+}
+
+CUtensorMapSwizzle swizzle_for(int bk) {
+    return bk == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (bk == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+}
+
+template <int BN, int BK>
+int launch(const Config &cfg, const CUtensorMap &ma, const CUtensorMap &mb, const KernelParams &kp, const EpiParams &epi,
+           cudaStream_t stream) {
+    using S = Smem<BN, BK>;
+    static bool configured = false;
+    auto kernel = conv_i8_tc_kernel<BN, BK>;
+    if (!configured) {
+        TSB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::kDynamic));
+        configured = true;
+    }
+    kernel<<<cfg.grid, kThreads, S::kDynamic, stream>>>(ma, mb, kp, epi);
+    TSB_LAUNCHED("conv_i8_tc_kernel");
+    return TSB_OK;
+}
+
+}  // namespace
+
+bool supported(const ConvGeom &g, const char **why) {
+    *why = "";
+    if (g.pad_value != 0) { *why = "non-zero padding_value"; return false; }
+    if (g.Cp % 64 != 0) { *why = "fewer than 33 input channels"; return false; }
+    // im2col tensor maps take box corners in [-128,127], filter offsets in [0,255] and traversal strides up to 8
+    const int up_w = (g.OW - 1) * g.sw - g.pad_l - (g.W - 1);
+    const int up_h = (g.OH - 1) * g.sh - g.pad_t - (g.H - 1);
+    if (g.pad_t > 128 || g.pad_l > 128 || g.pad_t < 0 || g.pad_l < 0 || up_w < -128 || up_w > 127 || up_h < -128 || up_h > 127) {
+        *why = "padding beyond the im2col corner range";
+        return false;
+    }
+    if ((g.KW - 1) * g.dw > 255 || (g.KH - 1) * g.dh > 255) { *why = "filter extent beyond the im2col offset range"; return false; }
+    if (g.sh > 8 || g.sw > 8) { *why = "stride beyond the traversal-stride range"; return false; }
+    if ((int64_t)g.N * g.OH * g.OW > INT32_MAX - 256) { *why = "too many output pixels"; return false; }
+    if ((int64_t)g.N * g.O * g.OH * g.OW > UINT32_MAX) { *why = "output too large for 32-bit indexing"; return false; }
+    return true;
+}
+
+Config choose_config(const ConvGeom &g, int sm_count) {
+    Config c;
+    c.bk = (g.Cp % 128 == 0) ? 128 : 64;
+    c.bn = g.O > 128 ? 256 : (g.O > 64 ? 128 : 64);
+    const int64_t M = (int64_t)g.N * g.OH * g.OW;
+    const int m_tiles = (int)ceil_div64(M, kBM);
+    // a narrower N tile when the wide one leaves most SMs idle or the last wave nearly empty
+    while (c.bn > 64) {
+        const int64_t tiles = (int64_t)m_tiles * ceil_div(g.O, c.bn);
+        const int64_t waves = ceil_div64(tiles, sm_count);
+        const double eff = (double)tiles / (double)(waves * sm_count);
+        if (eff >= 0.8) break;
+        const int64_t tiles2 = (int64_t)m_tiles * ceil_div(g.O, c.bn / 2);
+        const double eff2 = (double)tiles2 / (double)(ceil_div64(tiles2, sm_count) * sm_count);
+        if (eff2 <= eff) break;
+        c.bn /= 2;
+    }
+    c.num_m_tiles = m_tiles;
+    c.num_n_tiles = ceil_div(g.O, c.bn);
+    const int64_t tiles = (int64_t)c.num_m_tiles * c.num_n_tiles;
+    c.grid = (int)(tiles < sm_count ? tiles : sm_count);
+    return c;
+}
+
+int encode_weight_map(const ConvGeom &g, const Config &cfg, const int8_t *w_packed, CUtensorMap *map) {
+    int st = load_driver();
+    if (st != TSB_OK) return st;
+    const cuuint64_t ktot = (cuuint64_t)g.KH * g.KW * g.Cp;
+    cuuint64_t dims[2] = {ktot, (cuuint64_t)g.O};
+    cuuint64_t strides[1] = {ktot};
+    cuuint32_t box[2] = {(cuuint32_t)cfg.bk, (cuuint32_t)cfg.bn};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t *>(w_packed), dims, strides, box,
+                                estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(cfg.bk),
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(TSB_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled(weights) failed with %d", (int)r);
+    return TSB_OK;
+}
+
+int encode_activation_map(const ConvGeom &g, const Config &cfg, const int8_t *x_nhwc, CUtensorMap *map) {
+    int st = load_driver();
+    if (st != TSB_OK) return st;
+    if (reinterpret_cast<uintptr_t>(x_nhwc) % 16) return fail(TSB_ERR_INVALID_ARGUMENT, "NHWC activations must be 16-byte aligned");
+    cuuint64_t dims[4] = {(cuuint64_t)g.Cp, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.N};
+    cuuint64_t strides[3] = {(cuuint64_t)g.Cp, (cuuint64_t)g.Cp * g.W, (cuuint64_t)g.Cp * g.W * g.H};
+    // The box of base pixels: from -pad to the last position a filter can start at.  The far corner is chosen so
+    // that exactly OW x OH positions are visited with the traversal stride (floor semantics of the operator).
+    int lower[2] = {-g.pad_l, -g.pad_t};
+    int upper[2] = {(g.OW - 1) * g.sw - g.pad_l - (g.W - 1), (g.OH - 1) * g.sh - g.pad_t - (g.H - 1)};
+    cuuint32_t estr[4] = {1, (cuuint32_t)g.sw, (cuuint32_t)g.sh, 1};
+    CUresult r = g_encode_im2col(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<int8_t *>(x_nhwc), dims, strides, lower,
+                                 upper, (cuuint32_t)cfg.bk, (cuuint32_t)kBM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 swizzle_for(cfg.bk), CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(TSB_ERR_UNSUPPORTED, "cuTensorMapEncodeIm2col failed with %d", (int)r);
+    // Tensors under 128 KiB: drivers up to 13.1 set a descriptor bit that makes im2col loads of such small tensors
+    // misbehave; clearing it is the documented remedy used by NVIDIA's open-source templates.
+    int driver = 0;
+    cudaDriverGetVersion(&driver);
+    if (driver <= 13010 && (size_t)g.N * g.H * g.W * g.Cp < 131072)
+        reinterpret_cast<uint64_t *>(map)[1] &= ~(1ull << 21);
+    return TSB_OK;
+}
+
+int launch_conv_tc(const ConvGeom &g, const Config &cfg, const CUtensorMap &map_a, const CUtensorMap &map_b,
+                   const EpiParams &epi, int *status_word, cudaStream_t stream) {
+    KernelParams kp;
+    kp.M_total = g.N * g.OH * g.OW;
+    kp.OW = g.OW;
+    kp.P = g.OH * g.OW;
+    kp.KH = g.KH; kp.KW = g.KW;
+    kp.sh = g.sh; kp.sw = g.sw; kp.dh = g.dh; kp.dw = g.dw; kp.pad_t = g.pad_t; kp.pad_l = g.pad_l;
+    kp.Cp = g.Cp;
+    kp.num_m_tiles = cfg.num_m_tiles;
+    kp.num_n_tiles = cfg.num_n_tiles;
+    kp.per_sample_scale = (epi.nscales > 1 && epi.nscales == g.N && epi.group_len == (uint32_t)(g.O * g.OH * g.OW)) ? 1 : 0;
+    kp.status = status_word;
+#define TSB_TC_CASE(BN_, BK_) if (cfg.bn == BN_ && cfg.bk == BK_) return launch<BN_, BK_>(cfg, map_a, map_b, kp, epi, stream)
+    TSB_TC_CASE(64, 64);
+    TSB_TC_CASE(128, 64);
+    TSB_TC_CASE(256, 64);
+    TSB_TC_CASE(64, 128);
+    TSB_TC_CASE(128, 128);
+    TSB_TC_CASE(256, 128);
+#undef TSB_TC_CASE
+    return fail(TSB_ERR_UNSUPPORTED, "no tcgen05 kernel for tile %dx%d", cfg.bn, cfg.bk);
+}
+
+}  // namespace tc
+}  // namespace tsb

@@ -1,0 +1,311 @@
+// quantize (fp32 -> int8) and the layout staging kernels.  All of them are HBM-bound byte movers: wide
+// coalesced loads/stores, grid sized as a multiple of the SM count, no tensor cores.
+#include "common.cuh"
+
+#include <cmath>
+
+namespace tsb {
+
+QuantRule make_quant_rule(int64_t count, int nscales) {
+    QuantRule r;
+    r.nscales = nscales;
+    if (nscales == 1) {
+        r.rne_limit = (count >> 3) << 3;  // AVX body of the reference; the tail rounds half-away
+        r.group_len = count > 0 ? count : 1;
+    } else {
+        r.rne_limit = 0;
+        // int(std::ceil(static_cast<float>(count) / quantize_group)) evaluated in fp32, as the reference does
+        float len = std::ceil(static_cast<float>(static_cast<int>(count)) / static_cast<float>(static_cast<size_t>(nscales)));
+        r.group_len = static_cast<int64_t>(static_cast<int>(len));
+        if (r.group_len < 1) r.group_len = 1;
+    }
+    return r;
+}
+
+constexpr int kInlineScales = 64;
+struct ScaleArg {
+    const float *dev;             // used when nscales > kInlineScales
+    float inl[kInlineScales];
+    __device__ __forceinline__ float get(int g) const { return dev ? dev[g] : inl[g]; }
+};
+
+namespace {
+
+constexpr int kThreads = 256;
+
+// 16 consecutive elements per thread: 4 x float4 in, one 16-byte store out.
+__global__ void __launch_bounds__(kThreads)
+quantize_vec16_kernel(const float *__restrict__ x, int8_t *__restrict__ y, uint32_t count, QuantRule rule,
+                      ScaleArg scales) {
+    const uint32_t nvec = count >> 4;
+    const uint32_t rne_limit = (uint32_t)rule.rne_limit;
+    const uint32_t group_len = (uint32_t)rule.group_len;
+    const int nscales = rule.nscales;
+    for (uint32_t v = blockIdx.x * kThreads + threadIdx.x; v < nvec; v += gridDim.x * kThreads) {
+        const uint32_t i0 = v << 4;
+        const float4 *src = reinterpret_cast<const float4 *>(x + i0);
+        float f[16];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float4 t = __ldcs(src + k);  // streamed once
+            f[4 * k + 0] = t.x; f[4 * k + 1] = t.y; f[4 * k + 2] = t.z; f[4 * k + 3] = t.w;
+        }
+        uint32_t g0 = nscales == 1 ? 0u : i0 / group_len;
+        uint32_t g1 = nscales == 1 ? 0u : (i0 + 15u) / group_len;
+        uint32_t packed[4];
+        if (g1 >= (uint32_t)nscales || g0 != g1 || (i0 < rne_limit && i0 + 16u > rne_limit)) {
+            // a scale-group boundary, the end of the scale list or the rounding switch falls inside this vector
+            int4 old = *reinterpret_cast<const int4 *>(y + i0);
+            const int8_t *oldb = reinterpret_cast<const int8_t *>(&old);
+            int8_t *pb = reinterpret_cast<int8_t *>(packed);
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+                uint32_t i = i0 + k;
+                uint32_t g = nscales == 1 ? 0u : i / group_len;
+                pb[k] = g < (uint32_t)nscales ? (int8_t)q8(f[k], scales.get(g), i < rne_limit) : oldb[k];
+            }
+        } else {
+            const float s = scales.get(g0);
+            const bool he = i0 < rne_limit;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                int a = q8(f[4 * k + 0], s, he), b = q8(f[4 * k + 1], s, he);
+                int c = q8(f[4 * k + 2], s, he), d = q8(f[4 * k + 3], s, he);
+                packed[k] = (a & 0xff) | ((b & 0xff) << 8) | ((c & 0xff) << 16) | ((uint32_t)(d & 0xff) << 24);
+            }
+        }
+        __stcs(reinterpret_cast<int4 *>(y + i0), make_int4(packed[0], packed[1], packed[2], packed[3]));
+    }
+}
+
+// element-at-a-time: misaligned tensors and the < 16 element tail
+__global__ void __launch_bounds__(kThreads)
+quantize_scalar_kernel(const float *__restrict__ x, int8_t *__restrict__ y, uint32_t begin, uint32_t count,
+                       QuantRule rule, ScaleArg scales) {
+    const uint32_t rne_limit = (uint32_t)rule.rne_limit;
+    const uint32_t group_len = (uint32_t)rule.group_len;
+    for (uint32_t i = begin + blockIdx.x * kThreads + threadIdx.x; i < count; i += gridDim.x * kThreads) {
+        uint32_t g = rule.nscales == 1 ? 0u : i / group_len;
+        if (g < (uint32_t)rule.nscales) y[i] = (int8_t)q8(x[i], scales.get(g), i < rne_limit);
+    }
+}
+
+// [N][C][HW] (fp32, quantized on the fly, or int8) -> [N][HW][Cp] int8, padding channels zero.
+// One block moves 64 pixels x all channels, 64 channels at a time through a shared-memory tile.
+template <typename TIn>
+__global__ void __launch_bounds__(kThreads)
+nchw_to_nhwc_kernel(const TIn *__restrict__ x, int8_t *__restrict__ y, int C, int Cp, int HW, QuantRule rule,
+                    ScaleArg scales) {
+    __shared__ int8_t tile[64][64 + 4];
+    const int n = blockIdx.y;
+    const int p0 = blockIdx.x * 64;
+    const uint32_t rne_limit = (uint32_t)rule.rne_limit;
+    const uint32_t group_len = (uint32_t)rule.group_len;
+    const int pl = threadIdx.x & 63, cl = threadIdx.x >> 6;
+    const int sp = threadIdx.x >> 2, sq = threadIdx.x & 3;
+    for (int c0 = 0; c0 < Cp; c0 += 64) {
+        const int cw = min(64, Cp - c0);
+#pragma unroll 4
+        for (int i = 0; i < 16; ++i) {
+            const int ci = cl + 4 * i;
+            if (ci < cw) {
+                const int c = c0 + ci, p = p0 + pl;
+                int8_t v = 0;
+                if (c < C && p < HW) {
+                    const uint32_t idx = (uint32_t)(n * C + c) * (uint32_t)HW + (uint32_t)p;
+                    if (sizeof(TIn) == 1) {
+                        v = (int8_t)x[idx];
+                    } else {
+                        uint32_t g = rule.nscales == 1 ? 0u : idx / group_len;
+                        v = g < (uint32_t)rule.nscales ? (int8_t)q8((float)x[idx], scales.get(g), idx < rne_limit) : 0;
+                    }
+                }
+                tile[ci][pl] = v;
+            }
+        }
+        __syncthreads();
+        if (16 * sq < cw && p0 + sp < HW) {
+            uint32_t w[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                uint32_t b0 = (uint8_t)tile[16 * sq + 4 * k + 0][sp], b1 = (uint8_t)tile[16 * sq + 4 * k + 1][sp];
+                uint32_t b2 = (uint8_t)tile[16 * sq + 4 * k + 2][sp], b3 = (uint8_t)tile[16 * sq + 4 * k + 3][sp];
+                w[k] = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+            }
+            int8_t *dst = y + ((size_t)n * HW + p0 + sp) * Cp + c0 + 16 * sq;
+            *reinterpret_cast<int4 *>(dst) = make_int4(w[0], w[1], w[2], w[3]);
+        }
+        __syncthreads();
+    }
+}
+
+// [N][HW][Cp] int8 -> [N][C][HW] int8
+__global__ void __launch_bounds__(kThreads)
+nhwc_to_nchw_kernel(const int8_t *__restrict__ x, int8_t *__restrict__ y, int C, int Cp, int HW) {
+    __shared__ int8_t tile[64][64 + 4];  // [p][c]
+    const int n = blockIdx.y;
+    const int p0 = blockIdx.x * 64;
+    const int a = threadIdx.x & 63, b = threadIdx.x >> 6;
+    for (int c0 = 0; c0 < C; c0 += 64) {
+        for (int i = 0; i < 16; ++i) {
+            const int pi = b + 4 * i;
+            int8_t v = 0;
+            if (p0 + pi < HW && c0 + a < Cp) v = x[((size_t)n * HW + p0 + pi) * Cp + c0 + a];
+            tile[pi][a] = v;
+        }
+        __syncthreads();
+        for (int i = 0; i < 16; ++i) {
+            const int ci = b + 4 * i;
+            if (c0 + ci < C && p0 + a < HW) y[((size_t)n * C + c0 + ci) * HW + p0 + a] = tile[a][ci];
+        }
+        __syncthreads();
+    }
+}
+
+__global__ void __launch_bounds__(kThreads)
+add_bias_nchw_kernel(const float *__restrict__ x, float *__restrict__ y, int C, int HW, int64_t count,
+                     const float *__restrict__ bias) {
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < count; i += (int64_t)gridDim.x * kThreads) {
+        const int c = (int)((i / HW) % C);
+        y[i] = __fadd_rn(x[i], bias[c]);
+    }
+}
+
+__global__ void __launch_bounds__(kThreads)
+activation_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t count, int activation, float leaky) {
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < count; i += (int64_t)gridDim.x * kThreads) {
+        float v = x[i];
+        if (activation == TSB_ACT_RELU) v = v > 0.0f ? v : 0.0f;
+        else if (activation == TSB_ACT_LEAKY_RELU) v = v > 0.0f ? v : __fmul_rn(v, leaky);
+        y[i] = v;
+    }
+}
+
+int sm_count() {
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            sms = 148;
+    }
+    return sms;
+}
+
+int grid_for(int64_t work_items) {
+    int64_t blocks = ceil_div64(work_items, kThreads);
+    int64_t cap = (int64_t)sm_count() * 8;  // a whole number of waves of resident blocks
+    if (blocks < 1) blocks = 1;
+    return (int)(blocks < cap ? blocks : cap);
+}
+
+}  // namespace
+
+// Builds the scale argument.  More than kInlineScales scales (weight quantization at compile time, one scale
+// per output channel) go through a stream-ordered temporary; *tmp must be freed by the caller after launch.
+int make_scale_arg(const float *scales_host, int nscales, cudaStream_t stream, ScaleArg *arg, float **tmp) {
+    *tmp = nullptr;
+    arg->dev = nullptr;
+    if (nscales <= kInlineScales) {
+        for (int i = 0; i < nscales; ++i) arg->inl[i] = scales_host[i];
+        return TSB_OK;
+    }
+    TSB_CUDA(cudaMallocAsync((void **)tmp, sizeof(float) * (size_t)nscales, stream));
+    cudaError_t e = cudaMemcpyAsync(*tmp, scales_host, sizeof(float) * (size_t)nscales, cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) { cudaFreeAsync(*tmp, stream); *tmp = nullptr; return cuda_fail(e, "copy of quantize scales"); }
+    arg->dev = *tmp;
+    return TSB_OK;
+}
+
+int quantize_f32_i8(const float *x, int8_t *y, int64_t count, const float *scales_host, int nscales,
+                    cudaStream_t stream) {
+    if (!x || !y || !scales_host) return fail(TSB_ERR_INVALID_ARGUMENT, "quantize: null pointer");
+    if (nscales < 1) return fail(TSB_ERR_INVALID_ARGUMENT, "quantize: needs at least one scale");
+    if (count < 0 || count > INT32_MAX) return fail(TSB_ERR_INVALID_ARGUMENT, "quantize: count %lld out of range", (long long)count);
+    if (count == 0) return TSB_OK;
+    QuantRule rule = make_quant_rule(count, nscales);
+    ScaleArg arg;
+    float *tmp = nullptr;
+    int st = make_scale_arg(scales_host, nscales, stream, &arg, &tmp);
+    if (st != TSB_OK) return st;
+    const bool aligned = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (reinterpret_cast<uintptr_t>(y) % 16 == 0);
+    uint32_t done = 0;
+    if (aligned && count >= 16) {
+        quantize_vec16_kernel<<<grid_for(count >> 4), kThreads, 0, stream>>>(x, y, (uint32_t)count, rule, arg);
+        TSB_LAUNCHED("quantize_vec16_kernel");
+        done = (uint32_t)((count >> 4) << 4);
+    }
+    if (done < count) {
+        quantize_scalar_kernel<<<grid_for(count - done), kThreads, 0, stream>>>(x, y, done, (uint32_t)count, rule, arg);
+        TSB_LAUNCHED("quantize_scalar_kernel");
+    }
+    if (tmp) TSB_CUDA(cudaFreeAsync(tmp, stream));
+    return TSB_OK;
+}
+
+static int check_nchw(const void *x, const void *y, int n, int c, int h, int w, const char *who) {
+    if (!x || !y) return fail(TSB_ERR_INVALID_ARGUMENT, "%s: null pointer", who);
+    if (n < 1 || c < 1 || h < 1 || w < 1) return fail(TSB_ERR_INVALID_ARGUMENT, "%s: bad shape [%d,%d,%d,%d]", who, n, c, h, w);
+    if ((int64_t)n * tsb_padded_channels(c) * h * w > INT32_MAX) return fail(TSB_ERR_INVALID_ARGUMENT, "%s: tensor too large", who);
+    if (n > 65535) return fail(TSB_ERR_INVALID_ARGUMENT, "%s: batch %d too large", who, n);
+    return TSB_OK;
+}
+
+int quantize_f32_nchw_to_nhwc(const float *x, int8_t *y, int n, int c, int h, int w, const float *scales_host,
+                              int nscales, cudaStream_t stream) {
+    int st = check_nchw(x, y, n, c, h, w, "quantize_nchw_to_nhwc");
+    if (st != TSB_OK) return st;
+    if (!scales_host || nscales < 1) return fail(TSB_ERR_INVALID_ARGUMENT, "quantize_nchw_to_nhwc: needs scales");
+    if (reinterpret_cast<uintptr_t>(y) % 16) return fail(TSB_ERR_INVALID_ARGUMENT, "quantize_nchw_to_nhwc: output must be 16-byte aligned");
+    QuantRule rule = make_quant_rule((int64_t)n * c * h * w, nscales);
+    ScaleArg arg;
+    float *tmp = nullptr;
+    st = make_scale_arg(scales_host, nscales, stream, &arg, &tmp);
+    if (st != TSB_OK) return st;
+    dim3 grid(ceil_div(h * w, 64), n);
+    nchw_to_nhwc_kernel<float><<<grid, kThreads, 0, stream>>>(x, y, c, tsb_padded_channels(c), h * w, rule, arg);
+    TSB_LAUNCHED("nchw_to_nhwc_kernel<float>");
+    if (tmp) TSB_CUDA(cudaFreeAsync(tmp, stream));
+    return TSB_OK;
+}
+
+int repack_i8_nchw_to_nhwc(const int8_t *x, int8_t *y, int n, int c, int h, int w, cudaStream_t stream) {
+    int st = check_nchw(x, y, n, c, h, w, "repack_nchw_to_nhwc");
+    if (st != TSB_OK) return st;
+    if (reinterpret_cast<uintptr_t>(y) % 16) return fail(TSB_ERR_INVALID_ARGUMENT, "repack_nchw_to_nhwc: output must be 16-byte aligned");
+    QuantRule rule = make_quant_rule(1, 1);
+    ScaleArg arg;
+    arg.dev = nullptr;
+    dim3 grid(ceil_div(h * w, 64), n);
+    nchw_to_nhwc_kernel<int8_t><<<grid, kThreads, 0, stream>>>(x, y, c, tsb_padded_channels(c), h * w, rule, arg);
+    TSB_LAUNCHED("nchw_to_nhwc_kernel<int8_t>");
+    return TSB_OK;
+}
+
+int repack_i8_nhwc_to_nchw(const int8_t *x, int8_t *y, int n, int c, int h, int w, cudaStream_t stream) {
+    int st = check_nchw(x, y, n, c, h, w, "repack_nhwc_to_nchw");
+    if (st != TSB_OK) return st;
+    dim3 grid(ceil_div(h * w, 64), n);
+    nhwc_to_nchw_kernel<<<grid, kThreads, 0, stream>>>(x, y, c, tsb_padded_channels(c), h * w);
+    TSB_LAUNCHED("nhwc_to_nchw_kernel");
+    return TSB_OK;
+}
+
+int add_bias_f32_nchw(const float *x, float *y, int n, int c, int hw, const float *bias, cudaStream_t stream) {
+    if (!x || !y || !bias) return fail(TSB_ERR_INVALID_ARGUMENT, "add_bias: null pointer");
+    if (n < 1 || c < 1 || hw < 1) return fail(TSB_ERR_INVALID_ARGUMENT, "add_bias: bad shape");
+    const int64_t count = (int64_t)n * c * hw;
+    add_bias_nchw_kernel<<<grid_for(count), kThreads, 0, stream>>>(x, y, c, hw, count, bias);
+    TSB_LAUNCHED("add_bias_nchw_kernel");
+    return TSB_OK;
+}
+
+int activation_f32(const float *x, float *y, int64_t count, int activation, float leaky, cudaStream_t stream) {
+    if (!x || !y) return fail(TSB_ERR_INVALID_ARGUMENT, "activation: null pointer");
+    if (count < 0) return fail(TSB_ERR_INVALID_ARGUMENT, "activation: negative count");
+    if (count == 0) return TSB_OK;
+    activation_kernel<<<grid_for(count), kThreads, 0, stream>>>(x, y, count, activation, leaky);
+    TSB_LAUNCHED("activation_kernel");
+    return TSB_OK;
+}
+
+}  // namespace tsb

@@ -1,0 +1,232 @@
+"""Parity of the CUDA convolution kernels (tcgen05 implicit GEMM and the direct kernel) with the CPU checker,
+through the C ABI: int32 accumulators and int8 outputs bit-exact, fp32 outputs bit-exact up to the sign of
+zero (the stated bar is 1e-5 relative; every step is a single correctly rounded fp32 operation, so the
+tests ask for equality)."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import golden_cases, load_golden, same_bits
+
+pytestmark = pytest.mark.gpu
+
+ACT = {"none": 0, "relu": 1, "leaky_relu": 2}
+
+
+def run_gpu(x, w, pad, stride, dil, dq, bias=None, act="none", leaky=0.0, padding_value=0.0, kernel=0,
+            x_layout="nchw", residual=None, rq=None, i8_layout="nchw", f32_layout="nchw", want_acc=True):
+    """x int8 NCHW numpy.  Returns dict(kernel, acc, f32, i8) as NCHW numpy arrays."""
+    from tennis_b200 import _lib, ops
+    dev = torch.device("cuda")
+    xd = torch.from_numpy(np.ascontiguousarray(x)).to(dev)
+    wd = torch.from_numpy(np.ascontiguousarray(w)).to(dev)
+    plan = ops.ConvPlan(x.shape, w.shape, pad, stride, dil, padding_value, kernel, dev)
+    plan.set_weights(wd)
+    N, O, OH, OW = plan.out_shape
+    if x_layout == "nhwc":
+        xin, xl = ops.repack_nchw_to_nhwc(xd), _lib.LAYOUT_NHWC_PAD
+    else:
+        xin, xl = xd, _lib.LAYOUT_NCHW
+    out_acc = torch.full((N, O, OH, OW), -7, dtype=torch.int32, device=dev) if want_acc else None
+    f32_nhwc = f32_layout == "nhwc"
+    out_f32 = torch.full((N, OH, OW, O) if f32_nhwc else (N, O, OH, OW), float("nan"), dtype=torch.float32, device=dev)
+    res = None
+    if residual is not None:
+        r = np.ascontiguousarray(residual.transpose(0, 2, 3, 1)) if f32_nhwc else residual
+        res = torch.from_numpy(r).to(dev)
+    out_i8 = None
+    if rq is not None:
+        cp = ops.padded_channels(O)
+        out_i8 = torch.full((N, OH, OW, cp) if i8_layout == "nhwc" else (N, O, OH, OW), 99, dtype=torch.int8, device=dev)
+    plan.run(xin, xl, torch.from_numpy(dq).to(dev), bias=None if bias is None else torch.from_numpy(bias).to(dev),
+             residual=res, activation=ACT[act], leaky=leaky, out_f32=out_f32,
+             out_f32_layout=_lib.LAYOUT_NHWC_PAD if f32_nhwc else _lib.LAYOUT_NCHW, out_i8=out_i8,
+             out_i8_layout=_lib.LAYOUT_NHWC_PAD if i8_layout == "nhwc" else _lib.LAYOUT_NCHW,
+             requant_scales=None if rq is None else list(rq), out_acc=out_acc)
+    plan.status()
+    torch.cuda.synchronize()
+    r = dict(kernel=plan.kernel)
+    r["acc"] = out_acc.cpu().numpy() if want_acc else None
+    f = out_f32.cpu().numpy()
+    r["f32"] = f.transpose(0, 3, 1, 2) if f32_nhwc else f
+    if out_i8 is not None:
+        q = out_i8.cpu().numpy()
+        if i8_layout == "nhwc":
+            assert not q[..., O:].any(), "padding channels of the NHWC int8 output must be zero"
+            q = q[..., :O].transpose(0, 3, 1, 2)
+        r["i8"] = q
+    return r
+
+
+def check_case(checker, port, x, w, pad, stride, dil, dq, bias, act, leaky, pv, kernel, **kw):
+    want = checker.conv2d_quantized(x, w, pad, stride, dil, dq, pv)
+    _, want_acc = port.conv2d_quantized(x, w, pad, stride, dil, dq, pv, return_acc=True)
+    yb = checker.add_bias(want, bias) if bias is not None else want
+    residual = kw.get("residual")
+    if residual is not None:
+        yb = (yb + residual).astype(np.float32)
+    ya = checker.activation(yb, act, leaky)
+    got = run_gpu(x, w, pad, stride, dil, dq, bias, act, leaky, pv, kernel, **kw)
+    assert np.array_equal(got["acc"], want_acc), "int32 accumulators differ"
+    assert same_bits(got["f32"], ya), "fp32 output differs"
+    if kw.get("rq") is not None:
+        assert np.array_equal(got["i8"], checker.quantize(ya, kw["rq"])), "requantized int8 output differs"
+    return got
+
+
+@pytest.mark.parametrize("kernel", [1, 0])
+@pytest.mark.parametrize("name", golden_cases("c_"))
+def test_conv_golden(name, kernel):
+    """Fixtures produced by the reference's compiled operators."""
+    g = load_golden(name)
+    got = run_gpu(g["x"], g["w"], g["pad"], g["stride"], g["dilation"], g["dq"], g["bias"], str(g["act"]),
+                  float(g["leaky"]), float(g["padding_value"]), kernel, rq=g["rq"])
+    assert same_bits(got["f32"], g["y_act"])
+    assert np.array_equal(got["i8"], g["y_q"])
+    plain = run_gpu(g["x"], g["w"], g["pad"], g["stride"], g["dilation"], g["dq"], None, "none", 0.0,
+                    float(g["padding_value"]), kernel)
+    assert same_bits(plain["f32"], g["y_conv"])
+
+
+# N, C, H, W, O, KH, KW, pad(t,b,l,r), stride, dilation
+TC_CASES = [
+    (1, 64, 8, 8, 64, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1)),
+    (2, 64, 9, 11, 40, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1)),          # O not a multiple of 8/16, odd extents
+    (3, 128, 7, 7, 64, 1, 1, (0, 0, 0, 0), (1, 1), (1, 1)),          # 1x1, K block of 128
+    (2, 128, 14, 14, 256, 3, 3, (1, 1, 1, 1), (2, 2), (1, 1)),       # stride 2
+    (1, 64, 15, 13, 96, 3, 3, (2, 0, 1, 3), (2, 1), (2, 2)),         # asymmetric padding, dilation, mixed stride
+    (2, 70, 10, 10, 130, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1)),        # channels padded 70 -> 128
+    (1, 192, 6, 6, 300, 1, 1, (0, 0, 0, 0), (2, 2), (1, 1)),         # 1x1 stride 2, two N tiles
+    (5, 64, 12, 12, 64, 5, 5, (2, 2, 2, 2), (1, 1), (1, 1)),         # 5x5, several M tiles crossing images
+    (2, 256, 5, 5, 512, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1)),         # deep K, wide N
+    (1, 64, 3, 3, 16, 3, 3, (0, 0, 0, 0), (1, 1), (1, 1)),           # single output pixel
+    (1, 64, 40, 40, 64, 7, 7, (3, 3, 3, 3), (2, 2), (1, 1)),         # 7x7 stride 2
+]
+
+
+@pytest.mark.parametrize("case", TC_CASES)
+def test_tcgen05_kernel_cases(checker, port, case):
+    N, C, H, W, O, KH, KW, pad, stride, dil = case
+    rng = np.random.default_rng(N * 1000 + C + O)
+    x = rng.integers(-128, 128, size=(N, C, H, W), dtype=np.int8)
+    w = rng.integers(-127, 128, size=(O, C, KH, KW), dtype=np.int8)
+    dq = rng.uniform(0.001, 0.01, size=O).astype(np.float32)
+    bias = (rng.standard_normal(O) * 0.1).astype(np.float32)
+    got = check_case(checker, port, x, w, pad, stride, dil, dq, bias, "relu", 0.0, 0.0, 2)
+    assert got["kernel"] == 2
+    # NHWC_PAD input, leaky relu, requantize to NHWC_PAD with one scale per sample
+    rq = np.full(N, 0.9, dtype=np.float32)
+    check_case(checker, port, x, w, pad, stride, dil, dq, bias, "leaky_relu", 0.1, 0.0, 2, x_layout="nhwc", rq=rq,
+               i8_layout="nhwc")
+
+
+@pytest.mark.parametrize("case", [
+    (2, 3, 15, 17, 6, 7, 7, (3, 3, 3, 3), (2, 2), (1, 1), 0.0),
+    (1, 5, 6, 6, 3, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1), 3.0),
+    (2, 24, 9, 9, 20, 3, 3, (1, 2, 0, 1), (1, 2), (1, 1), -2.7),
+    (1, 64, 8, 8, 64, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1), 0.0),
+    (1, 600, 4, 4, 9, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1), 0.0),       # weight tile staged in several channel chunks
+])
+def test_direct_kernel_cases(checker, port, case):
+    N, C, H, W, O, KH, KW, pad, stride, dil, pv = case
+    rng = np.random.default_rng(C * 7 + O)
+    x = rng.integers(-128, 128, size=(N, C, H, W), dtype=np.int8)
+    w = rng.integers(-127, 128, size=(O, C, KH, KW), dtype=np.int8)
+    dq = rng.uniform(0.001, 0.01, size=O).astype(np.float32)
+    bias = (rng.standard_normal(O) * 0.1).astype(np.float32)
+    rq = np.full(N, 1.3, dtype=np.float32)
+    check_case(checker, port, x, w, pad, stride, dil, dq, bias, "relu", 0.0, pv, 1, rq=rq)
+    check_case(checker, port, x, w, pad, stride, dil, dq, None, "none", 0.0, pv, 1, x_layout="nhwc", rq=rq, i8_layout="nhwc")
+
+
+@pytest.mark.parametrize("kernel", [1, 2])
+def test_epilogue_variants(checker, port, kernel):
+    rng = np.random.default_rng(99)
+    N, C, H, W, O = 1, 64, 10, 10, 72
+    x = rng.integers(-128, 128, size=(N, C, H, W), dtype=np.int8)
+    w = rng.integers(-127, 128, size=(O, C, 3, 3), dtype=np.int8)
+    dq = rng.uniform(0.001, 0.01, size=O).astype(np.float32)
+    bias = (rng.standard_normal(O) * 0.1).astype(np.float32)
+    residual = rng.standard_normal((N, O, H, W)).astype(np.float32)
+    args = (x, w, (1, 1, 1, 1), (1, 1), (1, 1), dq)
+    # batch 1 + one requantize scale: half-to-even body and half-away tail on the NCHW index (7200 = 900*8, so
+    # use a scale that produces ties: outputs are multiples of dq, force exact .5 via a power-of-two scale)
+    for f32_layout in ("nchw", "nhwc"):
+        for i8_layout in ("nchw", "nhwc"):
+            check_case(checker, port, *args, bias, "relu", 0.0, 0.0, kernel, residual=residual, rq=np.array([8.0], np.float32),
+                       f32_layout=f32_layout, i8_layout=i8_layout)
+    check_case(checker, port, *args, None, "leaky_relu", 0.25, 0.0, kernel, rq=np.array([0.5], np.float32))
+
+
+def test_rounding_ties_in_fused_requantize(checker, port):
+    """dq = 0.5 and integer accumulators give outputs that are exact multiples of 0.5: every other value is a tie."""
+    rng = np.random.default_rng(1)
+    for N in (1, 2):
+        x = rng.integers(-3, 4, size=(N, 64, 5, 5), dtype=np.int8)
+        w = rng.integers(-1, 2, size=(19, 64, 1, 1), dtype=np.int8)
+        dq = np.full(19, 0.5, dtype=np.float32)
+        rq = np.full(N, 1.0, dtype=np.float32)
+        for kernel in (1, 2):
+            got = check_case(checker, port, x, w, (0, 0, 0, 0), (1, 1), (1, 1), dq, None, "none", 0.0, 0.0, kernel, rq=rq)
+            assert (np.abs(got["f32"] * 2) % 2 == 1).any(), "the case must contain ties"
+
+
+def test_operator_mirror_runs_like_the_reference_operator(checker):
+    from tennis_b200 import ops
+    rng = np.random.default_rng(4)
+    x = rng.standard_normal((2, 64, 12, 12)).astype(np.float32)
+    s = np.float32(127.0) / np.abs(x).max()
+    w = rng.integers(-127, 128, size=(32, 64, 3, 3), dtype=np.int8)
+    dq = rng.uniform(0.001, 0.01, size=32).astype(np.float32)
+    q = ops.Quantize()
+    q.set("quantize_scale", np.array([s, s], np.float32))
+    q.init()
+    conv = ops.Conv2DQuantized()
+    conv.set("format", "NCHW")
+    conv.set("padding", np.array([[0, 0], [0, 0], [1, 1], [1, 1]]))
+    conv.set("stride", np.array([1, 1, 1, 1]))
+    conv.set("dialations", np.array([1, 1, 1, 1]))
+    conv.set("dequantize_scales", dq)
+    conv.init()
+    xq = q.run([torch.from_numpy(x).cuda()])
+    y = conv.run([xq, torch.from_numpy(w).cuda()])
+    want_q = checker.quantize(x, [s, s])
+    assert np.array_equal(xq.cpu().numpy(), want_q)
+    assert same_bits(y.cpu().numpy(), checker.conv2d_quantized(want_q, w, (1, 1, 1, 1), (1, 1), (1, 1), dq))
+    y2 = conv.run([xq, torch.from_numpy(w).cuda()])  # second run reuses the plan
+    assert torch.equal(y, y2)
+
+
+def test_host_buffer_entry_point(checker):
+    import ctypes
+    from tennis_b200 import _lib, ops, workloads
+    layer = workloads.conv_layer("t", 2, 64, 10, 10, 48, 3, 1, 1)
+    d = workloads.make_layer_data(layer, seed=3)
+    plan = ops.ConvPlan((2, 64, 10, 10), (48, 64, 3, 3), (1, 1, 1, 1), (1, 1), (1, 1))
+    lib = _lib.load()
+    nbytes = lib.tsb_conv2d_host_scratch_bytes(plan.handle)
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    out = np.zeros(plan.out_shape, dtype=np.float32)
+    scales = [float(d["qscale"])] * 2
+    for resident in (0, 1):
+        out[:] = 0
+        _lib.check(lib.tsb_conv2d_quantized_host(
+            plan.handle, d["x"].ctypes.data, _lib.float_array(scales), 2, d["w"].ctypes.data, d["dq"].ctypes.data,
+            d["bias"].ctypes.data, _lib.ACT_RELU, 0.0, out.ctypes.data, scratch.data_ptr(), nbytes, resident,
+            ops._stream_ptr()))
+        xq = checker.quantize(d["x"], scales)
+        want = checker.conv_block(xq, d["w"], (1, 1, 1, 1), (1, 1), (1, 1), d["dq"], d["bias"], act="relu")
+        assert same_bits(out, want)
+
+
+def test_run_without_weights_is_rejected():
+    from tennis_b200 import _lib, ops
+    plan = ops.ConvPlan((1, 64, 8, 8), (64, 64, 3, 3), (1, 1, 1, 1), (1, 1), (1, 1))
+    x = torch.zeros((1, 64, 8, 8), dtype=torch.int8, device="cuda")
+    dq = torch.ones(64, device="cuda")
+    out = torch.zeros(plan.out_shape, device="cuda")
+    with pytest.raises(_lib.TsbError, match="set_weights"):
+        plan.run(x, _lib.LAYOUT_NCHW, dq, out_f32=out)
+    plan.set_weights(torch.zeros((64, 64, 3, 3), dtype=torch.int8, device="cuda"))
+    with pytest.raises(_lib.TsbError, match="no output requested"):
+        plan.run(x, _lib.LAYOUT_NCHW, dq)

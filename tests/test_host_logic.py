@@ -1,0 +1,130 @@
+"""Host-side behaviour that needs no GPU: attribute parsing and checks of the operator mirrors, argument
+validation of the C ABI (a rejected call launches nothing), kernel selection and the workload arithmetic."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from tennis_b200 import _lib, ops, workloads
+
+
+def make_conv(**over):
+    op = ops.Conv2DQuantized()
+    params = dict(format="NCHW", padding=np.array([[0, 0], [0, 0], [1, 1], [1, 1]]), stride=np.array([1, 1, 1, 1]),
+                  dilation=np.array([1, 1, 1, 1]), dequantize_scales=np.ones(4, np.float32))
+    params.update(over)
+    for k, v in params.items():
+        if v is not None:
+            op.set(k, v)
+    return op
+
+
+def test_quantize_fields_and_infer():
+    q = ops.Quantize()
+    with pytest.raises(ops.EjectionException, match="quantize_scale"):
+        q.init()
+    with pytest.raises(ops.EjectionException, match="Unidentified param"):
+        q.set("quantize_scales", [1.0])
+    q.set("quantize_scale", np.array([1.0, 2.0], np.float32))
+    q.init()
+    assert q.infer([torch.zeros(2, 3, 4, 4)]) == [("int8", (2, 3, 4, 4))]
+    with pytest.raises(ops.EjectionException, match=r"m_quantize_scales.size\(\) == x_tensor.sizes\(\)\[0\]"):
+        q.infer([torch.zeros(3, 3, 4, 4)])
+
+
+def test_conv_init_checks_follow_the_reference():
+    make_conv().init()
+    make_conv(dilation=None, dialations=np.array([1, 1, 2, 2])).init()  # the historical misspelling is accepted
+    with pytest.raises(ops.EjectionException, match="must set dilation or dialations"):
+        make_conv(dilation=None).init()
+    with pytest.raises(ops.EjectionException, match="do not support format: NCWH"):
+        make_conv(format="NCWH").init()
+    with pytest.raises(ops.EjectionException, match=r"do not support padding: \[1, 0, 0, 0, 1, 1, 1, 1\]"):
+        make_conv(padding=np.array([[1, 0], [0, 0], [1, 1], [1, 1]])).init()
+    with pytest.raises(ops.EjectionException, match=r"do not support stride: \[2, 1, 1, 1\]"):
+        make_conv(stride=np.array([2, 1, 1, 1])).init()
+    with pytest.raises(ops.EjectionException, match="do not support dialations"):
+        make_conv(dilation=np.array([1, 2, 1, 1])).init()
+    with pytest.raises(ops.EjectionException, match=r"padding_tensor.has_shape"):
+        make_conv(padding=np.zeros((4,), np.int32)).init()
+    with pytest.raises(ops.EjectionException, match="unsatisfied fields"):
+        make_conv(dequantize_scales=None).init()
+
+
+def test_conv_infer_shapes_and_checks():
+    op = make_conv(padding=np.array([[0, 0], [0, 0], [3, 3], [3, 3]]), stride=np.array([1, 1, 2, 2]))
+    op.init()
+    x = torch.zeros(2, 3, 224, 224, dtype=torch.int8)
+    w = torch.zeros(4, 3, 7, 7, dtype=torch.int8)
+    assert op.infer([x, w]) == [("float32", (2, 4, 112, 112))]
+    with pytest.raises(ops.EjectionException, match=r"w_tensor.size\(1\) == x_tensor.size\(1\)"):
+        op.infer([x, torch.zeros(4, 5, 7, 7, dtype=torch.int8)])
+    with pytest.raises(ops.EjectionException, match=r"x_tensor.dtype\(\) == INT8"):
+        op.infer([x.float(), w.float()])
+    with pytest.raises(ops.EjectionException, match=r"m_dequantize_scales.size\(\) == w_tensor.size\(0\)"):
+        op.infer([x, torch.zeros(5, 3, 7, 7, dtype=torch.int8)])
+
+
+def desc(**over):
+    d = _lib.ConvDesc()
+    base = dict(n=1, c=64, h=8, w=8, o=64, kh=3, kw=3, pad_top=1, pad_bottom=1, pad_left=1, pad_right=1, stride_h=1,
+                stride_w=1, dilation_h=1, dilation_w=1, padding_value=0.0, kernel=_lib.KERNEL_AUTO)
+    base.update(over)
+    for k, v in base.items():
+        setattr(d, k, v)
+    return d
+
+
+def create(d):
+    lib = _lib.load()
+    h = ctypes.c_void_p()
+    st = lib.tsb_conv2d_i8_plan_create(ctypes.byref(d), ctypes.byref(h))
+    return st, h
+
+
+def test_plan_create_validates_and_selects_kernel():
+    lib = _lib.load()
+    st, h = create(desc())
+    assert st == 0 and lib.tsb_conv2d_i8_kernel(h) == _lib.KERNEL_TCGEN05
+    shape = (ctypes.c_int * 4)()
+    lib.tsb_conv2d_i8_output_shape(h, shape)
+    assert list(shape) == [1, 64, 8, 8]
+    assert lib.tsb_conv2d_i8_workspace_bytes(h) >= 256 + 64 * 9 * 64 + 64 * 64
+    lib.tsb_conv2d_i8_plan_destroy(h)
+    # geometries the tensor-core kernel does not take resolve to the direct kernel
+    for over in (dict(c=3), dict(padding_value=3.0), dict(c=24)):
+        st, h = create(desc(**over))
+        assert st == 0 and lib.tsb_conv2d_i8_kernel(h) == _lib.KERNEL_DIRECT
+        lib.tsb_conv2d_i8_plan_destroy(h)
+    st, _ = create(desc(c=3, kernel=_lib.KERNEL_TCGEN05))
+    assert st == _lib.ERR_UNSUPPORTED and b"tcgen05 kernel not available" in lib.tsb_last_error()
+    for over in (dict(n=0), dict(stride_h=0), dict(pad_left=-1), dict(kh=11, h=4, pad_top=0, pad_bottom=0), dict(kernel=9)):
+        st, _ = create(desc(**over))
+        assert st == _lib.ERR_INVALID_ARGUMENT, over
+
+
+def test_run_rejects_bad_arguments_before_any_launch():
+    lib = _lib.load()
+    before = lib.tsb_kernel_launch_count()
+    st, h = create(desc())
+    e = _lib.ConvEpilogue()
+    assert lib.tsb_conv2d_i8_run(h, None, 0, ctypes.byref(e), None, 0, None) == _lib.ERR_INVALID_ARGUMENT
+    assert lib.tsb_conv2d_i8_set_weights(h, ctypes.c_void_p(256), ctypes.c_void_p(256), 16, None) == _lib.ERR_WORKSPACE_TOO_SMALL
+    assert lib.tsb_quantize_f32_i8(None, None, 4, _lib.float_array([1.0]), 1, None) == _lib.ERR_INVALID_ARGUMENT
+    assert lib.tsb_quantize_f32_i8(ctypes.c_void_p(256), ctypes.c_void_p(512), 4, _lib.float_array([1.0]), 0, None) == _lib.ERR_INVALID_ARGUMENT
+    assert lib.tsb_quantize_f32_i8(ctypes.c_void_p(256), ctypes.c_void_p(512), 2**31, _lib.float_array([1.0]), 1, None) == _lib.ERR_INVALID_ARGUMENT
+    assert lib.tsb_kernel_launch_count() == before
+    lib.tsb_conv2d_i8_plan_destroy(h)
+
+
+def test_workload_arithmetic():
+    l = workloads.CONFIG0[0]
+    assert workloads.out_hw(l) == (56, 56)
+    assert workloads.layer_ops(l) == 2 * 64 * 56 * 56 * 64 * 9
+    assert [workloads.out_hw(x) for x in workloads.CONFIG1] == [(14, 14), (28, 28), (14, 14), (7, 7), (112, 112)]
+    d = workloads.make_layer_data(workloads.conv_layer("t", 2, 3, 5, 5, 4, 3, 1, 1), seed=0)
+    d2 = workloads.make_layer_data(workloads.conv_layer("t", 2, 3, 5, 5, 4, 3, 1, 1), seed=0)
+    assert all(np.array_equal(d[k], d2[k]) for k in d)
+    assert abs(float(np.abs(d["x"]).max() * d["qscale"]) - 127.0) < 1e-3
+    assert d["w"].min() >= -127 and d["dq"].shape == (4,)
