@@ -8,11 +8,11 @@
 //   MMA         tcgen05.mma kind::i8, 128 x BN x 32 per instruction, int32 accumulators in tensor memory,
 //               issued by one thread; two accumulator buffers so the epilogue of tile i overlaps the
 //               main loop of tile i+1
-//   epilogue    four warps read the accumulators with tcgen05.ld and apply dequantize / bias / residual /
+//   epilogue    eight warps read the accumulators with tcgen05.ld and apply dequantize / bias / residual /
 //               activation / requantize in registers, then store fp32 (NCHW or NHWC) and/or int8
 //
-// Warp roles in a CTA of 192 threads: warp 0 = TMA producer, warp 1 = tensor-memory owner + MMA issuer,
-// warps 2..5 = epilogue.  The kernel is persistent: gridDim.x CTAs walk the tile list with stride gridDim.x.
+// Warp roles in a CTA of 320 threads: warp 0 = TMA producer, warp 1 = tensor-memory owner + MMA issuer,
+// warps 2..9 = epilogue.  The kernel is persistent: gridDim.x CTAs walk the tile list with stride gridDim.x.
 //
 // Every wait on an mbarrier is bounded; a wait that runs out records a code in *status, raises a CTA-wide
 // abort flag and all roles fall through to the common exit, where tensor memory is released.
@@ -26,8 +26,8 @@ namespace tsb {
 namespace tc {
 
 constexpr int kBM = 128;
-constexpr int kThreads = 192;
-constexpr int kEpiThreads = 128;
+constexpr int kThreads = 320;
+constexpr int kEpiThreads = 256;
 constexpr uint32_t kSmemBudget = 200 * 1024;  // stages; the rest holds barriers and epilogue tables
 
 // ---------------------------------------------------------------------------------------------------------
@@ -134,6 +134,130 @@ __device__ __forceinline__ constexpr uint32_t instr_desc() {
     return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
 }
 
+
+// ---------------------------------------------------------------------------------------------------------
+// epilogue: 32 accumulator columns of one output pixel (one thread) at a time
+// ---------------------------------------------------------------------------------------------------------
+constexpr int kEpiGeneric = 0;   // any combination of outputs, element by element
+constexpr int kEpiF32Nchw = 1;   // fp32 NCHW output only (the operator's own output)
+constexpr int kEpiI8Nhwc = 2;    // requantized int8 NHWC_PAD output only, half-away rounding, one scale per sample
+
+template <int ACT, bool HAS_BIAS>
+__device__ __forceinline__ float epi_value(int acc, float dq, float bias, float leaky) {
+    float f = __fmul_rn(__int2float_rn(acc), dq);
+    if (HAS_BIAS) f = __fadd_rn(f, bias);
+    if (ACT == TSB_ACT_RELU) f = f > 0.0f ? f : 0.0f;
+    if (ACT == TSB_ACT_LEAKY_RELU) f = f > 0.0f ? f : __fmul_rn(f, leaky);
+    return f;
+}
+
+// round-half-away quantization of an already scaled value with the reference's clamp and its -128 for NaN and
+// for products beyond the int32 range.  trunc(v + copysign(0.5, v)) is exact except for |v| just below 0.5,
+// where the sum rounds up to 1.0; that case is answered directly.
+__device__ __forceinline__ int q8_half_away_fast(float v) {
+    const float t = __fadd_rn(v, copysignf(0.5f, v));
+    int r;
+    asm("cvt.rzi.s8.f32 %0, %1;" : "=r"(r) : "f"(t));  // saturates to [-128,127]
+    r = fabsf(v) < 0.5f ? 0 : r;
+    return fabsf(v) < 2147483648.0f ? r : -128;
+}
+
+template <int ACT, bool HAS_BIAS>
+__device__ __forceinline__ void store_f32_nchw_t(const int (&v)[32], const float *dq, const float *bias, float leaky,
+                                                 float *dst, size_t stride) {
+#pragma unroll
+    for (int j4 = 0; j4 < 8; ++j4) {
+        const float4 d4 = *reinterpret_cast<const float4 *>(dq + 4 * j4);
+        const float4 b4 = *reinterpret_cast<const float4 *>(bias + 4 * j4);
+        dst[(size_t)(4 * j4 + 0) * stride] = epi_value<ACT, HAS_BIAS>(v[4 * j4 + 0], d4.x, b4.x, leaky);
+        dst[(size_t)(4 * j4 + 1) * stride] = epi_value<ACT, HAS_BIAS>(v[4 * j4 + 1], d4.y, b4.y, leaky);
+        dst[(size_t)(4 * j4 + 2) * stride] = epi_value<ACT, HAS_BIAS>(v[4 * j4 + 2], d4.z, b4.z, leaky);
+        dst[(size_t)(4 * j4 + 3) * stride] = epi_value<ACT, HAS_BIAS>(v[4 * j4 + 3], d4.w, b4.w, leaky);
+    }
+}
+
+template <int ACT, bool HAS_BIAS>
+__device__ __forceinline__ void store_i8_nhwc_t(const int (&v)[32], const float *dq, const float *bias, float leaky,
+                                                float rs, int8_t *dst) {
+    uint32_t q[8];
+#pragma unroll
+    for (int j4 = 0; j4 < 8; ++j4) {
+        const float4 d4 = *reinterpret_cast<const float4 *>(dq + 4 * j4);
+        const float4 b4 = *reinterpret_cast<const float4 *>(bias + 4 * j4);
+        const int a = q8_half_away_fast(__fmul_rn(epi_value<ACT, HAS_BIAS>(v[4 * j4 + 0], d4.x, b4.x, leaky), rs));
+        const int b = q8_half_away_fast(__fmul_rn(epi_value<ACT, HAS_BIAS>(v[4 * j4 + 1], d4.y, b4.y, leaky), rs));
+        const int c = q8_half_away_fast(__fmul_rn(epi_value<ACT, HAS_BIAS>(v[4 * j4 + 2], d4.z, b4.z, leaky), rs));
+        const int d = q8_half_away_fast(__fmul_rn(epi_value<ACT, HAS_BIAS>(v[4 * j4 + 3], d4.w, b4.w, leaky), rs));
+        q[j4] = (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) | ((uint32_t)(d & 0xff) << 24);
+    }
+    *reinterpret_cast<int4 *>(dst) = make_int4(q[0], q[1], q[2], q[3]);
+    *reinterpret_cast<int4 *>(dst + 16) = make_int4(q[4], q[5], q[6], q[7]);
+}
+
+#define TSB_EPI_DISPATCH(FN, ...)                                                                \
+    do {                                                                                         \
+        if (has_bias) {                                                                          \
+            if (act == TSB_ACT_RELU) FN<TSB_ACT_RELU, true>(__VA_ARGS__);                        \
+            else if (act == TSB_ACT_LEAKY_RELU) FN<TSB_ACT_LEAKY_RELU, true>(__VA_ARGS__);       \
+            else FN<TSB_ACT_NONE, true>(__VA_ARGS__);                                            \
+        } else {                                                                                 \
+            if (act == TSB_ACT_RELU) FN<TSB_ACT_RELU, false>(__VA_ARGS__);                       \
+            else if (act == TSB_ACT_LEAKY_RELU) FN<TSB_ACT_LEAKY_RELU, false>(__VA_ARGS__);      \
+            else FN<TSB_ACT_NONE, false>(__VA_ARGS__);                                           \
+        }                                                                                        \
+    } while (0)
+
+__device__ __forceinline__ void store_f32_nchw(const int (&v)[32], const float *dq, const float *bias, bool has_bias,
+                                               int act, float leaky, float *dst, size_t stride) {
+    TSB_EPI_DISPATCH(store_f32_nchw_t, v, dq, bias, leaky, dst, stride);
+}
+__device__ __forceinline__ void store_i8_nhwc(const int (&v)[32], const float *dq, const float *bias, bool has_bias,
+                                              int act, float leaky, float rs, int8_t *dst) {
+    TSB_EPI_DISPATCH(store_i8_nhwc_t, v, dq, bias, leaky, rs, dst);
+}
+
+// Everything else: several outputs at once, residual, NCHW int8, partial tiles.  o0 = first output channel.
+__device__ __noinline__ void store_generic(const int (&v)[32], const float *dq, const float *bias, const EpiParams &epi,
+                                           int per_sample_scale, int img, int p, int m, int o0) {
+    const EpilogueMath math{epi.activation, epi.leaky};
+    const uint32_t nchw0 = (uint32_t)(img * epi.O) * (uint32_t)epi.P + (uint32_t)p;  // + o*P
+    const uint32_t nhwc0 = (uint32_t)m * (uint32_t)epi.O;                             // + o
+    const bool has_bias = epi.bias != nullptr, has_res = epi.residual != nullptr;
+    const float row_scale = epi.nscales == 1 ? epi.rq_scales[0] : (per_sample_scale ? epi.rq_scales[img] : 0.0f);
+    uint32_t q[8];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        const int o = o0 + j;
+        int qv = 0;
+        if (o < epi.O) {
+            const uint32_t nchw = nchw0 + (uint32_t)o * (uint32_t)epi.P;
+            if (epi.out_acc) epi.out_acc[nchw] = v[j];
+            const uint32_t fidx = epi.f32_nhwc ? nhwc0 + (uint32_t)o : nchw;
+            const float r = has_res ? epi.residual[fidx] : 0.0f;
+            const float f = math(v[j], dq[j], bias[j], has_bias, r, has_res);
+            if (epi.out_f32) epi.out_f32[fidx] = f;
+            if (epi.out_i8) {
+                float s = row_scale;
+                bool write = true;
+                if (epi.nscales != 1 && !per_sample_scale) {
+                    const uint32_t g = nchw / epi.group_len;
+                    write = g < (uint32_t)epi.nscales;
+                    s = write ? epi.rq_scales[g] : 0.0f;
+                }
+                qv = q8(f, s, nchw < epi.rne_limit);
+                if (!epi.i8_nhwc && write) epi.out_i8[nchw] = (int8_t)qv;
+            }
+        }
+        if ((j & 3) == 0) q[j >> 2] = 0;
+        q[j >> 2] |= (uint32_t)(qv & 0xff) << (8 * (j & 3));
+    }
+    if (epi.out_i8 && epi.i8_nhwc) {
+        int8_t *dst = epi.out_i8 + (size_t)m * epi.out_cp + o0;
+        if (o0 < epi.out_cp) *reinterpret_cast<int4 *>(dst) = make_int4(q[0], q[1], q[2], q[3]);
+        if (o0 + 16 < epi.out_cp) *reinterpret_cast<int4 *>(dst + 16) = make_int4(q[4], q[5], q[6], q[7]);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // kernel
 // ---------------------------------------------------------------------------------------------------------
@@ -145,6 +269,7 @@ struct KernelParams {
     int Cp;          // channels of the NHWC_PAD input
     int num_m_tiles, num_n_tiles;
     int per_sample_scale;  // requantize: scale index = image index
+    int epi_mode;          // kEpi*: which epilogue code path full 32-column chunks take
     int *status;     // device word: 0 ok, else the code of the wait that ran out
 };
 
@@ -269,11 +394,15 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             }
         }
     } else {
-        // ------------------------------------------------------------------ epilogue (warps 2..5)
-        const int quarter = warp & 3;            // the 32 tensor-memory lanes this warp may read
-        const int et = threadIdx.x - 64;         // 0..127
+        // ------------------------------------------------------------------ epilogue (warps 2..9)
+        // A warp may read only the 32 tensor-memory lanes of its quarter (warp id mod 4); two warps share a
+        // quarter and split the tile's columns between them.
+        const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
+        const int et = threadIdx.x - 64;         // 0..255
         const int row = quarter * 32 + lane;     // row of the tile this thread owns
-        const EpilogueMath math{epi.activation, epi.leaky};
+        constexpr int kChunks = BN / 32;
+        constexpr int kChunksPerWarp = kChunks / 2;
         int local = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
             const int acc = local & 1;
@@ -286,8 +415,8 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 t_dq[j] = o < epi.O ? epi.dq[o] : 0.0f;
                 t_bias[j] = (o < epi.O && epi.bias) ? epi.bias[o] : 0.0f;
             }
-            // One collective decision per tile: the wait result is AND-reduced over the 128 epilogue threads, so either
-            // all four warps go on or all four leave (the reduction is also the barrier that publishes the tables).
+            // One collective decision per tile: the wait result is AND-reduced over the epilogue threads, so either
+            // all eight warps go on or all eight leave (the reduction is also the barrier that publishes the tables).
             int ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag) ? 1 : 0;
             int all_ok;
             asm volatile(
@@ -305,48 +434,25 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             const bool live = m < kp.M_total;
             const int img = live ? m / kp.P : 0;
             const int p = live ? m - img * kp.P : 0;
-            const uint32_t nchw0 = (uint32_t)(img * epi.O) * (uint32_t)epi.P + (uint32_t)p;  // + o*P
-            const uint32_t nhwc0 = (uint32_t)m * (uint32_t)epi.O;                             // + o
-            const bool has_bias = epi.bias != nullptr, has_res = epi.residual != nullptr;
-            const float row_scale = epi.nscales == 1 ? epi.rq_scales[0] : (kp.per_sample_scale ? epi.rq_scales[img] : 0.0f);
+            const uint32_t taddr0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int cc = 0; cc < kChunksPerWarp; ++cc) {
+                const int c = half * kChunksPerWarp + cc;
                 int v[32];
-                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + c * 32), v);
+                tmem_ld32(taddr0 + (uint32_t)(c * 32), v);
                 tmem_ld_wait();
-                if (live) {
-                    uint32_t q[8];
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int col = c * 32 + j, o = n0 + col;
-                        int qv = 0;
-                        if (o < epi.O) {
-                            const uint32_t nchw = nchw0 + (uint32_t)o * (uint32_t)epi.P;
-                            if (epi.out_acc) epi.out_acc[nchw] = v[j];
-                            const uint32_t fidx = epi.f32_nhwc ? nhwc0 + (uint32_t)o : nchw;
-                            const float r = has_res ? epi.residual[fidx] : 0.0f;
-                            const float f = math(v[j], t_dq[col], t_bias[col], has_bias, r, has_res);
-                            if (epi.out_f32) epi.out_f32[fidx] = f;
-                            if (epi.out_i8) {
-                                float s = row_scale;
-                                bool write = true;
-                                if (epi.nscales != 1 && !kp.per_sample_scale) {
-                                    const uint32_t g = nchw / epi.group_len;
-                                    write = g < (uint32_t)epi.nscales;
-                                    s = write ? epi.rq_scales[g] : 0.0f;
-                                }
-                                qv = q8(f, s, nchw < epi.rne_limit);
-                                if (!epi.i8_nhwc && write) epi.out_i8[nchw] = (int8_t)qv;
-                            }
-                        }
-                        if ((j & 3) == 0) q[j >> 2] = 0;
-                        q[j >> 2] |= (uint32_t)(qv & 0xff) << (8 * (j & 3));
-                    }
-                    if (epi.out_i8 && epi.i8_nhwc) {
-                        int8_t *dst = epi.out_i8 + (size_t)m * epi.out_cp + n0 + c * 32;
-                        if (n0 + c * 32 < epi.out_cp) *reinterpret_cast<int4 *>(dst) = make_int4(q[0], q[1], q[2], q[3]);
-                        if (n0 + c * 32 + 16 < epi.out_cp) *reinterpret_cast<int4 *>(dst + 16) = make_int4(q[4], q[5], q[6], q[7]);
-                    }
+                if (!live) continue;
+                const int col0 = c * 32;
+                const bool full = n0 + col0 + 32 <= epi.O;
+                if (kp.epi_mode == kEpiF32Nchw && full) {
+                    float *dst = epi.out_f32 + ((size_t)(img * epi.O + n0 + col0) * (size_t)epi.P + (size_t)p);
+                    store_f32_nchw(v, t_dq + col0, t_bias + col0, epi.bias != nullptr, epi.activation, epi.leaky, dst, (size_t)epi.P);
+                } else if (kp.epi_mode == kEpiI8Nhwc && full) {
+                    const float rs = epi.nscales == 1 ? epi.rq_scales[0] : epi.rq_scales[img];
+                    int8_t *dst = epi.out_i8 + (size_t)m * epi.out_cp + n0 + col0;
+                    store_i8_nhwc(v, t_dq + col0, t_bias + col0, epi.bias != nullptr, epi.activation, epi.leaky, rs, dst);
+                } else {
+                    store_generic(v, t_dq + col0, t_bias + col0, epi, kp.per_sample_scale, img, p, m, n0 + col0);
                 }
             }
             tc_fence_before();
@@ -505,6 +611,11 @@ int launch_conv_tc(const ConvGeom &g, const Config &cfg, const CUtensorMap &map_
     kp.num_n_tiles = cfg.num_n_tiles;
     kp.per_sample_scale = (epi.nscales > 1 && epi.nscales == g.N && epi.group_len == (uint32_t)(g.O * g.OH * g.OW)) ? 1 : 0;
     kp.status = status_word;
+    const bool plain = !epi.out_acc && !epi.residual;
+    kp.epi_mode = kEpiGeneric;
+    if (plain && epi.out_f32 && !epi.f32_nhwc && !epi.out_i8) kp.epi_mode = kEpiF32Nchw;
+    if (plain && epi.out_i8 && epi.i8_nhwc && !epi.out_f32 && epi.rne_limit == 0 && (epi.nscales == 1 || kp.per_sample_scale))
+        kp.epi_mode = kEpiI8Nhwc;
 #define TSB_TC_CASE(BN_, BK_) if (cfg.bn == BN_ && cfg.bk == BK_) return launch<BN_, BK_>(cfg, map_a, map_b, kp, epi, stream)
     TSB_TC_CASE(64, 64);
     TSB_TC_CASE(128, 64);

@@ -91,51 +91,50 @@ quantize_scalar_kernel(const float *__restrict__ x, int8_t *__restrict__ y, uint
 }
 
 // [N][C][HW] (fp32, quantized on the fly, or int8) -> [N][HW][Cp] int8, padding channels zero.
-// One block moves 64 pixels x all channels, 64 channels at a time through a shared-memory tile.
+// One block moves a 64-pixel x 64-channel tile through shared memory: reads are coalesced along pixels,
+// writes are 16-byte vectors along channels.  grid = (pixel tiles, channel chunks, N).
 template <typename TIn>
 __global__ void __launch_bounds__(kThreads)
 nchw_to_nhwc_kernel(const TIn *__restrict__ x, int8_t *__restrict__ y, int C, int Cp, int HW, QuantRule rule,
                     ScaleArg scales) {
     __shared__ int8_t tile[64][64 + 4];
-    const int n = blockIdx.y;
+    const int n = blockIdx.z;
     const int p0 = blockIdx.x * 64;
+    const int c0 = blockIdx.y * 64;
     const uint32_t rne_limit = (uint32_t)rule.rne_limit;
     const uint32_t group_len = (uint32_t)rule.group_len;
     const int pl = threadIdx.x & 63, cl = threadIdx.x >> 6;
     const int sp = threadIdx.x >> 2, sq = threadIdx.x & 3;
-    for (int c0 = 0; c0 < Cp; c0 += 64) {
-        const int cw = min(64, Cp - c0);
+    const int cw = min(64, Cp - c0);
 #pragma unroll 4
-        for (int i = 0; i < 16; ++i) {
-            const int ci = cl + 4 * i;
-            if (ci < cw) {
-                const int c = c0 + ci, p = p0 + pl;
-                int8_t v = 0;
-                if (c < C && p < HW) {
-                    const uint32_t idx = (uint32_t)(n * C + c) * (uint32_t)HW + (uint32_t)p;
-                    if (sizeof(TIn) == 1) {
-                        v = (int8_t)x[idx];
-                    } else {
-                        uint32_t g = rule.nscales == 1 ? 0u : idx / group_len;
-                        v = g < (uint32_t)rule.nscales ? (int8_t)q8((float)x[idx], scales.get(g), idx < rne_limit) : 0;
-                    }
+    for (int i = 0; i < 16; ++i) {
+        const int ci = cl + 4 * i;
+        if (ci < cw) {
+            const int c = c0 + ci, p = p0 + pl;
+            int8_t v = 0;
+            if (c < C && p < HW) {
+                const uint32_t idx = (uint32_t)(n * C + c) * (uint32_t)HW + (uint32_t)p;
+                if (sizeof(TIn) == 1) {
+                    v = (int8_t)x[idx];
+                } else {
+                    uint32_t g = rule.nscales == 1 ? 0u : idx / group_len;
+                    v = g < (uint32_t)rule.nscales ? (int8_t)q8((float)x[idx], scales.get(g), idx < rne_limit) : 0;
                 }
-                tile[ci][pl] = v;
             }
+            tile[ci][pl] = v;
         }
-        __syncthreads();
-        if (16 * sq < cw && p0 + sp < HW) {
-            uint32_t w[4];
+    }
+    __syncthreads();
+    if (16 * sq < cw && p0 + sp < HW) {
+        uint32_t w[4];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                uint32_t b0 = (uint8_t)tile[16 * sq + 4 * k + 0][sp], b1 = (uint8_t)tile[16 * sq + 4 * k + 1][sp];
-                uint32_t b2 = (uint8_t)tile[16 * sq + 4 * k + 2][sp], b3 = (uint8_t)tile[16 * sq + 4 * k + 3][sp];
-                w[k] = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
-            }
-            int8_t *dst = y + ((size_t)n * HW + p0 + sp) * Cp + c0 + 16 * sq;
-            *reinterpret_cast<int4 *>(dst) = make_int4(w[0], w[1], w[2], w[3]);
+        for (int k = 0; k < 4; ++k) {
+            uint32_t b0 = (uint8_t)tile[16 * sq + 4 * k + 0][sp], b1 = (uint8_t)tile[16 * sq + 4 * k + 1][sp];
+            uint32_t b2 = (uint8_t)tile[16 * sq + 4 * k + 2][sp], b3 = (uint8_t)tile[16 * sq + 4 * k + 3][sp];
+            w[k] = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
         }
-        __syncthreads();
+        int8_t *dst = y + ((size_t)n * HW + p0 + sp) * Cp + c0 + 16 * sq;
+        *reinterpret_cast<int4 *>(dst) = make_int4(w[0], w[1], w[2], w[3]);
     }
 }
 
@@ -261,7 +260,7 @@ int quantize_f32_nchw_to_nhwc(const float *x, int8_t *y, int n, int c, int h, in
     float *tmp = nullptr;
     st = make_scale_arg(scales_host, nscales, stream, &arg, &tmp);
     if (st != TSB_OK) return st;
-    dim3 grid(ceil_div(h * w, 64), n);
+    dim3 grid(ceil_div(h * w, 64), ceil_div(tsb_padded_channels(c), 64), n);
     nchw_to_nhwc_kernel<float><<<grid, kThreads, 0, stream>>>(x, y, c, tsb_padded_channels(c), h * w, rule, arg);
     TSB_LAUNCHED("nchw_to_nhwc_kernel<float>");
     if (tmp) TSB_CUDA(cudaFreeAsync(tmp, stream));
@@ -275,7 +274,7 @@ int repack_i8_nchw_to_nhwc(const int8_t *x, int8_t *y, int n, int c, int h, int 
     QuantRule rule = make_quant_rule(1, 1);
     ScaleArg arg;
     arg.dev = nullptr;
-    dim3 grid(ceil_div(h * w, 64), n);
+    dim3 grid(ceil_div(h * w, 64), ceil_div(tsb_padded_channels(c), 64), n);
     nchw_to_nhwc_kernel<int8_t><<<grid, kThreads, 0, stream>>>(x, y, c, tsb_padded_channels(c), h * w, rule, arg);
     TSB_LAUNCHED("nchw_to_nhwc_kernel<int8_t>");
     return TSB_OK;
