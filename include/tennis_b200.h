@@ -68,6 +68,28 @@ TSB_API int tsb_quantize_f32_i8(const float *x, int8_t *y, int64_t count, const 
                         void *stream);
 
 /*
+ * quantize without any allocation (this entry point has no counterpart in the reference).
+ *
+ * For callers that are not allowed to obtain device memory at call time: a serving process that handed the whole
+ * GPU to its own arena at start-up and treats any later cudaMalloc as a bug, a latency-critical loop that cannot
+ * afford the device-wide synchronisation an allocation or free may imply, or a host that forbids plugins to
+ * allocate after initialisation.  tsb_quantize_f32_i8 needs a device-side scale table when it is given more than
+ * 64 scales and takes it from a stream-ordered temporary; this variant keeps the table in storage built into the
+ * library instead.  Results are bit-identical to tsb_quantize_f32_i8.
+ *
+ *   - Limit: nscales <= 4096.  More is rejected with TSB_ERR_UNSUPPORTED before anything is launched.
+ *   - Cost: the table is a fixed 16 KiB of device memory on every GPU that loads the library, held until exit.
+ *   - The first call on each GPU looks up the table's device address (once, then remembered).  Make that first
+ *     call ahead of any CUDA stream capture on that GPU.
+ *   - All calls on one GPU share the table, and each call overwrites the entries it uses.  Calls whose work may
+ *     overlap on the GPU (different streams) therefore race: keep them on one stream or order them with events.
+ *   - It calls no cudaMalloc/cudaFree (nor their async forms) and no allocating library routine; x, y and the
+ *     host scale list are the caller's.  The host list may be reused as soon as the call returns.
+ */
+TSB_API int tsb_quantize_f32_i8_static(const float *x, int8_t *y, int64_t count, const float *scales_host,
+                                       int nscales, void *stream);
+
+/*
  * The same arithmetic on an NCHW fp32 tensor (rounding positions and scale groups follow the NCHW element
  * index), written in the internal NHWC_PAD layout that the tcgen05 convolution consumes directly.
  */

@@ -53,6 +53,7 @@ SYMBOLS = {
     "tsb_version": (_i, []),
     "tsb_padded_channels": (_i, [_i]),
     "tsb_quantize_f32_i8": (_i, [_vp, _vp, _i64, _fp, _i, _vp]),
+    "tsb_quantize_f32_i8_static": (_i, [_vp, _vp, _i64, _fp, _i, _vp]),
     "tsb_quantize_f32_nchw_to_nhwc": (_i, [_vp, _vp, _i, _i, _i, _i, _fp, _i, _vp]),
     "tsb_repack_i8_nchw_to_nhwc": (_i, [_vp, _vp, _i, _i, _i, _i, _vp]),
     "tsb_repack_i8_nhwc_to_nchw": (_i, [_vp, _vp, _i, _i, _i, _i, _vp]),

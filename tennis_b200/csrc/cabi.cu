@@ -16,6 +16,7 @@ std::atomic<int64_t> g_launches{0};
 
 // quantize.cu
 int quantize_f32_i8(const float *, int8_t *, int64_t, const float *, int, cudaStream_t);
+int quantize_f32_i8_static(const float *, int8_t *, int64_t, const float *, int, cudaStream_t);
 int quantize_f32_nchw_to_nhwc(const float *, int8_t *, int, int, int, int, const float *, int, cudaStream_t);
 int repack_i8_nchw_to_nhwc(const int8_t *, int8_t *, int, int, int, int, cudaStream_t);
 int repack_i8_nhwc_to_nchw(const int8_t *, int8_t *, int, int, int, int, cudaStream_t);
@@ -84,6 +85,10 @@ int64_t tsb_kernel_launch_count(void) { return g_launches.load(); }
 
 int tsb_quantize_f32_i8(const float *x, int8_t *y, int64_t count, const float *scales_host, int nscales, void *stream) {
     return quantize_f32_i8(x, y, count, scales_host, nscales, (cudaStream_t)stream);
+}
+int tsb_quantize_f32_i8_static(const float *x, int8_t *y, int64_t count, const float *scales_host, int nscales,
+                               void *stream) {
+    return quantize_f32_i8_static(x, y, count, scales_host, nscales, (cudaStream_t)stream);
 }
 int tsb_quantize_f32_nchw_to_nhwc(const float *x, int8_t *y, int n, int c, int h, int w, const float *scales_host,
                                   int nscales, void *stream) {

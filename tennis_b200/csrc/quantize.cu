@@ -3,6 +3,7 @@
 #include "common.cuh"
 
 #include <cmath>
+#include <mutex>
 
 namespace tsb {
 
@@ -28,6 +29,11 @@ struct ScaleArg {
     float inl[kInlineScales];
     __device__ __forceinline__ float get(int g) const { return dev ? dev[g] : inl[g]; }
 };
+
+// Scale table of tsb_quantize_f32_i8_static: fixed device storage that exists from the moment the library is loaded
+// on a GPU until the process exits (16 KiB per GPU), so that entry point never has to ask the driver for memory.
+constexpr int kStaticScaleCapacity = 4096;
+static __device__ __align__(256) float g_static_scale_table[kStaticScaleCapacity];
 
 namespace {
 
@@ -304,6 +310,57 @@ int activation_f32(const float *x, float *y, int64_t count, int activation, floa
     if (count == 0) return TSB_OK;
     activation_kernel<<<grid_for(count), kThreads, 0, stream>>>(x, y, count, activation, leaky);
     TSB_LAUNCHED("activation_kernel");
+    return TSB_OK;
+}
+
+// quantize for callers that must not allocate: identical arithmetic and kernels to quantize_f32_i8, but the scale
+// list always travels through g_static_scale_table instead of kernel arguments or a stream-ordered temporary.
+//
+// In host code the array's name is only a handle; the device address comes from cudaGetSymbolAddress, asked once per
+// device (with that device current) on the first call made there and remembered.
+int quantize_f32_i8_static(const float *x, int8_t *y, int64_t count, const float *scales_host, int nscales,
+                           cudaStream_t stream) {
+    if (!x || !y || !scales_host) return fail(TSB_ERR_INVALID_ARGUMENT, "quantize_static: null pointer");
+    if (nscales < 1) return fail(TSB_ERR_INVALID_ARGUMENT, "quantize_static: needs at least one scale");
+    if (nscales > kStaticScaleCapacity)
+        return fail(TSB_ERR_UNSUPPORTED, "quantize_static: %d scales exceed the built-in table of %d; use tsb_quantize_f32_i8",
+                    nscales, kStaticScaleCapacity);
+    if (count < 0 || count > INT32_MAX) return fail(TSB_ERR_INVALID_ARGUMENT, "quantize_static: count %lld out of range", (long long)count);
+    if (count == 0) return TSB_OK;
+
+    constexpr int kMaxDevices = 64;
+    static float *table_on_device[kMaxDevices] = {};
+    static std::mutex table_lock;
+    int dev = -1;
+    TSB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail(TSB_ERR_UNSUPPORTED, "quantize_static: device index %d not supported", dev);
+    float *table = nullptr;
+    {
+        std::lock_guard<std::mutex> guard(table_lock);
+        if (!table_on_device[dev]) {
+            void *addr = nullptr;
+            TSB_CUDA(cudaGetSymbolAddress(&addr, g_static_scale_table));
+            table_on_device[dev] = static_cast<float *>(addr);
+        }
+        table = table_on_device[dev];
+    }
+    // every call overwrites the part of the table it uses; nothing has to start at zero
+    TSB_CUDA(cudaMemcpyAsync(table, scales_host, sizeof(float) * (size_t)nscales, cudaMemcpyHostToDevice, stream));
+
+    QuantRule rule = make_quant_rule(count, nscales);
+    ScaleArg arg;
+    arg.dev = table;
+    const bool aligned = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (reinterpret_cast<uintptr_t>(y) % 16 == 0);
+    uint32_t done = 0;
+    if (aligned && count >= 16) {
+        quantize_vec16_kernel<<<grid_for(count >> 4), kThreads, 0, stream>>>(x, y, (uint32_t)count, rule, arg);
+        TSB_LAUNCHED("quantize_vec16_kernel");
+        done = (uint32_t)((count >> 4) << 4);
+    }
+    if (done < count) {
+        quantize_scalar_kernel<<<grid_for(count - done), kThreads, 0, stream>>>(x, y, done, (uint32_t)count, rule, arg);
+        TSB_LAUNCHED("quantize_scalar_kernel");
+    }
     return TSB_OK;
 }
 
