@@ -27,17 +27,6 @@ namespace {
 
 size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
 
-// [O][C][KH][KW] -> [O][KH][KW][Cp], padding channels zero
-__global__ void pack_weights_kernel(const int8_t *__restrict__ w, int8_t *__restrict__ wp, int O, int C, int Cp, int taps) {
-    const int64_t total = (int64_t)O * taps * Cp;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int c = (int)(i % Cp);
-        const int t = (int)((i / Cp) % taps);
-        const int o = (int)(i / ((int64_t)Cp * taps));
-        wp[i] = c < C ? w[((int64_t)o * C + c) * taps + t] : (int8_t)0;
-    }
-}
-
 }  // namespace
 }  // namespace tsb
 
@@ -46,6 +35,7 @@ struct tsb_conv_plan {
     tsb::ConvGeom geom;
     int kernel;                      // resolved TSB_KERNEL_*
     const char *why_not_tc;
+    tsb::tc::View view;
     tsb::tc::Config cfg;
     size_t off_weights, off_stage, ws_bytes;
     // state bound by set_weights / run
@@ -77,7 +67,6 @@ int tsb_version(void) { return 100; }
 
 int tsb_padded_channels(int channels) {
     if (channels <= 16) return 16;
-    if (channels <= 32) return 32;
     return round_up(channels, 64);
 }
 
@@ -142,7 +131,7 @@ int tsb_conv2d_i8_plan_create(const tsb_conv_desc *d, tsb_conv_plan **out) {
     g.Cp = tsb_padded_channels(d->c);
     g.pad_value = (int)(int8_t)d->padding_value;  // T(padding_value) of the reference's im2col call
     p->why_not_tc = "";
-    const bool tc_ok = tc::supported(g, &p->why_not_tc);
+    const bool tc_ok = tc::make_view(g, &p->view, &p->why_not_tc);
     if (d->kernel == TSB_KERNEL_TCGEN05 && !tc_ok) {
         int st = fail(TSB_ERR_UNSUPPORTED, "plan_create: tcgen05 kernel not available: %s", p->why_not_tc);
         delete p;
@@ -155,13 +144,13 @@ int tsb_conv2d_i8_plan_create(const tsb_conv_desc *d, tsb_conv_plan **out) {
         int sms = 148, dev = 0;
         if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (sms <= 0) sms = 148;
-        p->cfg = tc::choose_config(g, sms);
-        end = p->off_weights + align256((size_t)g.O * g.KH * g.KW * g.Cp);
+        p->cfg = tc::choose_config(p->view, sms);
+        end = p->off_weights + align256(p->view.weight_bytes);
     }
     p->off_stage = end;
     // NHWC_PAD staging of an operator-visible NCHW input (either kernel can read NHWC_PAD; only the tensor-core
     // kernel needs it)
-    if (p->kernel == TSB_KERNEL_TCGEN05) end += align256((size_t)g.N * g.H * g.W * g.Cp);
+    if (p->kernel == TSB_KERNEL_TCGEN05) end += align256(p->view.stage_bytes);
     p->ws_bytes = end;
     p->weights_oihw = nullptr;
     p->weights_ws = nullptr;
@@ -195,13 +184,10 @@ int tsb_conv2d_i8_set_weights(tsb_conv_plan *plan, const int8_t *w_oihw, void *w
     plan->weights_oihw = w_oihw;
     plan->weights_ws = workspace;
     if (plan->kernel == TSB_KERNEL_TCGEN05) {
-        const ConvGeom &g = plan->geom;
         int8_t *wp = static_cast<int8_t *>(workspace) + plan->off_weights;
-        const int64_t total = (int64_t)g.O * g.KH * g.KW * g.Cp;
-        const int blocks = (int)std::min<int64_t>(ceil_div64(total, 256), 148 * 8);
-        pack_weights_kernel<<<blocks, 256, 0, stream>>>(w_oihw, wp, g.O, g.C, g.Cp, g.KH * g.KW);
-        TSB_LAUNCHED("pack_weights_kernel");
-        int st = tc::encode_weight_map(g, plan->cfg, wp, &plan->map_b);
+        int st0 = tc::pack_weights(plan->view, w_oihw, wp, stream);
+        if (st0 != TSB_OK) return st0;
+        int st = tc::encode_weight_map(plan->view, plan->cfg, wp, &plan->map_b);
         if (st != TSB_OK) return st;
     }
     return TSB_OK;
@@ -257,19 +243,23 @@ int tsb_conv2d_i8_run(tsb_conv_plan *plan, const int8_t *x, int x_layout, const 
     if (plan->kernel == TSB_KERNEL_DIRECT)
         return launch_conv_direct(g, x, x_layout == TSB_LAYOUT_NHWC_PAD, plan->weights_oihw, epi, stream);
 
-    const int8_t *x_nhwc = x;
-    if (x_layout == TSB_LAYOUT_NCHW) {
-        int8_t *stage = static_cast<int8_t *>(workspace) + plan->off_stage;
+    const int8_t *x_tc = x;
+    int8_t *stage = static_cast<int8_t *>(workspace) + plan->off_stage;
+    if (plan->view.fold) {
+        st = tc::stage_folded(plan->view, x, x_layout == TSB_LAYOUT_NHWC_PAD, stage, stream);
+        if (st != TSB_OK) return st;
+        x_tc = stage;
+    } else if (x_layout == TSB_LAYOUT_NCHW) {
         st = repack_i8_nchw_to_nhwc(x, stage, g.N, g.C, g.H, g.W, stream);
         if (st != TSB_OK) return st;
-        x_nhwc = stage;
+        x_tc = stage;
     }
-    if (plan->map_a_ptr != x_nhwc) {
-        st = tc::encode_activation_map(g, plan->cfg, x_nhwc, &plan->map_a);
+    if (plan->map_a_ptr != x_tc) {
+        st = tc::encode_activation_map(plan->view, plan->cfg, x_tc, &plan->map_a);
         if (st != TSB_OK) return st;
-        plan->map_a_ptr = x_nhwc;
+        plan->map_a_ptr = x_tc;
     }
-    return tc::launch_conv_tc(g, plan->cfg, plan->map_a, plan->map_b, epi, static_cast<int *>(workspace), stream);
+    return tc::launch_conv_tc(plan->view, plan->cfg, plan->map_a, plan->map_b, epi, static_cast<int *>(workspace), stream);
 }
 
 int tsb_conv2d_i8_status(tsb_conv_plan *plan, void *workspace, void *stream_) {

@@ -22,6 +22,8 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
+#include <algorithm>
+
 namespace tsb {
 namespace tc {
 
@@ -516,25 +518,55 @@ int launch(const Config &cfg, const CUtensorMap &ma, const CUtensorMap &mb, cons
 
 }  // namespace
 
-bool supported(const ConvGeom &g, const char **why) {
+bool make_view(const ConvGeom &g, View *view, const char **why) {
     *why = "";
+    View v;
+    v.real = g;
+    v.g = g;
     if (g.pad_value != 0) { *why = "non-zero padding_value"; return false; }
-    if (g.Cp % 64 != 0) { *why = "fewer than 33 input channels"; return false; }
+    if (g.C <= 16) {
+        // fold the filter row into the channel dimension
+        const int cpix = (g.C <= 8 && g.sw % 2 == 0) ? 8 : 16;
+        const int span = (g.KW - 1) * g.dw + 1;
+        const int bkf = round_up(span * cpix, 64);
+        if (bkf > 128) { *why = "filter row too wide to fold into one K block"; return false; }
+        const int unit = 16 / cpix;  // pixels per 16 bytes: rows of the staging are whole 16-byte units
+        const int need = std::max(g.W + g.pad_l, (g.OW - 1) * g.sw + bkf / cpix);
+        v.fold = 1;
+        v.cpix = cpix;
+        v.Wp = round_up(need, unit);
+        v.g.C = bkf; v.g.Cp = bkf; v.g.W = g.OW; v.g.KW = 1; v.g.sw = 1; v.g.dw = 1; v.g.pad_l = 0;
+        v.stride_w = (uint64_t)g.sw * cpix;
+        v.stride_h = (uint64_t)v.Wp * cpix;
+        v.stride_n = v.stride_h * g.H;
+        v.stage_bytes = (size_t)v.stride_n * g.N;
+    } else {
+        if (g.Cp % 64 != 0) { *why = "channel padding is not a multiple of 64"; return false; }
+        v.stride_w = (uint64_t)g.Cp;
+        v.stride_h = (uint64_t)g.Cp * g.W;
+        v.stride_n = v.stride_h * g.H;
+        v.stage_bytes = (size_t)v.stride_n * g.N;
+    }
+    const ConvGeom &t = v.g;
+    v.weight_bytes = (size_t)t.O * t.KH * t.KW * t.Cp;
     // im2col tensor maps take box corners in [-128,127], filter offsets in [0,255] and traversal strides up to 8
-    const int up_w = (g.OW - 1) * g.sw - g.pad_l - (g.W - 1);
-    const int up_h = (g.OH - 1) * g.sh - g.pad_t - (g.H - 1);
-    if (g.pad_t > 128 || g.pad_l > 128 || g.pad_t < 0 || g.pad_l < 0 || up_w < -128 || up_w > 127 || up_h < -128 || up_h > 127) {
+    const int up_w = (t.OW - 1) * t.sw - t.pad_l - (t.W - 1);
+    const int up_h = (t.OH - 1) * t.sh - t.pad_t - (t.H - 1);
+    if (t.pad_t > 128 || t.pad_l > 128 || t.pad_t < 0 || t.pad_l < 0 || up_w < -128 || up_w > 127 || up_h < -128 || up_h > 127) {
         *why = "padding beyond the im2col corner range";
         return false;
     }
-    if ((g.KW - 1) * g.dw > 255 || (g.KH - 1) * g.dh > 255) { *why = "filter extent beyond the im2col offset range"; return false; }
-    if (g.sh > 8 || g.sw > 8) { *why = "stride beyond the traversal-stride range"; return false; }
-    if ((int64_t)g.N * g.OH * g.OW > INT32_MAX - 256) { *why = "too many output pixels"; return false; }
-    if ((int64_t)g.N * g.O * g.OH * g.OW > UINT32_MAX) { *why = "output too large for 32-bit indexing"; return false; }
+    if ((t.KW - 1) * t.dw > 255 || (t.KH - 1) * t.dh > 255) { *why = "filter extent beyond the im2col offset range"; return false; }
+    if (t.sh > 8 || t.sw > 8) { *why = "stride beyond the traversal-stride range"; return false; }
+    if ((int64_t)t.N * t.OH * t.OW > INT32_MAX - 256) { *why = "too many output pixels"; return false; }
+    if ((int64_t)t.N * t.O * t.OH * t.OW > UINT32_MAX) { *why = "output too large for 32-bit indexing"; return false; }
+    if (v.stage_bytes > (size_t)INT32_MAX) { *why = "staged input too large"; return false; }
+    *view = v;
     return true;
 }
 
-Config choose_config(const ConvGeom &g, int sm_count) {
+Config choose_config(const View &v, int sm_count) {
+    const ConvGeom &g = v.g;
     Config c;
     c.bk = (g.Cp % 128 == 0) ? 128 : 64;
     c.bn = g.O > 128 ? 256 : (g.O > 64 ? 128 : 64);
@@ -558,9 +590,10 @@ Config choose_config(const ConvGeom &g, int sm_count) {
     return c;
 }
 
-int encode_weight_map(const ConvGeom &g, const Config &cfg, const int8_t *w_packed, CUtensorMap *map) {
+int encode_weight_map(const View &v, const Config &cfg, const int8_t *w_packed, CUtensorMap *map) {
     int st = load_driver();
     if (st != TSB_OK) return st;
+    const ConvGeom &g = v.g;
     const cuuint64_t ktot = (cuuint64_t)g.KH * g.KW * g.Cp;
     cuuint64_t dims[2] = {ktot, (cuuint64_t)g.O};
     cuuint64_t strides[1] = {ktot};
@@ -573,18 +606,19 @@ int encode_weight_map(const ConvGeom &g, const Config &cfg, const int8_t *w_pack
     return TSB_OK;
 }
 
-int encode_activation_map(const ConvGeom &g, const Config &cfg, const int8_t *x_nhwc, CUtensorMap *map) {
+int encode_activation_map(const View &v, const Config &cfg, const int8_t *x, CUtensorMap *map) {
     int st = load_driver();
     if (st != TSB_OK) return st;
-    if (reinterpret_cast<uintptr_t>(x_nhwc) % 16) return fail(TSB_ERR_INVALID_ARGUMENT, "NHWC activations must be 16-byte aligned");
+    if (reinterpret_cast<uintptr_t>(x) % 16) return fail(TSB_ERR_INVALID_ARGUMENT, "staged activations must be 16-byte aligned");
+    const ConvGeom &g = v.g;
     cuuint64_t dims[4] = {(cuuint64_t)g.Cp, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.N};
-    cuuint64_t strides[3] = {(cuuint64_t)g.Cp, (cuuint64_t)g.Cp * g.W, (cuuint64_t)g.Cp * g.W * g.H};
+    cuuint64_t strides[3] = {v.stride_w, v.stride_h, v.stride_n};
     // The box of base pixels: from -pad to the last position a filter can start at.  The far corner is chosen so
     // that exactly OW x OH positions are visited with the traversal stride (floor semantics of the operator).
     int lower[2] = {-g.pad_l, -g.pad_t};
     int upper[2] = {(g.OW - 1) * g.sw - g.pad_l - (g.W - 1), (g.OH - 1) * g.sh - g.pad_t - (g.H - 1)};
     cuuint32_t estr[4] = {1, (cuuint32_t)g.sw, (cuuint32_t)g.sh, 1};
-    CUresult r = g_encode_im2col(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<int8_t *>(x_nhwc), dims, strides, lower,
+    CUresult r = g_encode_im2col(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<int8_t *>(x), dims, strides, lower,
                                  upper, (cuuint32_t)cfg.bk, (cuuint32_t)kBM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                  swizzle_for(cfg.bk), CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -593,13 +627,91 @@ int encode_activation_map(const ConvGeom &g, const Config &cfg, const int8_t *x_
     // misbehave; clearing it is the documented remedy used by NVIDIA's open-source templates.
     int driver = 0;
     cudaDriverGetVersion(&driver);
-    if (driver <= 13010 && (size_t)g.N * g.H * g.W * g.Cp < 131072)
+    if (driver <= 13010 && v.stage_bytes < 131072)
         reinterpret_cast<uint64_t *>(map)[1] &= ~(1ull << 21);
     return TSB_OK;
 }
 
-int launch_conv_tc(const ConvGeom &g, const Config &cfg, const CUtensorMap &map_a, const CUtensorMap &map_b,
+namespace {
+
+// [O][C][KH][KW] -> [O][KH][KW][Cp], padding channels zero
+__global__ void pack_weights_kernel(const int8_t *__restrict__ w, int8_t *__restrict__ wp, int O, int C, int Cp, int taps) {
+    const int64_t total = (int64_t)O * taps * Cp;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int c = (int)(i % Cp);
+        const int t = (int)((i / Cp) % taps);
+        const int o = (int)(i / ((int64_t)Cp * taps));
+        wp[i] = c < C ? w[((int64_t)o * C + c) * taps + t] : (int8_t)0;
+    }
+}
+
+// [O][C][KH][KW] -> [O][KH][bkf]: byte j of a filter row belongs to pixel offset j / cpix and channel j % cpix
+__global__ void pack_weights_folded_kernel(const int8_t *__restrict__ w, int8_t *__restrict__ wp, int O, int C, int KH,
+                                           int KW, int dw, int cpix, int bkf) {
+    const int64_t total = (int64_t)O * KH * bkf;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int j = (int)(i % bkf);
+        const int kh = (int)((i / bkf) % KH);
+        const int o = (int)(i / ((int64_t)bkf * KH));
+        const int pj = j / cpix, c = j % cpix;
+        int8_t val = 0;
+        if (c < C && pj % dw == 0 && pj / dw < KW) val = w[(((int64_t)o * C + c) * KH + kh) * KW + pj / dw];
+        wp[i] = val;
+    }
+}
+
+// int8 [N][C][H][W] (or NHWC_PAD [N][H][W][Cp]) -> [N][H][Wp][cpix]; one thread writes 16 bytes
+__global__ void stage_folded_kernel(const int8_t *__restrict__ x, int x_nhwc, int Cp, int8_t *__restrict__ y, int N, int C,
+                                    int H, int W, int Wp, int cpix, int pad_l) {
+    const int units_per_row = Wp * cpix / 16;
+    const int64_t total = (int64_t)N * H * units_per_row;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int u = (int)(i % units_per_row);
+        const int h = (int)((i / units_per_row) % H);
+        const int n = (int)(i / ((int64_t)units_per_row * H));
+        uint32_t word[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int b = 0; b < 16; ++b) {
+            const int byte = u * 16 + b;
+            const int wp = byte / cpix, c = byte % cpix;
+            const int wi = wp - pad_l;
+            int8_t v = 0;
+            if (c < C && wi >= 0 && wi < W)
+                v = x_nhwc ? x[(((int64_t)n * H + h) * W + wi) * Cp + c] : x[(((int64_t)n * C + c) * H + h) * W + wi];
+            word[b >> 2] |= (uint32_t)(uint8_t)v << (8 * (b & 3));
+        }
+        *reinterpret_cast<int4 *>(y + i * 16) = make_int4(word[0], word[1], word[2], word[3]);
+    }
+}
+
+}  // namespace
+
+int pack_weights(const View &v, const int8_t *w_oihw, int8_t *w_packed, cudaStream_t stream) {
+    const ConvGeom &r = v.real;
+    const int64_t total = (int64_t)v.weight_bytes;
+    const int blocks = (int)std::min<int64_t>(ceil_div64(total, 256), 148 * 8);
+    if (v.fold) {
+        pack_weights_folded_kernel<<<blocks, 256, 0, stream>>>(w_oihw, w_packed, r.O, r.C, r.KH, r.KW, r.dw, v.cpix, v.g.Cp);
+        TSB_LAUNCHED("pack_weights_folded_kernel");
+    } else {
+        pack_weights_kernel<<<blocks, 256, 0, stream>>>(w_oihw, w_packed, r.O, r.C, r.Cp, r.KH * r.KW);
+        TSB_LAUNCHED("pack_weights_kernel");
+    }
+    return TSB_OK;
+}
+
+int stage_folded(const View &v, const int8_t *x, int x_nhwc, int8_t *staged, cudaStream_t stream) {
+    const ConvGeom &r = v.real;
+    const int64_t total = (int64_t)v.stage_bytes / 16;
+    const int blocks = (int)std::min<int64_t>(ceil_div64(total, 256), 148 * 16);
+    stage_folded_kernel<<<blocks, 256, 0, stream>>>(x, x_nhwc, r.Cp, staged, r.N, r.C, r.H, r.W, v.Wp, v.cpix, r.pad_l);
+    TSB_LAUNCHED("stage_folded_kernel");
+    return TSB_OK;
+}
+
+int launch_conv_tc(const View &v, const Config &cfg, const CUtensorMap &map_a, const CUtensorMap &map_b,
                    const EpiParams &epi, int *status_word, cudaStream_t stream) {
+    const ConvGeom &g = v.g;
     KernelParams kp;
     kp.M_total = g.N * g.OH * g.OW;
     kp.OW = g.OW;

@@ -8,6 +8,23 @@
 namespace tsb {
 namespace tc {
 
+// The convolution as the tensor-core kernel sees it.
+//  fold == 0: activations are NHWC_PAD [N][H][W][Cp]; `g` is the real geometry.
+//  fold == 1 (at most 16 input channels): activations are staged as [N][H][Wp][cpix] with pixel w at column
+//            w + pad_left and zeros elsewhere.  The KW taps of one filter row are then one contiguous run of bytes,
+//            so the kernel sees a KH x 1 filter over `g.Cp` = round_up(((KW-1)*dw+1)*cpix, 64) virtual channels whose
+//            pixel stride is stride_w*cpix bytes (the tensor map's rows overlap); `g` is that virtual geometry.
+struct View {
+    ConvGeom g;          // geometry handed to the kernel and the tensor maps
+    ConvGeom real;       // geometry of the operator
+    int fold = 0;
+    int cpix = 0;        // bytes per pixel of the folded staging
+    int Wp = 0;          // pixels per row of the folded staging
+    uint64_t stride_w = 0, stride_h = 0, stride_n = 0;  // bytes between neighbours along W, H, N as the tensor map sees them
+    size_t stage_bytes = 0;    // NHWC_PAD or folded staging of one input
+    size_t weight_bytes = 0;   // packed weights
+};
+
 struct Config {
     int bn = 0, bk = 0;               // tile width in output channels, K block in bytes (= swizzle span)
     int num_m_tiles = 0, num_n_tiles = 0;
@@ -15,13 +32,17 @@ struct Config {
 };
 
 // Whether the tensor-core kernel covers this geometry; *why names the reason when it does not.
-bool supported(const ConvGeom &g, const char **why);
-Config choose_config(const ConvGeom &g, int sm_count);
-// w_packed: [O][KH][KW][Cp] int8
-int encode_weight_map(const ConvGeom &g, const Config &cfg, const int8_t *w_packed, CUtensorMap *map);
-// x_nhwc: [N][H][W][Cp] int8, 16-byte aligned
-int encode_activation_map(const ConvGeom &g, const Config &cfg, const int8_t *x_nhwc, CUtensorMap *map);
-int launch_conv_tc(const ConvGeom &g, const Config &cfg, const CUtensorMap &map_a, const CUtensorMap &map_b,
+bool make_view(const ConvGeom &g, View *view, const char **why);
+Config choose_config(const View &v, int sm_count);
+// w_packed: [O][KH][KW][Cp] int8 of the view's geometry
+int encode_weight_map(const View &v, const Config &cfg, const int8_t *w_packed, CUtensorMap *map);
+// x: the staged activations (NHWC_PAD or folded), 16-byte aligned
+int encode_activation_map(const View &v, const Config &cfg, const int8_t *x, CUtensorMap *map);
+// OIHW weights -> the packed layout of the view
+int pack_weights(const View &v, const int8_t *w_oihw, int8_t *w_packed, cudaStream_t stream);
+// int8 input (NCHW, or NHWC_PAD when x_nhwc) -> folded staging (fold views only)
+int stage_folded(const View &v, const int8_t *x, int x_nhwc, int8_t *staged, cudaStream_t stream);
+int launch_conv_tc(const View &v, const Config &cfg, const CUtensorMap &map_a, const CUtensorMap &map_b,
                    const EpiParams &epi, int *status_word, cudaStream_t stream);
 
 }  // namespace tc

@@ -34,7 +34,7 @@ def test_simple_host_calls_work_without_gpu():
     from tennis_b200 import _lib
     lib = _lib.load()
     assert lib.tsb_version() >= 100
-    assert [lib.tsb_padded_channels(c) for c in (1, 3, 16, 17, 32, 33, 64, 65, 2048)] == [16, 16, 16, 32, 32, 64, 64, 128, 2048]
+    assert [lib.tsb_padded_channels(c) for c in (1, 3, 16, 17, 32, 33, 64, 65, 2048)] == [16, 16, 16, 64, 64, 64, 64, 128, 2048]
     assert lib.tsb_status_string(0) == b"ok"
     assert lib.tsb_status_string(_lib.ERR_DEVICE_TIMEOUT).startswith(b"a device-side wait")
 

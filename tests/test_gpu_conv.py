@@ -101,6 +101,14 @@ TC_CASES = [
     (2, 256, 5, 5, 512, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1)),         # deep K, wide N
     (1, 64, 3, 3, 16, 3, 3, (0, 0, 0, 0), (1, 1), (1, 1)),           # single output pixel
     (1, 64, 40, 40, 64, 7, 7, (3, 3, 3, 3), (2, 2), (1, 1)),         # 7x7 stride 2
+    # at most 16 input channels: the filter row is folded into the K dimension
+    (2, 3, 15, 17, 6, 7, 7, (3, 3, 3, 3), (2, 2), (1, 1)),           # stem-like, 8 bytes per pixel
+    (1, 3, 20, 20, 8, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1)),           # stride 1: 16 bytes per pixel
+    (2, 8, 12, 12, 16, 5, 5, (2, 2, 2, 2), (2, 2), (1, 1)),
+    (1, 16, 9, 9, 10, 3, 3, (1, 1, 1, 1), (1, 1), (2, 2)),           # dilation: 128-byte folded row
+    (1, 4, 10, 12, 6, 3, 3, (2, 0, 1, 3), (2, 1), (2, 2)),
+    (3, 3, 33, 35, 70, 7, 7, (3, 3, 3, 3), (2, 2), (1, 1)),          # several M tiles, O not a multiple of 64
+    (2, 24, 9, 9, 20, 3, 3, (1, 2, 0, 1), (1, 2), (1, 1)),           # 24 channels padded to 64
 ]
 
 

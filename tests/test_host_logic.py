@@ -92,12 +92,17 @@ def test_plan_create_validates_and_selects_kernel():
     assert list(shape) == [1, 64, 8, 8]
     assert lib.tsb_conv2d_i8_workspace_bytes(h) >= 256 + 64 * 9 * 64 + 64 * 64
     lib.tsb_conv2d_i8_plan_destroy(h)
+    # small channel counts run on the tensor cores too (folded filter rows / channel padding)
+    for over in (dict(c=3), dict(c=24), dict(c=3, kh=7, kw=7, pad_top=3, pad_bottom=3, pad_left=3, pad_right=3, stride_h=2, stride_w=2, h=32, w=32)):
+        st, h = create(desc(**over))
+        assert st == 0 and lib.tsb_conv2d_i8_kernel(h) == _lib.KERNEL_TCGEN05
+        lib.tsb_conv2d_i8_plan_destroy(h)
     # geometries the tensor-core kernel does not take resolve to the direct kernel
-    for over in (dict(c=3), dict(padding_value=3.0), dict(c=24)):
+    for over in (dict(padding_value=3.0), dict(c=3, kw=11, w=16, pad_left=5, pad_right=5)):
         st, h = create(desc(**over))
         assert st == 0 and lib.tsb_conv2d_i8_kernel(h) == _lib.KERNEL_DIRECT
         lib.tsb_conv2d_i8_plan_destroy(h)
-    st, _ = create(desc(c=3, kernel=_lib.KERNEL_TCGEN05))
+    st, _ = create(desc(padding_value=3.0, kernel=_lib.KERNEL_TCGEN05))
     assert st == _lib.ERR_UNSUPPORTED and b"tcgen05 kernel not available" in lib.tsb_last_error()
     for over in (dict(n=0), dict(stride_h=0), dict(pad_left=-1), dict(kh=11, h=4, pad_top=0, pad_bottom=0), dict(kernel=9)):
         st, _ = create(desc(**over))
