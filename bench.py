@@ -175,7 +175,7 @@ def run_ours(args):
     import numpy as np
     import torch
     import torch.distributed as dist
-    from tennis_b200 import _lib, ops, workloads
+    from tennis_b200 import _lib, ops, sharding, workloads
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -194,16 +194,14 @@ def run_ours(args):
     # ---- resident state: inputs, weights, plans, outputs ----
     state = []
     for layer in layers:
-        d = workloads.make_layer_data(layer, seed=rank)  # per-shard seed
+        d = workloads.make_layer_data(layer, seed=sharding.shard_seed(0, rank))  # per-shard seed
         x = torch.from_numpy(d["x"]).to(dev)
         w = torch.from_numpy(d["w"]).to(dev)
         pad = (layer["pad"],) * 4
         plan = ops.ConvPlan(x.shape, w.shape, pad, (layer["stride"],) * 2, (layer["dilation"],) * 2, 0.0, _lib.KERNEL_AUTO, dev)
         plan.set_weights(w)
         tc = plan.kernel == _lib.KERNEL_TCGEN05
-        cp = ops.padded_channels(layer["c"])
-        xq = torch.empty((layer["n"], layer["h"], layer["w"], cp) if tc else x.shape, dtype=torch.int8, device=dev)
-        state.append(dict(layer=layer, d=d, x=x, w=w, plan=plan, tc=tc, xq=xq,
+        state.append(dict(layer=layer, d=d, x=x, w=w, plan=plan, tc=tc,
                           scales=_lib.float_array([float(d["qscale"])] * layer["n"]),
                           dq=torch.from_numpy(d["dq"]).to(dev), bias=torch.from_numpy(d["bias"]).to(dev),
                           out=torch.empty(plan.out_shape, dtype=torch.float32, device=dev)))
@@ -212,16 +210,11 @@ def run_ours(args):
         return ops._stream_ptr()
 
     def quantize(s):
-        l = s["layer"]
-        if s["tc"]:
-            _lib.check(lib.tsb_quantize_f32_nchw_to_nhwc(s["x"].data_ptr(), s["xq"].data_ptr(), l["n"], l["c"], l["h"], l["w"],
-                                                         s["scales"], l["n"], sptr()))
-        else:
-            _lib.check(lib.tsb_quantize_f32_i8(s["x"].data_ptr(), s["xq"].data_ptr(), s["x"].numel(), s["scales"], l["n"], sptr()))
+        # fp32 NCHW -> the int8 layout the plan's kernel reads, inside the plan's workspace
+        s["plan"].quantize_input(s["x"], s["scales"])
 
     def conv(s):
-        s["plan"].run(s["xq"], _lib.LAYOUT_NHWC_PAD if s["tc"] else _lib.LAYOUT_NCHW, s["dq"], bias=s["bias"],
-                      activation=_lib.ACT_RELU, out_f32=s["out"])
+        s["plan"].run(None, _lib.LAYOUT_STAGED, s["dq"], bias=s["bias"], activation=_lib.ACT_RELU, out_f32=s["out"])
 
     def step():
         for s in state:
@@ -329,12 +322,11 @@ def run_ours(args):
 
     # ---- reduce over ranks: max of the device time, sum of the work ----
     ops_per_step = sum(workloads.layer_ops(l) for l in layers)
-    t = torch.tensor([total_ms, e2e_s], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms_max, e2e_s_max = float(t[0]), float(t[1])
-    value = ops_per_step * world * args.steps / (total_ms_max / 1e3) / 1e12
-    e2e_value = ops_per_step * world / e2e_s_max / 1e12
+    total_ms_max, ops_all = sharding.aggregate(total_ms, ops_per_step * args.steps, dev)
+    e2e_ms_max, e2e_ops_all = sharding.aggregate(e2e_s * 1e3, ops_per_step, dev)
+    e2e_s_max = e2e_ms_max / 1e3
+    value = ops_all / (total_ms_max / 1e3) / 1e12
+    e2e_value = e2e_ops_all / e2e_s_max / 1e12
 
     if rank == 0:
         tc_layers = [p for p in per_layer if p["kernel"] == "tcgen05"]

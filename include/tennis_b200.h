@@ -42,6 +42,7 @@ extern "C" {
 /* memory layouts of activations */
 #define TSB_LAYOUT_NCHW 0     /* the operator-visible layout of TenniS tensors */
 #define TSB_LAYOUT_NHWC_PAD 1 /* internal: [N][H][W][Cp], Cp = tsb_padded_channels(C), padding channels zero */
+#define TSB_LAYOUT_STAGED 2   /* input only: already in the plan's workspace, written by tsb_conv2d_i8_quantize_input */
 
 /* which convolution kernel a plan uses */
 #define TSB_KERNEL_AUTO 0
@@ -165,6 +166,15 @@ TSB_API size_t tsb_conv2d_i8_workspace_bytes(const tsb_conv_plan *plan);
  */
 TSB_API int tsb_conv2d_i8_set_weights(tsb_conv_plan *plan, const int8_t *w_oihw, void *workspace, size_t workspace_bytes,
                               void *stream);
+/*
+ * quantize (rules of tsb_quantize_f32_i8 on the NCHW element index) an fp32 NCHW input straight into the layout
+ * this plan's kernel reads, inside the plan's workspace.  Follow with tsb_conv2d_i8_run(plan, NULL,
+ * TSB_LAYOUT_STAGED, ...).  This is the shortest route from an fp32 tensor to the convolution: no int8 NCHW
+ * tensor is materialised and no separate repack runs.
+ */
+TSB_API int tsb_conv2d_i8_quantize_input(tsb_conv_plan *plan, const float *x_f32_nchw, const float *scales_host,
+                                         int nscales, void *workspace, size_t workspace_bytes, void *stream);
+
 /*
  * Run one convolution.  x_layout says whether x is operator-visible NCHW int8 or the internal NHWC_PAD
  * tensor written by tsb_quantize_f32_nchw_to_nhwc / a previous run's out_i8.

@@ -16,7 +16,7 @@ ERR_WORKSPACE_TOO_SMALL = -3
 ERR_DEVICE_TIMEOUT = -4
 
 ACT_NONE, ACT_RELU, ACT_LEAKY_RELU = 0, 1, 2
-LAYOUT_NCHW, LAYOUT_NHWC_PAD = 0, 1
+LAYOUT_NCHW, LAYOUT_NHWC_PAD, LAYOUT_STAGED = 0, 1, 2
 KERNEL_AUTO, KERNEL_DIRECT, KERNEL_TCGEN05 = 0, 1, 2
 
 
@@ -63,6 +63,7 @@ SYMBOLS = {
     "tsb_conv2d_i8_kernel": (_i, [_vp]),
     "tsb_conv2d_i8_workspace_bytes": (_sz, [_vp]),
     "tsb_conv2d_i8_set_weights": (_i, [_vp, _vp, _vp, _sz, _vp]),
+    "tsb_conv2d_i8_quantize_input": (_i, [_vp, _vp, _fp, _i, _vp, _sz, _vp]),
     "tsb_conv2d_i8_run": (_i, [_vp, _vp, _i, ctypes.POINTER(ConvEpilogue), _vp, _sz, _vp]),
     "tsb_conv2d_i8_status": (_i, [_vp, _vp, _vp]),
     "tsb_conv2d_host_scratch_bytes": (_sz, [_vp]),

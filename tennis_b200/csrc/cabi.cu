@@ -18,6 +18,7 @@ std::atomic<int64_t> g_launches{0};
 int quantize_f32_i8(const float *, int8_t *, int64_t, const float *, int, cudaStream_t);
 int quantize_f32_i8_static(const float *, int8_t *, int64_t, const float *, int, cudaStream_t);
 int quantize_f32_nchw_to_nhwc(const float *, int8_t *, int, int, int, int, const float *, int, cudaStream_t);
+int quantize_stage(const float *, int8_t *, int, int, int, int, int, int, int, int, const float *, int, cudaStream_t);
 int repack_i8_nchw_to_nhwc(const int8_t *, int8_t *, int, int, int, int, cudaStream_t);
 int repack_i8_nhwc_to_nchw(const int8_t *, int8_t *, int, int, int, int, cudaStream_t);
 int add_bias_f32_nchw(const float *, float *, int, int, int, const float *, cudaStream_t);
@@ -151,6 +152,7 @@ int tsb_conv2d_i8_plan_create(const tsb_conv_desc *d, tsb_conv_plan **out) {
     // NHWC_PAD staging of an operator-visible NCHW input (either kernel can read NHWC_PAD; only the tensor-core
     // kernel needs it)
     if (p->kernel == TSB_KERNEL_TCGEN05) end += align256(p->view.stage_bytes);
+    else end += align256((size_t)g.N * g.C * g.H * g.W);
     p->ws_bytes = end;
     p->weights_oihw = nullptr;
     p->weights_ws = nullptr;
@@ -229,23 +231,43 @@ static int build_epilogue(const tsb_conv_plan *plan, const tsb_conv_epilogue *e,
     return TSB_OK;
 }
 
+int tsb_conv2d_i8_quantize_input(tsb_conv_plan *plan, const float *x_f32_nchw, const float *scales_host, int nscales,
+                                 void *workspace, size_t workspace_bytes, void *stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (!plan || !x_f32_nchw || !workspace) return fail(TSB_ERR_INVALID_ARGUMENT, "quantize_input: null pointer");
+    if (workspace_bytes < plan->ws_bytes) return fail(TSB_ERR_WORKSPACE_TOO_SMALL, "quantize_input: workspace %zu < %zu", workspace_bytes, plan->ws_bytes);
+    if (reinterpret_cast<uintptr_t>(workspace) % 256) return fail(TSB_ERR_INVALID_ARGUMENT, "quantize_input: workspace must be 256-byte aligned");
+    const ConvGeom &g = plan->geom;
+    int8_t *stage = static_cast<int8_t *>(workspace) + plan->off_stage;
+    if (plan->kernel == TSB_KERNEL_TCGEN05 && plan->view.fold)
+        return quantize_stage(x_f32_nchw, stage, g.N, g.C, g.H, g.W, 1, plan->view.Wp, plan->view.cpix, g.pad_l, scales_host, nscales, stream);
+    if (plan->kernel == TSB_KERNEL_TCGEN05)
+        return quantize_stage(x_f32_nchw, stage, g.N, g.C, g.H, g.W, 0, 0, 0, 0, scales_host, nscales, stream);
+    return quantize_f32_i8(x_f32_nchw, stage, (int64_t)g.N * g.C * g.H * g.W, scales_host, nscales, stream);  // direct kernel: NCHW
+}
+
 int tsb_conv2d_i8_run(tsb_conv_plan *plan, const int8_t *x, int x_layout, const tsb_conv_epilogue *epilogue,
                       void *workspace, size_t workspace_bytes, void *stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
-    if (!plan || !x || !epilogue || !workspace) return fail(TSB_ERR_INVALID_ARGUMENT, "run: null pointer");
-    if (x_layout != TSB_LAYOUT_NCHW && x_layout != TSB_LAYOUT_NHWC_PAD) return fail(TSB_ERR_INVALID_ARGUMENT, "run: unknown x_layout %d", x_layout);
+    if (!plan || !epilogue || !workspace) return fail(TSB_ERR_INVALID_ARGUMENT, "run: null pointer");
+    if (x_layout != TSB_LAYOUT_NCHW && x_layout != TSB_LAYOUT_NHWC_PAD && x_layout != TSB_LAYOUT_STAGED) return fail(TSB_ERR_INVALID_ARGUMENT, "run: unknown x_layout %d", x_layout);
+    if (!x && x_layout != TSB_LAYOUT_STAGED) return fail(TSB_ERR_INVALID_ARGUMENT, "run: null input");
     if (workspace_bytes < plan->ws_bytes) return fail(TSB_ERR_WORKSPACE_TOO_SMALL, "run: workspace %zu < %zu", workspace_bytes, plan->ws_bytes);
     if (plan->weights_ws != workspace || !plan->weights_oihw) return fail(TSB_ERR_INVALID_ARGUMENT, "run: tsb_conv2d_i8_set_weights was not called with this workspace");
     EpiParams epi;
     int st = build_epilogue(plan, epilogue, &epi);
     if (st != TSB_OK) return st;
     const ConvGeom &g = plan->geom;
-    if (plan->kernel == TSB_KERNEL_DIRECT)
+    int8_t *stage = static_cast<int8_t *>(workspace) + plan->off_stage;
+    if (plan->kernel == TSB_KERNEL_DIRECT) {
+        if (x_layout == TSB_LAYOUT_STAGED) return launch_conv_direct(g, stage, 0, plan->weights_oihw, epi, stream);
         return launch_conv_direct(g, x, x_layout == TSB_LAYOUT_NHWC_PAD, plan->weights_oihw, epi, stream);
+    }
 
     const int8_t *x_tc = x;
-    int8_t *stage = static_cast<int8_t *>(workspace) + plan->off_stage;
-    if (plan->view.fold) {
+    if (x_layout == TSB_LAYOUT_STAGED) {
+        x_tc = stage;
+    } else if (plan->view.fold) {
         st = tc::stage_folded(plan->view, x, x_layout == TSB_LAYOUT_NHWC_PAD, stage, stream);
         if (st != TSB_OK) return st;
         x_tc = stage;
@@ -275,14 +297,13 @@ int tsb_conv2d_i8_status(tsb_conv_plan *plan, void *workspace, void *stream_) {
 // ---- host-buffer convenience --------------------------------------------------------------------------
 namespace {
 struct HostScratch {
-    size_t x_f32, x_q, w, dq, bias, out, ws, total;
+    size_t x_f32, w, dq, bias, out, ws, total;
 };
 HostScratch host_layout(const tsb_conv_plan *p) {
     const ConvGeom &g = p->geom;
     HostScratch s;
     size_t off = 0;
     s.x_f32 = off; off += align256((size_t)g.N * g.C * g.H * g.W * 4);
-    s.x_q = off;   off += align256((size_t)g.N * g.Cp * g.H * g.W);
     s.w = off;     off += align256((size_t)g.O * g.C * g.KH * g.KW);
     s.dq = off;    off += align256((size_t)g.O * 4);
     s.bias = off;  off += align256((size_t)g.O * 4);
@@ -309,7 +330,6 @@ int tsb_conv2d_quantized_host(tsb_conv_plan *plan, const float *x_host, const fl
     if (nq != g.N) return fail(TSB_ERR_INVALID_ARGUMENT, "conv2d_quantized_host: %d quantize scales for batch %d (one per sample, base_quantize.cpp:26)", nq, g.N);
     char *base = static_cast<char *>(scratch);
     float *d_x = reinterpret_cast<float *>(base + L.x_f32);
-    int8_t *d_xq = reinterpret_cast<int8_t *>(base + L.x_q);
     int8_t *d_w = reinterpret_cast<int8_t *>(base + L.w);
     float *d_dq = reinterpret_cast<float *>(base + L.dq);
     float *d_bias = reinterpret_cast<float *>(base + L.bias);
@@ -324,14 +344,7 @@ int tsb_conv2d_quantized_host(tsb_conv_plan *plan, const float *x_host, const fl
         st = tsb_conv2d_i8_set_weights(plan, d_w, ws, plan->ws_bytes, stream);
         if (st != TSB_OK) return st;
     }
-    int x_layout;
-    if (plan->kernel == TSB_KERNEL_TCGEN05) {
-        st = quantize_f32_nchw_to_nhwc(d_x, d_xq, g.N, g.C, g.H, g.W, qscales_host, nq, stream);
-        x_layout = TSB_LAYOUT_NHWC_PAD;
-    } else {
-        st = quantize_f32_i8(d_x, d_xq, (int64_t)g.N * g.C * g.H * g.W, qscales_host, nq, stream);
-        x_layout = TSB_LAYOUT_NCHW;
-    }
+    st = tsb_conv2d_i8_quantize_input(plan, d_x, qscales_host, nq, ws, plan->ws_bytes, stream);
     if (st != TSB_OK) return st;
     tsb_conv_epilogue e;
     std::memset(&e, 0, sizeof(e));
@@ -341,7 +354,7 @@ int tsb_conv2d_quantized_host(tsb_conv_plan *plan, const float *x_host, const fl
     e.leaky_scale = leaky;
     e.out_f32 = d_out;
     e.out_f32_layout = TSB_LAYOUT_NCHW;
-    st = tsb_conv2d_i8_run(plan, d_xq, x_layout, &e, ws, plan->ws_bytes, stream);
+    st = tsb_conv2d_i8_run(plan, nullptr, TSB_LAYOUT_STAGED, &e, ws, plan->ws_bytes, stream);
     if (st != TSB_OK) return st;
     TSB_CUDA(cudaMemcpyAsync(out_host, d_out, (size_t)g.N * g.O * g.OH * g.OW * 4, cudaMemcpyDeviceToHost, stream));
     TSB_CUDA(cudaStreamSynchronize(stream));

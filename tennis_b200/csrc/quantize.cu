@@ -167,6 +167,63 @@ nhwc_to_nchw_kernel(const int8_t *__restrict__ x, int8_t *__restrict__ y, int C,
     }
 }
 
+// fp32 NCHW -> int8 in the layout a convolution consumes, quantized on the way.  One thread produces 16 output
+// bytes: 16 channels of one pixel (NHWC_PAD, or the folded layout with 16 bytes per pixel) or 8 channels of two
+// neighbouring pixels (folded layout with 8 bytes per pixel).  Consecutive threads read consecutive pixels of each
+// channel plane (full 32-byte sectors) and write consecutive 16-byte units (fully coalesced), so no shared memory
+// is needed.  Rounding and scale groups follow the NCHW element index.
+struct StageDesc {
+    int N, C, H, W;
+    int folded;      // 0: [N][H][W][Cp]; 1: [N][H][Wp][cpix] with pixel w at column w + pad_l
+    int Cp;          // NHWC_PAD channels
+    int Wp, cpix, pad_l;
+};
+
+__global__ void __launch_bounds__(kThreads)
+quantize_stage_kernel(const float *__restrict__ x, int8_t *__restrict__ y, StageDesc d, int64_t units, QuantRule rule,
+                      ScaleArg scales) {
+    const uint32_t rne_limit = (uint32_t)rule.rne_limit;
+    const uint32_t group_len = (uint32_t)rule.group_len;
+    const int HW = d.H * d.W;
+    const int units_per_pixel = d.Cp / 16;                 // NHWC_PAD
+    const int units_per_row = d.folded ? d.Wp * d.cpix / 16 : 0;
+    for (int64_t u = (int64_t)blockIdx.x * kThreads + threadIdx.x; u < units; u += (int64_t)gridDim.x * kThreads) {
+        int n, h, w0, c0, npix, nch;
+        if (!d.folded) {
+            const int64_t pix = u / units_per_pixel;
+            c0 = (int)(u - pix * units_per_pixel) * 16;
+            n = (int)(pix / HW);
+            const int p = (int)(pix - (int64_t)n * HW);
+            h = p / d.W;
+            w0 = p - h * d.W;
+            npix = 1; nch = 16;
+        } else {
+            const int ur = (int)(u % units_per_row);
+            const int64_t row = u / units_per_row;
+            h = (int)(row % d.H);
+            n = (int)(row / d.H);
+            npix = 16 / d.cpix; nch = d.cpix;
+            w0 = ur * npix - d.pad_l;
+            c0 = 0;
+        }
+        uint32_t word[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int b = 0; b < 16; ++b) {
+            const int pi = npix == 1 ? 0 : (b >> 3);       // two pixels of 8 channels, or one pixel of 16
+            const int c = c0 + (npix == 1 ? b : (b & 7));
+            const int w = w0 + pi;
+            int q = 0;
+            if (c < d.C && (unsigned)w < (unsigned)d.W && (npix == 1 ? b : (b & 7)) < nch) {
+                const uint32_t idx = (uint32_t)((n * d.C + c) * d.H + h) * (uint32_t)d.W + (uint32_t)w;
+                const uint32_t g = rule.nscales == 1 ? 0u : idx / group_len;
+                if (g < (uint32_t)rule.nscales) q = q8(x[idx], scales.get(g), idx < rne_limit);
+            }
+            word[b >> 2] |= (uint32_t)(q & 0xff) << (8 * (b & 3));
+        }
+        *reinterpret_cast<int4 *>(y + u * 16) = make_int4(word[0], word[1], word[2], word[3]);
+    }
+}
+
 __global__ void __launch_bounds__(kThreads)
 add_bias_nchw_kernel(const float *__restrict__ x, float *__restrict__ y, int C, int HW, int64_t count,
                      const float *__restrict__ bias) {
@@ -255,22 +312,36 @@ static int check_nchw(const void *x, const void *y, int n, int c, int h, int w, 
     return TSB_OK;
 }
 
-int quantize_f32_nchw_to_nhwc(const float *x, int8_t *y, int n, int c, int h, int w, const float *scales_host,
-                              int nscales, cudaStream_t stream) {
-    int st = check_nchw(x, y, n, c, h, w, "quantize_nchw_to_nhwc");
+// fp32 NCHW -> staged int8.  folded == 0: NHWC_PAD with tsb_padded_channels(c) channels; folded == 1: rows of wp
+// pixels of cpix bytes, pixel w at column w + pad_l.
+int quantize_stage(const float *x, int8_t *y, int n, int c, int h, int w, int folded, int wp, int cpix, int pad_l,
+                   const float *scales_host, int nscales, cudaStream_t stream) {
+    int st = check_nchw(x, y, n, c, h, w, "quantize_stage");
     if (st != TSB_OK) return st;
-    if (!scales_host || nscales < 1) return fail(TSB_ERR_INVALID_ARGUMENT, "quantize_nchw_to_nhwc: needs scales");
-    if (reinterpret_cast<uintptr_t>(y) % 16) return fail(TSB_ERR_INVALID_ARGUMENT, "quantize_nchw_to_nhwc: output must be 16-byte aligned");
+    if (!scales_host || nscales < 1) return fail(TSB_ERR_INVALID_ARGUMENT, "quantize_stage: needs scales");
+    if (reinterpret_cast<uintptr_t>(y) % 16) return fail(TSB_ERR_INVALID_ARGUMENT, "quantize_stage: output must be 16-byte aligned");
+    if (folded && (c > cpix || (cpix != 8 && cpix != 16) || (wp * cpix) % 16 != 0))
+        return fail(TSB_ERR_INVALID_ARGUMENT, "quantize_stage: bad folded layout");
     QuantRule rule = make_quant_rule((int64_t)n * c * h * w, nscales);
     ScaleArg arg;
     float *tmp = nullptr;
     st = make_scale_arg(scales_host, nscales, stream, &arg, &tmp);
     if (st != TSB_OK) return st;
-    dim3 grid(ceil_div(h * w, 64), ceil_div(tsb_padded_channels(c), 64), n);
-    nchw_to_nhwc_kernel<float><<<grid, kThreads, 0, stream>>>(x, y, c, tsb_padded_channels(c), h * w, rule, arg);
-    TSB_LAUNCHED("nchw_to_nhwc_kernel<float>");
+    StageDesc d;
+    d.N = n; d.C = c; d.H = h; d.W = w;
+    d.folded = folded;
+    d.Cp = tsb_padded_channels(c);
+    d.Wp = wp; d.cpix = cpix; d.pad_l = pad_l;
+    const int64_t units = folded ? (int64_t)n * h * (wp * cpix / 16) : (int64_t)n * h * w * (d.Cp / 16);
+    quantize_stage_kernel<<<grid_for(units), kThreads, 0, stream>>>(x, y, d, units, rule, arg);
+    TSB_LAUNCHED("quantize_stage_kernel");
     if (tmp) TSB_CUDA(cudaFreeAsync(tmp, stream));
     return TSB_OK;
+}
+
+int quantize_f32_nchw_to_nhwc(const float *x, int8_t *y, int n, int c, int h, int w, const float *scales_host,
+                              int nscales, cudaStream_t stream) {
+    return quantize_stage(x, y, n, c, h, w, 0, 0, 0, 0, scales_host, nscales, stream);
 }
 
 int repack_i8_nchw_to_nhwc(const int8_t *x, int8_t *y, int n, int c, int h, int w, cudaStream_t stream) {

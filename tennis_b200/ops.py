@@ -17,7 +17,7 @@ import torch
 
 from . import _lib
 from ._lib import (ACT_LEAKY_RELU, ACT_NONE, ACT_RELU, KERNEL_AUTO, KERNEL_DIRECT, KERNEL_TCGEN05, LAYOUT_NCHW,
-                   LAYOUT_NHWC_PAD, ConvDesc, ConvEpilogue, TsbError, check, float_array)
+                   LAYOUT_NHWC_PAD, LAYOUT_STAGED, ConvDesc, ConvEpilogue, TsbError, check, float_array)
 
 REQUIRED, OPTIONAL = "required", "optional"
 
@@ -160,6 +160,12 @@ class ConvPlan:
         self.weights = w.contiguous()  # the direct kernel reads this tensor at run time
         check(_lib.load().tsb_conv2d_i8_set_weights(self.handle, _ptr(self.weights), _ptr(self.workspace), self.ws_bytes,
                                                     _stream_ptr(stream)))
+
+    def quantize_input(self, x_f32, scales, stream=None):
+        """fp32 NCHW -> the plan's staged int8 input; run() is then called with x=None, x_layout=LAYOUT_STAGED."""
+        arr = scales if not isinstance(scales, (list, tuple)) else float_array(scales)
+        check(_lib.load().tsb_conv2d_i8_quantize_input(self.handle, _ptr(x_f32), arr, len(arr), _ptr(self.workspace),
+                                                       self.ws_bytes, _stream_ptr(stream)))
 
     def run(self, x, x_layout, dq, bias=None, residual=None, activation=ACT_NONE, leaky=0.0, out_f32=None,
             out_f32_layout=LAYOUT_NCHW, out_i8=None, out_i8_layout=LAYOUT_NCHW, requant_scales=None, out_acc=None,

@@ -18,13 +18,8 @@ def run_layer(layer, d, requant=None):
     plan = ops.ConvPlan(x.shape, w.shape, pad, (layer["stride"],) * 2, (layer["dilation"],) * 2, 0.0, 0, dev)
     plan.set_weights(w)
     scales = [float(d["qscale"])] * layer["n"]
-    if plan.kernel == _lib.KERNEL_TCGEN05:
-        xq, xl = ops.quantize_nchw_to_nhwc(x, scales), _lib.LAYOUT_NHWC_PAD
-    else:
-        q = ops.Quantize()
-        q.set("quantize_scale", np.asarray(scales, np.float32))
-        q.init()
-        xq, xl = q.run([x]), _lib.LAYOUT_NCHW
+    plan.quantize_input(x, scales)
+    xq, xl = None, _lib.LAYOUT_STAGED
     out = torch.empty(plan.out_shape, dtype=torch.float32, device=dev)
     acc = torch.empty(plan.out_shape, dtype=torch.int32, device=dev)
     plan.run(xq, xl, torch.from_numpy(d["dq"]).to(dev), bias=torch.from_numpy(d["bias"]).to(dev),

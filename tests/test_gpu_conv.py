@@ -205,6 +205,36 @@ def test_operator_mirror_runs_like_the_reference_operator(checker):
     assert torch.equal(y, y2)
 
 
+@pytest.mark.parametrize("case", [
+    (2, 64, 9, 9, 40, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1), 0.0),      # tensor cores, NHWC_PAD staging
+    (2, 3, 15, 17, 6, 7, 7, (3, 3, 3, 3), (2, 2), (1, 1), 0.0),      # tensor cores, folded staging, 8 bytes per pixel
+    (1, 5, 11, 12, 7, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1), 0.0),      # folded staging, 16 bytes per pixel
+    (3, 70, 6, 6, 9, 1, 1, (0, 0, 0, 0), (1, 1), (1, 1), 0.0),       # channels padded 70 -> 128
+    (2, 5, 6, 6, 3, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1), 3.0),        # direct kernel (padding_value)
+])
+def test_quantize_into_the_plan_then_run_staged(checker, case):
+    """fp32 input -> tsb_conv2d_i8_quantize_input -> run(TSB_LAYOUT_STAGED) equals quantize + conv2d_quantized."""
+    from tennis_b200 import _lib, ops
+    N, C, H, W, O, KH, KW, pad, stride, dil, pv = case
+    rng = np.random.default_rng(C + 17 * O)
+    x = (rng.standard_normal((N, C, H, W)) * 50).astype(np.float32)
+    x.reshape(-1)[::7] = np.round(x.reshape(-1)[::7]) + 0.5   # ties
+    w = rng.integers(-127, 128, size=(O, C, KH, KW), dtype=np.int8)
+    dq = rng.uniform(0.001, 0.01, size=O).astype(np.float32)
+    bias = (rng.standard_normal(O) * 0.1).astype(np.float32)
+    for scales in ([1.0] * N, list(rng.uniform(0.5, 2.0, size=N))):
+        xq = checker.quantize(x, scales)
+        want = checker.conv_block(xq, w, pad, stride, dil, dq, bias, act="relu", padding_value=pv)
+        plan = ops.ConvPlan(x.shape, w.shape, pad, stride, dil, pv)
+        plan.set_weights(torch.from_numpy(w).cuda())
+        plan.quantize_input(torch.from_numpy(x).cuda(), [float(v) for v in scales])
+        out = torch.empty(plan.out_shape, dtype=torch.float32, device="cuda")
+        plan.run(None, _lib.LAYOUT_STAGED, torch.from_numpy(dq).cuda(), bias=torch.from_numpy(bias).cuda(),
+                 activation=_lib.ACT_RELU, out_f32=out)
+        plan.status()
+        assert same_bits(out.cpu().numpy(), want)
+
+
 def test_host_buffer_entry_point(checker):
     import ctypes
     from tennis_b200 import _lib, ops, workloads
