@@ -207,6 +207,10 @@ TSB_API int tsb_add_bias_f32_nchw(const float *x, float *y, int n, int c, int hw
 TSB_API int tsb_relu_f32(const float *x, float *y, int64_t count, void *stream);
 TSB_API int tsb_leaky_relu_f32(const float *x, float *y, int64_t count, float scale, void *stream);
 
+/* Debugging aid: while a device buffer of 2048 bytes is set, CTA 0 of each tensor-core convolution launch records a
+ * timeline (eight nanosecond stamps per tile for its first 32 tiles) into it.  NULL (the default) switches it off. */
+TSB_API int tsb_debug_set_trace_buffer(void *device_buffer);
+
 /* Number of kernels this library has launched on the calling process since load (bench bookkeeping). */
 TSB_API int64_t tsb_kernel_launch_count(void);
 

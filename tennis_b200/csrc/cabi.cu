@@ -3,6 +3,7 @@
 #include "conv_common.cuh"
 #include "conv_tc.h"
 
+#include <cstdlib>
 #include <cstring>
 #include <new>
 
@@ -68,10 +69,16 @@ int tsb_version(void) { return 100; }
 
 int tsb_padded_channels(int channels) {
     if (channels <= 16) return 16;
-    return round_up(channels, 64);
+    static const int unit = getenv("TSB_PAD128") ? 128 : 64;
+    return round_up(channels, unit);
 }
 
 int64_t tsb_kernel_launch_count(void) { return g_launches.load(); }
+
+int tsb_debug_set_trace_buffer(void *device_buffer) {
+    tc::set_trace_buffer(static_cast<unsigned long long *>(device_buffer));
+    return TSB_OK;
+}
 
 int tsb_quantize_f32_i8(const float *x, int8_t *y, int64_t count, const float *scales_host, int nscales, void *stream) {
     return quantize_f32_i8(x, y, count, scales_host, nscales, (cudaStream_t)stream);

@@ -23,6 +23,7 @@
 #include <cudaTypedefs.h>
 
 #include <algorithm>
+#include <cstdlib>
 
 namespace tsb {
 namespace tc {
@@ -219,7 +220,7 @@ __device__ __forceinline__ void store_i8_nhwc(const int (&v)[32], const float *d
 }
 
 // Everything else: several outputs at once, residual, NCHW int8, partial tiles.  o0 = first output channel.
-__device__ __noinline__ void store_generic(const int (&v)[32], const float *dq, const float *bias, const EpiParams &epi,
+__device__ __forceinline__ void store_generic(const int (&v)[32], const float *dq, const float *bias, const EpiParams &epi,
                                            int per_sample_scale, int img, int p, int m, int o0) {
     const EpilogueMath math{epi.activation, epi.leaky};
     const uint32_t nchw0 = (uint32_t)(img * epi.O) * (uint32_t)epi.P + (uint32_t)p;  // + o*P
@@ -272,52 +273,81 @@ struct KernelParams {
     int num_m_tiles, num_n_tiles;
     int per_sample_scale;  // requantize: scale index = image index
     int epi_mode;          // kEpi*: which epilogue code path full 32-column chunks take
+    int a_tiled;           // activations are a plain [M][Cp] matrix (1x1, stride 1, no padding): 2-D tile loads
+    // shared-memory plan (bytes from the 1024-aligned base)
+    int stages;            // pipeline stages (<= kMaxStages)
+    uint32_t stage_bytes;  // one stage: the A tile, followed by the B tile unless the weights are resident
+    int b_resident;        // all K blocks of this CTA's weight tile stay in shared memory; only activations stream
+    uint32_t b_off;        // offset of the resident weights
+    uint32_t bar_off;      // offset of the mbarriers; tensor-memory slot, abort flag and epilogue tables follow
     int *status;     // device word: 0 ok, else the code of the wait that ran out
+    unsigned long long *trace;  // optional timeline of CTA 0 (debugging aid): 8 stamps per tile, 32 tiles
 };
 
-template <int BN, int BK>
-struct Smem {
-    static constexpr uint32_t kABytes = kBM * BK;
-    static constexpr uint32_t kBBytes = BN * BK;
-    static constexpr uint32_t kStageBytes = kABytes + kBBytes;
-    static constexpr int kStages = (kSmemBudget / kStageBytes) > 8 ? 8 : (kSmemBudget / kStageBytes);
-    static constexpr uint32_t kTileBytes = kStages * kStageBytes;
-    // after the tiles: full[kStages], empty[kStages], tmem_full[2], tmem_empty[2], tmem base, abort flag, tables
-    static constexpr uint32_t kBarOff = kTileBytes;
-    static constexpr uint32_t kTmemSlotOff = kBarOff + 8 * (2 * kStages + 4);
-    static constexpr uint32_t kAbortOff = kTmemSlotOff + 4;
-    static constexpr uint32_t kTableOff = (kAbortOff + 4 + 15) & ~15u;
-    static constexpr uint32_t kTotal = kTableOff + 2 * 2 * BN * 4;  // dq and bias, double buffered
-    static constexpr uint32_t kDynamic = kTotal + 1024;             // slack to align the tiles to 1024 bytes
-};
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define TSB_TRACE(tile_index, slot)                                                              \
+    do {                                                                                         \
+        if (kp.trace && blockIdx.x == 0 && (tile_index) < 32) kp.trace[(tile_index) * 8 + (slot)] = global_ns(); \
+    } while (0)
+
+constexpr int kMaxStages = 8;
+constexpr uint32_t kMaxDynamicSmem = 227 * 1024;
+
+// barriers: full[stages], empty[stages], tmem_full[2], tmem_empty[2], b_full, b_free
+__host__ __device__ constexpr uint32_t num_barriers(int stages) { return 2u * (uint32_t)stages + 6u; }
 
 template <int BN, int BK>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ KernelParams kp, const __grid_constant__ EpiParams epi) {
-    using S = Smem<BN, BK>;
-    constexpr int kStages = S::kStages;
+    constexpr uint32_t kABytes = kBM * BK, kBBytes = BN * BK;
     constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // power of two for BN in {32,64,128,256}
+    const int kStages = kp.stages;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t *base_ptr = smem_raw + (base - raw);
-    const uint32_t bar_full = base + S::kBarOff;
+    const uint32_t bar_full = base + kp.bar_off;
     const uint32_t bar_empty = bar_full + 8 * kStages;
     const uint32_t bar_tfull = bar_empty + 8 * kStages;
     const uint32_t bar_tempty = bar_tfull + 16;
-    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + S::kTmemSlotOff);
-    volatile int *abort_flag = reinterpret_cast<volatile int *>(base_ptr + S::kAbortOff);
-    float *table = reinterpret_cast<float *>(base_ptr + S::kTableOff);
+    const uint32_t bar_bfull = bar_tempty + 16;
+    const uint32_t bar_bfree = bar_bfull + 8;
+    const uint32_t slot_off = kp.bar_off + 8 * num_barriers(kStages);
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + slot_off);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(base_ptr + slot_off + 4);
+    float *table = reinterpret_cast<float *>(base_ptr + ((slot_off + 8 + 15) & ~15u));
+    const uint32_t b_res = base + kp.b_off;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_tiles = kp.num_m_tiles * kp.num_n_tiles;
     const int k_iters = kp.KH * kp.KW * (kp.Cp / BK);
+    // This CTA's tiles.  Streaming weights: tiles blockIdx.x, +gridDim.x, ... with the N tile running fastest.
+    // Resident weights: one contiguous range of the N-major tile order, so the weight tile changes at most a few times.
+    const int tile_lo = kp.b_resident ? (int)((long long)blockIdx.x * total_tiles / gridDim.x) : 0;
+    const int tile_hi = kp.b_resident ? (int)((long long)(blockIdx.x + 1) * total_tiles / gridDim.x) : 0;
+    const int my_tiles = kp.b_resident ? tile_hi - tile_lo : (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    auto decode = [&](int i, int &m_tile, int &n_tile) {
+        if (kp.b_resident) {
+            const int t = tile_lo + i;
+            n_tile = t / kp.num_m_tiles; m_tile = t - n_tile * kp.num_m_tiles;
+        } else {
+            const int t = (int)blockIdx.x + i * (int)gridDim.x;
+            m_tile = t / kp.num_n_tiles; n_tile = t - m_tile * kp.num_n_tiles;
+        }
+    };
 
     if (threadIdx.x == 0) {
+        TSB_TRACE(0, 7);
         for (int s = 0; s < kStages; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, kEpiThreads); }
+        mbar_init(bar_bfull, 1);
+        mbar_init(bar_bfree, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -336,12 +366,27 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         if (lane == 0) {
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int n_tile = tile % kp.num_n_tiles, m_tile = tile / kp.num_n_tiles;
+            int cur_n = -1, b_loads = 0;
+            for (int i = 0; i < my_tiles && ok; ++i) {
+                TSB_TRACE(i, 0);
+                int m_tile, n_tile;
+                decode(i, m_tile, n_tile);
                 const int m0 = m_tile * kBM;
                 const int img = m0 / kp.P, rem = m0 - img * kp.P;
                 const int oh = rem / kp.OW, ow = rem - oh * kp.OW;
                 const int wc = ow * kp.sw - kp.pad_l, hc = oh * kp.sh - kp.pad_t;
+                if (kp.b_resident && n_tile != cur_n) {
+                    // (re)load the whole weight tile; wait until the MMAs that read the previous one are done
+                    if (b_loads > 0 && !mbar_wait(bar_bfree, (uint32_t)(b_loads - 1) & 1u, abort_flag)) {
+                        if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 5); }
+                        break;
+                    }
+                    mbar_arrive_expect_tx(bar_bfull, (uint32_t)k_iters * kBBytes);
+                    for (int it = 0; it < k_iters; ++it)
+                        tma_load_2d(b_res + (uint32_t)it * kBBytes, &map_b, bar_bfull, it * BK, n_tile * BN);
+                    cur_n = n_tile;
+                    ++b_loads;
+                }
                 for (int kh = 0; kh < kp.KH && ok; ++kh)
                     for (int kw = 0; kw < kp.KW && ok; ++kw)
                         for (int cb = 0; cb < kp.Cp; cb += BK) {
@@ -350,13 +395,22 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                                 ok = false;
                                 break;
                             }
-                            const uint32_t sa = base + stage * S::kStageBytes, sb = sa + S::kABytes;
-                            mbar_arrive_expect_tx(bar_full + 8 * stage, S::kStageBytes);
-                            tma_load_im2col_4d(sa, &map_a, bar_full + 8 * stage, cb, wc, hc, img,
-                                               (uint16_t)(kw * kp.dw), (uint16_t)(kh * kp.dh));
-                            tma_load_2d(sb, &map_b, bar_full + 8 * stage, (kh * kp.KW + kw) * kp.Cp + cb, n_tile * BN);
+                            const uint32_t sa = base + stage * kp.stage_bytes, sb = sa + kABytes;
+                            if (kp.trace && blockIdx.x == 0 && i == 3) {
+                                const int itx = (kh * kp.KW + kw) * (kp.Cp / BK) + cb / BK;
+                                if (itx < 16) kp.trace[256 + itx] = global_ns();
+                            }
+                            mbar_arrive_expect_tx(bar_full + 8 * stage, kp.b_resident ? kABytes : kABytes + kBBytes);
+                            if (kp.a_tiled)
+                                tma_load_2d(sa, &map_a, bar_full + 8 * stage, cb, m0);
+                            else
+                                tma_load_im2col_4d(sa, &map_a, bar_full + 8 * stage, cb, wc, hc, img,
+                                                   (uint16_t)(kw * kp.dw), (uint16_t)(kh * kp.dh));
+                            if (!kp.b_resident)
+                                tma_load_2d(sb, &map_b, bar_full + 8 * stage, (kh * kp.KW + kw) * kp.Cp + cb, n_tile * BN);
                             if (++stage == kStages) { stage = 0; phase ^= 1u; }
                         }
+                TSB_TRACE(i, 1);
             }
         }
     } else if (warp == 1) {
@@ -365,15 +419,26 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             constexpr uint32_t idesc = instr_desc<BN>();
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
-            int local = 0;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+            int cur_n = -1, b_loads = 0;
+            for (int local = 0; local < my_tiles && ok; ++local) {
+                int m_tile, n_tile;
+                decode(local, m_tile, n_tile);
                 const int acc = local & 1;
                 const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
                 if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag)) {
                     if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 2); }
                     break;
                 }
+                if (kp.b_resident && n_tile != cur_n) {
+                    if (!mbar_wait(bar_bfull, (uint32_t)b_loads & 1u, abort_flag)) {
+                        if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 6); }
+                        break;
+                    }
+                    cur_n = n_tile;
+                    ++b_loads;
+                }
                 tc_fence_after();
+                TSB_TRACE(local, 2);
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
                 for (int it = 0; it < k_iters; ++it) {
                     if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
@@ -382,7 +447,10 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t sa = base + stage * S::kStageBytes, sb = sa + S::kABytes;
+                    if (it == 0) TSB_TRACE(local, 3);
+                    if (kp.trace && blockIdx.x == 0 && local == 3 && it < 16) kp.trace[272 + it] = global_ns();
+                    const uint32_t sa = base + stage * kp.stage_bytes;
+                    const uint32_t sb = kp.b_resident ? b_res + (uint32_t)it * kBBytes : sa + kABytes;
                     const uint64_t da = smem_desc<BK>(sa), db = smem_desc<BK>(sb);
 #pragma unroll
                     for (int k = 0; k < BK / 32; ++k) {
@@ -393,6 +461,12 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
                 if (ok) tc_commit(bar_tfull + 8 * acc);  // accumulator complete
+                if (ok && kp.b_resident) {
+                    int nm, nn = -1;
+                    if (local + 1 < my_tiles) decode(local + 1, nm, nn);
+                    if (nn != cur_n) tc_commit(bar_bfree);  // the resident weights may be replaced
+                }
+                TSB_TRACE(local, 4);
             }
         }
     } else {
@@ -405,11 +479,11 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         const int row = quarter * 32 + lane;     // row of the tile this thread owns
         constexpr int kChunks = BN / 32;
         constexpr int kChunksPerWarp = kChunks / 2;
-        int local = 0;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
+        for (int local = 0; local < my_tiles; ++local) {
             const int acc = local & 1;
             const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
-            const int n_tile = tile % kp.num_n_tiles, m_tile = tile / kp.num_n_tiles;
+            int m_tile, n_tile;
+            decode(local, m_tile, n_tile);
             const int n0 = n_tile * BN;
             float *t_dq = table + acc * 2 * BN, *t_bias = t_dq + BN;
             for (int j = et; j < BN; j += kEpiThreads) {
@@ -432,33 +506,38 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 break;
             }
             tc_fence_after();
+            if (et == 0) TSB_TRACE(local, 5);
             const int m = m_tile * kBM + row;
             const bool live = m < kp.M_total;
             const int img = live ? m / kp.P : 0;
             const int p = live ? m - img * kp.P : 0;
             const uint32_t taddr0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
-#pragma unroll 1
+            // two register buffers: the load of the next 32 columns is in flight while the current ones are processed
+            int v[2][32];
+            tmem_ld32(taddr0 + (uint32_t)(half * kChunksPerWarp * 32), v[0]);
+#pragma unroll
             for (int cc = 0; cc < kChunksPerWarp; ++cc) {
                 const int c = half * kChunksPerWarp + cc;
-                int v[32];
-                tmem_ld32(taddr0 + (uint32_t)(c * 32), v);
                 tmem_ld_wait();
+                if (cc + 1 < kChunksPerWarp) tmem_ld32(taddr0 + (uint32_t)((c + 1) * 32), v[(cc + 1) & 1]);
                 if (!live) continue;
+                const int (&vc)[32] = v[cc & 1];
                 const int col0 = c * 32;
                 const bool full = n0 + col0 + 32 <= epi.O;
                 if (kp.epi_mode == kEpiF32Nchw && full) {
                     float *dst = epi.out_f32 + ((size_t)(img * epi.O + n0 + col0) * (size_t)epi.P + (size_t)p);
-                    store_f32_nchw(v, t_dq + col0, t_bias + col0, epi.bias != nullptr, epi.activation, epi.leaky, dst, (size_t)epi.P);
+                    store_f32_nchw(vc, t_dq + col0, t_bias + col0, epi.bias != nullptr, epi.activation, epi.leaky, dst, (size_t)epi.P);
                 } else if (kp.epi_mode == kEpiI8Nhwc && full) {
                     const float rs = epi.nscales == 1 ? epi.rq_scales[0] : epi.rq_scales[img];
                     int8_t *dst = epi.out_i8 + (size_t)m * epi.out_cp + n0 + col0;
-                    store_i8_nhwc(v, t_dq + col0, t_bias + col0, epi.bias != nullptr, epi.activation, epi.leaky, rs, dst);
+                    store_i8_nhwc(vc, t_dq + col0, t_bias + col0, epi.bias != nullptr, epi.activation, epi.leaky, rs, dst);
                 } else {
-                    store_generic(v, t_dq + col0, t_bias + col0, epi, kp.per_sample_scale, img, p, m, n0 + col0);
+                    store_generic(vc, t_dq + col0, t_bias + col0, epi, kp.per_sample_scale, img, p, m, n0 + col0);
                 }
             }
             tc_fence_before();
             mbar_arrive(bar_tempty + 8 * acc);
+            if (et == 0) TSB_TRACE(local, 6);
         }
     }
 
@@ -481,6 +560,7 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 // ---------------------------------------------------------------------------------------------------------
 namespace {
 
+unsigned long long *g_trace = nullptr;  // set through set_trace_buffer(); null in normal operation
 PFN_cuTensorMapEncodeTiled_v12000 g_encode_tiled = nullptr;
 PFN_cuTensorMapEncodeIm2col_v12000 g_encode_im2col = nullptr;
 
@@ -504,19 +584,20 @@ CUtensorMapSwizzle swizzle_for(int bk) {
 template <int BN, int BK>
 int launch(const Config &cfg, const CUtensorMap &ma, const CUtensorMap &mb, const KernelParams &kp, const EpiParams &epi,
            cudaStream_t stream) {
-    using S = Smem<BN, BK>;
     static bool configured = false;
     auto kernel = conv_i8_tc_kernel<BN, BK>;
     if (!configured) {
-        TSB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::kDynamic));
+        TSB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynamicSmem));
         configured = true;
     }
-    kernel<<<cfg.grid, kThreads, S::kDynamic, stream>>>(ma, mb, kp, epi);
+    kernel<<<cfg.grid, kThreads, cfg.dyn_smem, stream>>>(ma, mb, kp, epi);
     TSB_LAUNCHED("conv_i8_tc_kernel");
     return TSB_OK;
 }
 
 }  // namespace
+
+void set_trace_buffer(unsigned long long *device_buffer) { g_trace = device_buffer; }
 
 bool make_view(const ConvGeom &g, View *view, const char **why) {
     *why = "";
@@ -526,7 +607,7 @@ bool make_view(const ConvGeom &g, View *view, const char **why) {
     if (g.pad_value != 0) { *why = "non-zero padding_value"; return false; }
     if (g.C <= 16) {
         // fold the filter row into the channel dimension
-        const int cpix = (g.C <= 8 && g.sw % 2 == 0) ? 8 : 16;
+        const int cpix = (g.C <= 8 && g.sw % 2 == 0 && !getenv("TSB_FOLD16")) ? 8 : 16;
         const int span = (g.KW - 1) * g.dw + 1;
         const int bkf = round_up(span * cpix, 64);
         if (bkf > 128) { *why = "filter row too wide to fold into one K block"; return false; }
@@ -547,6 +628,8 @@ bool make_view(const ConvGeom &g, View *view, const char **why) {
         v.stride_n = v.stride_h * g.H;
         v.stage_bytes = (size_t)v.stride_n * g.N;
     }
+    v.a_tiled = (!v.fold && g.KH == 1 && g.KW == 1 && g.sh == 1 && g.sw == 1 && g.pad_t == 0 && g.pad_l == 0 &&
+                 g.OH == g.H && g.OW == g.W && !getenv("TSB_NO_TILED_A")) ? 1 : 0;
     const ConvGeom &t = v.g;
     v.weight_bytes = (size_t)t.O * t.KH * t.KW * t.Cp;
     // im2col tensor maps take box corners in [-128,127], filter offsets in [0,255] and traversal strides up to 8
@@ -587,6 +670,27 @@ Config choose_config(const View &v, int sm_count) {
     c.num_n_tiles = ceil_div(g.O, c.bn);
     const int64_t tiles = (int64_t)c.num_m_tiles * c.num_n_tiles;
     c.grid = (int)(tiles < sm_count ? tiles : sm_count);
+    // shared-memory plan: keep the CTA's whole weight tile resident when it is small enough to leave room for
+    // at least four activation stages; otherwise stream activations and weights together
+    const uint32_t a_bytes = (uint32_t)kBM * c.bk, b_bytes = (uint32_t)c.bn * c.bk;
+    const uint32_t k_iters = (uint32_t)g.KH * g.KW * (g.Cp / c.bk);
+    const uint32_t b_total = k_iters * b_bytes;
+    const bool want_resident = !getenv("TSB_NO_RESIDENT_B") && tiles > c.grid;  // pays off only when a CTA runs several tiles
+    if (want_resident && b_total <= 128 * 1024 && (kSmemBudget - b_total) / a_bytes >= 4) {
+        c.b_resident = 1;
+        c.stage_bytes = a_bytes;
+        c.stages = std::min<int>(kMaxStages, (int)((kSmemBudget - b_total) / a_bytes));
+        c.b_off = (uint32_t)c.stages * c.stage_bytes;
+        c.bar_off = c.b_off + b_total;
+    } else {
+        c.b_resident = 0;
+        c.stage_bytes = a_bytes + b_bytes;
+        c.stages = std::min<int>(kMaxStages, (int)(kSmemBudget / c.stage_bytes));
+        c.b_off = 0;
+        c.bar_off = (uint32_t)c.stages * c.stage_bytes;
+    }
+    const uint32_t tables = ((c.bar_off + 8 * num_barriers(c.stages) + 8 + 15) & ~15u) + 2 * 2 * (uint32_t)c.bn * 4;
+    c.dyn_smem = tables + 1024;  // slack to align the tiles to 1024 bytes
     return c;
 }
 
@@ -611,6 +715,17 @@ int encode_activation_map(const View &v, const Config &cfg, const int8_t *x, CUt
     if (st != TSB_OK) return st;
     if (reinterpret_cast<uintptr_t>(x) % 16) return fail(TSB_ERR_INVALID_ARGUMENT, "staged activations must be 16-byte aligned");
     const ConvGeom &g = v.g;
+    if (v.a_tiled) {
+        cuuint64_t dims2[2] = {(cuuint64_t)g.Cp, (cuuint64_t)g.N * g.H * g.W};
+        cuuint64_t strides2[1] = {(cuuint64_t)g.Cp};
+        cuuint32_t box2[2] = {(cuuint32_t)cfg.bk, (cuuint32_t)kBM};
+        cuuint32_t estr2[2] = {1, 1};
+        CUresult r2 = g_encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t *>(x), dims2, strides2, box2,
+                                     estr2, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(cfg.bk),
+                                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r2 != CUDA_SUCCESS) return fail(TSB_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled(activations) failed with %d", (int)r2);
+        return TSB_OK;
+    }
     cuuint64_t dims[4] = {(cuuint64_t)g.Cp, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.N};
     cuuint64_t strides[3] = {v.stride_w, v.stride_h, v.stride_n};
     // The box of base pixels: from -pad to the last position a filter can start at.  The far corner is chosen so
@@ -723,6 +838,11 @@ int launch_conv_tc(const View &v, const Config &cfg, const CUtensorMap &map_a, c
     kp.num_n_tiles = cfg.num_n_tiles;
     kp.per_sample_scale = (epi.nscales > 1 && epi.nscales == g.N && epi.group_len == (uint32_t)(g.O * g.OH * g.OW)) ? 1 : 0;
     kp.status = status_word;
+    kp.trace = g_trace;
+    kp.a_tiled = v.a_tiled;
+    kp.stages = cfg.stages; kp.stage_bytes = cfg.stage_bytes; kp.b_resident = cfg.b_resident;
+    kp.b_off = cfg.b_off; kp.bar_off = cfg.bar_off;
+    if (cfg.dyn_smem > kMaxDynamicSmem) return fail(TSB_ERR_UNSUPPORTED, "shared-memory plan of %u bytes does not fit", cfg.dyn_smem);
     const bool plain = !epi.out_acc && !epi.residual;
     kp.epi_mode = kEpiGeneric;
     if (plain && epi.out_f32 && !epi.f32_nhwc && !epi.out_i8) kp.epi_mode = kEpiF32Nchw;

@@ -18,6 +18,7 @@ struct View {
     ConvGeom g;          // geometry handed to the kernel and the tensor maps
     ConvGeom real;       // geometry of the operator
     int fold = 0;
+    int a_tiled = 0;     // 1x1 / stride 1 / no padding: the activations are the [M][Cp] matrix itself, loaded as 2-D tiles
     int cpix = 0;        // bytes per pixel of the folded staging
     int Wp = 0;          // pixels per row of the folded staging
     uint64_t stride_w = 0, stride_h = 0, stride_n = 0;  // bytes between neighbours along W, H, N as the tensor map sees them
@@ -29,6 +30,9 @@ struct Config {
     int bn = 0, bk = 0;               // tile width in output channels, K block in bytes (= swizzle span)
     int num_m_tiles = 0, num_n_tiles = 0;
     int grid = 0;                     // persistent CTAs
+    // shared-memory plan of the kernel
+    int stages = 0, b_resident = 0;
+    uint32_t stage_bytes = 0, b_off = 0, bar_off = 0, dyn_smem = 0;
 };
 
 // Whether the tensor-core kernel covers this geometry; *why names the reason when it does not.
@@ -42,6 +46,9 @@ int encode_activation_map(const View &v, const Config &cfg, const int8_t *x, CUt
 int pack_weights(const View &v, const int8_t *w_oihw, int8_t *w_packed, cudaStream_t stream);
 // int8 input (NCHW, or NHWC_PAD when x_nhwc) -> folded staging (fold views only)
 int stage_folded(const View &v, const int8_t *x, int x_nhwc, int8_t *staged, cudaStream_t stream);
+// Debugging aid: CTA 0 of later launches writes 8 time stamps (ns) per tile for its first 32 tiles into this device
+// buffer of 256 x 8 bytes; null switches it off.
+void set_trace_buffer(unsigned long long *device_buffer);
 int launch_conv_tc(const View &v, const Config &cfg, const CUtensorMap &map_a, const CUtensorMap &map_b,
                    const EpiParams &epi, int *status_word, cudaStream_t stream);
 
