@@ -80,9 +80,11 @@ __device__ __forceinline__ int q8_half_even(float v) {
 }
 __device__ __forceinline__ int q8_half_away(float v) {
     if (!(fabsf(v) < 2147483648.0f)) return -128;
-    float r = roundf(v);  // half away from zero
-    r = fminf(fmaxf(r, -128.0f), 127.0f);
-    return __float2int_rz(r);
+    // floor(|v| + 0.5) computed exactly: the sum is rounded toward zero, so it can never reach the next integer early
+    // (a round-to-nearest sum would for |v| just below 0.5); then the sign is put back
+    const float mag = __fadd_rz(fabsf(v), 0.5f);
+    const int r = __float2int_rz(copysignf(mag, v));
+    return max(-128, min(127, r));
 }
 __device__ __forceinline__ int q8(float x, float scale, bool half_even) {
     const float v = __fmul_rn(x, scale);  // one rounding, never contracted

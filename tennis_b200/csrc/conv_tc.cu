@@ -149,52 +149,72 @@ template <int ACT, bool HAS_BIAS>
 __device__ __forceinline__ float epi_value(int acc, float dq, float bias, float leaky) {
     float f = __fmul_rn(__int2float_rn(acc), dq);
     if (HAS_BIAS) f = __fadd_rn(f, bias);
-    if (ACT == TSB_ACT_RELU) f = f > 0.0f ? f : 0.0f;
+    if (ACT == TSB_ACT_RELU) f = fmaxf(f, 0.0f);   // finite values only: same result as x > 0 ? x : 0
     if (ACT == TSB_ACT_LEAKY_RELU) f = f > 0.0f ? f : __fmul_rn(f, leaky);
     return f;
 }
 
-// round-half-away quantization of an already scaled value with the reference's clamp and its -128 for NaN and
-// for products beyond the int32 range.  trunc(v + copysign(0.5, v)) is exact except for |v| just below 0.5,
-// where the sum rounds up to 1.0; that case is answered directly.
-__device__ __forceinline__ int q8_half_away_fast(float v) {
-    const float t = __fadd_rn(v, copysignf(0.5f, v));
-    int r;
-    asm("cvt.rzi.s8.f32 %0, %1;" : "=r"(r) : "f"(t));  // saturates to [-128,127]
-    r = fabsf(v) < 0.5f ? 0 : r;
-    return fabsf(v) < 2147483648.0f ? r : -128;
+// Round-half-away of an already scaled value t, as a signed 32-bit integer (three instructions per value):
+// floor(|t| + 0.5) is obtained exactly as trunc(round_toward_zero(|t| + 0.5)) -- a round-to-nearest sum would be wrong
+// for |t| just below 0.5 -- and the sign is put back before the (saturating) conversion.
+__device__ __forceinline__ int half_away_s32(float t) {
+    const float mag = __fadd_rz(fabsf(t), 0.5f);
+    const float signed_mag = __int_as_float((__float_as_int(mag) & 0x7fffffff) | (__float_as_int(t) & 0x80000000));
+    return __float2int_rz(signed_mag);
+}
+
+// four signed integers -> four int8 with saturation to [-128,127], v0 in the lowest byte
+__device__ __forceinline__ uint32_t pack_sat_s8(int v0, int v1, int v2, int v3) {
+    uint32_t hi, out;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(v3), "r"(v2), "r"(0));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(v1), "r"(v0), "r"(hi));
+    return out;
+}
+
+// max that keeps a NaN once it has seen one
+__device__ __forceinline__ float max_nan(float a, float b) {
+    float r;
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    return r;
 }
 
 template <int ACT, bool HAS_BIAS>
 __device__ __forceinline__ void store_f32_nchw_t(const int (&v)[32], const float *dq, const float *bias, float leaky,
-                                                 float *dst, size_t stride) {
+                                                 float *dst, uint32_t stride) {
 #pragma unroll
     for (int j4 = 0; j4 < 8; ++j4) {
         const float4 d4 = *reinterpret_cast<const float4 *>(dq + 4 * j4);
         const float4 b4 = *reinterpret_cast<const float4 *>(bias + 4 * j4);
-        dst[(size_t)(4 * j4 + 0) * stride] = epi_value<ACT, HAS_BIAS>(v[4 * j4 + 0], d4.x, b4.x, leaky);
-        dst[(size_t)(4 * j4 + 1) * stride] = epi_value<ACT, HAS_BIAS>(v[4 * j4 + 1], d4.y, b4.y, leaky);
-        dst[(size_t)(4 * j4 + 2) * stride] = epi_value<ACT, HAS_BIAS>(v[4 * j4 + 2], d4.z, b4.z, leaky);
-        dst[(size_t)(4 * j4 + 3) * stride] = epi_value<ACT, HAS_BIAS>(v[4 * j4 + 3], d4.w, b4.w, leaky);
+        dst[(uint32_t)(4 * j4 + 0) * stride] = epi_value<ACT, HAS_BIAS>(v[4 * j4 + 0], d4.x, b4.x, leaky);
+        dst[(uint32_t)(4 * j4 + 1) * stride] = epi_value<ACT, HAS_BIAS>(v[4 * j4 + 1], d4.y, b4.y, leaky);
+        dst[(uint32_t)(4 * j4 + 2) * stride] = epi_value<ACT, HAS_BIAS>(v[4 * j4 + 2], d4.z, b4.z, leaky);
+        dst[(uint32_t)(4 * j4 + 3) * stride] = epi_value<ACT, HAS_BIAS>(v[4 * j4 + 3], d4.w, b4.w, leaky);
     }
 }
 
+// Requantized int8 output.  Returns false when a scaled value was NaN or beyond the int32 range -- those quantize to
+// -128 in the reference (x86 integer-indefinite), which the saturating fast path does not reproduce; the caller
+// then redoes the chunk element by element.
 template <int ACT, bool HAS_BIAS>
-__device__ __forceinline__ void store_i8_nhwc_t(const int (&v)[32], const float *dq, const float *bias, float leaky,
+__device__ __forceinline__ bool store_i8_nhwc_t(const int (&v)[32], const float *dq, const float *bias, float leaky,
                                                 float rs, int8_t *dst) {
     uint32_t q[8];
+    float worst = 0.0f;
 #pragma unroll
     for (int j4 = 0; j4 < 8; ++j4) {
         const float4 d4 = *reinterpret_cast<const float4 *>(dq + 4 * j4);
         const float4 b4 = *reinterpret_cast<const float4 *>(bias + 4 * j4);
-        const int a = q8_half_away_fast(__fmul_rn(epi_value<ACT, HAS_BIAS>(v[4 * j4 + 0], d4.x, b4.x, leaky), rs));
-        const int b = q8_half_away_fast(__fmul_rn(epi_value<ACT, HAS_BIAS>(v[4 * j4 + 1], d4.y, b4.y, leaky), rs));
-        const int c = q8_half_away_fast(__fmul_rn(epi_value<ACT, HAS_BIAS>(v[4 * j4 + 2], d4.z, b4.z, leaky), rs));
-        const int d = q8_half_away_fast(__fmul_rn(epi_value<ACT, HAS_BIAS>(v[4 * j4 + 3], d4.w, b4.w, leaky), rs));
-        q[j4] = (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) | ((uint32_t)(d & 0xff) << 24);
+        const float t0 = __fmul_rn(epi_value<ACT, HAS_BIAS>(v[4 * j4 + 0], d4.x, b4.x, leaky), rs);
+        const float t1 = __fmul_rn(epi_value<ACT, HAS_BIAS>(v[4 * j4 + 1], d4.y, b4.y, leaky), rs);
+        const float t2 = __fmul_rn(epi_value<ACT, HAS_BIAS>(v[4 * j4 + 2], d4.z, b4.z, leaky), rs);
+        const float t3 = __fmul_rn(epi_value<ACT, HAS_BIAS>(v[4 * j4 + 3], d4.w, b4.w, leaky), rs);
+        worst = max_nan(max_nan(worst, fabsf(t0)), max_nan(fabsf(t1), max_nan(fabsf(t2), fabsf(t3))));
+        q[j4] = pack_sat_s8(half_away_s32(t0), half_away_s32(t1), half_away_s32(t2), half_away_s32(t3));
     }
+    if (!(worst < 2147483648.0f)) return false;
     *reinterpret_cast<int4 *>(dst) = make_int4(q[0], q[1], q[2], q[3]);
     *reinterpret_cast<int4 *>(dst + 16) = make_int4(q[4], q[5], q[6], q[7]);
+    return true;
 }
 
 #define TSB_EPI_DISPATCH(FN, ...)                                                                \
@@ -211,12 +231,24 @@ __device__ __forceinline__ void store_i8_nhwc_t(const int (&v)[32], const float 
     } while (0)
 
 __device__ __forceinline__ void store_f32_nchw(const int (&v)[32], const float *dq, const float *bias, bool has_bias,
-                                               int act, float leaky, float *dst, size_t stride) {
+                                               int act, float leaky, float *dst, uint32_t stride) {
     TSB_EPI_DISPATCH(store_f32_nchw_t, v, dq, bias, leaky, dst, stride);
 }
-__device__ __forceinline__ void store_i8_nhwc(const int (&v)[32], const float *dq, const float *bias, bool has_bias,
+__device__ __forceinline__ bool store_i8_nhwc(const int (&v)[32], const float *dq, const float *bias, bool has_bias,
                                               int act, float leaky, float rs, int8_t *dst) {
-    TSB_EPI_DISPATCH(store_i8_nhwc_t, v, dq, bias, leaky, rs, dst);
+    bool ok = true;
+#define TSB_I8(A_, B_) ok = store_i8_nhwc_t<A_, B_>(v, dq, bias, leaky, rs, dst)
+    if (has_bias) {
+        if (act == TSB_ACT_RELU) TSB_I8(TSB_ACT_RELU, true);
+        else if (act == TSB_ACT_LEAKY_RELU) TSB_I8(TSB_ACT_LEAKY_RELU, true);
+        else TSB_I8(TSB_ACT_NONE, true);
+    } else {
+        if (act == TSB_ACT_RELU) TSB_I8(TSB_ACT_RELU, false);
+        else if (act == TSB_ACT_LEAKY_RELU) TSB_I8(TSB_ACT_LEAKY_RELU, false);
+        else TSB_I8(TSB_ACT_NONE, false);
+    }
+#undef TSB_I8
+    return ok;
 }
 
 // Everything else: several outputs at once, residual, NCHW int8, partial tiles.  o0 = first output channel.
@@ -281,6 +313,7 @@ struct KernelParams {
     uint32_t b_off;        // offset of the resident weights
     uint32_t bar_off;      // offset of the mbarriers; tensor-memory slot, abort flag and epilogue tables follow
     int *status;     // device word: 0 ok, else the code of the wait that ran out
+    int dbg;         // experiments only (0 in normal operation)
     unsigned long long *trace;  // optional timeline of CTA 0 (debugging aid): 8 stamps per tile, 32 tiles
 };
 
@@ -294,7 +327,7 @@ __device__ __forceinline__ unsigned long long global_ns() {
         if (kp.trace && blockIdx.x == 0 && (tile_index) < 32) kp.trace[(tile_index) * 8 + (slot)] = global_ns(); \
     } while (0)
 
-constexpr int kMaxStages = 8;
+constexpr int kMaxStages = 24;
 constexpr uint32_t kMaxDynamicSmem = 227 * 1024;
 
 // barriers: full[stages], empty[stages], tmem_full[2], tmem_empty[2], b_full, b_free
@@ -441,11 +474,14 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 TSB_TRACE(local, 2);
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
                 for (int it = 0; it < k_iters; ++it) {
+                    const bool tr = kp.trace && blockIdx.x == 0 && local == 3 && it < 8;
+                    if (tr) kp.trace[320 + it * 4] = global_ns();
                     if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
                         if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 3); }
                         ok = false;
                         break;
                     }
+                    if (tr) kp.trace[320 + it * 4 + 1] = global_ns();
                     tc_fence_after();
                     if (it == 0) TSB_TRACE(local, 3);
                     if (kp.trace && blockIdx.x == 0 && local == 3 && it < 16) kp.trace[272 + it] = global_ns();
@@ -457,7 +493,9 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                         // +32 bytes along K inside the swizzle span = +2 in the descriptor's 16-byte address units
                         mma_i8(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (it | k) != 0 ? 1u : 0u);
                     }
+                    if (tr) kp.trace[320 + it * 4 + 2] = global_ns();
                     tc_commit(bar_empty + 8 * stage);  // frees the stage once these MMAs have read it
+                    if (tr) kp.trace[320 + it * 4 + 3] = global_ns();
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
                 if (ok) tc_commit(bar_tfull + 8 * acc);  // accumulator complete
@@ -518,22 +556,41 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 #pragma unroll
             for (int cc = 0; cc < kChunksPerWarp; ++cc) {
                 const int c = half * kChunksPerWarp + cc;
+                if (kp.trace && blockIdx.x == 0 && local == 3 && et == 0) kp.trace[288 + cc * 3] = global_ns();
                 tmem_ld_wait();
+                if (kp.trace && blockIdx.x == 0 && local == 3 && et == 0) kp.trace[288 + cc * 3 + 1] = global_ns();
                 if (cc + 1 < kChunksPerWarp) tmem_ld32(taddr0 + (uint32_t)((c + 1) * 32), v[(cc + 1) & 1]);
                 if (!live) continue;
                 const int (&vc)[32] = v[cc & 1];
                 const int col0 = c * 32;
+                if (kp.dbg == 1) continue;
+                if (kp.dbg == 2) {  // arithmetic only, one store
+                    float sacc = 0.f;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) sacc += fmaxf(__fadd_rn(__fmul_rn(__int2float_rn(vc[j]), t_dq[col0 + j]), t_bias[col0 + j]), 0.0f);
+                    if (sacc == 12345.678f) epi.out_f32[0] = sacc;
+                    continue;
+                }
+                if (kp.dbg == 3) {  // no conversions, no table
+                    float sacc = 0.f;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) sacc += __int_as_float(vc[j]);
+                    if (sacc == 12345.678f) epi.out_f32[0] = sacc;
+                    continue;
+                }
                 const bool full = n0 + col0 + 32 <= epi.O;
                 if (kp.epi_mode == kEpiF32Nchw && full) {
                     float *dst = epi.out_f32 + ((size_t)(img * epi.O + n0 + col0) * (size_t)epi.P + (size_t)p);
-                    store_f32_nchw(vc, t_dq + col0, t_bias + col0, epi.bias != nullptr, epi.activation, epi.leaky, dst, (size_t)epi.P);
+                    store_f32_nchw(vc, t_dq + col0, t_bias + col0, epi.bias != nullptr, epi.activation, epi.leaky, dst, (uint32_t)epi.P);
                 } else if (kp.epi_mode == kEpiI8Nhwc && full) {
                     const float rs = epi.nscales == 1 ? epi.rq_scales[0] : epi.rq_scales[img];
                     int8_t *dst = epi.out_i8 + (size_t)m * epi.out_cp + n0 + col0;
-                    store_i8_nhwc(vc, t_dq + col0, t_bias + col0, epi.bias != nullptr, epi.activation, epi.leaky, rs, dst);
+                    if (!store_i8_nhwc(vc, t_dq + col0, t_bias + col0, epi.bias != nullptr, epi.activation, epi.leaky, rs, dst))
+                        store_generic(vc, t_dq + col0, t_bias + col0, epi, kp.per_sample_scale, img, p, m, n0 + col0);
                 } else {
                     store_generic(vc, t_dq + col0, t_bias + col0, epi, kp.per_sample_scale, img, p, m, n0 + col0);
                 }
+                if (kp.trace && blockIdx.x == 0 && local == 3 && et == 0) kp.trace[288 + cc * 3 + 2] = global_ns();
             }
             tc_fence_before();
             mbar_arrive(bar_tempty + 8 * acc);
@@ -839,6 +896,7 @@ int launch_conv_tc(const View &v, const Config &cfg, const CUtensorMap &map_a, c
     kp.per_sample_scale = (epi.nscales > 1 && epi.nscales == g.N && epi.group_len == (uint32_t)(g.O * g.OH * g.OW)) ? 1 : 0;
     kp.status = status_word;
     kp.trace = g_trace;
+    kp.dbg = getenv("TSB_DBG") ? atoi(getenv("TSB_DBG")) : 0;
     kp.a_tiled = v.a_tiled;
     kp.stages = cfg.stages; kp.stage_bytes = cfg.stage_bytes; kp.b_resident = cfg.b_resident;
     kp.b_off = cfg.b_off; kp.bar_off = cfg.bar_off;

@@ -180,47 +180,73 @@ struct StageDesc {
 };
 
 __global__ void __launch_bounds__(kThreads)
-quantize_stage_kernel(const float *__restrict__ x, int8_t *__restrict__ y, StageDesc d, int64_t units, QuantRule rule,
+quantize_stage_kernel(const float *__restrict__ x, int8_t *__restrict__ y, StageDesc d, uint32_t units, QuantRule rule,
                       ScaleArg scales) {
     const uint32_t rne_limit = (uint32_t)rule.rne_limit;
     const uint32_t group_len = (uint32_t)rule.group_len;
-    const int HW = d.H * d.W;
-    const int units_per_pixel = d.Cp / 16;                 // NHWC_PAD
-    const int units_per_row = d.folded ? d.Wp * d.cpix / 16 : 0;
-    for (int64_t u = (int64_t)blockIdx.x * kThreads + threadIdx.x; u < units; u += (int64_t)gridDim.x * kThreads) {
-        int n, h, w0, c0, npix, nch;
+    const uint32_t HW = (uint32_t)(d.H * d.W);
+    const uint32_t CHW = (uint32_t)d.C * HW;
+    const bool per_sample = rule.nscales > 1 && group_len == CHW;   // the usual case: one scale per image
+    const uint32_t upp = (uint32_t)d.Cp / 16u;                       // NHWC_PAD: 16-byte units per pixel
+    const uint32_t upr = d.folded ? (uint32_t)(d.Wp * d.cpix) / 16u : 1u;  // folded: units per staged row
+    for (uint32_t t = blockIdx.x * kThreads + threadIdx.x; t < units; t += gridDim.x * kThreads) {
+        // Thread -> output unit.  NHWC_PAD: the 32 lanes of a warp take 32 consecutive pixels of one 16-channel group,
+        // so every load instruction reads 128 contiguous bytes of one channel plane.
+        uint32_t u, n, h, c0;
+        int w0;
         if (!d.folded) {
-            const int64_t pix = u / units_per_pixel;
-            c0 = (int)(u - pix * units_per_pixel) * 16;
-            n = (int)(pix / HW);
-            const int p = (int)(pix - (int64_t)n * HW);
-            h = p / d.W;
-            w0 = p - h * d.W;
-            npix = 1; nch = 16;
+            const uint32_t lane = t & 31u, grp = t >> 5;
+            const uint32_t cg = grp % upp, pblock = grp / upp;
+            const uint32_t pix = pblock * 32u + lane;
+            const uint32_t npix_total = (uint32_t)d.N * HW;
+            if (pix >= npix_total) continue;
+            u = pix * upp + cg;
+            n = pix / HW;
+            const uint32_t p = pix - n * HW;
+            h = p / (uint32_t)d.W;
+            w0 = (int)(p - h * (uint32_t)d.W);
+            c0 = cg * 16u;
         } else {
-            const int ur = (int)(u % units_per_row);
-            const int64_t row = u / units_per_row;
-            h = (int)(row % d.H);
-            n = (int)(row / d.H);
-            npix = 16 / d.cpix; nch = d.cpix;
-            w0 = ur * npix - d.pad_l;
+            u = t;
+            const uint32_t ur = t % upr, row = t / upr;
+            h = row % (uint32_t)d.H;
+            n = row / (uint32_t)d.H;
+            w0 = (int)(ur * (16u / (uint32_t)d.cpix)) - d.pad_l;
             c0 = 0;
         }
+        const bool two_pixels = d.folded && d.cpix == 8;
+        const uint32_t base = (n * (uint32_t)d.C * (uint32_t)d.H + h) * (uint32_t)d.W;   // + c*H*W + w
+        // all sixteen loads first (indices clamped so they can be issued unconditionally), arithmetic afterwards
+        float val[16];
+        uint32_t idx[16];
+        bool ok[16];
+#pragma unroll
+        for (int b = 0; b < 16; ++b) {
+            const int pi = two_pixels ? (b >> 3) : 0;
+            const uint32_t c = c0 + (uint32_t)(two_pixels ? (b & 7) : b);
+            const int w = w0 + pi;
+            ok[b] = c < (uint32_t)d.C && (unsigned)w < (unsigned)d.W && (!d.folded || (two_pixels ? (b & 7) : b) < d.cpix);
+            idx[b] = ok[b] ? base + c * HW + (uint32_t)w : 0u;
+            val[b] = __ldg(x + idx[b]);
+        }
+        const float sample_scale = scales.get(per_sample ? (int)n : 0);
         uint32_t word[4] = {0, 0, 0, 0};
 #pragma unroll
         for (int b = 0; b < 16; ++b) {
-            const int pi = npix == 1 ? 0 : (b >> 3);       // two pixels of 8 channels, or one pixel of 16
-            const int c = c0 + (npix == 1 ? b : (b & 7));
-            const int w = w0 + pi;
             int q = 0;
-            if (c < d.C && (unsigned)w < (unsigned)d.W && (npix == 1 ? b : (b & 7)) < nch) {
-                const uint32_t idx = (uint32_t)((n * d.C + c) * d.H + h) * (uint32_t)d.W + (uint32_t)w;
-                const uint32_t g = rule.nscales == 1 ? 0u : idx / group_len;
-                if (g < (uint32_t)rule.nscales) q = q8(x[idx], scales.get(g), idx < rne_limit);
+            if (ok[b]) {
+                float s = sample_scale;
+                bool in_range = true;
+                if (rule.nscales != 1 && !per_sample) {
+                    const uint32_t g = idx[b] / group_len;
+                    in_range = g < (uint32_t)rule.nscales;
+                    s = in_range ? scales.get((int)g) : 0.0f;
+                }
+                if (in_range) q = q8(val[b], s, idx[b] < rne_limit);
             }
             word[b >> 2] |= (uint32_t)(q & 0xff) << (8 * (b & 3));
         }
-        *reinterpret_cast<int4 *>(y + u * 16) = make_int4(word[0], word[1], word[2], word[3]);
+        *reinterpret_cast<int4 *>(y + (size_t)u * 16) = make_int4(word[0], word[1], word[2], word[3]);
     }
 }
 
@@ -332,8 +358,11 @@ int quantize_stage(const float *x, int8_t *y, int n, int c, int h, int w, int fo
     d.folded = folded;
     d.Cp = tsb_padded_channels(c);
     d.Wp = wp; d.cpix = cpix; d.pad_l = pad_l;
-    const int64_t units = folded ? (int64_t)n * h * (wp * cpix / 16) : (int64_t)n * h * w * (d.Cp / 16);
-    quantize_stage_kernel<<<grid_for(units), kThreads, 0, stream>>>(x, y, d, units, rule, arg);
+    // NHWC_PAD: threads are laid out in groups of 32 pixels x (Cp/16) channel groups (the last group may be partial)
+    const int64_t units = folded ? (int64_t)n * h * (wp * cpix / 16)
+                                 : ceil_div64((int64_t)n * h * w, 32) * 32 * (d.Cp / 16);
+    if (units > (int64_t)UINT32_MAX) return fail(TSB_ERR_UNSUPPORTED, "quantize_stage: tensor too large");
+    quantize_stage_kernel<<<grid_for(units), kThreads, 0, stream>>>(x, y, d, (uint32_t)units, rule, arg);
     TSB_LAUNCHED("quantize_stage_kernel");
     if (tmp) TSB_CUDA(cudaFreeAsync(tmp, stream));
     return TSB_OK;
