@@ -313,7 +313,6 @@ struct KernelParams {
     uint32_t b_off;        // offset of the resident weights
     uint32_t bar_off;      // offset of the mbarriers; tensor-memory slot, abort flag and epilogue tables follow
     int *status;     // device word: 0 ok, else the code of the wait that ran out
-    int dbg;         // experiments only (0 in normal operation)
     unsigned long long *trace;  // optional timeline of CTA 0 (debugging aid): 8 stamps per tile, 32 tiles
 };
 
@@ -333,11 +332,63 @@ constexpr uint32_t kMaxDynamicSmem = 227 * 1024;
 // barriers: full[stages], empty[stages], tmem_full[2], tmem_empty[2], b_full, b_free
 __host__ __device__ constexpr uint32_t num_barriers(int stages) { return 2u * (uint32_t)stages + 6u; }
 
-template <int BN, int BK>
+// Swapped-orientation epilogue helpers: a thread owns one output CHANNEL (its tensor-memory lane) and 32 consecutive
+// output PIXELS (columns).  dq / bias are per-thread scalars.
+template <int ACT, bool HAS_BIAS>
+__device__ __forceinline__ void swap_f32_run(const int (&v)[32], float dq, float bias, float leaky, float *dst) {
+    // 32 consecutive pixels of one channel plane: 128 contiguous bytes
+    if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+        for (int j4 = 0; j4 < 8; ++j4) {
+            float4 o;
+            o.x = epi_value<ACT, HAS_BIAS>(v[4 * j4 + 0], dq, bias, leaky);
+            o.y = epi_value<ACT, HAS_BIAS>(v[4 * j4 + 1], dq, bias, leaky);
+            o.z = epi_value<ACT, HAS_BIAS>(v[4 * j4 + 2], dq, bias, leaky);
+            o.w = epi_value<ACT, HAS_BIAS>(v[4 * j4 + 3], dq, bias, leaky);
+            reinterpret_cast<float4 *>(dst)[j4] = o;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) dst[j] = epi_value<ACT, HAS_BIAS>(v[j], dq, bias, leaky);
+    }
+}
+
+// int8 NHWC_PAD output: for one pixel the 32 lanes of the warp hold 32 consecutive channels, so each byte store
+// instruction of the warp writes one full 32-byte sector.  rs0 applies to the first `split` pixels, rs1 to the rest
+// (a chunk crosses at most one image boundary).  Returns false if a value needs the slow path (NaN / beyond int32).
+template <int ACT, bool HAS_BIAS>
+__device__ __forceinline__ bool swap_i8_run(const int (&v)[32], float dq, float bias, float leaky, float rs0, float rs1,
+                                            int split, bool write, int8_t *dst, uint32_t pixel_stride, int npix) {
+    float worst = 0.0f;
+    int q[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        const float t = __fmul_rn(epi_value<ACT, HAS_BIAS>(v[j], dq, bias, leaky), j < split ? rs0 : rs1);
+        worst = max_nan(worst, fabsf(t));
+        q[j] = max(-128, min(127, half_away_s32(t)));
+    }
+    // the decision must be the same for the whole warp (the slow path stores the entire chunk)
+    if (__any_sync(0xffffffffu, !(worst < 2147483648.0f))) return false;
+    if (write) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (j < npix) dst[(uint32_t)j * pixel_stride] = (int8_t)q[j];
+    }
+    return true;
+}
+
+// PIX pixels x CH channels per tile.  Normal orientation: the pixel tile is the MMA's A operand (M = 128 pixels), the
+// weight tile its B operand (N = BN channels).  Swapped orientation: the weight tile is A (M = 128 channels, rows
+// beyond O zero-filled by the tensor map) and the pixel tile is B (N = BN pixels).  An MMA instruction takes the same
+// 128 cycles whatever its N, so layers with at most 128 output channels run swapped: N = 256 pixels fills the
+// instruction where N = O would leave it half or three-quarters empty.
+template <int BN, int BK, bool SWAP>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ KernelParams kp, const __grid_constant__ EpiParams epi) {
-    constexpr uint32_t kABytes = kBM * BK, kBBytes = BN * BK;
+    constexpr int PIX = SWAP ? BN : kBM;      // pixels per tile
+    constexpr int CH = SWAP ? kBM : BN;       // output channels per tile
+    constexpr uint32_t kPixBytes = PIX * BK, kWgtBytes = CH * BK;
     constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // power of two for BN in {32,64,128,256}
     const int kStages = kp.stages;
 
@@ -355,17 +406,18 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + slot_off);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(base_ptr + slot_off + 4);
     float *table = reinterpret_cast<float *>(base_ptr + ((slot_off + 8 + 15) & ~15u));
-    const uint32_t b_res = base + kp.b_off;
+    const uint32_t w_res = base + kp.b_off;   // resident weights
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_tiles = kp.num_m_tiles * kp.num_n_tiles;
     const int k_iters = kp.KH * kp.KW * (kp.Cp / BK);
-    // This CTA's tiles.  Streaming weights: tiles blockIdx.x, +gridDim.x, ... with the N tile running fastest.
-    // Resident weights: one contiguous range of the N-major tile order, so the weight tile changes at most a few times.
+    // This CTA's tiles.  Streaming weights: tiles blockIdx.x, +gridDim.x, ... with the channel tile running fastest.
+    // Resident weights: one contiguous range of the channel-major tile order, so the weight tile changes at most a
+    // few times.
     const int tile_lo = kp.b_resident ? (int)((long long)blockIdx.x * total_tiles / gridDim.x) : 0;
     const int tile_hi = kp.b_resident ? (int)((long long)(blockIdx.x + 1) * total_tiles / gridDim.x) : 0;
     const int my_tiles = kp.b_resident ? tile_hi - tile_lo : (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-    auto decode = [&](int i, int &m_tile, int &n_tile) {
+    auto decode = [&](int i, int &m_tile, int &n_tile) {   // m_tile: pixel tile, n_tile: channel tile
         if (kp.b_resident) {
             const int t = tile_lo + i;
             n_tile = t / kp.num_m_tiles; m_tile = t - n_tile * kp.num_m_tiles;
@@ -399,26 +451,26 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         if (lane == 0) {
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
-            int cur_n = -1, b_loads = 0;
+            int cur_n = -1, w_loads = 0;
             for (int i = 0; i < my_tiles && ok; ++i) {
                 TSB_TRACE(i, 0);
                 int m_tile, n_tile;
                 decode(i, m_tile, n_tile);
-                const int m0 = m_tile * kBM;
+                const int m0 = m_tile * PIX;
                 const int img = m0 / kp.P, rem = m0 - img * kp.P;
                 const int oh = rem / kp.OW, ow = rem - oh * kp.OW;
                 const int wc = ow * kp.sw - kp.pad_l, hc = oh * kp.sh - kp.pad_t;
                 if (kp.b_resident && n_tile != cur_n) {
                     // (re)load the whole weight tile; wait until the MMAs that read the previous one are done
-                    if (b_loads > 0 && !mbar_wait(bar_bfree, (uint32_t)(b_loads - 1) & 1u, abort_flag)) {
+                    if (w_loads > 0 && !mbar_wait(bar_bfree, (uint32_t)(w_loads - 1) & 1u, abort_flag)) {
                         if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 5); }
                         break;
                     }
-                    mbar_arrive_expect_tx(bar_bfull, (uint32_t)k_iters * kBBytes);
+                    mbar_arrive_expect_tx(bar_bfull, (uint32_t)k_iters * kWgtBytes);
                     for (int it = 0; it < k_iters; ++it)
-                        tma_load_2d(b_res + (uint32_t)it * kBBytes, &map_b, bar_bfull, it * BK, n_tile * BN);
+                        tma_load_2d(w_res + (uint32_t)it * kWgtBytes, &map_b, bar_bfull, it * BK, n_tile * CH);
                     cur_n = n_tile;
-                    ++b_loads;
+                    ++w_loads;
                 }
                 for (int kh = 0; kh < kp.KH && ok; ++kh)
                     for (int kw = 0; kw < kp.KW && ok; ++kw)
@@ -428,19 +480,15 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                                 ok = false;
                                 break;
                             }
-                            const uint32_t sa = base + stage * kp.stage_bytes, sb = sa + kABytes;
-                            if (kp.trace && blockIdx.x == 0 && i == 3) {
-                                const int itx = (kh * kp.KW + kw) * (kp.Cp / BK) + cb / BK;
-                                if (itx < 16) kp.trace[256 + itx] = global_ns();
-                            }
-                            mbar_arrive_expect_tx(bar_full + 8 * stage, kp.b_resident ? kABytes : kABytes + kBBytes);
+                            const uint32_t sp = base + stage * kp.stage_bytes, sw = sp + kPixBytes;
+                            mbar_arrive_expect_tx(bar_full + 8 * stage, kp.b_resident ? kPixBytes : kPixBytes + kWgtBytes);
                             if (kp.a_tiled)
-                                tma_load_2d(sa, &map_a, bar_full + 8 * stage, cb, m0);
+                                tma_load_2d(sp, &map_a, bar_full + 8 * stage, cb, m0);
                             else
-                                tma_load_im2col_4d(sa, &map_a, bar_full + 8 * stage, cb, wc, hc, img,
+                                tma_load_im2col_4d(sp, &map_a, bar_full + 8 * stage, cb, wc, hc, img,
                                                    (uint16_t)(kw * kp.dw), (uint16_t)(kh * kp.dh));
                             if (!kp.b_resident)
-                                tma_load_2d(sb, &map_b, bar_full + 8 * stage, (kh * kp.KW + kw) * kp.Cp + cb, n_tile * BN);
+                                tma_load_2d(sw, &map_b, bar_full + 8 * stage, (kh * kp.KW + kw) * kp.Cp + cb, n_tile * CH);
                             if (++stage == kStages) { stage = 0; phase ^= 1u; }
                         }
                 TSB_TRACE(i, 1);
@@ -452,7 +500,7 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             constexpr uint32_t idesc = instr_desc<BN>();
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
-            int cur_n = -1, b_loads = 0;
+            int cur_n = -1, w_loads = 0;
             for (int local = 0; local < my_tiles && ok; ++local) {
                 int m_tile, n_tile;
                 decode(local, m_tile, n_tile);
@@ -463,39 +511,34 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     break;
                 }
                 if (kp.b_resident && n_tile != cur_n) {
-                    if (!mbar_wait(bar_bfull, (uint32_t)b_loads & 1u, abort_flag)) {
+                    if (!mbar_wait(bar_bfull, (uint32_t)w_loads & 1u, abort_flag)) {
                         if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 6); }
                         break;
                     }
                     cur_n = n_tile;
-                    ++b_loads;
+                    ++w_loads;
                 }
                 tc_fence_after();
                 TSB_TRACE(local, 2);
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
                 for (int it = 0; it < k_iters; ++it) {
-                    const bool tr = kp.trace && blockIdx.x == 0 && local == 3 && it < 8;
-                    if (tr) kp.trace[320 + it * 4] = global_ns();
                     if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
                         if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 3); }
                         ok = false;
                         break;
                     }
-                    if (tr) kp.trace[320 + it * 4 + 1] = global_ns();
                     tc_fence_after();
                     if (it == 0) TSB_TRACE(local, 3);
-                    if (kp.trace && blockIdx.x == 0 && local == 3 && it < 16) kp.trace[272 + it] = global_ns();
-                    const uint32_t sa = base + stage * kp.stage_bytes;
-                    const uint32_t sb = kp.b_resident ? b_res + (uint32_t)it * kBBytes : sa + kABytes;
-                    const uint64_t da = smem_desc<BK>(sa), db = smem_desc<BK>(sb);
+                    const uint32_t sp = base + stage * kp.stage_bytes;
+                    const uint32_t sw = kp.b_resident ? w_res + (uint32_t)it * kWgtBytes : sp + kPixBytes;
+                    const uint64_t dp = smem_desc<BK>(sp), dw = smem_desc<BK>(sw);
+                    const uint64_t da = SWAP ? dw : dp, db = SWAP ? dp : dw;
 #pragma unroll
                     for (int k = 0; k < BK / 32; ++k) {
                         // +32 bytes along K inside the swizzle span = +2 in the descriptor's 16-byte address units
                         mma_i8(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (it | k) != 0 ? 1u : 0u);
                     }
-                    if (tr) kp.trace[320 + it * 4 + 2] = global_ns();
                     tc_commit(bar_empty + 8 * stage);  // frees the stage once these MMAs have read it
-                    if (tr) kp.trace[320 + it * 4 + 3] = global_ns();
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
                 if (ok) tc_commit(bar_tfull + 8 * acc);  // accumulator complete
@@ -514,7 +557,7 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         const int quarter = warp & 3;
         const int half = (warp - 2) >> 2;
         const int et = threadIdx.x - 64;         // 0..255
-        const int row = quarter * 32 + lane;     // row of the tile this thread owns
+        const int row = quarter * 32 + lane;     // tensor-memory lane this thread reads
         constexpr int kChunks = BN / 32;
         constexpr int kChunksPerWarp = kChunks / 2;
         for (int local = 0; local < my_tiles; ++local) {
@@ -522,12 +565,14 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
             int m_tile, n_tile;
             decode(local, m_tile, n_tile);
-            const int n0 = n_tile * BN;
+            const int o_base = n_tile * CH;
             float *t_dq = table + acc * 2 * BN, *t_bias = t_dq + BN;
-            for (int j = et; j < BN; j += kEpiThreads) {
-                const int o = n0 + j;
-                t_dq[j] = o < epi.O ? epi.dq[o] : 0.0f;
-                t_bias[j] = (o < epi.O && epi.bias) ? epi.bias[o] : 0.0f;
+            if (!SWAP) {
+                for (int j = et; j < BN; j += kEpiThreads) {
+                    const int o = o_base + j;
+                    t_dq[j] = o < epi.O ? epi.dq[o] : 0.0f;
+                    t_bias[j] = (o < epi.O && epi.bias) ? epi.bias[o] : 0.0f;
+                }
             }
             // One collective decision per tile: the wait result is AND-reduced over the epilogue threads, so either
             // all eight warps go on or all eight leave (the reduction is also the barrier that publishes the tables).
@@ -545,52 +590,100 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             }
             tc_fence_after();
             if (et == 0) TSB_TRACE(local, 5);
-            const int m = m_tile * kBM + row;
-            const bool live = m < kp.M_total;
-            const int img = live ? m / kp.P : 0;
-            const int p = live ? m - img * kp.P : 0;
             const uint32_t taddr0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
             // two register buffers: the load of the next 32 columns is in flight while the current ones are processed
             int v[2][32];
             tmem_ld32(taddr0 + (uint32_t)(half * kChunksPerWarp * 32), v[0]);
+            if (!SWAP) {
+                const int m = m_tile * PIX + row;
+                const bool live = m < kp.M_total;
+                const int img = live ? m / kp.P : 0;
+                const int p = live ? m - img * kp.P : 0;
 #pragma unroll
-            for (int cc = 0; cc < kChunksPerWarp; ++cc) {
-                const int c = half * kChunksPerWarp + cc;
-                if (kp.trace && blockIdx.x == 0 && local == 3 && et == 0) kp.trace[288 + cc * 3] = global_ns();
-                tmem_ld_wait();
-                if (kp.trace && blockIdx.x == 0 && local == 3 && et == 0) kp.trace[288 + cc * 3 + 1] = global_ns();
-                if (cc + 1 < kChunksPerWarp) tmem_ld32(taddr0 + (uint32_t)((c + 1) * 32), v[(cc + 1) & 1]);
-                if (!live) continue;
-                const int (&vc)[32] = v[cc & 1];
-                const int col0 = c * 32;
-                if (kp.dbg == 1) continue;
-                if (kp.dbg == 2) {  // arithmetic only, one store
-                    float sacc = 0.f;
+                for (int cc = 0; cc < kChunksPerWarp; ++cc) {
+                    const int c = half * kChunksPerWarp + cc;
+                    tmem_ld_wait();
+                    if (cc + 1 < kChunksPerWarp) tmem_ld32(taddr0 + (uint32_t)((c + 1) * 32), v[(cc + 1) & 1]);
+                    if (!live) continue;
+                    const int (&vc)[32] = v[cc & 1];
+                    const int col0 = c * 32;
+                    const bool full = o_base + col0 + 32 <= epi.O;
+                    if (kp.epi_mode == kEpiF32Nchw && full) {
+                        float *dst = epi.out_f32 + ((size_t)(img * epi.O + o_base + col0) * (size_t)epi.P + (size_t)p);
+                        store_f32_nchw(vc, t_dq + col0, t_bias + col0, epi.bias != nullptr, epi.activation, epi.leaky, dst, (uint32_t)epi.P);
+                    } else if (kp.epi_mode == kEpiI8Nhwc && full) {
+                        const float rs = epi.nscales == 1 ? epi.rq_scales[0] : epi.rq_scales[img];
+                        int8_t *dst = epi.out_i8 + (size_t)m * epi.out_cp + o_base + col0;
+                        if (!store_i8_nhwc(vc, t_dq + col0, t_bias + col0, epi.bias != nullptr, epi.activation, epi.leaky, rs, dst))
+                            store_generic(vc, t_dq + col0, t_bias + col0, epi, kp.per_sample_scale, img, p, m, o_base + col0);
+                    } else {
+                        store_generic(vc, t_dq + col0, t_bias + col0, epi, kp.per_sample_scale, img, p, m, o_base + col0);
+                    }
+                }
+            } else {
+                // this thread's channel; its scale and bias live in registers
+                const int o = o_base + row;
+                const bool ch_live = o < epi.O;
+                const float my_dq = ch_live ? epi.dq[o] : 0.0f;
+                const float my_bias = (ch_live && epi.bias) ? epi.bias[o] : 0.0f;
+                const bool has_bias = epi.bias != nullptr;
+                const int act = epi.activation;
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) sacc += fmaxf(__fadd_rn(__fmul_rn(__int2float_rn(vc[j]), t_dq[col0 + j]), t_bias[col0 + j]), 0.0f);
-                    if (sacc == 12345.678f) epi.out_f32[0] = sacc;
-                    continue;
-                }
-                if (kp.dbg == 3) {  // no conversions, no table
-                    float sacc = 0.f;
+                for (int cc = 0; cc < kChunksPerWarp; ++cc) {
+                    const int c = half * kChunksPerWarp + cc;
+                    tmem_ld_wait();
+                    if (cc + 1 < kChunksPerWarp) tmem_ld32(taddr0 + (uint32_t)((c + 1) * 32), v[(cc + 1) & 1]);
+                    const int (&vc)[32] = v[cc & 1];
+                    const int mfirst = m_tile * PIX + c * 32;          // first pixel of this chunk
+                    if (mfirst >= kp.M_total) continue;                  // uniform over the warp
+                    const int npix = min(32, kp.M_total - mfirst);
+                    const int img0 = mfirst / kp.P, p0 = mfirst - img0 * kp.P;
+                    const int split = kp.P - p0;                         // pixels j >= split belong to later images
+                    bool done = false;
+                    if (kp.epi_mode == kEpiF32Nchw && npix == 32 && split >= 32) {
+                        if (ch_live) {
+                            float *dst = epi.out_f32 + ((size_t)(img0 * epi.O + o) * (size_t)epi.P + (size_t)p0);
+                            if (has_bias) {
+                                if (act == TSB_ACT_RELU) swap_f32_run<TSB_ACT_RELU, true>(vc, my_dq, my_bias, epi.leaky, dst);
+                                else if (act == TSB_ACT_LEAKY_RELU) swap_f32_run<TSB_ACT_LEAKY_RELU, true>(vc, my_dq, my_bias, epi.leaky, dst);
+                                else swap_f32_run<TSB_ACT_NONE, true>(vc, my_dq, my_bias, epi.leaky, dst);
+                            } else {
+                                if (act == TSB_ACT_RELU) swap_f32_run<TSB_ACT_RELU, false>(vc, my_dq, my_bias, epi.leaky, dst);
+                                else if (act == TSB_ACT_LEAKY_RELU) swap_f32_run<TSB_ACT_LEAKY_RELU, false>(vc, my_dq, my_bias, epi.leaky, dst);
+                                else swap_f32_run<TSB_ACT_NONE, false>(vc, my_dq, my_bias, epi.leaky, dst);
+                            }
+                        }
+                        done = true;
+                    } else if (kp.epi_mode == kEpiI8Nhwc && split + kp.P >= 32) {
+                        // at most one image boundary inside the chunk
+                        const float rs0 = epi.nscales == 1 ? epi.rq_scales[0] : epi.rq_scales[img0];
+                        const float rs1 = epi.nscales == 1 ? rs0 : epi.rq_scales[min(img0 + 1, epi.nscales - 1)];
+                        const bool write = o < epi.out_cp;               // padding channels are written as zeros
+                        int8_t *dst = epi.out_i8 + (size_t)mfirst * epi.out_cp + o;
+                        if (has_bias) {
+                            if (act == TSB_ACT_RELU) done = swap_i8_run<TSB_ACT_RELU, true>(vc, my_dq, my_bias, epi.leaky, rs0, rs1, split, write, dst, epi.out_cp, npix);
+                            else if (act == TSB_ACT_LEAKY_RELU) done = swap_i8_run<TSB_ACT_LEAKY_RELU, true>(vc, my_dq, my_bias, epi.leaky, rs0, rs1, split, write, dst, epi.out_cp, npix);
+                            else done = swap_i8_run<TSB_ACT_NONE, true>(vc, my_dq, my_bias, epi.leaky, rs0, rs1, split, write, dst, epi.out_cp, npix);
+                        } else {
+                            if (act == TSB_ACT_RELU) done = swap_i8_run<TSB_ACT_RELU, false>(vc, my_dq, my_bias, epi.leaky, rs0, rs1, split, write, dst, epi.out_cp, npix);
+                            else if (act == TSB_ACT_LEAKY_RELU) done = swap_i8_run<TSB_ACT_LEAKY_RELU, false>(vc, my_dq, my_bias, epi.leaky, rs0, rs1, split, write, dst, epi.out_cp, npix);
+                            else done = swap_i8_run<TSB_ACT_NONE, false>(vc, my_dq, my_bias, epi.leaky, rs0, rs1, split, write, dst, epi.out_cp, npix);
+                        }
+                    }
+                    if (!done) {
+                        // element by element: any combination of outputs, residual, partial chunks
+                        int img = img0, p = p0;
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) sacc += __int_as_float(vc[j]);
-                    if (sacc == 12345.678f) epi.out_f32[0] = sacc;
-                    continue;
+                        for (int j = 0; j < 32; ++j) {
+                            if (j < npix) {
+                                if (ch_live) epilogue_store_one(epi, img, o, p, vc[j]);
+                                else if (epi.out_i8 && epi.i8_nhwc && o < epi.out_cp)
+                                    epi.out_i8[(size_t)(img * epi.P + p) * epi.out_cp + o] = 0;
+                            }
+                            if (++p == kp.P) { p = 0; ++img; }
+                        }
+                    }
                 }
-                const bool full = n0 + col0 + 32 <= epi.O;
-                if (kp.epi_mode == kEpiF32Nchw && full) {
-                    float *dst = epi.out_f32 + ((size_t)(img * epi.O + n0 + col0) * (size_t)epi.P + (size_t)p);
-                    store_f32_nchw(vc, t_dq + col0, t_bias + col0, epi.bias != nullptr, epi.activation, epi.leaky, dst, (uint32_t)epi.P);
-                } else if (kp.epi_mode == kEpiI8Nhwc && full) {
-                    const float rs = epi.nscales == 1 ? epi.rq_scales[0] : epi.rq_scales[img];
-                    int8_t *dst = epi.out_i8 + (size_t)m * epi.out_cp + n0 + col0;
-                    if (!store_i8_nhwc(vc, t_dq + col0, t_bias + col0, epi.bias != nullptr, epi.activation, epi.leaky, rs, dst))
-                        store_generic(vc, t_dq + col0, t_bias + col0, epi, kp.per_sample_scale, img, p, m, n0 + col0);
-                } else {
-                    store_generic(vc, t_dq + col0, t_bias + col0, epi, kp.per_sample_scale, img, p, m, n0 + col0);
-                }
-                if (kp.trace && blockIdx.x == 0 && local == 3 && et == 0) kp.trace[288 + cc * 3 + 2] = global_ns();
             }
             tc_fence_before();
             mbar_arrive(bar_tempty + 8 * acc);
@@ -638,11 +731,11 @@ CUtensorMapSwizzle swizzle_for(int bk) {
     return bk == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (bk == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
 }
 
-template <int BN, int BK>
+template <int BN, int BK, bool SWAP>
 int launch(const Config &cfg, const CUtensorMap &ma, const CUtensorMap &mb, const KernelParams &kp, const EpiParams &epi,
            cudaStream_t stream) {
     static bool configured = false;
-    auto kernel = conv_i8_tc_kernel<BN, BK>;
+    auto kernel = conv_i8_tc_kernel<BN, BK, SWAP>;
     if (!configured) {
         TSB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynamicSmem));
         configured = true;
@@ -709,39 +802,52 @@ Config choose_config(const View &v, int sm_count) {
     const ConvGeom &g = v.g;
     Config c;
     c.bk = (g.Cp % 128 == 0) ? 128 : 64;
-    c.bn = g.O > 128 ? 256 : (g.O > 64 ? 128 : 64);
     const int64_t M = (int64_t)g.N * g.OH * g.OW;
-    const int m_tiles = (int)ceil_div64(M, kBM);
-    // a narrower N tile when the wide one leaves most SMs idle or the last wave nearly empty
-    while (c.bn > 64) {
-        const int64_t tiles = (int64_t)m_tiles * ceil_div(g.O, c.bn);
-        const int64_t waves = ceil_div64(tiles, sm_count);
-        const double eff = (double)tiles / (double)(waves * sm_count);
-        if (eff >= 0.8) break;
-        const int64_t tiles2 = (int64_t)m_tiles * ceil_div(g.O, c.bn / 2);
-        const double eff2 = (double)tiles2 / (double)(ceil_div64(tiles2, sm_count) * sm_count);
-        if (eff2 <= eff) break;
-        c.bn /= 2;
+    // An MMA instruction costs the same 128 cycles for any N up to 256, so N should be 256 whenever possible.
+    // Up to 128 output channels: swapped orientation (channels on M, 256 or 128 pixels on N).
+    // More: normal orientation (128 pixels on M, up to 256 channels on N).
+    c.swap = (g.O <= 128 && !getenv("TSB_NO_SWAP")) ? 1 : 0;
+    if (c.swap) {
+        c.ch = kBM;
+        c.bn = 256;
+        if (ceil_div64(M, 256) < sm_count && ceil_div64(M, 128) > ceil_div64(M, 256)) c.bn = 128;  // few pixels: more, smaller tiles
+        c.pix = c.bn;
+    } else {
+        c.bn = g.O > 128 ? 256 : (g.O > 64 ? 128 : 64);
+        const int m_tiles128 = (int)ceil_div64(M, kBM);
+        // a narrower N tile when the wide one leaves most SMs idle or the last wave nearly empty
+        while (c.bn > 64) {
+            const int64_t tiles = (int64_t)m_tiles128 * ceil_div(g.O, c.bn);
+            const int64_t waves = ceil_div64(tiles, sm_count);
+            const double eff = (double)tiles / (double)(waves * sm_count);
+            if (eff >= 0.8) break;
+            const int64_t tiles2 = (int64_t)m_tiles128 * ceil_div(g.O, c.bn / 2);
+            const double eff2 = (double)tiles2 / (double)(ceil_div64(tiles2, sm_count) * sm_count);
+            if (eff2 <= eff) break;
+            c.bn /= 2;
+        }
+        c.pix = kBM;
+        c.ch = c.bn;
     }
-    c.num_m_tiles = m_tiles;
-    c.num_n_tiles = ceil_div(g.O, c.bn);
+    c.num_m_tiles = (int)ceil_div64(M, c.pix);
+    c.num_n_tiles = ceil_div(g.O, c.ch);
     const int64_t tiles = (int64_t)c.num_m_tiles * c.num_n_tiles;
     c.grid = (int)(tiles < sm_count ? tiles : sm_count);
     // shared-memory plan: keep the CTA's whole weight tile resident when it is small enough to leave room for
     // at least four activation stages; otherwise stream activations and weights together
-    const uint32_t a_bytes = (uint32_t)kBM * c.bk, b_bytes = (uint32_t)c.bn * c.bk;
+    const uint32_t p_bytes = (uint32_t)c.pix * c.bk, w_bytes = (uint32_t)c.ch * c.bk;
     const uint32_t k_iters = (uint32_t)g.KH * g.KW * (g.Cp / c.bk);
-    const uint32_t b_total = k_iters * b_bytes;
+    const uint32_t w_total = k_iters * w_bytes;
     const bool want_resident = !getenv("TSB_NO_RESIDENT_B") && tiles > c.grid;  // pays off only when a CTA runs several tiles
-    if (want_resident && b_total <= 128 * 1024 && (kSmemBudget - b_total) / a_bytes >= 4) {
+    if (want_resident && w_total <= 128 * 1024 && (kSmemBudget - w_total) / p_bytes >= 4) {
         c.b_resident = 1;
-        c.stage_bytes = a_bytes;
-        c.stages = std::min<int>(kMaxStages, (int)((kSmemBudget - b_total) / a_bytes));
+        c.stage_bytes = p_bytes;
+        c.stages = std::min<int>(kMaxStages, (int)((kSmemBudget - w_total) / p_bytes));
         c.b_off = (uint32_t)c.stages * c.stage_bytes;
-        c.bar_off = c.b_off + b_total;
+        c.bar_off = c.b_off + w_total;
     } else {
         c.b_resident = 0;
-        c.stage_bytes = a_bytes + b_bytes;
+        c.stage_bytes = p_bytes + w_bytes;
         c.stages = std::min<int>(kMaxStages, (int)(kSmemBudget / c.stage_bytes));
         c.b_off = 0;
         c.bar_off = (uint32_t)c.stages * c.stage_bytes;
@@ -758,7 +864,7 @@ int encode_weight_map(const View &v, const Config &cfg, const int8_t *w_packed, 
     const cuuint64_t ktot = (cuuint64_t)g.KH * g.KW * g.Cp;
     cuuint64_t dims[2] = {ktot, (cuuint64_t)g.O};
     cuuint64_t strides[1] = {ktot};
-    cuuint32_t box[2] = {(cuuint32_t)cfg.bk, (cuuint32_t)cfg.bn};
+    cuuint32_t box[2] = {(cuuint32_t)cfg.bk, (cuuint32_t)cfg.ch};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = g_encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t *>(w_packed), dims, strides, box,
                                 estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(cfg.bk),
@@ -775,7 +881,7 @@ int encode_activation_map(const View &v, const Config &cfg, const int8_t *x, CUt
     if (v.a_tiled) {
         cuuint64_t dims2[2] = {(cuuint64_t)g.Cp, (cuuint64_t)g.N * g.H * g.W};
         cuuint64_t strides2[1] = {(cuuint64_t)g.Cp};
-        cuuint32_t box2[2] = {(cuuint32_t)cfg.bk, (cuuint32_t)kBM};
+        cuuint32_t box2[2] = {(cuuint32_t)cfg.bk, (cuuint32_t)cfg.pix};
         cuuint32_t estr2[2] = {1, 1};
         CUresult r2 = g_encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t *>(x), dims2, strides2, box2,
                                      estr2, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(cfg.bk),
@@ -791,7 +897,7 @@ int encode_activation_map(const View &v, const Config &cfg, const int8_t *x, CUt
     int upper[2] = {(g.OW - 1) * g.sw - g.pad_l - (g.W - 1), (g.OH - 1) * g.sh - g.pad_t - (g.H - 1)};
     cuuint32_t estr[4] = {1, (cuuint32_t)g.sw, (cuuint32_t)g.sh, 1};
     CUresult r = g_encode_im2col(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<int8_t *>(x), dims, strides, lower,
-                                 upper, (cuuint32_t)cfg.bk, (cuuint32_t)kBM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 upper, (cuuint32_t)cfg.bk, (cuuint32_t)cfg.pix, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                  swizzle_for(cfg.bk), CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(TSB_ERR_UNSUPPORTED, "cuTensorMapEncodeIm2col failed with %d", (int)r);
@@ -896,7 +1002,6 @@ int launch_conv_tc(const View &v, const Config &cfg, const CUtensorMap &map_a, c
     kp.per_sample_scale = (epi.nscales > 1 && epi.nscales == g.N && epi.group_len == (uint32_t)(g.O * g.OH * g.OW)) ? 1 : 0;
     kp.status = status_word;
     kp.trace = g_trace;
-    kp.dbg = getenv("TSB_DBG") ? atoi(getenv("TSB_DBG")) : 0;
     kp.a_tiled = v.a_tiled;
     kp.stages = cfg.stages; kp.stage_bytes = cfg.stage_bytes; kp.b_resident = cfg.b_resident;
     kp.b_off = cfg.b_off; kp.bar_off = cfg.bar_off;
@@ -906,13 +1011,18 @@ int launch_conv_tc(const View &v, const Config &cfg, const CUtensorMap &map_a, c
     if (plain && epi.out_f32 && !epi.f32_nhwc && !epi.out_i8) kp.epi_mode = kEpiF32Nchw;
     if (plain && epi.out_i8 && epi.i8_nhwc && !epi.out_f32 && epi.rne_limit == 0 && (epi.nscales == 1 || kp.per_sample_scale))
         kp.epi_mode = kEpiI8Nhwc;
-#define TSB_TC_CASE(BN_, BK_) if (cfg.bn == BN_ && cfg.bk == BK_) return launch<BN_, BK_>(cfg, map_a, map_b, kp, epi, stream)
-    TSB_TC_CASE(64, 64);
-    TSB_TC_CASE(128, 64);
-    TSB_TC_CASE(256, 64);
-    TSB_TC_CASE(64, 128);
-    TSB_TC_CASE(128, 128);
-    TSB_TC_CASE(256, 128);
+#define TSB_TC_CASE(BN_, BK_, SWAP_) \
+    if (cfg.bn == BN_ && cfg.bk == BK_ && (cfg.swap != 0) == SWAP_) return launch<BN_, BK_, SWAP_>(cfg, map_a, map_b, kp, epi, stream)
+    TSB_TC_CASE(64, 64, false);
+    TSB_TC_CASE(128, 64, false);
+    TSB_TC_CASE(256, 64, false);
+    TSB_TC_CASE(64, 128, false);
+    TSB_TC_CASE(128, 128, false);
+    TSB_TC_CASE(256, 128, false);
+    TSB_TC_CASE(128, 64, true);
+    TSB_TC_CASE(256, 64, true);
+    TSB_TC_CASE(128, 128, true);
+    TSB_TC_CASE(256, 128, true);
 #undef TSB_TC_CASE
     return fail(TSB_ERR_UNSUPPORTED, "no tcgen05 kernel for tile %dx%d", cfg.bn, cfg.bk);
 }

@@ -27,7 +27,9 @@ struct View {
 };
 
 struct Config {
-    int bn = 0, bk = 0;               // tile width in output channels, K block in bytes (= swizzle span)
+    int bn = 0, bk = 0;               // N of the MMA instruction, K block in bytes (= swizzle span)
+    int swap = 0;                     // 1: channels on the MMA's M side and pixels on its N side
+    int pix = 0, ch = 0;              // pixels and output channels per tile
     int num_m_tiles = 0, num_n_tiles = 0;
     int grid = 0;                     // persistent CTAs
     // shared-memory plan of the kernel
