@@ -8,11 +8,11 @@
 //   MMA         tcgen05.mma kind::i8, 128 x BN x 32 per instruction, int32 accumulators in tensor memory,
 //               issued by one thread; two accumulator buffers so the epilogue of tile i overlaps the
 //               main loop of tile i+1
-//   epilogue    eight warps read the accumulators with tcgen05.ld and apply dequantize / bias / residual /
+//   epilogue    sixteen warps read the accumulators with tcgen05.ld and apply dequantize / bias / residual /
 //               activation / requantize in registers, then store fp32 (NCHW or NHWC) and/or int8
 //
-// Warp roles in a CTA of 320 threads: warp 0 = TMA producer, warp 1 = tensor-memory owner + MMA issuer,
-// warps 2..9 = epilogue.  The kernel is persistent: gridDim.x CTAs walk the tile list with stride gridDim.x.
+// Warp roles in a CTA of 576 threads: warp 0 = TMA producer, warp 1 = tensor-memory owner + MMA issuer,
+// warps 2..17 = epilogue.  The kernel is persistent: gridDim.x CTAs walk the tile list with stride gridDim.x.
 //
 // Every wait on an mbarrier is bounded; a wait that runs out records a code in *status, raises a CTA-wide
 // abort flag and all roles fall through to the common exit, where tensor memory is released.
@@ -29,8 +29,8 @@ namespace tsb {
 namespace tc {
 
 constexpr int kBM = 128;
-constexpr int kThreads = 320;
-constexpr int kEpiThreads = 256;
+constexpr int kThreads = 576;
+constexpr int kEpiThreads = 512;
 constexpr uint32_t kSmemBudget = 200 * 1024;  // stages; the rest holds barriers and epilogue tables
 
 // ---------------------------------------------------------------------------------------------------------
@@ -178,9 +178,11 @@ __device__ __forceinline__ float max_nan(float a, float b) {
     return r;
 }
 
+// ---- fast paths, normal orientation: the thread owns one PIXEL (its tensor-memory lane) and 32 consecutive channels
 template <int ACT, bool HAS_BIAS>
-__device__ __forceinline__ void store_f32_nchw_t(const int (&v)[32], const float *dq, const float *bias, float leaky,
-                                                 float *dst, uint32_t stride) {
+__device__ __forceinline__ void store_f32_nchw_t(const int (&v)[32], const float *__restrict__ dq,
+                                                 const float *__restrict__ bias, float leaky, float *__restrict__ dst,
+                                                 uint32_t stride) {
 #pragma unroll
     for (int j4 = 0; j4 < 8; ++j4) {
         const float4 d4 = *reinterpret_cast<const float4 *>(dq + 4 * j4);
@@ -196,8 +198,9 @@ __device__ __forceinline__ void store_f32_nchw_t(const int (&v)[32], const float
 // -128 in the reference (x86 integer-indefinite), which the saturating fast path does not reproduce; the caller
 // then redoes the chunk element by element.
 template <int ACT, bool HAS_BIAS>
-__device__ __forceinline__ bool store_i8_nhwc_t(const int (&v)[32], const float *dq, const float *bias, float leaky,
-                                                float rs, int8_t *dst) {
+__device__ __forceinline__ bool store_i8_nhwc_t(const int (&v)[32], const float *__restrict__ dq,
+                                                const float *__restrict__ bias, float leaky, float rs,
+                                                int8_t *__restrict__ dst) {
     uint32_t q[8];
     float worst = 0.0f;
 #pragma unroll
@@ -217,80 +220,71 @@ __device__ __forceinline__ bool store_i8_nhwc_t(const int (&v)[32], const float 
     return true;
 }
 
-#define TSB_EPI_DISPATCH(FN, ...)                                                                \
-    do {                                                                                         \
-        if (has_bias) {                                                                          \
-            if (act == TSB_ACT_RELU) FN<TSB_ACT_RELU, true>(__VA_ARGS__);                        \
-            else if (act == TSB_ACT_LEAKY_RELU) FN<TSB_ACT_LEAKY_RELU, true>(__VA_ARGS__);       \
-            else FN<TSB_ACT_NONE, true>(__VA_ARGS__);                                            \
-        } else {                                                                                 \
-            if (act == TSB_ACT_RELU) FN<TSB_ACT_RELU, false>(__VA_ARGS__);                       \
-            else if (act == TSB_ACT_LEAKY_RELU) FN<TSB_ACT_LEAKY_RELU, false>(__VA_ARGS__);      \
-            else FN<TSB_ACT_NONE, false>(__VA_ARGS__);                                           \
-        }                                                                                        \
-    } while (0)
-
-__device__ __forceinline__ void store_f32_nchw(const int (&v)[32], const float *dq, const float *bias, bool has_bias,
-                                               int act, float leaky, float *dst, uint32_t stride) {
-    TSB_EPI_DISPATCH(store_f32_nchw_t, v, dq, bias, leaky, dst, stride);
-}
-__device__ __forceinline__ bool store_i8_nhwc(const int (&v)[32], const float *dq, const float *bias, bool has_bias,
-                                              int act, float leaky, float rs, int8_t *dst) {
-    bool ok = true;
-#define TSB_I8(A_, B_) ok = store_i8_nhwc_t<A_, B_>(v, dq, bias, leaky, rs, dst)
-    if (has_bias) {
-        if (act == TSB_ACT_RELU) TSB_I8(TSB_ACT_RELU, true);
-        else if (act == TSB_ACT_LEAKY_RELU) TSB_I8(TSB_ACT_LEAKY_RELU, true);
-        else TSB_I8(TSB_ACT_NONE, true);
+// ---- fast paths, swapped orientation: the thread owns one CHANNEL (its lane) and 32 consecutive pixels; dq and bias
+// are per-thread scalars
+template <int ACT, bool HAS_BIAS>
+__device__ __forceinline__ void swap_f32_run(const int (&v)[32], float dq, float bias, float leaky, float *__restrict__ dst) {
+    // 32 consecutive pixels of one channel plane: 128 contiguous bytes
+    if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+        for (int j4 = 0; j4 < 8; ++j4) {
+            float4 o;
+            o.x = epi_value<ACT, HAS_BIAS>(v[4 * j4 + 0], dq, bias, leaky);
+            o.y = epi_value<ACT, HAS_BIAS>(v[4 * j4 + 1], dq, bias, leaky);
+            o.z = epi_value<ACT, HAS_BIAS>(v[4 * j4 + 2], dq, bias, leaky);
+            o.w = epi_value<ACT, HAS_BIAS>(v[4 * j4 + 3], dq, bias, leaky);
+            reinterpret_cast<float4 *>(dst)[j4] = o;
+        }
     } else {
-        if (act == TSB_ACT_RELU) TSB_I8(TSB_ACT_RELU, false);
-        else if (act == TSB_ACT_LEAKY_RELU) TSB_I8(TSB_ACT_LEAKY_RELU, false);
-        else TSB_I8(TSB_ACT_NONE, false);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) dst[j] = epi_value<ACT, HAS_BIAS>(v[j], dq, bias, leaky);
     }
-#undef TSB_I8
-    return ok;
 }
 
-// Everything else: several outputs at once, residual, NCHW int8, partial tiles.  o0 = first output channel.
-__device__ __forceinline__ void store_generic(const int (&v)[32], const float *dq, const float *bias, const EpiParams &epi,
-                                           int per_sample_scale, int img, int p, int m, int o0) {
-    const EpilogueMath math{epi.activation, epi.leaky};
-    const uint32_t nchw0 = (uint32_t)(img * epi.O) * (uint32_t)epi.P + (uint32_t)p;  // + o*P
-    const uint32_t nhwc0 = (uint32_t)m * (uint32_t)epi.O;                             // + o
-    const bool has_bias = epi.bias != nullptr, has_res = epi.residual != nullptr;
-    const float row_scale = epi.nscales == 1 ? epi.rq_scales[0] : (per_sample_scale ? epi.rq_scales[img] : 0.0f);
-    uint32_t q[8];
+// int8 NHWC_PAD output: for one pixel the 32 lanes of the warp hold 32 consecutive channels, so each byte store
+// instruction of the warp writes one full 32-byte sector.  All 32 pixels lie in one image (one requantize scale).
+// Returns false if a value needs the slow path (NaN / beyond int32); the decision is uniform over the warp.
+template <int ACT, bool HAS_BIAS>
+__device__ __forceinline__ bool swap_i8_run(const int (&v)[32], float dq, float bias, float leaky, float rs, bool write,
+                                            int8_t *__restrict__ dst, uint32_t pixel_stride) {
+    float worst = 0.0f;
+    int q[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
-        const int o = o0 + j;
-        int qv = 0;
-        if (o < epi.O) {
-            const uint32_t nchw = nchw0 + (uint32_t)o * (uint32_t)epi.P;
-            if (epi.out_acc) epi.out_acc[nchw] = v[j];
-            const uint32_t fidx = epi.f32_nhwc ? nhwc0 + (uint32_t)o : nchw;
-            const float r = has_res ? epi.residual[fidx] : 0.0f;
-            const float f = math(v[j], dq[j], bias[j], has_bias, r, has_res);
-            if (epi.out_f32) epi.out_f32[fidx] = f;
-            if (epi.out_i8) {
-                float s = row_scale;
-                bool write = true;
-                if (epi.nscales != 1 && !per_sample_scale) {
-                    const uint32_t g = nchw / epi.group_len;
-                    write = g < (uint32_t)epi.nscales;
-                    s = write ? epi.rq_scales[g] : 0.0f;
-                }
-                qv = q8(f, s, nchw < epi.rne_limit);
-                if (!epi.i8_nhwc && write) epi.out_i8[nchw] = (int8_t)qv;
-            }
-        }
-        if ((j & 3) == 0) q[j >> 2] = 0;
-        q[j >> 2] |= (uint32_t)(qv & 0xff) << (8 * (j & 3));
+        const float t = __fmul_rn(epi_value<ACT, HAS_BIAS>(v[j], dq, bias, leaky), rs);
+        worst = max_nan(worst, fabsf(t));
+        const float mag = __fadd_rz(fabsf(t), 0.5f);
+        const float sm = __int_as_float((__float_as_int(mag) & 0x7fffffff) | (__float_as_int(t) & 0x80000000));
+        asm("cvt.rzi.s8.f32 %0, %1;" : "=r"(q[j]) : "f"(sm));  // float -> int8 conversions saturate
     }
-    if (epi.out_i8 && epi.i8_nhwc) {
-        int8_t *dst = epi.out_i8 + (size_t)m * epi.out_cp + o0;
-        if (o0 < epi.out_cp) *reinterpret_cast<int4 *>(dst) = make_int4(q[0], q[1], q[2], q[3]);
-        if (o0 + 16 < epi.out_cp) *reinterpret_cast<int4 *>(dst + 16) = make_int4(q[4], q[5], q[6], q[7]);
+    if (__any_sync(0xffffffffu, !(worst < 2147483648.0f))) return false;
+    if (write) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) dst[(uint32_t)j * pixel_stride] = (int8_t)q[j];
     }
+    return true;
+}
+
+// run FN<activation, has_bias>(args...) for the runtime activation / bias combination
+#define TSB_EPI_DISPATCH(RESULT, FN, ...)                                                                 \
+    do {                                                                                                  \
+        if (has_bias) {                                                                                   \
+            if (act == TSB_ACT_RELU) RESULT FN<TSB_ACT_RELU, true>(__VA_ARGS__);                          \
+            else if (act == TSB_ACT_LEAKY_RELU) RESULT FN<TSB_ACT_LEAKY_RELU, true>(__VA_ARGS__);         \
+            else RESULT FN<TSB_ACT_NONE, true>(__VA_ARGS__);                                              \
+        } else {                                                                                          \
+            if (act == TSB_ACT_RELU) RESULT FN<TSB_ACT_RELU, false>(__VA_ARGS__);                         \
+            else if (act == TSB_ACT_LEAKY_RELU) RESULT FN<TSB_ACT_LEAKY_RELU, false>(__VA_ARGS__);        \
+            else RESULT FN<TSB_ACT_NONE, false>(__VA_ARGS__);                                             \
+        }                                                                                                 \
+    } while (0)
+
+// one tensor-memory column of this warp's 32 lanes (used by the rolled, element-by-element paths)
+__device__ __forceinline__ int tmem_ld1(uint32_t taddr) {
+    int r;
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    return r;
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -301,14 +295,14 @@ struct KernelParams {
     int OW, P;       // P = OH*OW
     int KH, KW;
     int sh, sw, dh, dw, pad_t, pad_l;
-    int Cp;          // channels of the NHWC_PAD input
-    int num_m_tiles, num_n_tiles;
+    int Cp;          // channels of the staged input per filter tap
+    int num_m_tiles, num_n_tiles;   // pixel tiles, channel tiles
     int per_sample_scale;  // requantize: scale index = image index
     int epi_mode;          // kEpi*: which epilogue code path full 32-column chunks take
     int a_tiled;           // activations are a plain [M][Cp] matrix (1x1, stride 1, no padding): 2-D tile loads
     // shared-memory plan (bytes from the 1024-aligned base)
     int stages;            // pipeline stages (<= kMaxStages)
-    uint32_t stage_bytes;  // one stage: the A tile, followed by the B tile unless the weights are resident
+    uint32_t stage_bytes;  // one stage: the pixel tile, followed by the weight tile unless the weights are resident
     int b_resident;        // all K blocks of this CTA's weight tile stay in shared memory; only activations stream
     uint32_t b_off;        // offset of the resident weights
     uint32_t bar_off;      // offset of the mbarriers; tensor-memory slot, abort flag and epilogue tables follow
@@ -331,51 +325,6 @@ constexpr uint32_t kMaxDynamicSmem = 227 * 1024;
 
 // barriers: full[stages], empty[stages], tmem_full[2], tmem_empty[2], b_full, b_free
 __host__ __device__ constexpr uint32_t num_barriers(int stages) { return 2u * (uint32_t)stages + 6u; }
-
-// Swapped-orientation epilogue helpers: a thread owns one output CHANNEL (its tensor-memory lane) and 32 consecutive
-// output PIXELS (columns).  dq / bias are per-thread scalars.
-template <int ACT, bool HAS_BIAS>
-__device__ __forceinline__ void swap_f32_run(const int (&v)[32], float dq, float bias, float leaky, float *dst) {
-    // 32 consecutive pixels of one channel plane: 128 contiguous bytes
-    if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-#pragma unroll
-        for (int j4 = 0; j4 < 8; ++j4) {
-            float4 o;
-            o.x = epi_value<ACT, HAS_BIAS>(v[4 * j4 + 0], dq, bias, leaky);
-            o.y = epi_value<ACT, HAS_BIAS>(v[4 * j4 + 1], dq, bias, leaky);
-            o.z = epi_value<ACT, HAS_BIAS>(v[4 * j4 + 2], dq, bias, leaky);
-            o.w = epi_value<ACT, HAS_BIAS>(v[4 * j4 + 3], dq, bias, leaky);
-            reinterpret_cast<float4 *>(dst)[j4] = o;
-        }
-    } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) dst[j] = epi_value<ACT, HAS_BIAS>(v[j], dq, bias, leaky);
-    }
-}
-
-// int8 NHWC_PAD output: for one pixel the 32 lanes of the warp hold 32 consecutive channels, so each byte store
-// instruction of the warp writes one full 32-byte sector.  rs0 applies to the first `split` pixels, rs1 to the rest
-// (a chunk crosses at most one image boundary).  Returns false if a value needs the slow path (NaN / beyond int32).
-template <int ACT, bool HAS_BIAS>
-__device__ __forceinline__ bool swap_i8_run(const int (&v)[32], float dq, float bias, float leaky, float rs0, float rs1,
-                                            int split, bool write, int8_t *dst, uint32_t pixel_stride, int npix) {
-    float worst = 0.0f;
-    int q[32];
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-        const float t = __fmul_rn(epi_value<ACT, HAS_BIAS>(v[j], dq, bias, leaky), j < split ? rs0 : rs1);
-        worst = max_nan(worst, fabsf(t));
-        q[j] = max(-128, min(127, half_away_s32(t)));
-    }
-    // the decision must be the same for the whole warp (the slow path stores the entire chunk)
-    if (__any_sync(0xffffffffu, !(worst < 2147483648.0f))) return false;
-    if (write) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-            if (j < npix) dst[(uint32_t)j * pixel_stride] = (int8_t)q[j];
-    }
-    return true;
-}
 
 // PIX pixels x CH channels per tile.  Normal orientation: the pixel tile is the MMA's A operand (M = 128 pixels), the
 // weight tile its B operand (N = BN channels).  Swapped orientation: the weight tile is A (M = 128 channels, rows
@@ -551,15 +500,16 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             }
         }
     } else {
-        // ------------------------------------------------------------------ epilogue (warps 2..9)
-        // A warp may read only the 32 tensor-memory lanes of its quarter (warp id mod 4); two warps share a
-        // quarter and split the tile's columns between them.
+        // ------------------------------------------------------------------ epilogue (warps 2..17)
+        // A warp may read only the 32 tensor-memory lanes of its quarter (warp id mod 4); four warps share a
+        // quarter and split the tile's columns between them in chunks of 32.
         const int quarter = warp & 3;
-        const int half = (warp - 2) >> 2;
-        const int et = threadIdx.x - 64;         // 0..255
+        const int part = (warp - 2) >> 2;        // 0..3
+        const int et = threadIdx.x - 64;         // 0..511
         const int row = quarter * 32 + lane;     // tensor-memory lane this thread reads
         constexpr int kChunks = BN / 32;
-        constexpr int kChunksPerWarp = kChunks / 2;
+        const bool has_bias = epi.bias != nullptr;
+        const int act = epi.activation;
         for (int local = 0; local < my_tiles; ++local) {
             const int acc = local & 1;
             const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
@@ -575,7 +525,7 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 }
             }
             // One collective decision per tile: the wait result is AND-reduced over the epilogue threads, so either
-            // all eight warps go on or all eight leave (the reduction is also the barrier that publishes the tables).
+            // all warps go on or all leave (the reduction is also the barrier that publishes the tables).
             int ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag) ? 1 : 0;
             int all_ok;
             asm volatile(
@@ -591,95 +541,84 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             tc_fence_after();
             if (et == 0) TSB_TRACE(local, 5);
             const uint32_t taddr0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
-            // two register buffers: the load of the next 32 columns is in flight while the current ones are processed
-            int v[2][32];
-            tmem_ld32(taddr0 + (uint32_t)(half * kChunksPerWarp * 32), v[0]);
             if (!SWAP) {
                 const int m = m_tile * PIX + row;
                 const bool live = m < kp.M_total;
                 const int img = live ? m / kp.P : 0;
                 const int p = live ? m - img * kp.P : 0;
-#pragma unroll
-                for (int cc = 0; cc < kChunksPerWarp; ++cc) {
-                    const int c = half * kChunksPerWarp + cc;
-                    tmem_ld_wait();
-                    if (cc + 1 < kChunksPerWarp) tmem_ld32(taddr0 + (uint32_t)((c + 1) * 32), v[(cc + 1) & 1]);
-                    if (!live) continue;
-                    const int (&vc)[32] = v[cc & 1];
+#pragma unroll 1
+                for (int c = part; c < kChunks; c += 4) {
                     const int col0 = c * 32;
                     const bool full = o_base + col0 + 32 <= epi.O;
-                    if (kp.epi_mode == kEpiF32Nchw && full) {
-                        float *dst = epi.out_f32 + ((size_t)(img * epi.O + o_base + col0) * (size_t)epi.P + (size_t)p);
-                        store_f32_nchw(vc, t_dq + col0, t_bias + col0, epi.bias != nullptr, epi.activation, epi.leaky, dst, (uint32_t)epi.P);
-                    } else if (kp.epi_mode == kEpiI8Nhwc && full) {
-                        const float rs = epi.nscales == 1 ? epi.rq_scales[0] : epi.rq_scales[img];
-                        int8_t *dst = epi.out_i8 + (size_t)m * epi.out_cp + o_base + col0;
-                        if (!store_i8_nhwc(vc, t_dq + col0, t_bias + col0, epi.bias != nullptr, epi.activation, epi.leaky, rs, dst))
-                            store_generic(vc, t_dq + col0, t_bias + col0, epi, kp.per_sample_scale, img, p, m, o_base + col0);
-                    } else {
-                        store_generic(vc, t_dq + col0, t_bias + col0, epi, kp.per_sample_scale, img, p, m, o_base + col0);
+                    bool done = false;
+                    if (full && kp.epi_mode != kEpiGeneric) {
+                        int v[32];
+                        tmem_ld32(taddr0 + (uint32_t)col0, v);
+                        tmem_ld_wait();
+                        if (kp.epi_mode == kEpiF32Nchw) {
+                            if (live) {
+                                float *dst = epi.out_f32 + ((size_t)(img * epi.O + o_base + col0) * (size_t)epi.P + (size_t)p);
+                                TSB_EPI_DISPATCH(, store_f32_nchw_t, v, t_dq + col0, t_bias + col0, epi.leaky, dst, (uint32_t)epi.P);
+                            }
+                            done = true;
+                        } else {
+                            const float rs = epi.nscales == 1 ? epi.rq_scales[0] : epi.rq_scales[img];
+                            int8_t *dst = epi.out_i8 + (size_t)m * epi.out_cp + o_base + col0;
+                            bool fine = true;
+                            if (live) TSB_EPI_DISPATCH(fine =, store_i8_nhwc_t, v, t_dq + col0, t_bias + col0, epi.leaky, rs, dst);
+                            done = !__any_sync(0xffffffffu, !fine);
+                        }
+                    }
+                    if (!done) {
+                        // element by element: any combination of outputs, residual, partial channel chunks
+                        for (int j = 0; j < 32; ++j) {
+                            const int a = tmem_ld1(taddr0 + (uint32_t)(col0 + j));
+                            const int o = o_base + col0 + j;
+                            if (!live) continue;
+                            if (o < epi.O) epilogue_store_one(epi, img, o, p, a);
+                            else if (epi.out_i8 && epi.i8_nhwc && o < epi.out_cp) epi.out_i8[(size_t)m * epi.out_cp + o] = 0;
+                        }
                     }
                 }
             } else {
                 // this thread's channel; its scale and bias live in registers
                 const int o = o_base + row;
                 const bool ch_live = o < epi.O;
+                const bool quarter_live = o_base + quarter * 32 < max(epi.O, epi.out_i8 && epi.i8_nhwc ? epi.out_cp : 0);
                 const float my_dq = ch_live ? epi.dq[o] : 0.0f;
                 const float my_bias = (ch_live && epi.bias) ? epi.bias[o] : 0.0f;
-                const bool has_bias = epi.bias != nullptr;
-                const int act = epi.activation;
-#pragma unroll
-                for (int cc = 0; cc < kChunksPerWarp; ++cc) {
-                    const int c = half * kChunksPerWarp + cc;
-                    tmem_ld_wait();
-                    if (cc + 1 < kChunksPerWarp) tmem_ld32(taddr0 + (uint32_t)((c + 1) * 32), v[(cc + 1) & 1]);
-                    const int (&vc)[32] = v[cc & 1];
-                    const int mfirst = m_tile * PIX + c * 32;          // first pixel of this chunk
-                    if (mfirst >= kp.M_total) continue;                  // uniform over the warp
+#pragma unroll 1
+                for (int c = part; c < kChunks && quarter_live; c += 4) {
+                    const int col0 = c * 32;
+                    const int mfirst = m_tile * PIX + col0;              // first pixel of this chunk
+                    if (mfirst >= kp.M_total) break;                     // uniform over the warp
                     const int npix = min(32, kp.M_total - mfirst);
                     const int img0 = mfirst / kp.P, p0 = mfirst - img0 * kp.P;
-                    const int split = kp.P - p0;                         // pixels j >= split belong to later images
+                    const bool one_image = npix == 32 && p0 + 32 <= kp.P;
                     bool done = false;
-                    if (kp.epi_mode == kEpiF32Nchw && npix == 32 && split >= 32) {
-                        if (ch_live) {
-                            float *dst = epi.out_f32 + ((size_t)(img0 * epi.O + o) * (size_t)epi.P + (size_t)p0);
-                            if (has_bias) {
-                                if (act == TSB_ACT_RELU) swap_f32_run<TSB_ACT_RELU, true>(vc, my_dq, my_bias, epi.leaky, dst);
-                                else if (act == TSB_ACT_LEAKY_RELU) swap_f32_run<TSB_ACT_LEAKY_RELU, true>(vc, my_dq, my_bias, epi.leaky, dst);
-                                else swap_f32_run<TSB_ACT_NONE, true>(vc, my_dq, my_bias, epi.leaky, dst);
-                            } else {
-                                if (act == TSB_ACT_RELU) swap_f32_run<TSB_ACT_RELU, false>(vc, my_dq, my_bias, epi.leaky, dst);
-                                else if (act == TSB_ACT_LEAKY_RELU) swap_f32_run<TSB_ACT_LEAKY_RELU, false>(vc, my_dq, my_bias, epi.leaky, dst);
-                                else swap_f32_run<TSB_ACT_NONE, false>(vc, my_dq, my_bias, epi.leaky, dst);
+                    if (one_image && kp.epi_mode != kEpiGeneric) {
+                        int v[32];
+                        tmem_ld32(taddr0 + (uint32_t)col0, v);
+                        tmem_ld_wait();
+                        if (kp.epi_mode == kEpiF32Nchw) {
+                            if (ch_live) {
+                                float *dst = epi.out_f32 + ((size_t)(img0 * epi.O + o) * (size_t)epi.P + (size_t)p0);
+                                TSB_EPI_DISPATCH(, swap_f32_run, v, my_dq, my_bias, epi.leaky, dst);
                             }
-                        }
-                        done = true;
-                    } else if (kp.epi_mode == kEpiI8Nhwc && split + kp.P >= 32) {
-                        // at most one image boundary inside the chunk
-                        const float rs0 = epi.nscales == 1 ? epi.rq_scales[0] : epi.rq_scales[img0];
-                        const float rs1 = epi.nscales == 1 ? rs0 : epi.rq_scales[min(img0 + 1, epi.nscales - 1)];
-                        const bool write = o < epi.out_cp;               // padding channels are written as zeros
-                        int8_t *dst = epi.out_i8 + (size_t)mfirst * epi.out_cp + o;
-                        if (has_bias) {
-                            if (act == TSB_ACT_RELU) done = swap_i8_run<TSB_ACT_RELU, true>(vc, my_dq, my_bias, epi.leaky, rs0, rs1, split, write, dst, epi.out_cp, npix);
-                            else if (act == TSB_ACT_LEAKY_RELU) done = swap_i8_run<TSB_ACT_LEAKY_RELU, true>(vc, my_dq, my_bias, epi.leaky, rs0, rs1, split, write, dst, epi.out_cp, npix);
-                            else done = swap_i8_run<TSB_ACT_NONE, true>(vc, my_dq, my_bias, epi.leaky, rs0, rs1, split, write, dst, epi.out_cp, npix);
+                            done = true;
                         } else {
-                            if (act == TSB_ACT_RELU) done = swap_i8_run<TSB_ACT_RELU, false>(vc, my_dq, my_bias, epi.leaky, rs0, rs1, split, write, dst, epi.out_cp, npix);
-                            else if (act == TSB_ACT_LEAKY_RELU) done = swap_i8_run<TSB_ACT_LEAKY_RELU, false>(vc, my_dq, my_bias, epi.leaky, rs0, rs1, split, write, dst, epi.out_cp, npix);
-                            else done = swap_i8_run<TSB_ACT_NONE, false>(vc, my_dq, my_bias, epi.leaky, rs0, rs1, split, write, dst, epi.out_cp, npix);
+                            const float rs = epi.nscales == 1 ? epi.rq_scales[0] : epi.rq_scales[img0];
+                            int8_t *dst = epi.out_i8 + (size_t)mfirst * epi.out_cp + o;
+                            TSB_EPI_DISPATCH(done =, swap_i8_run, v, my_dq, my_bias, epi.leaky, rs, o < epi.out_cp, dst, (uint32_t)epi.out_cp);
                         }
                     }
                     if (!done) {
-                        // element by element: any combination of outputs, residual, partial chunks
                         int img = img0, p = p0;
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            if (j < npix) {
-                                if (ch_live) epilogue_store_one(epi, img, o, p, vc[j]);
-                                else if (epi.out_i8 && epi.i8_nhwc && o < epi.out_cp)
-                                    epi.out_i8[(size_t)(img * epi.P + p) * epi.out_cp + o] = 0;
-                            }
+                        for (int j = 0; j < npix; ++j) {
+                            const int a = tmem_ld1(taddr0 + (uint32_t)(col0 + j));
+                            if (ch_live) epilogue_store_one(epi, img, o, p, a);
+                            else if (epi.out_i8 && epi.i8_nhwc && o < epi.out_cp)
+                                epi.out_i8[(size_t)(img * epi.P + p) * epi.out_cp + o] = 0;
                             if (++p == kp.P) { p = 0; ++img; }
                         }
                     }
@@ -804,9 +743,11 @@ Config choose_config(const View &v, int sm_count) {
     c.bk = (g.Cp % 128 == 0) ? 128 : 64;
     const int64_t M = (int64_t)g.N * g.OH * g.OW;
     // An MMA instruction costs the same 128 cycles for any N up to 256, so N should be 256 whenever possible.
-    // Up to 128 output channels: swapped orientation (channels on M, 256 or 128 pixels on N).
-    // More: normal orientation (128 pixels on M, up to 256 channels on N).
-    c.swap = (g.O <= 128 && !getenv("TSB_NO_SWAP")) ? 1 : 0;
+    // Normal orientation: 128 pixels on M, up to 256 output channels on N.  Swapped orientation: channels on M,
+    // 256 (or 128) pixels on N -- it halves the MMA count of narrow layers but its epilogue (one channel per thread)
+    // is dearer, so it is taken where it measured faster: multi-tap filters with at most 64 output channels.
+    const char *force = getenv("TSB_SWAP");
+    c.swap = force ? (atoi(force) != 0 && g.O <= 128) : (g.O <= 64 && g.KH * g.KW >= 9 && !v.fold);
     if (c.swap) {
         c.ch = kBM;
         c.bn = 256;

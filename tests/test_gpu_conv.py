@@ -14,7 +14,7 @@ ACT = {"none": 0, "relu": 1, "leaky_relu": 2}
 
 
 def run_gpu(x, w, pad, stride, dil, dq, bias=None, act="none", leaky=0.0, padding_value=0.0, kernel=0,
-            x_layout="nchw", residual=None, rq=None, i8_layout="nchw", f32_layout="nchw", want_acc=True):
+            x_layout="nchw", residual=None, rq=None, i8_layout="nchw", f32_layout="nchw", want_acc=True, want_f32=True):
     """x int8 NCHW numpy.  Returns dict(kernel, acc, f32, i8) as NCHW numpy arrays."""
     from tennis_b200 import _lib, ops
     dev = torch.device("cuda")
@@ -29,7 +29,7 @@ def run_gpu(x, w, pad, stride, dil, dq, bias=None, act="none", leaky=0.0, paddin
         xin, xl = xd, _lib.LAYOUT_NCHW
     out_acc = torch.full((N, O, OH, OW), -7, dtype=torch.int32, device=dev) if want_acc else None
     f32_nhwc = f32_layout == "nhwc"
-    out_f32 = torch.full((N, OH, OW, O) if f32_nhwc else (N, O, OH, OW), float("nan"), dtype=torch.float32, device=dev)
+    out_f32 = torch.full((N, OH, OW, O) if f32_nhwc else (N, O, OH, OW), float("nan"), dtype=torch.float32, device=dev) if want_f32 else None
     res = None
     if residual is not None:
         r = np.ascontiguousarray(residual.transpose(0, 2, 3, 1)) if f32_nhwc else residual
@@ -47,8 +47,9 @@ def run_gpu(x, w, pad, stride, dil, dq, bias=None, act="none", leaky=0.0, paddin
     torch.cuda.synchronize()
     r = dict(kernel=plan.kernel)
     r["acc"] = out_acc.cpu().numpy() if want_acc else None
-    f = out_f32.cpu().numpy()
-    r["f32"] = f.transpose(0, 3, 1, 2) if f32_nhwc else f
+    if want_f32:
+        f = out_f32.cpu().numpy()
+        r["f32"] = f.transpose(0, 3, 1, 2) if f32_nhwc else f
     if out_i8 is not None:
         q = out_i8.cpu().numpy()
         if i8_layout == "nhwc":
@@ -67,7 +68,8 @@ def check_case(checker, port, x, w, pad, stride, dil, dq, bias, act, leaky, pv, 
         yb = (yb + residual).astype(np.float32)
     ya = checker.activation(yb, act, leaky)
     got = run_gpu(x, w, pad, stride, dil, dq, bias, act, leaky, pv, kernel, **kw)
-    assert np.array_equal(got["acc"], want_acc), "int32 accumulators differ"
+    if kw.get("want_acc", True):
+        assert np.array_equal(got["acc"], want_acc), "int32 accumulators differ"
     assert same_bits(got["f32"], ya), "fp32 output differs"
     if kw.get("rq") is not None:
         assert np.array_equal(got["i8"], checker.quantize(ya, kw["rq"])), "requantized int8 output differs"
@@ -126,6 +128,34 @@ def test_tcgen05_kernel_cases(checker, port, case):
     rq = np.full(N, 0.9, dtype=np.float32)
     check_case(checker, port, x, w, pad, stride, dil, dq, bias, "leaky_relu", 0.1, 0.0, 2, x_layout="nhwc", rq=rq,
                i8_layout="nhwc")
+
+
+@pytest.mark.parametrize("swap", ["1", "0"])
+@pytest.mark.parametrize("case", [
+    (2, 64, 20, 20, 64, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1)),      # several 256-pixel tiles, image boundaries inside chunks
+    (3, 128, 9, 9, 40, 3, 3, (1, 1, 1, 1), (2, 2), (1, 1)),       # O not a multiple of 32
+    (1, 64, 7, 7, 128, 1, 1, (0, 0, 0, 0), (1, 1), (1, 1)),       # fewer pixels than one tile
+    (5, 64, 12, 12, 96, 5, 5, (2, 2, 2, 2), (1, 1), (1, 1)),
+    (2, 3, 33, 35, 16, 7, 7, (3, 3, 3, 3), (2, 2), (1, 1)),       # folded input
+    (4, 192, 14, 14, 100, 1, 1, (0, 0, 0, 0), (1, 1), (1, 1)),    # 1x1 with tiled activation loads
+])
+def test_both_mma_orientations(checker, port, monkeypatch, case, swap):
+    """Layers with at most 128 output channels can run with channels or with pixels on the MMA's M side; the
+    library picks one by a heuristic, the test forces each in turn (TSB_SWAP is read when the plan is created)."""
+    monkeypatch.setenv("TSB_SWAP", swap)
+    N, C, H, W, O, KH, KW, pad, stride, dil = case
+    rng = np.random.default_rng(N * 100 + C + O + int(swap))
+    x = rng.integers(-128, 128, size=(N, C, H, W), dtype=np.int8)
+    w = rng.integers(-127, 128, size=(O, C, KH, KW), dtype=np.int8)
+    dq = rng.uniform(0.001, 0.01, size=O).astype(np.float32)
+    bias = (rng.standard_normal(O) * 0.1).astype(np.float32)
+    check_case(checker, port, x, w, pad, stride, dil, dq, bias, "relu", 0.0, 0.0, 2)                        # fp32 NCHW fast path
+    check_case(checker, port, x, w, pad, stride, dil, dq, None, "leaky_relu", 0.1, 0.0, 2, want_acc=False,
+               x_layout="nhwc", rq=np.full(N, 0.7, dtype=np.float32), i8_layout="nhwc", f32_layout="nhwc")  # generic path
+    got = run_gpu(x, w, pad, stride, dil, dq, bias, "relu", 0.0, 0.0, 2, x_layout="nhwc", rq=np.full(N, 0.7, dtype=np.float32),
+                  i8_layout="nhwc", want_acc=False, want_f32=False)                                           # int8 NHWC fast path
+    want = checker.quantize(checker.relu(checker.add_bias(checker.conv2d_quantized(x, w, pad, stride, dil, dq), bias)), np.full(N, 0.7, np.float32))
+    assert np.array_equal(got["i8"], want)
 
 
 @pytest.mark.parametrize("case", [
