@@ -337,7 +337,10 @@ def run_ours(args):
         roofline = {"kernel": "conv_i8_tc_kernel", "bound": "tensor", "achieved": achieved, "peak": int8_peak,
                     "unit": "TOPS", "frac": achieved / int8_peak,
                     "peak_source": "2 x %s burst bf16 TFLOP/s (the driver's file has no int8 figure; dense int8 is nominally twice bf16)" % peaks["source"],
-                    "traffic": None,
+                    # dram__bytes_read.sum + dram__bytes_write.sum per conv launch, averaged over the five launches of one
+                    # step, from the ncu capture summarised in profiles/conv_i8_tc_kernel_config1.md
+                    "traffic": 15.2e6, "traffic_unit": "bytes per launch (ncu capture of this workload; fp32 outputs still in L2 at kernel end)",
+                    "algorithmic_bytes_per_launch": sum(p["conv_bytes"] for p in tc_layers) / max(1, len(tc_layers)),
                     "hbm_view": {"achieved_gbs": sum(p["conv_bytes"] for p in tc_layers) / tc_ms / 1e6 if tc_layers else 0.0,
                                  "peak_gbs": peaks["hbm_gbs"]}}
         line = {
