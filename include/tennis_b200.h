@@ -207,6 +207,22 @@ TSB_API int tsb_add_bias_f32_nchw(const float *x, float *y, int n, int c, int hw
 TSB_API int tsb_relu_f32(const float *x, float *y, int64_t count, void *stream);
 TSB_API int tsb_leaky_relu_f32(const float *x, float *y, int64_t count, float scale, void *stream);
 
+/*
+ * The operators around the convolutions of a quantized ResNet-style network, on the convolution path's layouts.
+ *  - max pooling (operator "pooling2d", type max; src/kernels/gpu/pooling2d_core.cu) on int8 NHWC_PAD: because
+ *    quantize is monotonic, pooling the int8 tensor equals quantizing the pooled fp32 tensor with the same scale;
+ *    taps outside the image are ignored (identical to zero padding for post-ReLU inputs);
+ *  - global average pooling ("global_pooling2d", type avg) on fp32 [N][pixels][C] -> [N][C];
+ *  - inner product ("inner_prod"; the reference calls cuBLAS SGEMM) y[n][o] = sum_k x[n][k] * w[o][k] + bias[o].
+ * The two fp32 reductions sum in a fixed order that differs from the CPU reference's, so they agree to rounding
+ * (1e-5 relative), not bit for bit.
+ */
+TSB_API int tsb_maxpool_i8_nhwc(const int8_t *x, int8_t *y, int n, int h, int w, int channels, int k, int stride, int pad,
+                                void *stream);
+TSB_API int tsb_global_avgpool_f32_nhwc(const float *x, float *y, int n, int pixels, int channels, void *stream);
+TSB_API int tsb_inner_prod_f32(const float *x, const float *w, const float *bias, float *y, int n, int k, int o,
+                               void *stream);
+
 /* Debugging aid: while a device buffer of 2048 bytes is set, CTA 0 of each tensor-core convolution launch records a
  * timeline (eight nanosecond stamps per tile for its first 32 tiles) into it.  NULL (the default) switches it off. */
 TSB_API int tsb_debug_set_trace_buffer(void *device_buffer);

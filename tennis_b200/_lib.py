@@ -71,6 +71,9 @@ SYMBOLS = {
     "tsb_add_bias_f32_nchw": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp]),
     "tsb_relu_f32": (_i, [_vp, _vp, _i64, _vp]),
     "tsb_leaky_relu_f32": (_i, [_vp, _vp, _i64, _f, _vp]),
+    "tsb_maxpool_i8_nhwc": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
+    "tsb_global_avgpool_f32_nhwc": (_i, [_vp, _vp, _i, _i, _i, _vp]),
+    "tsb_inner_prod_f32": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "tsb_debug_set_trace_buffer": (_i, [_vp]),
     "tsb_kernel_launch_count": (_i64, []),
 }

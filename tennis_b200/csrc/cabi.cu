@@ -24,6 +24,10 @@ int repack_i8_nchw_to_nhwc(const int8_t *, int8_t *, int, int, int, int, cudaStr
 int repack_i8_nhwc_to_nchw(const int8_t *, int8_t *, int, int, int, int, cudaStream_t);
 int add_bias_f32_nchw(const float *, float *, int, int, int, const float *, cudaStream_t);
 int activation_f32(const float *, float *, int64_t, int, float, cudaStream_t);
+// netops.cu
+int maxpool_i8_nhwc(const int8_t *, int8_t *, int, int, int, int, int, int, int, cudaStream_t);
+int global_avgpool_f32_nhwc(const float *, float *, int, int, int, cudaStream_t);
+int inner_prod_f32(const float *, const float *, const float *, float *, int, int, int, cudaStream_t);
 
 namespace {
 
@@ -105,6 +109,16 @@ int tsb_relu_f32(const float *x, float *y, int64_t count, void *stream) {
 }
 int tsb_leaky_relu_f32(const float *x, float *y, int64_t count, float scale, void *stream) {
     return activation_f32(x, y, count, TSB_ACT_LEAKY_RELU, scale, (cudaStream_t)stream);
+}
+
+int tsb_maxpool_i8_nhwc(const int8_t *x, int8_t *y, int n, int h, int w, int channels, int k, int stride, int pad, void *stream) {
+    return maxpool_i8_nhwc(x, y, n, h, w, channels, k, stride, pad, (cudaStream_t)stream);
+}
+int tsb_global_avgpool_f32_nhwc(const float *x, float *y, int n, int pixels, int channels, void *stream) {
+    return global_avgpool_f32_nhwc(x, y, n, pixels, channels, (cudaStream_t)stream);
+}
+int tsb_inner_prod_f32(const float *x, const float *w, const float *bias, float *y, int n, int k, int o, void *stream) {
+    return inner_prod_f32(x, w, bias, y, n, k, o, (cudaStream_t)stream);
 }
 
 int tsb_conv2d_i8_plan_create(const tsb_conv_desc *d, tsb_conv_plan **out) {

@@ -144,6 +144,7 @@ __device__ __forceinline__ constexpr uint32_t instr_desc() {
 constexpr int kEpiGeneric = 0;   // any combination of outputs, element by element
 constexpr int kEpiF32Nchw = 1;   // fp32 NCHW output only (the operator's own output)
 constexpr int kEpiI8Nhwc = 2;    // requantized int8 NHWC_PAD output only, half-away rounding, one scale per sample
+constexpr int kEpiNhwc = 3;      // fp32 [N][P][O] residual in and/or fp32 [N][P][O] out and/or int8 NHWC_PAD out (normal orientation)
 
 template <int ACT, bool HAS_BIAS>
 __device__ __forceinline__ float epi_value(int acc, float dq, float bias, float leaky) {
@@ -217,6 +218,47 @@ __device__ __forceinline__ bool store_i8_nhwc_t(const int (&v)[32], const float 
     if (!(worst < 2147483648.0f)) return false;
     *reinterpret_cast<int4 *>(dst) = make_int4(q[0], q[1], q[2], q[3]);
     *reinterpret_cast<int4 *>(dst + 16) = make_int4(q[4], q[5], q[6], q[7]);
+    return true;
+}
+
+// Block-output epilogue of a residual network: v = act(dq*acc + bias + residual); fp32 copy for the next residual and
+// int8 copy for the next convolution.  Each pointer may be null.  All three tensors are pixel-major, so the thread's 32
+// channels are contiguous: 16-byte loads and stores.
+template <int ACT, bool HAS_BIAS>
+__device__ __forceinline__ bool store_nhwc_t(const int (&v)[32], const float *__restrict__ dq, const float *__restrict__ bias,
+                                             float leaky, const float *__restrict__ res, float *__restrict__ out_f32,
+                                             int8_t *__restrict__ out_i8, float rs) {
+    uint32_t q[8];
+    float worst = 0.0f;
+#pragma unroll
+    for (int j4 = 0; j4 < 8; ++j4) {
+        const float4 d4 = *reinterpret_cast<const float4 *>(dq + 4 * j4);
+        const float4 b4 = *reinterpret_cast<const float4 *>(bias + 4 * j4);
+        float4 r4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (res) r4 = __ldg(reinterpret_cast<const float4 *>(res) + j4);
+        float f[4];
+        const float dd[4] = {d4.x, d4.y, d4.z, d4.w}, bb[4] = {b4.x, b4.y, b4.z, b4.w}, rr[4] = {r4.x, r4.y, r4.z, r4.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float t = __fmul_rn(__int2float_rn(v[4 * j4 + k]), dd[k]);
+            if (HAS_BIAS) t = __fadd_rn(t, bb[k]);
+            if (res) t = __fadd_rn(t, rr[k]);
+            if (ACT == TSB_ACT_RELU) t = fmaxf(t, 0.0f);
+            if (ACT == TSB_ACT_LEAKY_RELU) t = t > 0.0f ? t : __fmul_rn(t, leaky);
+            f[k] = t;
+        }
+        if (out_f32) reinterpret_cast<float4 *>(out_f32)[j4] = make_float4(f[0], f[1], f[2], f[3]);
+        if (out_i8) {
+            const float t0 = __fmul_rn(f[0], rs), t1 = __fmul_rn(f[1], rs), t2 = __fmul_rn(f[2], rs), t3 = __fmul_rn(f[3], rs);
+            worst = max_nan(max_nan(worst, fabsf(t0)), max_nan(fabsf(t1), max_nan(fabsf(t2), fabsf(t3))));
+            q[j4] = pack_sat_s8(half_away_s32(t0), half_away_s32(t1), half_away_s32(t2), half_away_s32(t3));
+        }
+    }
+    if (out_i8) {
+        if (!(worst < 2147483648.0f)) return false;
+        *reinterpret_cast<int4 *>(out_i8) = make_int4(q[0], q[1], q[2], q[3]);
+        *reinterpret_cast<int4 *>(out_i8 + 16) = make_int4(q[4], q[5], q[6], q[7]);
+    }
     return true;
 }
 
@@ -561,11 +603,20 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                                 TSB_EPI_DISPATCH(, store_f32_nchw_t, v, t_dq + col0, t_bias + col0, epi.leaky, dst, (uint32_t)epi.P);
                             }
                             done = true;
-                        } else {
+                        } else if (kp.epi_mode == kEpiI8Nhwc) {
                             const float rs = epi.nscales == 1 ? epi.rq_scales[0] : epi.rq_scales[img];
                             int8_t *dst = epi.out_i8 + (size_t)m * epi.out_cp + o_base + col0;
                             bool fine = true;
                             if (live) TSB_EPI_DISPATCH(fine =, store_i8_nhwc_t, v, t_dq + col0, t_bias + col0, epi.leaky, rs, dst);
+                            done = !__any_sync(0xffffffffu, !fine);
+                        } else {
+                            const float rs = epi.nscales == 1 ? epi.rq_scales[0] : epi.rq_scales[img];
+                            const size_t f_off = (size_t)m * epi.O + o_base + col0;
+                            const float *res = epi.residual ? epi.residual + f_off : nullptr;
+                            float *of = epi.out_f32 ? epi.out_f32 + f_off : nullptr;
+                            int8_t *oi = epi.out_i8 ? epi.out_i8 + (size_t)m * epi.out_cp + o_base + col0 : nullptr;
+                            bool fine = true;
+                            if (live) TSB_EPI_DISPATCH(fine =, store_nhwc_t, v, t_dq + col0, t_bias + col0, epi.leaky, res, of, oi, rs);
                             done = !__any_sync(0xffffffffu, !fine);
                         }
                     }
@@ -950,8 +1001,12 @@ int launch_conv_tc(const View &v, const Config &cfg, const CUtensorMap &map_a, c
     const bool plain = !epi.out_acc && !epi.residual;
     kp.epi_mode = kEpiGeneric;
     if (plain && epi.out_f32 && !epi.f32_nhwc && !epi.out_i8) kp.epi_mode = kEpiF32Nchw;
-    if (plain && epi.out_i8 && epi.i8_nhwc && !epi.out_f32 && epi.rne_limit == 0 && (epi.nscales == 1 || kp.per_sample_scale))
-        kp.epi_mode = kEpiI8Nhwc;
+    const bool i8_fast = !epi.out_i8 || (epi.i8_nhwc && epi.rne_limit == 0 && (epi.nscales == 1 || kp.per_sample_scale));
+    if (plain && epi.out_i8 && !epi.out_f32 && i8_fast) kp.epi_mode = kEpiI8Nhwc;
+    // pixel-major fp32 tensors (block outputs and residuals of a network): 16-byte accesses need O % 4 == 0
+    if (!cfg.swap && !epi.out_acc && (epi.out_f32 || epi.residual) && epi.f32_nhwc && i8_fast && g.O % 4 == 0 &&
+        ((reinterpret_cast<uintptr_t>(epi.out_f32) | reinterpret_cast<uintptr_t>(epi.residual)) & 15) == 0)
+        kp.epi_mode = kEpiNhwc;
 #define TSB_TC_CASE(BN_, BK_, SWAP_) \
     if (cfg.bn == BN_ && cfg.bk == BK_ && (cfg.swap != 0) == SWAP_) return launch<BN_, BK_, SWAP_>(cfg, map_a, map_b, kp, epi, stream)
     TSB_TC_CASE(64, 64, false);

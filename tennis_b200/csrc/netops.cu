@@ -1,0 +1,116 @@
+// The non-convolution operators a quantized ResNet-style network needs between and after its convolutions,
+// on the layouts the convolution path keeps activations in.  All are memory-bound byte / float movers.
+//   pooling2d (max)       src/kernels/gpu/pooling2d_core.cu, src/backend/base/base_pooling2d.cpp
+//   global_pooling2d (avg) src/kernels/gpu/global_pooling2d.cu
+//   inner_prod             src/kernels/gpu/inner_prod.cu (cuBLAS SGEMM in the reference)
+#include "common.cuh"
+
+namespace tsb {
+namespace {
+
+constexpr int kThreads = 256;
+
+// int8 NHWC_PAD max pooling; taps outside the image are ignored.  quantize is monotonic, so pooling the int8
+// tensor gives exactly quantize(pool(x)) for the same scale; for post-ReLU inputs ignoring the halo and padding it
+// with zeros are the same thing.  One thread produces 16 channels of one output pixel.
+__global__ void __launch_bounds__(kThreads)
+maxpool_i8_nhwc_kernel(const int8_t *__restrict__ x, int8_t *__restrict__ y, int N, int H, int W, int Cp, int OH, int OW,
+                       int K, int S, int pad) {
+    const int units = Cp / 16;
+    const int64_t total = (int64_t)N * OH * OW * units;
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < total; i += (int64_t)gridDim.x * kThreads) {
+        const int u = (int)(i % units);
+        const int64_t pix = i / units;
+        const int ow = (int)(pix % OW), oh = (int)((pix / OW) % OH), n = (int)(pix / ((int64_t)OW * OH));
+        int best[16];
+#pragma unroll
+        for (int b = 0; b < 16; ++b) best[b] = -128;
+        for (int kh = 0; kh < K; ++kh) {
+            const int ih = oh * S - pad + kh;
+            if ((unsigned)ih >= (unsigned)H) continue;
+            for (int kw = 0; kw < K; ++kw) {
+                const int iw = ow * S - pad + kw;
+                if ((unsigned)iw >= (unsigned)W) continue;
+                const int4 v = *reinterpret_cast<const int4 *>(x + (((int64_t)n * H + ih) * W + iw) * Cp + u * 16);
+                const int8_t *b8 = reinterpret_cast<const int8_t *>(&v);
+#pragma unroll
+                for (int b = 0; b < 16; ++b) best[b] = max(best[b], (int)b8[b]);
+            }
+        }
+        uint32_t w4[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int b = 0; b < 16; ++b) w4[b >> 2] |= (uint32_t)(best[b] & 0xff) << (8 * (b & 3));
+        *reinterpret_cast<int4 *>(y + pix * Cp + u * 16) = make_int4(w4[0], w4[1], w4[2], w4[3]);
+    }
+}
+
+// fp32 [N][P][C] -> [N][C]: sum over the P pixels in index order, one multiply by 1/P... no: divided by P as the
+// reference's average pooling does (sum / count).
+__global__ void __launch_bounds__(kThreads)
+global_avgpool_f32_nhwc_kernel(const float *__restrict__ x, float *__restrict__ y, int N, int P, int C) {
+    const int64_t total = (int64_t)N * C;
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < total; i += (int64_t)gridDim.x * kThreads) {
+        const int c = (int)(i % C), n = (int)(i / C);
+        float s = 0.0f;
+        for (int p = 0; p < P; ++p) s = __fadd_rn(s, x[((int64_t)n * P + p) * C + c]);
+        y[i] = __fdiv_rn(s, (float)P);
+    }
+}
+
+// y[n][o] = sum_k x[n][k] * w[o][k] + bias[o]; one warp per output, lanes stride over k, tree reduction.
+__global__ void __launch_bounds__(kThreads)
+inner_prod_f32_kernel(const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
+                      float *__restrict__ y, int N, int K, int O) {
+    const int warps_per_block = kThreads / 32;
+    const int lane = threadIdx.x & 31;
+    const int64_t total = (int64_t)N * O;
+    for (int64_t i = (int64_t)blockIdx.x * warps_per_block + (threadIdx.x >> 5); i < total; i += (int64_t)gridDim.x * warps_per_block) {
+        const int o = (int)(i % O), n = (int)(i / O);
+        float s = 0.0f;
+        for (int k = lane; k < K; k += 32) s = fmaf(x[(int64_t)n * K + k], w[(int64_t)o * K + k], s);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+        if (lane == 0) y[i] = bias ? s + bias[o] : s;
+    }
+}
+
+int grid_for(int64_t items, int per_block) {
+    int64_t blocks = (items + per_block - 1) / per_block;
+    if (blocks < 1) blocks = 1;
+    return (int)(blocks < 148 * 16 ? blocks : 148 * 16);
+}
+
+}  // namespace
+
+int maxpool_i8_nhwc(const int8_t *x, int8_t *y, int n, int h, int w, int channels, int k, int stride, int pad,
+                    cudaStream_t stream) {
+    if (!x || !y) return fail(TSB_ERR_INVALID_ARGUMENT, "maxpool: null pointer");
+    if (n < 1 || h < 1 || w < 1 || channels < 1 || k < 1 || stride < 1 || pad < 0 || pad >= k)
+        return fail(TSB_ERR_INVALID_ARGUMENT, "maxpool: bad geometry");
+    const int cp = tsb_padded_channels(channels);
+    const int oh = (h + 2 * pad - k) / stride + 1, ow = (w + 2 * pad - k) / stride + 1;
+    if (oh < 1 || ow < 1) return fail(TSB_ERR_INVALID_ARGUMENT, "maxpool: empty output");
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) % 16) return fail(TSB_ERR_INVALID_ARGUMENT, "maxpool: tensors must be 16-byte aligned");
+    const int64_t items = (int64_t)n * oh * ow * (cp / 16);
+    maxpool_i8_nhwc_kernel<<<grid_for(items, kThreads), kThreads, 0, stream>>>(x, y, n, h, w, cp, oh, ow, k, stride, pad);
+    TSB_LAUNCHED("maxpool_i8_nhwc_kernel");
+    return TSB_OK;
+}
+
+int global_avgpool_f32_nhwc(const float *x, float *y, int n, int pixels, int channels, cudaStream_t stream) {
+    if (!x || !y) return fail(TSB_ERR_INVALID_ARGUMENT, "global_avgpool: null pointer");
+    if (n < 1 || pixels < 1 || channels < 1) return fail(TSB_ERR_INVALID_ARGUMENT, "global_avgpool: bad shape");
+    global_avgpool_f32_nhwc_kernel<<<grid_for((int64_t)n * channels, kThreads), kThreads, 0, stream>>>(x, y, n, pixels, channels);
+    TSB_LAUNCHED("global_avgpool_f32_nhwc_kernel");
+    return TSB_OK;
+}
+
+int inner_prod_f32(const float *x, const float *w, const float *bias, float *y, int n, int k, int o, cudaStream_t stream) {
+    if (!x || !w || !y) return fail(TSB_ERR_INVALID_ARGUMENT, "inner_prod: null pointer");
+    if (n < 1 || k < 1 || o < 1) return fail(TSB_ERR_INVALID_ARGUMENT, "inner_prod: bad shape");
+    inner_prod_f32_kernel<<<grid_for((int64_t)n * o, kThreads / 32), kThreads, 0, stream>>>(x, w, bias, y, n, k, o);
+    TSB_LAUNCHED("inner_prod_f32_kernel");
+    return TSB_OK;
+}
+
+}  // namespace tsb

@@ -1,0 +1,211 @@
+"""Quantized bottleneck ResNets (the ResNet-50-shaped int8 network of the benchmark configurations) on the fused path.
+
+A network is a list of convolution specs plus the fixed glue of a bottleneck ResNet: stem 7x7/2 -> max pool 3x3/2 ->
+stages of [1x1, 3x3, 1x1(x4)] blocks with a 1x1 projection shortcut on the first block of each stage -> fp32 global
+average pool -> fp32 inner product.  BatchNorm is folded into per-channel scale and bias, ReLU is fused, activations
+travel between convolutions as int8 NHWC_PAD (requantized in the producing convolution's epilogue with the consumer's
+quantize scale), residual adds are fp32.  In TenniS operator terms every convolution is
+``quantize -> conv2d_quantized -> add_bias -> [add] -> relu`` and the results are bit-identical to running those
+operators one by one.
+
+Weights are synthetic (seeded): int8 uniform in [-127,127], per-channel weight scales U(0.001,0.01), bias N(0,0.1).
+Activation scales are calibrated once on a sample batch (127 / max|activation| per tensor).
+"""
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import ACT_NONE, ACT_RELU, LAYOUT_NHWC_PAD, LAYOUT_STAGED, check
+from . import ops
+
+
+def resnet_spec(image=224, widths=(64, 128, 256, 512), blocks=(3, 4, 6, 3), stem_channels=64, classes=1000, expansion=4):
+    """Topology of a bottleneck ResNet as plain data.  ResNet-50: the defaults (53 convolutions)."""
+    convs = []
+
+    def conv(name, cin, cout, k, stride, pad, size_in):
+        size_out = (size_in + 2 * pad - k) // stride + 1
+        convs.append(dict(name=name, c=cin, o=cout, k=k, stride=stride, pad=pad, h=size_in, oh=size_out))
+        return size_out
+
+    size = conv("stem", 3, stem_channels, 7, 2, 3, image)
+    pooled = (size + 2 * 1 - 3) // 2 + 1
+    stages = []
+    cin, size = stem_channels, pooled
+    for si, (width, nblocks) in enumerate(zip(widths, blocks)):
+        stage = []
+        for bi in range(nblocks):
+            stride = 2 if (bi == 0 and si > 0) else 1
+            cout = width * expansion
+            b = dict(name="s%db%d" % (si + 1, bi + 1), projection=(bi == 0))
+            b["conv1"] = len(convs); conv(b["name"] + ".conv1", cin, width, 1, 1, 0, size)
+            b["conv2"] = len(convs); size_out = conv(b["name"] + ".conv2", width, width, 3, stride, 1, size)
+            b["conv3"] = len(convs); conv(b["name"] + ".conv3", width, cout, 1, 1, 0, size_out)
+            if b["projection"]:
+                b["proj"] = len(convs); conv(b["name"] + ".proj", cin, cout, 1, stride, 0, size)
+            stage.append(b)
+            cin, size = cout, size_out
+        stages.append(stage)
+    return dict(image=image, convs=convs, stages=stages, stem_pooled=pooled, features=cin, classes=classes, final_size=size)
+
+
+def conv_ops(spec, batch):
+    """2 * N * O * OH * OW * C * KH * KW summed over the convolutions."""
+    return sum(2 * batch * c["o"] * c["oh"] * c["oh"] * c["c"] * c["k"] * c["k"] for c in spec["convs"])
+
+
+def make_params(spec, seed=0):
+    """Seeded synthetic parameters (numpy).  dq holds the per-channel WEIGHT scales; the dequantize scales of a layer are
+    weight scale / input quantize scale, computed once the activation scales are known."""
+    rng = np.random.default_rng(seed)
+    params = []
+    for c in spec["convs"]:
+        w = rng.integers(-127, 128, size=(c["o"], c["c"], c["k"], c["k"]), dtype=np.int8)
+        sw = rng.uniform(0.001, 0.01, size=c["o"]).astype(np.float32)
+        bias = (rng.standard_normal(c["o"]) * 0.1).astype(np.float32)
+        params.append(dict(w=w, sw=sw, bias=bias))
+    fc_w = (rng.standard_normal((spec["classes"], spec["features"])) * 0.01).astype(np.float32)
+    fc_b = (rng.standard_normal(spec["classes"]) * 0.01).astype(np.float32)
+    return dict(convs=params, fc_w=fc_w, fc_b=fc_b)
+
+
+class QuantResNet:
+    """The network on one GPU: plans, weights and activation buffers are built once; forward() launches only kernels of
+    libtennis_b200.so (quantize, convolutions with fused epilogues, max pool, average pool, inner product)."""
+
+    def __init__(self, spec, params, batch, device="cuda"):
+        self.spec, self.batch, self.dev = spec, batch, torch.device(device)
+        self.lib = _lib.load()
+        dev = self.dev
+        self.convs = []
+        for c, p in zip(spec["convs"], params["convs"]):
+            xshape = (batch, c["c"], c["h"], c["h"])
+            wshape = (c["o"], c["c"], c["k"], c["k"])
+            plan = ops.ConvPlan(xshape, wshape, (c["pad"],) * 4, (c["stride"],) * 2, (1, 1), 0.0, _lib.KERNEL_AUTO, dev)
+            plan.set_weights(torch.from_numpy(p["w"]).to(dev))
+            self.convs.append(dict(spec=c, plan=plan, sw=p["sw"], bias=torch.from_numpy(p["bias"]).to(dev), dq=None,
+                                   in_scale=None, out_scale=None))
+        self.fc_w = torch.from_numpy(params["fc_w"]).to(dev)
+        self.fc_b = torch.from_numpy(params["fc_b"]).to(dev)
+        self.buffers = {}
+        self.calibrated = False
+
+    # ---- buffers ------------------------------------------------------------------------------------------------
+    def _i8(self, key, pixels_hw, channels):
+        shape = (self.batch, pixels_hw, pixels_hw, ops.padded_channels(channels))
+        if key not in self.buffers:
+            self.buffers[key] = torch.zeros(shape, dtype=torch.int8, device=self.dev)
+        return self.buffers[key]
+
+    def _f32(self, key, pixels_hw, channels):
+        shape = (self.batch, pixels_hw, pixels_hw, channels)
+        if key not in self.buffers:
+            self.buffers[key] = torch.zeros(shape, dtype=torch.float32, device=self.dev)
+        return self.buffers[key]
+
+    # ---- one convolution ----------------------------------------------------------------------------------------
+    def _conv(self, idx, x_i8, key, act, want_i8=True, want_f32=False, residual=None, staged=False):
+        L = self.convs[idx]
+        c = L["spec"]
+        out_i8 = self._i8(key + ".i8", c["oh"], c["o"]) if want_i8 else None
+        out_f32 = self._f32(key + ".f32", c["oh"], c["o"]) if want_f32 else None
+        L["plan"].run(None if staged else x_i8, LAYOUT_STAGED if staged else LAYOUT_NHWC_PAD, L["dq"], bias=L["bias"],
+                      residual=residual, activation=act, out_f32=out_f32, out_f32_layout=LAYOUT_NHWC_PAD, out_i8=out_i8,
+                      out_i8_layout=LAYOUT_NHWC_PAD,
+                      requant_scales=L["out_scale_arr"] if want_i8 else None)
+        return out_i8, out_f32
+
+    def _set_in_scale(self, idx, scale):
+        L = self.convs[idx]
+        L["in_scale"] = np.float32(scale)
+        L["dq"] = torch.from_numpy((L["sw"] / np.float32(scale)).astype(np.float32)).to(self.dev)
+
+    def _set_out_scale(self, idx, scale):
+        L = self.convs[idx]
+        L["out_scale"] = np.float32(scale)
+        L["out_scale_arr"] = _lib.float_array([float(scale)] * self.batch)
+
+    # ---- calibration: run layer by layer in fp32-out mode, fix 127/max|activation| as the next quantize scale ------
+    def calibrate(self, x):
+        """x: fp32 NCHW sample batch on the device.  Fixes every activation scale; returns them as a dict."""
+        spec = self.spec
+        amax = float(x.abs().max())
+        self.input_scale = np.float32(127.0) / np.float32(amax if amax > 0 else 1.0)
+        self._set_in_scale(0, self.input_scale)
+
+        def out_scale_of(idx, x_i8, key, act, residual=None, staged=False):
+            L = self.convs[idx]
+            c = L["spec"]
+            f = self._f32(key + ".cal", c["oh"], c["o"])
+            L["plan"].run(None if staged else x_i8, LAYOUT_STAGED if staged else LAYOUT_NHWC_PAD, L["dq"], bias=L["bias"],
+                          residual=residual, activation=act, out_f32=f, out_f32_layout=LAYOUT_NHWC_PAD)
+            m = float(f.abs().max())
+            del self.buffers[key + ".cal"]
+            return np.float32(127.0) / np.float32(m if m > 0 else 1.0)
+
+        self.input_scale_arr = _lib.float_array([float(self.input_scale)] * self.batch)
+        self.convs[0]["plan"].quantize_input(x, self.input_scale_arr)
+        self._set_out_scale(0, out_scale_of(0, None, "stem", ACT_RELU, staged=True))
+        cur_scale = self.convs[0]["out_scale"]          # scale of the int8 tensor entering the next convolutions
+        x_i8 = self._forward_stem(x)
+        x_f32 = None
+        for stage in spec["stages"]:
+            for b in stage:
+                i1, i2, i3 = b["conv1"], b["conv2"], b["conv3"]
+                self._set_in_scale(i1, cur_scale)
+                self._set_out_scale(i1, out_scale_of(i1, x_i8, b["name"] + ".a", ACT_RELU))
+                a, _ = self._conv(i1, x_i8, b["name"] + ".a", ACT_RELU)
+                self._set_in_scale(i2, self.convs[i1]["out_scale"])
+                self._set_out_scale(i2, out_scale_of(i2, a, b["name"] + ".b", ACT_RELU))
+                bb, _ = self._conv(i2, a, b["name"] + ".b", ACT_RELU)
+                if b["projection"]:
+                    ip = b["proj"]
+                    self._set_in_scale(ip, cur_scale)
+                    _, sc = self._conv(ip, x_i8, b["name"] + ".sc", ACT_NONE, want_i8=False, want_f32=True)
+                else:
+                    sc = x_f32
+                self._set_in_scale(i3, self.convs[i2]["out_scale"])
+                self._set_out_scale(i3, out_scale_of(i3, bb, b["name"] + ".y", ACT_RELU, residual=sc))
+                y_i8, y_f32 = self._conv(i3, bb, b["name"] + ".y", ACT_RELU, want_i8=True, want_f32=True, residual=sc)
+                x_i8, x_f32, cur_scale = y_i8, y_f32, self.convs[i3]["out_scale"]
+        self.calibrated = True
+        torch.cuda.synchronize()
+        return dict(input=self.input_scale, convs=[(L["in_scale"], L["out_scale"]) for L in self.convs])
+
+    def _forward_stem(self, x):
+        spec = self.spec
+        L = self.convs[0]
+        L["plan"].quantize_input(x, self.input_scale_arr)
+        s_i8, _ = self._conv(0, None, "stem", ACT_RELU, staged=True)
+        c = L["spec"]
+        pooled = self._i8("stem.pool", spec["stem_pooled"], c["o"])
+        check(self.lib.tsb_maxpool_i8_nhwc(s_i8.data_ptr(), pooled.data_ptr(), self.batch, c["oh"], c["oh"], c["o"], 3, 2, 1,
+                                           ops._stream_ptr()))
+        return pooled
+
+    def forward(self, x):
+        """x: fp32 NCHW [batch, 3, image, image] on the device -> fp32 logits [batch, classes]."""
+        assert self.calibrated, "call calibrate() first"
+        spec = self.spec
+        x_i8 = self._forward_stem(x)
+        x_f32 = None
+        for stage in spec["stages"]:
+            for b in stage:
+                a, _ = self._conv(b["conv1"], x_i8, b["name"] + ".a", ACT_RELU)
+                bb, _ = self._conv(b["conv2"], a, b["name"] + ".b", ACT_RELU)
+                if b["projection"]:
+                    _, sc = self._conv(b["proj"], x_i8, b["name"] + ".sc", ACT_NONE, want_i8=False, want_f32=True)
+                else:
+                    sc = x_f32
+                x_i8, x_f32 = self._conv(b["conv3"], bb, b["name"] + ".y", ACT_RELU, want_i8=True, want_f32=True, residual=sc)
+        feat = self.buffers.setdefault("feat", torch.empty((self.batch, spec["features"]), dtype=torch.float32, device=self.dev))
+        logits = self.buffers.setdefault("logits", torch.empty((self.batch, spec["classes"]), dtype=torch.float32, device=self.dev))
+        P = spec["final_size"] * spec["final_size"]
+        check(self.lib.tsb_global_avgpool_f32_nhwc(x_f32.data_ptr(), feat.data_ptr(), self.batch, P, spec["features"], ops._stream_ptr()))
+        check(self.lib.tsb_inner_prod_f32(feat.data_ptr(), self.fc_w.data_ptr(), self.fc_b.data_ptr(), logits.data_ptr(), self.batch,
+                                          spec["features"], spec["classes"], ops._stream_ptr()))
+        return logits
+
+    def status(self):
+        for L in self.convs:
+            L["plan"].status()

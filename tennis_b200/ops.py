@@ -182,7 +182,7 @@ class ConvPlan:
         e.out_i8_layout = int(out_i8_layout)
         keep = None
         if requant_scales is not None:
-            keep = float_array(requant_scales)
+            keep = requant_scales if isinstance(requant_scales, ctypes.Array) else float_array(requant_scales)
             e.requant_scales_host = keep
             e.n_requant_scales = len(requant_scales)
         e.out_acc = out_acc.data_ptr() if out_acc is not None else None
