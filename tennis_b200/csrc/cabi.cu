@@ -42,14 +42,16 @@ struct tsb_conv_plan {
     int kernel;                      // resolved TSB_KERNEL_*
     const char *why_not_tc;
     tsb::tc::View view;
-    tsb::tc::Config cfg;
+    tsb::tc::Config cfg;             // orientation chosen by the geometry heuristic
+    tsb::tc::Config cfg_alt;         // the other orientation (alt_valid): taken when the epilogue is pixel-major fp32
+    int alt_valid;
     size_t off_weights, off_stage, ws_bytes;
     // state bound by set_weights / run
     const int8_t *weights_oihw;      // direct kernel reads the caller's tensor
     const void *weights_ws;          // workspace the packed weights live in
-    CUtensorMap map_b;
-    const int8_t *map_a_ptr;
-    CUtensorMap map_a;
+    CUtensorMap map_b, map_b_alt;
+    const int8_t *map_a_ptr, *map_a_alt_ptr;
+    CUtensorMap map_a, map_a_alt;
 };
 
 using namespace tsb;
@@ -166,7 +168,9 @@ int tsb_conv2d_i8_plan_create(const tsb_conv_desc *d, tsb_conv_plan **out) {
         int sms = 148, dev = 0;
         if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (sms <= 0) sms = 148;
-        p->cfg = tc::choose_config(p->view, sms);
+        p->cfg = tc::choose_config(p->view, sms, -1);
+        p->cfg_alt = tc::choose_config(p->view, sms, p->cfg.swap ? 0 : 1);
+        p->alt_valid = p->cfg_alt.swap != p->cfg.swap;
         end = p->off_weights + align256(p->view.weight_bytes);
     }
     p->off_stage = end;
@@ -178,6 +182,7 @@ int tsb_conv2d_i8_plan_create(const tsb_conv_desc *d, tsb_conv_plan **out) {
     p->weights_oihw = nullptr;
     p->weights_ws = nullptr;
     p->map_a_ptr = nullptr;
+    p->map_a_alt_ptr = nullptr;
     *out = p;
     return TSB_OK;
 }
@@ -212,6 +217,10 @@ int tsb_conv2d_i8_set_weights(tsb_conv_plan *plan, const int8_t *w_oihw, void *w
         if (st0 != TSB_OK) return st0;
         int st = tc::encode_weight_map(plan->view, plan->cfg, wp, &plan->map_b);
         if (st != TSB_OK) return st;
+        if (plan->alt_valid) {
+            st = tc::encode_weight_map(plan->view, plan->cfg_alt, wp, &plan->map_b_alt);
+            if (st != TSB_OK) return st;
+        }
     }
     return TSB_OK;
 }
@@ -296,6 +305,18 @@ int tsb_conv2d_i8_run(tsb_conv_plan *plan, const int8_t *x, int x_layout, const 
         st = repack_i8_nchw_to_nhwc(x, stage, g.N, g.C, g.H, g.W, stream);
         if (st != TSB_OK) return st;
         x_tc = stage;
+    }
+    // Pixel-major fp32 tensors (a network's residuals and block outputs) are stored coalesced when a thread owns a
+    // channel, i.e. in the swapped orientation; everything else follows the geometry heuristic.
+    const bool want_swap = (epi.out_f32 || epi.residual) && epi.f32_nhwc && !epi.out_acc;
+    const bool use_alt = plan->alt_valid && !getenv("TSB_SWAP") && (want_swap != (plan->cfg.swap != 0)) && (want_swap ? plan->cfg_alt.swap : 0);
+    if (use_alt) {
+        if (plan->map_a_alt_ptr != x_tc) {
+            st = tc::encode_activation_map(plan->view, plan->cfg_alt, x_tc, &plan->map_a_alt);
+            if (st != TSB_OK) return st;
+            plan->map_a_alt_ptr = x_tc;
+        }
+        return tc::launch_conv_tc(plan->view, plan->cfg_alt, plan->map_a_alt, plan->map_b_alt, epi, static_cast<int *>(workspace), stream);
     }
     if (plan->map_a_ptr != x_tc) {
         st = tc::encode_activation_map(plan->view, plan->cfg, x_tc, &plan->map_a);

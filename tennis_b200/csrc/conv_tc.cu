@@ -307,6 +307,42 @@ __device__ __forceinline__ bool swap_i8_run(const int (&v)[32], float dq, float 
     return true;
 }
 
+// Pixel-major fp32 tensors in the swapped orientation: for one pixel the warp's 32 lanes touch 32 consecutive floats
+// (residual read, fp32 write) and 32 consecutive int8 (requantized write): every access is one coalesced line.
+template <int ACT, bool HAS_BIAS>
+__device__ __forceinline__ bool swap_nhwc_run(const int (&v)[32], float dq, float bias, float leaky,
+                                              const float *__restrict__ res, float *__restrict__ out_f32,
+                                              int8_t *__restrict__ out_i8, bool write_i8, float rs, uint32_t O,
+                                              uint32_t out_cp, bool ch_live) {
+    float worst = 0.0f;
+#pragma unroll
+    for (int j0 = 0; j0 < 32; j0 += 8) {
+        float r[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) r[k] = (res && ch_live) ? __ldg(res + (uint32_t)(j0 + k) * O) : 0.0f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int j = j0 + k;
+            float t = __fmul_rn(__int2float_rn(v[j]), dq);
+            if (HAS_BIAS) t = __fadd_rn(t, bias);
+            if (res) t = __fadd_rn(t, r[k]);
+            if (ACT == TSB_ACT_RELU) t = fmaxf(t, 0.0f);
+            if (ACT == TSB_ACT_LEAKY_RELU) t = t > 0.0f ? t : __fmul_rn(t, leaky);
+            if (out_f32 && ch_live) out_f32[(uint32_t)j * O] = t;
+            if (out_i8) {
+                const float u = __fmul_rn(t, rs);
+                worst = max_nan(worst, fabsf(u));
+                const float mag = __fadd_rz(fabsf(u), 0.5f);
+                const float sm = __int_as_float((__float_as_int(mag) & 0x7fffffff) | (__float_as_int(u) & 0x80000000));
+                int q;
+                asm("cvt.rzi.s8.f32 %0, %1;" : "=r"(q) : "f"(sm));
+                if (write_i8) out_i8[(uint32_t)j * out_cp] = (int8_t)q;   // redone by the caller if the check below fails
+            }
+        }
+    }
+    return !__any_sync(0xffffffffu, !(worst < 2147483648.0f));
+}
+
 // run FN<activation, has_bias>(args...) for the runtime activation / bias combination
 #define TSB_EPI_DISPATCH(RESULT, FN, ...)                                                                 \
     do {                                                                                                  \
@@ -657,10 +693,18 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                                 TSB_EPI_DISPATCH(, swap_f32_run, v, my_dq, my_bias, epi.leaky, dst);
                             }
                             done = true;
-                        } else {
+                        } else if (kp.epi_mode == kEpiI8Nhwc) {
                             const float rs = epi.nscales == 1 ? epi.rq_scales[0] : epi.rq_scales[img0];
                             int8_t *dst = epi.out_i8 + (size_t)mfirst * epi.out_cp + o;
                             TSB_EPI_DISPATCH(done =, swap_i8_run, v, my_dq, my_bias, epi.leaky, rs, o < epi.out_cp, dst, (uint32_t)epi.out_cp);
+                        } else {
+                            const float rs = epi.nscales == 1 ? epi.rq_scales[0] : epi.rq_scales[img0];
+                            const size_t f_off = (size_t)mfirst * epi.O + (ch_live ? o : 0);
+                            const float *res = epi.residual ? epi.residual + f_off : nullptr;
+                            float *of = epi.out_f32 ? epi.out_f32 + f_off : nullptr;
+                            int8_t *oi = epi.out_i8 ? epi.out_i8 + (size_t)mfirst * epi.out_cp + o : nullptr;
+                            TSB_EPI_DISPATCH(done =, swap_nhwc_run, v, my_dq, my_bias, epi.leaky, res, of, oi, o < epi.out_cp, rs,
+                                             (uint32_t)epi.O, (uint32_t)epi.out_cp, ch_live);
                         }
                     }
                     if (!done) {
@@ -788,7 +832,7 @@ bool make_view(const ConvGeom &g, View *view, const char **why) {
     return true;
 }
 
-Config choose_config(const View &v, int sm_count) {
+Config choose_config(const View &v, int sm_count, int orientation) {
     const ConvGeom &g = v.g;
     Config c;
     c.bk = (g.Cp % 128 == 0) ? 128 : 64;
@@ -798,7 +842,8 @@ Config choose_config(const View &v, int sm_count) {
     // 256 (or 128) pixels on N -- it halves the MMA count of narrow layers but its epilogue (one channel per thread)
     // is dearer, so it is taken where it measured faster: multi-tap filters with at most 64 output channels.
     const char *force = getenv("TSB_SWAP");
-    c.swap = force ? (atoi(force) != 0 && g.O <= 128) : (g.O <= 64 && g.KH * g.KW >= 9 && !v.fold);
+    if (orientation >= 0) c.swap = orientation;
+    else c.swap = force ? (atoi(force) != 0 && g.O <= 128) : (g.O <= 64 && g.KH * g.KW >= 9 && !v.fold);
     if (c.swap) {
         c.ch = kBM;
         c.bn = 256;
@@ -1004,8 +1049,8 @@ int launch_conv_tc(const View &v, const Config &cfg, const CUtensorMap &map_a, c
     const bool i8_fast = !epi.out_i8 || (epi.i8_nhwc && epi.rne_limit == 0 && (epi.nscales == 1 || kp.per_sample_scale));
     if (plain && epi.out_i8 && !epi.out_f32 && i8_fast) kp.epi_mode = kEpiI8Nhwc;
     // pixel-major fp32 tensors (block outputs and residuals of a network): 16-byte accesses need O % 4 == 0
-    if (!cfg.swap && !epi.out_acc && (epi.out_f32 || epi.residual) && epi.f32_nhwc && i8_fast && g.O % 4 == 0 &&
-        ((reinterpret_cast<uintptr_t>(epi.out_f32) | reinterpret_cast<uintptr_t>(epi.residual)) & 15) == 0)
+    if (!epi.out_acc && (epi.out_f32 || epi.residual) && epi.f32_nhwc && i8_fast && (const void *)epi.residual != (const void *)epi.out_f32 &&
+        (cfg.swap || (g.O % 4 == 0 && ((reinterpret_cast<uintptr_t>(epi.out_f32) | reinterpret_cast<uintptr_t>(epi.residual)) & 15) == 0)))
         kp.epi_mode = kEpiNhwc;
 #define TSB_TC_CASE(BN_, BK_, SWAP_) \
     if (cfg.bn == BN_ && cfg.bk == BK_ && (cfg.swap != 0) == SWAP_) return launch<BN_, BK_, SWAP_>(cfg, map_a, map_b, kp, epi, stream)

@@ -39,7 +39,8 @@ struct Config {
 
 // Whether the tensor-core kernel covers this geometry; *why names the reason when it does not.
 bool make_view(const ConvGeom &g, View *view, const char **why);
-Config choose_config(const View &v, int sm_count);
+// orientation: -1 = by heuristic, 0 = normal, 1 = swapped (any number of output channels, 128 per channel tile)
+Config choose_config(const View &v, int sm_count, int orientation);
 // w_packed: [O][KH][KW][Cp] int8 of the view's geometry
 int encode_weight_map(const View &v, const Config &cfg, const int8_t *w_packed, CUtensorMap *map);
 // x: the staged activations (NHWC_PAD or folded), 16-byte aligned

@@ -69,6 +69,11 @@ def make_params(spec, seed=0):
     return dict(convs=params, fc_w=fc_w, fc_b=fc_b)
 
 
+def dequantize_scales(weight_scales, bn, input_scale):
+    """Per-channel dequantize scales of a layer: weight scale x folded BatchNorm factor / input quantize scale, in fp32."""
+    return (weight_scales * np.float32(bn) / np.float32(input_scale)).astype(np.float32)
+
+
 class QuantResNet:
     """The network on one GPU: plans, weights and activation buffers are built once; forward() launches only kernels of
     libtennis_b200.so (quantize, convolutions with fused epilogues, max pool, average pool, inner product)."""
@@ -84,7 +89,7 @@ class QuantResNet:
             plan = ops.ConvPlan(xshape, wshape, (c["pad"],) * 4, (c["stride"],) * 2, (1, 1), 0.0, _lib.KERNEL_AUTO, dev)
             plan.set_weights(torch.from_numpy(p["w"]).to(dev))
             self.convs.append(dict(spec=c, plan=plan, sw=p["sw"], bias=torch.from_numpy(p["bias"]).to(dev), dq=None,
-                                   in_scale=None, out_scale=None))
+                                   in_scale=None, out_scale=None, bn=np.float32(1.0)))
         self.fc_w = torch.from_numpy(params["fc_w"]).to(dev)
         self.fc_b = torch.from_numpy(params["fc_b"]).to(dev)
         self.buffers = {}
@@ -118,7 +123,7 @@ class QuantResNet:
     def _set_in_scale(self, idx, scale):
         L = self.convs[idx]
         L["in_scale"] = np.float32(scale)
-        L["dq"] = torch.from_numpy((L["sw"] / np.float32(scale)).astype(np.float32)).to(self.dev)
+        L["dq"] = torch.from_numpy(dequantize_scales(L["sw"], L["bn"], scale)).to(self.dev)
 
     def _set_out_scale(self, idx, scale):
         L = self.convs[idx]
@@ -137,6 +142,13 @@ class QuantResNet:
             L = self.convs[idx]
             c = L["spec"]
             f = self._f32(key + ".cal", c["oh"], c["o"])
+            # folded BatchNorm: one factor per layer that brings the convolution's own output to a maximum of 4, so
+            # that activations stay bounded through the 53 layers whatever the synthetic weight scales are
+            L["plan"].run(None if staged else x_i8, LAYOUT_STAGED if staged else LAYOUT_NHWC_PAD, L["dq"], out_f32=f,
+                          out_f32_layout=LAYOUT_NHWC_PAD)
+            m0 = float(f.abs().max())
+            L["bn"] = np.float32(4.0 / m0) if m0 > 0 else np.float32(1.0)
+            self._set_in_scale(idx, L["in_scale"])
             L["plan"].run(None if staged else x_i8, LAYOUT_STAGED if staged else LAYOUT_NHWC_PAD, L["dq"], bias=L["bias"],
                           residual=residual, activation=act, out_f32=f, out_f32_layout=LAYOUT_NHWC_PAD)
             m = float(f.abs().max())
@@ -161,6 +173,7 @@ class QuantResNet:
                 if b["projection"]:
                     ip = b["proj"]
                     self._set_in_scale(ip, cur_scale)
+                    out_scale_of(ip, x_i8, b["name"] + ".sc", ACT_NONE)   # fixes the layer's folded-BN factor
                     _, sc = self._conv(ip, x_i8, b["name"] + ".sc", ACT_NONE, want_i8=False, want_f32=True)
                 else:
                     sc = x_f32
@@ -170,7 +183,8 @@ class QuantResNet:
                 x_i8, x_f32, cur_scale = y_i8, y_f32, self.convs[i3]["out_scale"]
         self.calibrated = True
         torch.cuda.synchronize()
-        return dict(input=self.input_scale, convs=[(L["in_scale"], L["out_scale"]) for L in self.convs])
+        return dict(input=self.input_scale, convs=[(L["in_scale"], L["out_scale"]) for L in self.convs],
+                    bn=[L["bn"] for L in self.convs])
 
     def _forward_stem(self, x):
         spec = self.spec

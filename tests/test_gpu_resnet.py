@@ -24,13 +24,14 @@ def maxpool_f32(x, k=3, s=2, p=1):
 
 def reference_forward(spec, params, scales, x, chk):
     """The network as a chain of reference operators.  Returns (int8 block outputs, fp32 last block output, logits)."""
+    from tennis_b200 import nets
     n = x.shape[0]
     convs, P = spec["convs"], params["convs"]
 
     def block(idx, xq, act, residual=None, requant=True):
         c, p = convs[idx], P[idx]
         s_in, s_out = scales["convs"][idx]
-        dq = (p["sw"] / np.float32(s_in)).astype(np.float32)
+        dq = nets.dequantize_scales(p["sw"], scales["bn"][idx], s_in)
         rq = [float(s_out)] * n if requant else None
         return chk.conv_block(xq, p["w"], (c["pad"],) * 4, (c["stride"],) * 2, (1, 1), dq, p["bias"], act=act,
                               residual=residual, requant_scales=rq)
