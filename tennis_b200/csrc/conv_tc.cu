@@ -284,16 +284,17 @@ __device__ __forceinline__ void swap_f32_run(const int (&v)[32], float dq, float
 }
 
 // int8 NHWC_PAD output: for one pixel the 32 lanes of the warp hold 32 consecutive channels, so each byte store
-// instruction of the warp writes one full 32-byte sector.  All 32 pixels lie in one image (one requantize scale).
+// instruction of the warp writes one full 32-byte sector.  The first `split` pixels use rs0, the rest rs1 (the chunk
+// crosses at most one image boundary).
 // Returns false if a value needs the slow path (NaN / beyond int32); the decision is uniform over the warp.
 template <int ACT, bool HAS_BIAS>
-__device__ __forceinline__ bool swap_i8_run(const int (&v)[32], float dq, float bias, float leaky, float rs, bool write,
-                                            int8_t *__restrict__ dst, uint32_t pixel_stride) {
+__device__ __forceinline__ bool swap_i8_run(const int (&v)[32], float dq, float bias, float leaky, float rs0, float rs1,
+                                            int split, bool write, int8_t *__restrict__ dst, uint32_t pixel_stride) {
     float worst = 0.0f;
     int q[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
-        const float t = __fmul_rn(epi_value<ACT, HAS_BIAS>(v[j], dq, bias, leaky), rs);
+        const float t = __fmul_rn(epi_value<ACT, HAS_BIAS>(v[j], dq, bias, leaky), j < split ? rs0 : rs1);
         worst = max_nan(worst, fabsf(t));
         const float mag = __fadd_rz(fabsf(t), 0.5f);
         const float sm = __int_as_float((__float_as_int(mag) & 0x7fffffff) | (__float_as_int(t) & 0x80000000));
@@ -312,8 +313,8 @@ __device__ __forceinline__ bool swap_i8_run(const int (&v)[32], float dq, float 
 template <int ACT, bool HAS_BIAS>
 __device__ __forceinline__ bool swap_nhwc_run(const int (&v)[32], float dq, float bias, float leaky,
                                               const float *__restrict__ res, float *__restrict__ out_f32,
-                                              int8_t *__restrict__ out_i8, bool write_i8, float rs, uint32_t O,
-                                              uint32_t out_cp, bool ch_live) {
+                                              int8_t *__restrict__ out_i8, bool write_i8, float rs0, float rs1, int split,
+                                              uint32_t O, uint32_t out_cp, bool ch_live) {
     float worst = 0.0f;
 #pragma unroll
     for (int j0 = 0; j0 < 32; j0 += 8) {
@@ -330,7 +331,7 @@ __device__ __forceinline__ bool swap_nhwc_run(const int (&v)[32], float dq, floa
             if (ACT == TSB_ACT_LEAKY_RELU) t = t > 0.0f ? t : __fmul_rn(t, leaky);
             if (out_f32 && ch_live) out_f32[(uint32_t)j * O] = t;
             if (out_i8) {
-                const float u = __fmul_rn(t, rs);
+                const float u = __fmul_rn(t, j < split ? rs0 : rs1);
                 worst = max_nan(worst, fabsf(u));
                 const float mag = __fadd_rz(fabsf(u), 0.5f);
                 const float sm = __int_as_float((__float_as_int(mag) & 0x7fffffff) | (__float_as_int(u) & 0x80000000));
@@ -681,12 +682,18 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     if (mfirst >= kp.M_total) break;                     // uniform over the warp
                     const int npix = min(32, kp.M_total - mfirst);
                     const int img0 = mfirst / kp.P, p0 = mfirst - img0 * kp.P;
-                    const bool one_image = npix == 32 && p0 + 32 <= kp.P;
+                    const int split = kp.P - p0;                           // pixels j >= split belong to the next image
+                    const bool one_image = npix == 32 && split >= 32;
+                    // pixel-major outputs are linear in the pixel index: an image boundary inside the chunk only switches
+                    // the requantize scale (at most once when an image has at least 32 pixels)
+                    const bool linear_ok = npix == 32 && kp.P >= 32;
                     bool done = false;
-                    if (one_image && kp.epi_mode != kEpiGeneric) {
+                    if (kp.epi_mode != kEpiGeneric && (kp.epi_mode == kEpiF32Nchw ? one_image : linear_ok)) {
                         int v[32];
                         tmem_ld32(taddr0 + (uint32_t)col0, v);
                         tmem_ld_wait();
+                        const float rs0 = epi.nscales == 1 ? epi.rq_scales[0] : epi.rq_scales[img0];
+                        const float rs1 = epi.nscales == 1 ? rs0 : epi.rq_scales[min(img0 + 1, epi.nscales - 1)];
                         if (kp.epi_mode == kEpiF32Nchw) {
                             if (ch_live) {
                                 float *dst = epi.out_f32 + ((size_t)(img0 * epi.O + o) * (size_t)epi.P + (size_t)p0);
@@ -694,16 +701,14 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                             }
                             done = true;
                         } else if (kp.epi_mode == kEpiI8Nhwc) {
-                            const float rs = epi.nscales == 1 ? epi.rq_scales[0] : epi.rq_scales[img0];
                             int8_t *dst = epi.out_i8 + (size_t)mfirst * epi.out_cp + o;
-                            TSB_EPI_DISPATCH(done =, swap_i8_run, v, my_dq, my_bias, epi.leaky, rs, o < epi.out_cp, dst, (uint32_t)epi.out_cp);
+                            TSB_EPI_DISPATCH(done =, swap_i8_run, v, my_dq, my_bias, epi.leaky, rs0, rs1, split, o < epi.out_cp, dst, (uint32_t)epi.out_cp);
                         } else {
-                            const float rs = epi.nscales == 1 ? epi.rq_scales[0] : epi.rq_scales[img0];
                             const size_t f_off = (size_t)mfirst * epi.O + (ch_live ? o : 0);
                             const float *res = epi.residual ? epi.residual + f_off : nullptr;
                             float *of = epi.out_f32 ? epi.out_f32 + f_off : nullptr;
                             int8_t *oi = epi.out_i8 ? epi.out_i8 + (size_t)mfirst * epi.out_cp + o : nullptr;
-                            TSB_EPI_DISPATCH(done =, swap_nhwc_run, v, my_dq, my_bias, epi.leaky, res, of, oi, o < epi.out_cp, rs,
+                            TSB_EPI_DISPATCH(done =, swap_nhwc_run, v, my_dq, my_bias, epi.leaky, res, of, oi, o < epi.out_cp, rs0, rs1, split,
                                              (uint32_t)epi.O, (uint32_t)epi.out_cp, ch_live);
                         }
                     }

@@ -158,6 +158,33 @@ def test_both_mma_orientations(checker, port, monkeypatch, case, swap):
     assert np.array_equal(got["i8"], want)
 
 
+@pytest.mark.parametrize("swap", [None, "0", "1"])
+@pytest.mark.parametrize("case", [
+    (5, 64, 7, 7, 256),      # 49 pixels per image: most 32-pixel chunks cross an image boundary
+    (3, 128, 14, 14, 160),   # 196 pixels per image
+    (4, 64, 5, 5, 64),       # fewer than 32 pixels per image: several boundaries in one chunk
+])
+def test_residual_tail_pixel_major_with_per_sample_scales(checker, port, monkeypatch, case, swap):
+    """1x1 convolution + residual + relu with pixel-major fp32 in/out and a fused requantize whose scale differs from
+    sample to sample: a chunk of 32 pixels that crosses an image boundary must switch scales at the boundary."""
+    if swap is None:
+        monkeypatch.delenv("TSB_SWAP", raising=False)
+    else:
+        monkeypatch.setenv("TSB_SWAP", swap)
+    N, C, H, W, O = case
+    rng = np.random.default_rng(N * 31 + O)
+    x = rng.integers(-128, 128, size=(N, C, H, W), dtype=np.int8)
+    w = rng.integers(-127, 128, size=(O, C, 1, 1), dtype=np.int8)
+    dq = rng.uniform(0.001, 0.01, size=O).astype(np.float32)
+    bias = (rng.standard_normal(O) * 0.1).astype(np.float32)
+    residual = rng.standard_normal((N, O, H, W)).astype(np.float32)
+    rq = rng.uniform(0.5, 4.0, size=N).astype(np.float32)
+    check_case(checker, port, x, w, (0, 0, 0, 0), (1, 1), (1, 1), dq, bias, "relu", 0.0, 0.0, 2, want_acc=False,
+               x_layout="nhwc", residual=residual, rq=rq, f32_layout="nhwc", i8_layout="nhwc")
+    check_case(checker, port, x, w, (0, 0, 0, 0), (1, 1), (1, 1), dq, bias, "none", 0.0, 0.0, 2, want_acc=False,
+               x_layout="nhwc", rq=rq, f32_layout="nchw", i8_layout="nhwc")
+
+
 @pytest.mark.parametrize("case", [
     (2, 3, 15, 17, 6, 7, 7, (3, 3, 3, 3), (2, 2), (1, 1), 0.0),
     (1, 5, 6, 6, 3, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1), 3.0),
