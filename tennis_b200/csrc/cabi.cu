@@ -316,14 +316,14 @@ int tsb_conv2d_i8_run(tsb_conv_plan *plan, const int8_t *x, int x_layout, const 
             if (st != TSB_OK) return st;
             plan->map_a_alt_ptr = x_tc;
         }
-        return tc::launch_conv_tc(plan->view, plan->cfg_alt, plan->map_a_alt, plan->map_b_alt, epi, static_cast<int *>(workspace), stream);
+        return tc::launch_conv_tc(plan->view, plan->cfg_alt, plan->map_a_alt, plan->map_b_alt, x_tc, epi, static_cast<int *>(workspace), stream);
     }
     if (plan->map_a_ptr != x_tc) {
         st = tc::encode_activation_map(plan->view, plan->cfg, x_tc, &plan->map_a);
         if (st != TSB_OK) return st;
         plan->map_a_ptr = x_tc;
     }
-    return tc::launch_conv_tc(plan->view, plan->cfg, plan->map_a, plan->map_b, epi, static_cast<int *>(workspace), stream);
+    return tc::launch_conv_tc(plan->view, plan->cfg, plan->map_a, plan->map_b, x_tc, epi, static_cast<int *>(workspace), stream);
 }
 
 int tsb_conv2d_i8_status(tsb_conv_plan *plan, void *workspace, void *stream_) {

@@ -75,6 +75,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
+
+// plain (untiled) bulk copy global -> shared; both addresses and the size are multiples of 16 bytes
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 :: "r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
 __device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c, int w,
                                                    int h, int n, uint16_t off_w, uint16_t off_h) {
     asm volatile(
@@ -129,6 +135,19 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr) {
     d |= (uint64_t)1 << 46;                       // descriptor version of this architecture
     d |= layout << 61;
     return d;
+}
+
+// Descriptor of a pixel operand whose rows OVERLAP in shared memory (raw-row mode): no swizzle, K-major.  In that canonical
+// layout row r, 16-byte K chunk j sits at (r % 8) * 16 + (r / 8) * SBO + j * LBO; with SBO = 128 and LBO = 16 that is
+// r * 16 + j * 16: pixel r reads the bytes that start 16 bytes after pixel r-1's, which is exactly a convolution window
+// sliding by one pixel stride over one staged image row.
+__device__ __forceinline__ uint64_t smem_desc_sliding(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)(16 >> 4) << 16;               // leading byte offset: next 16-byte chunk along K
+    d |= (uint64_t)(128 >> 4) << 32;              // stride byte offset: next group of 8 rows
+    d |= (uint64_t)1 << 46;                       // descriptor version of this architecture
+    return d;                                     // layout 0: no swizzle
 }
 
 // Instruction descriptor: int32 accumulate, signed 8-bit A and B, both K-major, M = 128, N = BN.
@@ -369,6 +388,23 @@ __device__ __forceinline__ int tmem_ld1(uint32_t taddr) {
 // ---------------------------------------------------------------------------------------------------------
 // kernel
 // ---------------------------------------------------------------------------------------------------------
+// Division by a divisor known at launch time as multiply-high, add and shift (round-up method for 32-bit unsigned
+// numerators below 2^31): the role threads divide once or twice per tile and a hardware-less 32-bit division costs them
+// more than a hundred cycles each.
+struct FastDiv {
+    uint32_t mul = 0, shr = 0;
+    FastDiv() = default;
+    explicit FastDiv(uint32_t d) {
+        uint32_t l = 0;
+        while ((1ull << l) < d) ++l;
+        shr = l;
+        mul = (uint32_t)((((1ull << 32) * ((1ull << l) - d)) / d) + 1);
+    }
+    __device__ __forceinline__ int div(int n) const {
+        return (int)(((uint64_t)__umulhi((uint32_t)n, mul) + (uint32_t)n) >> shr);
+    }
+};
+
 struct KernelParams {
     int M_total;     // N*OH*OW
     int OW, P;       // P = OH*OW
@@ -376,6 +412,7 @@ struct KernelParams {
     int sh, sw, dh, dw, pad_t, pad_l;
     int Cp;          // channels of the staged input per filter tap
     int num_m_tiles, num_n_tiles;   // pixel tiles, channel tiles
+    FastDiv d_P, d_OW, d_m_tiles, d_n_tiles, d_segs, d_OH, d_dh;   // dividers by P, OW, num_m_tiles, num_n_tiles, rows_segs, rows_OH, dh
     int per_sample_scale;  // requantize: scale index = image index
     int epi_mode;          // kEpi*: which epilogue code path full 32-column chunks take
     int a_tiled;           // activations are a plain [M][Cp] matrix (1x1, stride 1, no padding): 2-D tile loads
@@ -385,6 +422,13 @@ struct KernelParams {
     int b_resident;        // all K blocks of this CTA's weight tile stay in shared memory; only activations stream
     uint32_t b_off;        // offset of the resident weights
     uint32_t bar_off;      // offset of the mbarriers; tensor-memory slot, abort flag and epilogue tables follow
+    // raw-row mode (rows_segs > 0): a tile is up to 128 consecutive pixels of ONE output row; per filter row the
+    // producer copies the staged bytes under those pixels once, and the MMA reads them through a sliding descriptor
+    int rows_segs;         // tiles per output row (0: mode off)
+    int rows_OH, rows_H;   // output rows per image, staged input rows per image
+    uint32_t rows_bytes;   // bytes copied per tile and filter row
+    long long rows_stride_h, rows_stride_n;   // bytes between staged rows / images
+    const int8_t *rows_x;  // the folded staging
     int *status;     // device word: 0 ok, else the code of the wait that ran out
     unsigned long long *trace;  // optional timeline of CTA 0 (debugging aid): 8 stamps per tile, 32 tiles
 };
@@ -398,6 +442,13 @@ __device__ __forceinline__ unsigned long long global_ns() {
     do {                                                                                         \
         if (kp.trace && blockIdx.x == 0 && (tile_index) < 32) kp.trace[(tile_index) * 8 + (slot)] = global_ns(); \
     } while (0)
+
+// raw-row mode: the filter rows kh_lo..kh_hi that meet an input row for output row oh (a contiguous, non-empty range)
+__device__ __forceinline__ void rows_span(const KernelParams &kp, int oh, int &kh_lo, int &kh_hi) {
+    const int top = oh * kp.sh - kp.pad_t;                 // input row under filter row 0
+    kh_lo = top >= 0 ? 0 : kp.d_dh.div(-top + kp.dh - 1);
+    kh_hi = min(kp.KH - 1, kp.d_dh.div(kp.rows_H - 1 - top));
+}
 
 constexpr int kMaxStages = 24;
 constexpr uint32_t kMaxDynamicSmem = 227 * 1024;
@@ -448,10 +499,10 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     auto decode = [&](int i, int &m_tile, int &n_tile) {   // m_tile: pixel tile, n_tile: channel tile
         if (kp.b_resident) {
             const int t = tile_lo + i;
-            n_tile = t / kp.num_m_tiles; m_tile = t - n_tile * kp.num_m_tiles;
+            n_tile = kp.d_m_tiles.div(t); m_tile = t - n_tile * kp.num_m_tiles;
         } else {
             const int t = (int)blockIdx.x + i * (int)gridDim.x;
-            m_tile = t / kp.num_n_tiles; n_tile = t - m_tile * kp.num_n_tiles;
+            m_tile = kp.d_n_tiles.div(t); n_tile = t - m_tile * kp.num_n_tiles;
         }
     };
 
@@ -485,8 +536,8 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 int m_tile, n_tile;
                 decode(i, m_tile, n_tile);
                 const int m0 = m_tile * PIX;
-                const int img = m0 / kp.P, rem = m0 - img * kp.P;
-                const int oh = rem / kp.OW, ow = rem - oh * kp.OW;
+                const int img = kp.d_P.div(m0), rem = m0 - img * kp.P;
+                const int oh = kp.d_OW.div(rem), ow = rem - oh * kp.OW;
                 const int wc = ow * kp.sw - kp.pad_l, hc = oh * kp.sh - kp.pad_t;
                 if (kp.b_resident && n_tile != cur_n) {
                     // (re)load the whole weight tile; wait until the MMAs that read the previous one are done
@@ -500,6 +551,24 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     cur_n = n_tile;
                     ++w_loads;
                 }
+                if (kp.rows_segs) {
+                    // one copy per tile: the staged bytes from the first to the last input row the filter meets
+                    const int row_id = kp.d_segs.div(m_tile), seg = m_tile - row_id * kp.rows_segs;
+                    const int r_img = kp.d_OH.div(row_id), r_oh = row_id - r_img * kp.rows_OH;
+                    int kh_lo, kh_hi;
+                    rows_span(kp, r_oh, kh_lo, kh_hi);
+                    if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) {
+                        if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 1); }
+                        break;
+                    }
+                    const int ih_lo = r_oh * kp.sh - kp.pad_t + kh_lo * kp.dh;
+                    const uint32_t bytes = (uint32_t)((kh_hi - kh_lo) * kp.dh) * (uint32_t)kp.rows_stride_h + kp.rows_bytes;
+                    mbar_arrive_expect_tx(bar_full + 8 * stage, bytes);
+                    bulk_load(base + stage * kp.stage_bytes,
+                              kp.rows_x + r_img * kp.rows_stride_n + ih_lo * kp.rows_stride_h + (long long)seg * (PIX * 16),
+                              bytes, bar_full + 8 * stage);
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                } else
                 for (int kh = 0; kh < kp.KH && ok; ++kh)
                     for (int kw = 0; kw < kp.KW && ok; ++kw)
                         for (int cb = 0; cb < kp.Cp; cb += BK) {
@@ -549,6 +618,30 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 tc_fence_after();
                 TSB_TRACE(local, 2);
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                uint32_t accumulate = 0;
+                if (!SWAP && kp.rows_segs) {
+                    const int row_id = kp.d_segs.div(m_tile);
+                    int kh_lo, kh_hi;
+                    rows_span(kp, row_id - kp.d_OH.div(row_id) * kp.rows_OH, kh_lo, kh_hi);
+                    if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
+                        if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 3); }
+                        break;
+                    }
+                    tc_fence_after();
+                    TSB_TRACE(local, 3);
+                    const uint32_t sp = base + stage * kp.stage_bytes;
+                    for (int kh = kh_lo; kh <= kh_hi; ++kh) {
+                        const uint64_t da = smem_desc_sliding(sp + (uint32_t)((kh - kh_lo) * kp.dh) * (uint32_t)kp.rows_stride_h);
+                        const uint64_t db = smem_desc<BK>(w_res + (uint32_t)kh * kWgtBytes);
+#pragma unroll
+                        for (int k = 0; k < BK / 32; ++k) {
+                            mma_i8(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, accumulate);
+                            accumulate = 1u;
+                        }
+                    }
+                    tc_commit(bar_empty + 8 * stage);
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                } else
                 for (int it = 0; it < k_iters; ++it) {
                     if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
                         if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 3); }
@@ -563,8 +656,10 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     const uint64_t da = SWAP ? dw : dp, db = SWAP ? dp : dw;
 #pragma unroll
                     for (int k = 0; k < BK / 32; ++k) {
-                        // +32 bytes along K inside the swizzle span = +2 in the descriptor's 16-byte address units
-                        mma_i8(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (it | k) != 0 ? 1u : 0u);
+                        // +32 bytes along K = +2 in the descriptor's 16-byte address units (inside the swizzle span, or
+                        // along the raw row)
+                        mma_i8(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, accumulate);
+                        accumulate = 1u;
                     }
                     tc_commit(bar_empty + 8 * stage);  // frees the stage once these MMAs have read it
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -621,9 +716,14 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             if (et == 0) TSB_TRACE(local, 5);
             const uint32_t taddr0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
             if (!SWAP) {
-                const int m = m_tile * PIX + row;
-                const bool live = m < kp.M_total;
-                const int img = live ? m / kp.P : 0;
+                int m = m_tile * PIX + row;
+                bool live = m < kp.M_total;
+                if (kp.rows_segs) {
+                    const int row_id = kp.d_segs.div(m_tile), ow = (m_tile - row_id * kp.rows_segs) * PIX + row;
+                    live = ow < kp.OW;
+                    m = row_id * kp.OW + ow;
+                }
+                const int img = live ? kp.d_P.div(m) : 0;
                 const int p = live ? m - img * kp.P : 0;
 #pragma unroll 1
                 for (int c = part; c < kChunks; c += 4) {
@@ -681,7 +781,7 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     const int mfirst = m_tile * PIX + col0;              // first pixel of this chunk
                     if (mfirst >= kp.M_total) break;                     // uniform over the warp
                     const int npix = min(32, kp.M_total - mfirst);
-                    const int img0 = mfirst / kp.P, p0 = mfirst - img0 * kp.P;
+                    const int img0 = kp.d_P.div(mfirst), p0 = mfirst - img0 * kp.P;
                     const int split = kp.P - p0;                           // pixels j >= split belong to the next image
                     const bool one_image = npix == 32 && split >= 32;
                     // pixel-major outputs are linear in the pixel index: an image boundary inside the chunk only switches
@@ -810,6 +910,26 @@ bool make_view(const ConvGeom &g, View *view, const char **why) {
         v.stride_h = (uint64_t)v.Wp * cpix;
         v.stride_n = v.stride_h * g.H;
         v.stage_bytes = (size_t)v.stride_n * g.N;
+        // raw-row mode: pixel stride of exactly one 16-byte unit, every output row meets at least one input row, and
+        // output rows long enough to fill most of a 128-pixel tile (TSB_ROWS=1/0 forces it on/off where it is possible)
+        bool rows_ok = v.stride_w == 16 && (size_t)g.KH * bkf * std::min(round_up(g.O, 64), 256) <= 96 * 1024 &&
+                       (size_t)(g.KH - 1) * g.dh * v.stride_h + 4096 <= 40 * 1024;
+        for (int oh = 0; oh < g.OH && rows_ok; ++oh) {
+            bool any = false;
+            for (int kh = 0; kh < g.KH; ++kh) {
+                const int ih = oh * g.sh - g.pad_t + kh * g.dh;
+                any = any || (ih >= 0 && ih < g.H);
+            }
+            rows_ok = any;
+        }
+        const int segs = ceil_div(g.OW, kBM);
+        const char *force_rows = getenv("TSB_ROWS");
+        const bool rows_pay = (double)g.OW / (double)(segs * kBM) >= 0.75;
+        if (rows_ok && (force_rows ? atoi(force_rows) != 0 : rows_pay)) {
+            v.rows = 1;
+            v.rows_segs = segs;
+            v.stage_bytes += (size_t)kBM * 16 + 256;   // the copy under the last tile of the last row runs past the row's end
+        }
     } else {
         if (g.Cp % 64 != 0) { *why = "channel padding is not a multiple of 64"; return false; }
         v.stride_w = (uint64_t)g.Cp;
@@ -847,7 +967,8 @@ Config choose_config(const View &v, int sm_count, int orientation) {
     // 256 (or 128) pixels on N -- it halves the MMA count of narrow layers but its epilogue (one channel per thread)
     // is dearer, so it is taken where it measured faster: multi-tap filters with at most 64 output channels.
     const char *force = getenv("TSB_SWAP");
-    if (orientation >= 0) c.swap = orientation;
+    if (v.rows) c.swap = 0;
+    else if (orientation >= 0) c.swap = orientation;
     else c.swap = force ? (atoi(force) != 0 && g.O <= 128) : (g.O <= 64 && g.KH * g.KW >= 9 && !v.fold);
     if (c.swap) {
         c.ch = kBM;
@@ -871,16 +992,20 @@ Config choose_config(const View &v, int sm_count, int orientation) {
         c.pix = kBM;
         c.ch = c.bn;
     }
-    c.num_m_tiles = (int)ceil_div64(M, c.pix);
+    c.num_m_tiles = v.rows ? g.N * g.OH * v.rows_segs : (int)ceil_div64(M, c.pix);
     c.num_n_tiles = ceil_div(g.O, c.ch);
     const int64_t tiles = (int64_t)c.num_m_tiles * c.num_n_tiles;
     c.grid = (int)(tiles < sm_count ? tiles : sm_count);
     // shared-memory plan: keep the CTA's whole weight tile resident when it is small enough to leave room for
     // at least four activation stages; otherwise stream activations and weights together
-    const uint32_t p_bytes = (uint32_t)c.pix * c.bk, w_bytes = (uint32_t)c.ch * c.bk;
+    // raw-row mode stages, per tile, the KH staged image rows under 128 sliding windows (127 pixel strides of 16 bytes
+    // plus one window in the last row)
+    const uint32_t p_bytes = v.rows ? (uint32_t)round_up((g.KH - 1) * g.dh * (int)v.stride_h + (kBM - 1) * 16 + c.bk, 128)
+                                    : (uint32_t)c.pix * c.bk;
+    const uint32_t w_bytes = (uint32_t)c.ch * c.bk;
     const uint32_t k_iters = (uint32_t)g.KH * g.KW * (g.Cp / c.bk);
     const uint32_t w_total = k_iters * w_bytes;
-    const bool want_resident = !getenv("TSB_NO_RESIDENT_B") && tiles > c.grid;  // pays off only when a CTA runs several tiles
+    const bool want_resident = v.rows || (!getenv("TSB_NO_RESIDENT_B") && tiles > c.grid);  // pays off only when a CTA runs several tiles
     if (want_resident && w_total <= 128 * 1024 && (kSmemBudget - w_total) / p_bytes >= 4) {
         c.b_resident = 1;
         c.stage_bytes = p_bytes;
@@ -1030,7 +1155,7 @@ int stage_folded(const View &v, const int8_t *x, int x_nhwc, int8_t *staged, cud
 }
 
 int launch_conv_tc(const View &v, const Config &cfg, const CUtensorMap &map_a, const CUtensorMap &map_b,
-                   const EpiParams &epi, int *status_word, cudaStream_t stream) {
+                   const int8_t *x_staged, const EpiParams &epi, int *status_word, cudaStream_t stream) {
     const ConvGeom &g = v.g;
     KernelParams kp;
     kp.M_total = g.N * g.OH * g.OW;
@@ -1041,12 +1166,25 @@ int launch_conv_tc(const View &v, const Config &cfg, const CUtensorMap &map_a, c
     kp.Cp = g.Cp;
     kp.num_m_tiles = cfg.num_m_tiles;
     kp.num_n_tiles = cfg.num_n_tiles;
+    kp.d_P = FastDiv((uint32_t)kp.P); kp.d_OW = FastDiv((uint32_t)kp.OW);
+    kp.d_m_tiles = FastDiv((uint32_t)cfg.num_m_tiles); kp.d_n_tiles = FastDiv((uint32_t)cfg.num_n_tiles);
+    kp.d_segs = FastDiv((uint32_t)std::max(1, v.rows_segs)); kp.d_OH = FastDiv((uint32_t)g.OH); kp.d_dh = FastDiv((uint32_t)g.dh);
     kp.per_sample_scale = (epi.nscales > 1 && epi.nscales == g.N && epi.group_len == (uint32_t)(g.O * g.OH * g.OW)) ? 1 : 0;
     kp.status = status_word;
     kp.trace = g_trace;
     kp.a_tiled = v.a_tiled;
     kp.stages = cfg.stages; kp.stage_bytes = cfg.stage_bytes; kp.b_resident = cfg.b_resident;
     kp.b_off = cfg.b_off; kp.bar_off = cfg.bar_off;
+    kp.rows_segs = 0; kp.rows_OH = g.OH; kp.rows_H = g.H; kp.rows_bytes = 0; kp.rows_stride_h = 0; kp.rows_stride_n = 0;
+    kp.rows_x = nullptr;
+    if (v.rows) {
+        if (cfg.swap || !cfg.b_resident || !x_staged) return fail(TSB_ERR_UNSUPPORTED, "raw-row mode needs the normal orientation and resident weights");
+        kp.rows_segs = v.rows_segs;
+        kp.rows_bytes = (uint32_t)round_up((kBM - 1) * 16 + cfg.bk, 16);
+        kp.rows_stride_h = (long long)v.stride_h;
+        kp.rows_stride_n = (long long)v.stride_n;
+        kp.rows_x = x_staged;
+    }
     if (cfg.dyn_smem > kMaxDynamicSmem) return fail(TSB_ERR_UNSUPPORTED, "shared-memory plan of %u bytes does not fit", cfg.dyn_smem);
     const bool plain = !epi.out_acc && !epi.residual;
     kp.epi_mode = kEpiGeneric;

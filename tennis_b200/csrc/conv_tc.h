@@ -14,10 +14,16 @@ namespace tc {
 //            w + pad_left and zeros elsewhere.  The KW taps of one filter row are then one contiguous run of bytes,
 //            so the kernel sees a KH x 1 filter over `g.Cp` = round_up(((KW-1)*dw+1)*cpix, 64) virtual channels whose
 //            pixel stride is stride_w*cpix bytes (the tensor map's rows overlap); `g` is that virtual geometry.
+//  rows == 1 (a fold view whose pixel stride is exactly 16 bytes and whose output rows are long): "raw-row" mode.  A tile
+//            is up to 128 consecutive pixels of one output row; per filter row the kernel copies the staged bytes under
+//            those pixels ONCE (about 2 KB instead of 128 windows of 64 B) and the MMA reads the overlapping windows
+//            straight out of that copy through a no-swizzle descriptor whose rows are 16 bytes apart.
 struct View {
     ConvGeom g;          // geometry handed to the kernel and the tensor maps
     ConvGeom real;       // geometry of the operator
     int fold = 0;
+    int rows = 0;        // raw-row mode
+    int rows_segs = 0;   // tiles per output row in raw-row mode
     int a_tiled = 0;     // 1x1 / stride 1 / no padding: the activations are the [M][Cp] matrix itself, loaded as 2-D tiles
     int cpix = 0;        // bytes per pixel of the folded staging
     int Wp = 0;          // pixels per row of the folded staging
@@ -52,8 +58,9 @@ int stage_folded(const View &v, const int8_t *x, int x_nhwc, int8_t *staged, cud
 // Debugging aid: CTA 0 of later launches writes 8 time stamps (ns) per tile for its first 32 tiles into this device
 // buffer of 256 x 8 bytes; null switches it off.
 void set_trace_buffer(unsigned long long *device_buffer);
+// x_staged: the activations the map_a was encoded for (read directly in raw-row mode)
 int launch_conv_tc(const View &v, const Config &cfg, const CUtensorMap &map_a, const CUtensorMap &map_b,
-                   const EpiParams &epi, int *status_word, cudaStream_t stream);
+                   const int8_t *x_staged, const EpiParams &epi, int *status_word, cudaStream_t stream);
 
 }  // namespace tc
 }  // namespace tsb

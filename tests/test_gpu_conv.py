@@ -158,6 +158,37 @@ def test_both_mma_orientations(checker, port, monkeypatch, case, swap):
     assert np.array_equal(got["i8"], want)
 
 
+@pytest.mark.parametrize("case", [
+    (2, 3, 20, 235, 64, 7, 7, (3, 3, 3, 3), (2, 2), (1, 1)),     # stem shape, one tile per output row (115 of 128 pixels)
+    (1, 3, 12, 300, 32, 7, 7, (3, 3, 3, 3), (2, 2), (1, 1)),     # two tiles per output row
+    (2, 16, 9, 140, 48, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1)),     # 16 bytes per pixel, stride 1
+    (1, 8, 10, 70, 24, 5, 5, (2, 2, 2, 2), (2, 2), (1, 1)),      # short rows
+    (1, 4, 11, 64, 16, 3, 3, (0, 2, 1, 0), (2, 2), (2, 1)),      # asymmetric padding, dilated filter rows
+    (3, 3, 33, 35, 16, 7, 7, (3, 3, 3, 3), (2, 2), (1, 1)),
+    (1, 3, 6, 260, 300, 3, 3, (1, 1, 1, 1), (2, 2), (1, 1)),     # two channel tiles: resident weights are reloaded
+    (1, 5, 9, 40, 8, 3, 3, (2, 2, 1, 1), (1, 1), (1, 2)),        # two padding rows above, dilated taps inside a row
+])
+def test_raw_row_mode(checker, port, monkeypatch, case):
+    """Few input channels with a pixel stride of 16 staged bytes: the kernel copies each staged image row once per
+    tile and the MMA reads the overlapping windows through a sliding descriptor.  Forced on here for short rows too."""
+    monkeypatch.setenv("TSB_ROWS", "1")
+    N, C, H, W, O, KH, KW, pad, stride, dil = case
+    rng = np.random.default_rng(N * 77 + C + O + W)
+    x = rng.integers(-128, 128, size=(N, C, H, W), dtype=np.int8)
+    w = rng.integers(-127, 128, size=(O, C, KH, KW), dtype=np.int8)
+    dq = rng.uniform(0.001, 0.01, size=O).astype(np.float32)
+    bias = (rng.standard_normal(O) * 0.1).astype(np.float32)
+    got = check_case(checker, port, x, w, pad, stride, dil, dq, bias, "relu", 0.0, 0.0, 2)
+    assert got["kernel"] == 2
+    rq = np.full(N, 0.7, dtype=np.float32)
+    check_case(checker, port, x, w, pad, stride, dil, dq, None, "leaky_relu", 0.1, 0.0, 2, want_acc=False,
+               x_layout="nhwc", rq=rq, i8_layout="nhwc", f32_layout="nhwc")
+    got = run_gpu(x, w, pad, stride, dil, dq, bias, "relu", 0.0, 0.0, 2, x_layout="nhwc", rq=rq, i8_layout="nhwc",
+                  want_acc=False, want_f32=False)
+    want = checker.quantize(checker.relu(checker.add_bias(checker.conv2d_quantized(x, w, pad, stride, dil, dq), bias)), rq)
+    assert np.array_equal(got["i8"], want)
+
+
 @pytest.mark.parametrize("swap", [None, "0", "1"])
 @pytest.mark.parametrize("case", [
     (5, 64, 7, 7, 256),      # 49 pixels per image: most 32-pixel chunks cross an image boundary
