@@ -8,6 +8,7 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <string>
 
 #include "../../include/tennis_b200.h"
@@ -47,6 +48,33 @@ inline int cuda_fail(cudaError_t e, const char *what) {
         cudaError_t e__ = cudaGetLastError();                           \
         if (e__ != cudaSuccess) return ::tsb::cuda_fail(e__, name);     \
     } while (0)
+
+// Launch with programmatic stream serialization: the grid may start while the previous kernel of the stream is still
+// draining, so its prologue overlaps that kernel's tail.  Only for kernels whose every thread executes pdl_sync() before
+// its first access to global memory.  TSB_NO_PDL=1 switches back to plain launches.
+#ifdef __CUDACC__
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args &&...args) {
+    static const bool off = getenv("TSB_NO_PDL") != nullptr;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = off ? 0 : 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+// Waits until the kernels this grid depends on have completed and their writes are visible, then lets the next grid of
+// the stream start its own prologue.
+__device__ __forceinline__ void pdl_sync() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+#endif
 
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }

@@ -524,6 +524,7 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_sync();   // everything above touched only shared and tensor memory
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -879,7 +880,7 @@ int launch(const Config &cfg, const CUtensorMap &ma, const CUtensorMap &mb, cons
         TSB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynamicSmem));
         configured = true;
     }
-    kernel<<<cfg.grid, kThreads, cfg.dyn_smem, stream>>>(ma, mb, kp, epi);
+    TSB_CUDA(launch_pdl(kernel, dim3(cfg.grid), dim3(kThreads), cfg.dyn_smem, stream, ma, mb, kp, epi));
     TSB_LAUNCHED("conv_i8_tc_kernel");
     return TSB_OK;
 }

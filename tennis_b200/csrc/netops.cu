@@ -16,6 +16,7 @@ constexpr int kThreads = 256;
 __global__ void __launch_bounds__(kThreads)
 maxpool_i8_nhwc_kernel(const int8_t *__restrict__ x, int8_t *__restrict__ y, int N, int H, int W, int Cp, int OH, int OW,
                        int K, int S, int pad) {
+    pdl_sync();
     const int units = Cp / 16;
     const int64_t total = (int64_t)N * OH * OW * units;
     for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < total; i += (int64_t)gridDim.x * kThreads) {
@@ -48,6 +49,7 @@ maxpool_i8_nhwc_kernel(const int8_t *__restrict__ x, int8_t *__restrict__ y, int
 // reference's average pooling does (sum / count).
 __global__ void __launch_bounds__(kThreads)
 global_avgpool_f32_nhwc_kernel(const float *__restrict__ x, float *__restrict__ y, int N, int P, int C) {
+    pdl_sync();
     const int64_t total = (int64_t)N * C;
     for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < total; i += (int64_t)gridDim.x * kThreads) {
         const int c = (int)(i % C), n = (int)(i / C);
@@ -61,6 +63,7 @@ global_avgpool_f32_nhwc_kernel(const float *__restrict__ x, float *__restrict__ 
 __global__ void __launch_bounds__(kThreads)
 inner_prod_f32_kernel(const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
                       float *__restrict__ y, int N, int K, int O) {
+    pdl_sync();
     const int warps_per_block = kThreads / 32;
     const int lane = threadIdx.x & 31;
     const int64_t total = (int64_t)N * O;
@@ -92,7 +95,7 @@ int maxpool_i8_nhwc(const int8_t *x, int8_t *y, int n, int h, int w, int channel
     if (oh < 1 || ow < 1) return fail(TSB_ERR_INVALID_ARGUMENT, "maxpool: empty output");
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) % 16) return fail(TSB_ERR_INVALID_ARGUMENT, "maxpool: tensors must be 16-byte aligned");
     const int64_t items = (int64_t)n * oh * ow * (cp / 16);
-    maxpool_i8_nhwc_kernel<<<grid_for(items, kThreads), kThreads, 0, stream>>>(x, y, n, h, w, cp, oh, ow, k, stride, pad);
+    TSB_CUDA(launch_pdl(maxpool_i8_nhwc_kernel, dim3(grid_for(items, kThreads)), dim3(kThreads), 0, stream, x, y, n, h, w, cp, oh, ow, k, stride, pad));
     TSB_LAUNCHED("maxpool_i8_nhwc_kernel");
     return TSB_OK;
 }
@@ -100,7 +103,7 @@ int maxpool_i8_nhwc(const int8_t *x, int8_t *y, int n, int h, int w, int channel
 int global_avgpool_f32_nhwc(const float *x, float *y, int n, int pixels, int channels, cudaStream_t stream) {
     if (!x || !y) return fail(TSB_ERR_INVALID_ARGUMENT, "global_avgpool: null pointer");
     if (n < 1 || pixels < 1 || channels < 1) return fail(TSB_ERR_INVALID_ARGUMENT, "global_avgpool: bad shape");
-    global_avgpool_f32_nhwc_kernel<<<grid_for((int64_t)n * channels, kThreads), kThreads, 0, stream>>>(x, y, n, pixels, channels);
+    TSB_CUDA(launch_pdl(global_avgpool_f32_nhwc_kernel, dim3(grid_for((int64_t)n * channels, kThreads)), dim3(kThreads), 0, stream, x, y, n, pixels, channels));
     TSB_LAUNCHED("global_avgpool_f32_nhwc_kernel");
     return TSB_OK;
 }
@@ -108,7 +111,7 @@ int global_avgpool_f32_nhwc(const float *x, float *y, int n, int pixels, int cha
 int inner_prod_f32(const float *x, const float *w, const float *bias, float *y, int n, int k, int o, cudaStream_t stream) {
     if (!x || !w || !y) return fail(TSB_ERR_INVALID_ARGUMENT, "inner_prod: null pointer");
     if (n < 1 || k < 1 || o < 1) return fail(TSB_ERR_INVALID_ARGUMENT, "inner_prod: bad shape");
-    inner_prod_f32_kernel<<<grid_for((int64_t)n * o, kThreads / 32), kThreads, 0, stream>>>(x, w, bias, y, n, k, o);
+    TSB_CUDA(launch_pdl(inner_prod_f32_kernel, dim3(grid_for((int64_t)n * o, kThreads / 32)), dim3(kThreads), 0, stream, x, w, bias, y, n, k, o));
     TSB_LAUNCHED("inner_prod_f32_kernel");
     return TSB_OK;
 }

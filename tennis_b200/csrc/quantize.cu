@@ -182,6 +182,7 @@ struct StageDesc {
 __global__ void __launch_bounds__(kThreads)
 quantize_stage_kernel(const float *__restrict__ x, int8_t *__restrict__ y, StageDesc d, uint32_t units, QuantRule rule,
                       ScaleArg scales) {
+    pdl_sync();
     const uint32_t rne_limit = (uint32_t)rule.rne_limit;
     const uint32_t group_len = (uint32_t)rule.group_len;
     const uint32_t HW = (uint32_t)(d.H * d.W);
@@ -362,7 +363,7 @@ int quantize_stage(const float *x, int8_t *y, int n, int c, int h, int w, int fo
     const int64_t units = folded ? (int64_t)n * h * (wp * cpix / 16)
                                  : ceil_div64((int64_t)n * h * w, 32) * 32 * (d.Cp / 16);
     if (units > (int64_t)UINT32_MAX) return fail(TSB_ERR_UNSUPPORTED, "quantize_stage: tensor too large");
-    quantize_stage_kernel<<<grid_for(units), kThreads, 0, stream>>>(x, y, d, (uint32_t)units, rule, arg);
+    TSB_CUDA(launch_pdl(quantize_stage_kernel, dim3(grid_for(units)), dim3(kThreads), 0, stream, x, y, d, (uint32_t)units, rule, arg));
     TSB_LAUNCHED("quantize_stage_kernel");
     if (tmp) TSB_CUDA(cudaFreeAsync(tmp, stream));
     return TSB_OK;
