@@ -201,6 +201,18 @@ TSB_API int tsb_conv2d_quantized_host(tsb_conv_plan *plan, const float *x_f32_ho
                               const float *bias_host, int activation, float leaky_scale, float *out_f32_host,
                               void *device_scratch, size_t device_scratch_bytes, int weights_resident,
                               void *stream);
+/*
+ * The same without the final wait: every copy and kernel is enqueued on `stream` and the call returns; the result in
+ * `out_f32_host` is valid once the caller has synchronised that stream.  Host buffers should be pinned, otherwise the
+ * copies are not asynchronous.  Calls on different streams (each plan with its own scratch) overlap: one layer's
+ * upload runs under another's kernels and a third's download.  No counterpart in the reference, whose tensors
+ * synchronise on every host view (src/memory/memory_gpu.cpp:106-108).
+ */
+TSB_API int tsb_conv2d_quantized_host_async(tsb_conv_plan *plan, const float *x_f32_host, const float *quantize_scales_host,
+                              int n_quantize_scales, const int8_t *w_host, const float *dequantize_scales_host,
+                              const float *bias_host, int activation, float leaky_scale, float *out_f32_host,
+                              void *device_scratch, size_t device_scratch_bytes, int weights_resident,
+                              void *stream);
 
 /* Standalone fp32 epilogue operators on NCHW tensors (what follows conv2d_quantized when nothing is fused). */
 TSB_API int tsb_add_bias_f32_nchw(const float *x, float *y, int n, int c, int hw, const float *bias, void *stream);

@@ -68,6 +68,7 @@ SYMBOLS = {
     "tsb_conv2d_i8_status": (_i, [_vp, _vp, _vp]),
     "tsb_conv2d_host_scratch_bytes": (_sz, [_vp]),
     "tsb_conv2d_quantized_host": (_i, [_vp, _vp, _fp, _i, _vp, _vp, _vp, _i, _f, _vp, _vp, _sz, _i, _vp]),
+    "tsb_conv2d_quantized_host_async": (_i, [_vp, _vp, _fp, _i, _vp, _vp, _vp, _i, _f, _vp, _vp, _sz, _i, _vp]),
     "tsb_add_bias_f32_nchw": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp]),
     "tsb_relu_f32": (_i, [_vp, _vp, _i64, _vp]),
     "tsb_leaky_relu_f32": (_i, [_vp, _vp, _i64, _f, _vp]),

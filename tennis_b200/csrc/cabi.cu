@@ -358,11 +358,10 @@ HostScratch host_layout(const tsb_conv_plan *p) {
 
 size_t tsb_conv2d_host_scratch_bytes(const tsb_conv_plan *plan) { return plan ? host_layout(plan).total : 0; }
 
-int tsb_conv2d_quantized_host(tsb_conv_plan *plan, const float *x_host, const float *qscales_host, int nq,
-                              const int8_t *w_host, const float *dq_host, const float *bias_host, int activation,
-                              float leaky, float *out_host, void *scratch, size_t scratch_bytes, int weights_resident,
-                              void *stream_) {
-    cudaStream_t stream = (cudaStream_t)stream_;
+static int conv2d_quantized_host(tsb_conv_plan *plan, const float *x_host, const float *qscales_host, int nq,
+                                 const int8_t *w_host, const float *dq_host, const float *bias_host, int activation,
+                                 float leaky, float *out_host, void *scratch, size_t scratch_bytes, int weights_resident,
+                                 cudaStream_t stream, bool wait) {
     if (!plan || !x_host || !qscales_host || !out_host || !scratch) return fail(TSB_ERR_INVALID_ARGUMENT, "conv2d_quantized_host: null pointer");
     if (!weights_resident && (!w_host || !dq_host)) return fail(TSB_ERR_INVALID_ARGUMENT, "conv2d_quantized_host: weights and dequantize scales are required");
     const HostScratch L = host_layout(plan);
@@ -399,8 +398,24 @@ int tsb_conv2d_quantized_host(tsb_conv_plan *plan, const float *x_host, const fl
     st = tsb_conv2d_i8_run(plan, nullptr, TSB_LAYOUT_STAGED, &e, ws, plan->ws_bytes, stream);
     if (st != TSB_OK) return st;
     TSB_CUDA(cudaMemcpyAsync(out_host, d_out, (size_t)g.N * g.O * g.OH * g.OW * 4, cudaMemcpyDeviceToHost, stream));
-    TSB_CUDA(cudaStreamSynchronize(stream));
+    if (wait) TSB_CUDA(cudaStreamSynchronize(stream));
     return TSB_OK;
+}
+
+int tsb_conv2d_quantized_host(tsb_conv_plan *plan, const float *x_host, const float *qscales_host, int nq,
+                              const int8_t *w_host, const float *dq_host, const float *bias_host, int activation,
+                              float leaky, float *out_host, void *scratch, size_t scratch_bytes, int weights_resident,
+                              void *stream) {
+    return conv2d_quantized_host(plan, x_host, qscales_host, nq, w_host, dq_host, bias_host, activation, leaky, out_host,
+                                 scratch, scratch_bytes, weights_resident, (cudaStream_t)stream, true);
+}
+
+int tsb_conv2d_quantized_host_async(tsb_conv_plan *plan, const float *x_host, const float *qscales_host, int nq,
+                                    const int8_t *w_host, const float *dq_host, const float *bias_host, int activation,
+                                    float leaky, float *out_host, void *scratch, size_t scratch_bytes,
+                                    int weights_resident, void *stream) {
+    return conv2d_quantized_host(plan, x_host, qscales_host, nq, w_host, dq_host, bias_host, activation, leaky, out_host,
+                                 scratch, scratch_bytes, weights_resident, (cudaStream_t)stream, false);
 }
 
 }  // extern "C"

@@ -345,6 +345,36 @@ def test_host_buffer_entry_point(checker):
         assert same_bits(out, want)
 
 
+def test_host_buffer_entry_point_async_on_two_streams(checker):
+    """Two layers enqueued with the non-waiting host call on two streams; results are read after both streams are
+    synchronised."""
+    from tennis_b200 import _lib, ops, workloads
+    lib = _lib.load()
+    jobs = []
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    for i, (c, o, k) in enumerate([(64, 48, 3), (128, 96, 1)]):
+        layer = workloads.conv_layer("t", 3, c, 12, 12, o, k, 1, k // 2)
+        d = workloads.make_layer_data(layer, seed=5 + i)
+        plan = ops.ConvPlan((3, c, 12, 12), (o, c, k, k), (k // 2,) * 4, (1, 1), (1, 1))
+        nbytes = lib.tsb_conv2d_host_scratch_bytes(plan.handle)
+        jobs.append(dict(d=d, plan=plan, nbytes=nbytes, k=k, scratch=torch.empty(nbytes, dtype=torch.uint8, device="cuda"),
+                         x=torch.from_numpy(d["x"]).pin_memory(), out=torch.zeros(plan.out_shape, dtype=torch.float32).pin_memory(),
+                         scales=_lib.float_array([float(d["qscale"])] * 3)))
+    torch.cuda.synchronize()
+    for j, st in zip(jobs, streams):
+        d = j["d"]
+        _lib.check(lib.tsb_conv2d_quantized_host_async(
+            j["plan"].handle, j["x"].data_ptr(), j["scales"], 3, d["w"].ctypes.data, d["dq"].ctypes.data, d["bias"].ctypes.data,
+            _lib.ACT_RELU, 0.0, j["out"].data_ptr(), j["scratch"].data_ptr(), j["nbytes"], 0, st.cuda_stream))
+    for st in streams:
+        st.synchronize()
+    for j in jobs:
+        d = j["d"]
+        xq = checker.quantize(d["x"], [float(d["qscale"])] * 3)
+        want = checker.conv_block(xq, d["w"], (j["k"] // 2,) * 4, (1, 1), (1, 1), d["dq"], d["bias"], act="relu")
+        assert same_bits(j["out"].numpy(), want)
+
+
 def test_run_without_weights_is_rejected():
     from tennis_b200 import _lib, ops
     plan = ops.ConvPlan((1, 64, 8, 8), (64, 64, 3, 3), (1, 1, 1, 1), (1, 1), (1, 1))
