@@ -81,6 +81,11 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  :: "r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c, int w, int h, int n) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n) : "memory");
+}
 __device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c, int w,
                                                    int h, int n, uint16_t off_w, uint16_t off_h) {
     asm volatile(
@@ -133,6 +138,21 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr) {
     d |= (uint64_t)1 << 16;                       // leading byte offset: unused for swizzled K-major
     d |= (uint64_t)((8 * BK) >> 4) << 32;         // stride byte offset
     d |= (uint64_t)1 << 46;                       // descriptor version of this architecture
+    d |= layout << 61;
+    return d;
+}
+
+// The same with a run-time stride between 8-row groups and a start that need not be 1024-byte aligned (patch mode).
+// The swizzle is a function of the absolute shared-memory address (measured: any 128-byte-aligned start and any group
+// stride read back what a tensor-map copy with the same swizzle wrote; the base-offset field stays 0).
+template <int BK>
+__device__ __forceinline__ uint64_t smem_desc_strided(uint32_t saddr, uint32_t group_stride_bytes) {
+    constexpr uint64_t layout = BK == 128 ? 2 : (BK == 64 ? 4 : 6);
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(group_stride_bytes >> 4) << 32;
+    d |= (uint64_t)1 << 46;
     d |= layout << 61;
     return d;
 }
@@ -199,12 +219,12 @@ __device__ __forceinline__ float max_nan(float a, float b) {
 }
 
 // ---- fast paths, normal orientation: the thread owns one PIXEL (its tensor-memory lane) and 32 consecutive channels
-template <int ACT, bool HAS_BIAS>
-__device__ __forceinline__ void store_f32_nchw_t(const int (&v)[32], const float *__restrict__ dq,
+template <int ACT, bool HAS_BIAS, int W>
+__device__ __forceinline__ void store_f32_nchw_t(const int (&v)[W], const float *__restrict__ dq,
                                                  const float *__restrict__ bias, float leaky, float *__restrict__ dst,
                                                  uint32_t stride) {
 #pragma unroll
-    for (int j4 = 0; j4 < 8; ++j4) {
+    for (int j4 = 0; j4 < W / 4; ++j4) {
         const float4 d4 = *reinterpret_cast<const float4 *>(dq + 4 * j4);
         const float4 b4 = *reinterpret_cast<const float4 *>(bias + 4 * j4);
         dst[(uint32_t)(4 * j4 + 0) * stride] = epi_value<ACT, HAS_BIAS>(v[4 * j4 + 0], d4.x, b4.x, leaky);
@@ -217,14 +237,14 @@ __device__ __forceinline__ void store_f32_nchw_t(const int (&v)[32], const float
 // Requantized int8 output.  Returns false when a scaled value was NaN or beyond the int32 range -- those quantize to
 // -128 in the reference (x86 integer-indefinite), which the saturating fast path does not reproduce; the caller
 // then redoes the chunk element by element.
-template <int ACT, bool HAS_BIAS>
-__device__ __forceinline__ bool store_i8_nhwc_t(const int (&v)[32], const float *__restrict__ dq,
+template <int ACT, bool HAS_BIAS, int W>
+__device__ __forceinline__ bool store_i8_nhwc_t(const int (&v)[W], const float *__restrict__ dq,
                                                 const float *__restrict__ bias, float leaky, float rs,
                                                 int8_t *__restrict__ dst) {
-    uint32_t q[8];
+    uint32_t q[W / 4];
     float worst = 0.0f;
 #pragma unroll
-    for (int j4 = 0; j4 < 8; ++j4) {
+    for (int j4 = 0; j4 < W / 4; ++j4) {
         const float4 d4 = *reinterpret_cast<const float4 *>(dq + 4 * j4);
         const float4 b4 = *reinterpret_cast<const float4 *>(bias + 4 * j4);
         const float t0 = __fmul_rn(epi_value<ACT, HAS_BIAS>(v[4 * j4 + 0], d4.x, b4.x, leaky), rs);
@@ -235,22 +255,22 @@ __device__ __forceinline__ bool store_i8_nhwc_t(const int (&v)[32], const float 
         q[j4] = pack_sat_s8(half_away_s32(t0), half_away_s32(t1), half_away_s32(t2), half_away_s32(t3));
     }
     if (!(worst < 2147483648.0f)) return false;
-    *reinterpret_cast<int4 *>(dst) = make_int4(q[0], q[1], q[2], q[3]);
-    *reinterpret_cast<int4 *>(dst + 16) = make_int4(q[4], q[5], q[6], q[7]);
+#pragma unroll
+    for (int h = 0; h < W / 16; ++h) *reinterpret_cast<int4 *>(dst + 16 * h) = make_int4(q[4 * h], q[4 * h + 1], q[4 * h + 2], q[4 * h + 3]);
     return true;
 }
 
 // Block-output epilogue of a residual network: v = act(dq*acc + bias + residual); fp32 copy for the next residual and
 // int8 copy for the next convolution.  Each pointer may be null.  All three tensors are pixel-major, so the thread's 32
 // channels are contiguous: 16-byte loads and stores.
-template <int ACT, bool HAS_BIAS>
-__device__ __forceinline__ bool store_nhwc_t(const int (&v)[32], const float *__restrict__ dq, const float *__restrict__ bias,
+template <int ACT, bool HAS_BIAS, int W>
+__device__ __forceinline__ bool store_nhwc_t(const int (&v)[W], const float *__restrict__ dq, const float *__restrict__ bias,
                                              float leaky, const float *__restrict__ res, float *__restrict__ out_f32,
                                              int8_t *__restrict__ out_i8, float rs) {
-    uint32_t q[8];
+    uint32_t q[W / 4];
     float worst = 0.0f;
 #pragma unroll
-    for (int j4 = 0; j4 < 8; ++j4) {
+    for (int j4 = 0; j4 < W / 4; ++j4) {
         const float4 d4 = *reinterpret_cast<const float4 *>(dq + 4 * j4);
         const float4 b4 = *reinterpret_cast<const float4 *>(bias + 4 * j4);
         float4 r4 = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -275,8 +295,8 @@ __device__ __forceinline__ bool store_nhwc_t(const int (&v)[32], const float *__
     }
     if (out_i8) {
         if (!(worst < 2147483648.0f)) return false;
-        *reinterpret_cast<int4 *>(out_i8) = make_int4(q[0], q[1], q[2], q[3]);
-        *reinterpret_cast<int4 *>(out_i8 + 16) = make_int4(q[4], q[5], q[6], q[7]);
+#pragma unroll
+        for (int h = 0; h < W / 16; ++h) *reinterpret_cast<int4 *>(out_i8 + 16 * h) = make_int4(q[4 * h], q[4 * h + 1], q[4 * h + 2], q[4 * h + 3]);
     }
     return true;
 }
@@ -327,6 +347,58 @@ __device__ __forceinline__ bool swap_i8_run(const int (&v)[32], float dq, float 
     return true;
 }
 
+// Patch mode, swapped orientation: the 32 accumulators of a chunk are 4 tile rows of 8 pixels of one channel.
+// rows_live / cols_live say how much of that 4 x 8 block lies inside the image (uniform over the warp).
+template <int ACT, bool HAS_BIAS>
+__device__ __forceinline__ bool patch_i8_run(const int (&v)[32], float dq, float bias, float leaky, float rs, bool write,
+                                             int8_t *__restrict__ dst, uint32_t pixel_stride, uint32_t row_stride,
+                                             int rows_live, int cols_live) {
+    float worst = 0.0f;
+    int q[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        const float t = __fmul_rn(epi_value<ACT, HAS_BIAS>(v[j], dq, bias, leaky), rs);
+        const bool live = (j >> 3) < rows_live && (j & 7) < cols_live;
+        worst = max_nan(worst, live ? fabsf(t) : 0.0f);
+        const float mag = __fadd_rz(fabsf(t), 0.5f);
+        const float sm = __int_as_float((__float_as_int(mag) & 0x7fffffff) | (__float_as_int(t) & 0x80000000));
+        asm("cvt.rzi.s8.f32 %0, %1;" : "=r"(q[j]) : "f"(sm));
+    }
+    if (__any_sync(0xffffffffu, !(worst < 2147483648.0f))) return false;
+    if (write) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if ((j >> 3) < rows_live && (j & 7) < cols_live) dst[(uint32_t)(j >> 3) * row_stride + (uint32_t)(j & 7) * pixel_stride] = (int8_t)q[j];
+    }
+    return true;
+}
+template <int ACT, bool HAS_BIAS>
+__device__ __forceinline__ void patch_f32_run(const int (&v)[32], float dq, float bias, float leaky, float *__restrict__ dst,
+                                              uint32_t row_stride, int rows_live, int cols_live) {
+    // fp32 NCHW: each tile row is 8 consecutive floats of one channel plane
+    const bool vec = cols_live == 8 && ((reinterpret_cast<uintptr_t>(dst) | ((uintptr_t)row_stride * 4)) & 15) == 0;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        if (r >= rows_live) break;
+        float *row = dst + (size_t)r * row_stride;
+        if (vec) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                float4 o;
+                o.x = epi_value<ACT, HAS_BIAS>(v[8 * r + 4 * h + 0], dq, bias, leaky);
+                o.y = epi_value<ACT, HAS_BIAS>(v[8 * r + 4 * h + 1], dq, bias, leaky);
+                o.z = epi_value<ACT, HAS_BIAS>(v[8 * r + 4 * h + 2], dq, bias, leaky);
+                o.w = epi_value<ACT, HAS_BIAS>(v[8 * r + 4 * h + 3], dq, bias, leaky);
+                reinterpret_cast<float4 *>(row)[h] = o;
+            }
+        } else {
+#pragma unroll
+            for (int cidx = 0; cidx < 8; ++cidx)
+                if (cidx < cols_live) row[cidx] = epi_value<ACT, HAS_BIAS>(v[8 * r + cidx], dq, bias, leaky);
+        }
+    }
+}
+
 // Pixel-major fp32 tensors in the swapped orientation: for one pixel the warp's 32 lanes touch 32 consecutive floats
 // (residual read, fp32 write) and 32 consecutive int8 (requantized write): every access is one coalesced line.
 template <int ACT, bool HAS_BIAS>
@@ -364,6 +436,18 @@ __device__ __forceinline__ bool swap_nhwc_run(const int (&v)[32], float dq, floa
 }
 
 // run FN<activation, has_bias>(args...) for the runtime activation / bias combination
+#define TSB_EPI_DISPATCH_W(RESULT, FN, W_, ...)                                                           \
+    do {                                                                                                  \
+        if (has_bias) {                                                                                   \
+            if (act == TSB_ACT_RELU) RESULT FN<TSB_ACT_RELU, true, W_>(__VA_ARGS__);                      \
+            else if (act == TSB_ACT_LEAKY_RELU) RESULT FN<TSB_ACT_LEAKY_RELU, true, W_>(__VA_ARGS__);     \
+            else RESULT FN<TSB_ACT_NONE, true, W_>(__VA_ARGS__);                                          \
+        } else {                                                                                          \
+            if (act == TSB_ACT_RELU) RESULT FN<TSB_ACT_RELU, false, W_>(__VA_ARGS__);                     \
+            else if (act == TSB_ACT_LEAKY_RELU) RESULT FN<TSB_ACT_LEAKY_RELU, false, W_>(__VA_ARGS__);    \
+            else RESULT FN<TSB_ACT_NONE, false, W_>(__VA_ARGS__);                                         \
+        }                                                                                                 \
+    } while (0)
 #define TSB_EPI_DISPATCH(RESULT, FN, ...)                                                                 \
     do {                                                                                                  \
         if (has_bias) {                                                                                   \
@@ -376,6 +460,16 @@ __device__ __forceinline__ bool swap_nhwc_run(const int (&v)[32], float dq, floa
             else RESULT FN<TSB_ACT_NONE, false>(__VA_ARGS__);                                             \
         }                                                                                                 \
     } while (0)
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ldw(uint32_t taddr, int (&v)[32]) { tmem_ld32(taddr, v); }
+__device__ __forceinline__ void tmem_ldw(uint32_t taddr, int (&v)[16]) { tmem_ld16(taddr, v); }
 
 // one tensor-memory column of this warp's 32 lanes (used by the rolled, element-by-element paths)
 __device__ __forceinline__ int tmem_ld1(uint32_t taddr) {
@@ -429,6 +523,15 @@ struct KernelParams {
     uint32_t rows_bytes;   // bytes copied per tile and filter row
     long long rows_stride_h, rows_stride_n;   // bytes between staged rows / images
     const int8_t *rows_x;  // the folded staging
+    // patch mode (patch != 0; stride-1 filters with several taps): a tile is 8 pixels wide and PIX/8 pixels high; ONE
+    // tiled tensor-map load per channel block brings the input patch under it, halo included, and every filter tap reads
+    // its shifted window out of that patch through a descriptor whose start is moved by whole pixels
+    int patch;
+    int patch_tiles_w, patch_tiles_hw;        // tiles across an image, tiles per image
+    int patch_pw;                             // patch width in pixels: 8 + (KW-1)*dw
+    uint32_t patch_bytes;                     // bytes of one patch (one channel block)
+    int OH;
+    FastDiv d_tiles_w, d_tiles_hw;
     int *status;     // device word: 0 ok, else the code of the wait that ran out
     unsigned long long *trace;  // optional timeline of CTA 0 (debugging aid): 8 stamps per tile, 32 tiles
 };
@@ -450,6 +553,7 @@ __device__ __forceinline__ void rows_span(const KernelParams &kp, int oh, int &k
     kh_hi = min(kp.KH - 1, kp.d_dh.div(kp.rows_H - 1 - top));
 }
 
+constexpr int kModeGeneral = 0, kModeRows = 1, kModePatch = 2;
 constexpr int kMaxStages = 24;
 constexpr uint32_t kMaxDynamicSmem = 227 * 1024;
 
@@ -461,7 +565,9 @@ __host__ __device__ constexpr uint32_t num_barriers(int stages) { return 2u * (u
 // beyond O zero-filled by the tensor map) and the pixel tile is B (N = BN pixels).  An MMA instruction takes the same
 // 128 cycles whatever its N, so layers with at most 128 output channels run swapped: N = 256 pixels fills the
 // instruction where N = O would leave it half or three-quarters empty.
-template <int BN, int BK, bool SWAP>
+// MODE: how activations reach shared memory -- kModeGeneral (im2col or plain 2-D tile loads), kModeRows (raw-row), kModePatch.
+// A compile-time parameter: the role loops of each mode stay short and keep their registers.
+template <int BN, int BK, bool SWAP, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ KernelParams kp, const __grid_constant__ EpiParams epi) {
@@ -552,7 +658,21 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     cur_n = n_tile;
                     ++w_loads;
                 }
-                if (kp.rows_segs) {
+                if (MODE == kModePatch) {
+                    const int p_img = kp.d_tiles_hw.div(m_tile), p_rem = m_tile - p_img * kp.patch_tiles_hw;
+                    const int p_r = kp.d_tiles_w.div(p_rem), p_c = p_rem - p_r * kp.patch_tiles_w;
+                    const int h0 = p_r * (PIX / 8) - kp.pad_t, w0 = p_c * 8 - kp.pad_l;
+                    for (int cb = 0; cb < kp.Cp && ok; cb += BK) {
+                        if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) {
+                            if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 1); }
+                            ok = false;
+                            break;
+                        }
+                        mbar_arrive_expect_tx(bar_full + 8 * stage, kp.patch_bytes);
+                        tma_load_4d(base + stage * kp.stage_bytes, &map_a, bar_full + 8 * stage, cb, w0, h0, p_img);
+                        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                    }
+                } else if (MODE == kModeRows) {
                     // one copy per tile: the staged bytes from the first to the last input row the filter meets
                     const int row_id = kp.d_segs.div(m_tile), seg = m_tile - row_id * kp.rows_segs;
                     const int r_img = kp.d_OH.div(row_id), r_oh = row_id - r_img * kp.rows_OH;
@@ -620,7 +740,34 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 TSB_TRACE(local, 2);
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
                 uint32_t accumulate = 0;
-                if (!SWAP && kp.rows_segs) {
+                if (MODE == kModePatch) {
+                    const int n_cb = kp.Cp / BK;
+                    for (int cbi = 0; cbi < n_cb && ok; ++cbi) {
+                        if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
+                            if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 3); }
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        if (cbi == 0) TSB_TRACE(local, 3);
+                        const uint32_t sp = base + stage * kp.stage_bytes;
+                        const uint32_t group_stride = (uint32_t)kp.patch_pw * BK;   // next tile row = next patch row
+                        for (int kh = 0; kh < kp.KH; ++kh)
+                            for (int kw = 0; kw < kp.KW; ++kw) {
+                                const uint32_t shift = (uint32_t)(kh * kp.dh * kp.patch_pw + kw * kp.dw) * BK;
+                                const uint64_t dp = smem_desc_strided<BK>(sp + shift, group_stride);
+                                const uint64_t dw = smem_desc<BK>(w_res + (uint32_t)((kh * kp.KW + kw) * n_cb + cbi) * kWgtBytes);
+                                const uint64_t da = SWAP ? dw : dp, db = SWAP ? dp : dw;
+#pragma unroll
+                                for (int k = 0; k < BK / 32; ++k) {
+                                    mma_i8(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, accumulate);
+                                    accumulate = 1u;
+                                }
+                            }
+                        tc_commit(bar_empty + 8 * stage);
+                        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                    }
+                } else if (!SWAP && MODE == kModeRows) {
                     const int row_id = kp.d_segs.div(m_tile);
                     int kh_lo, kh_hi;
                     rows_span(kp, row_id - kp.d_OH.div(row_id) * kp.rows_OH, kh_lo, kh_hi);
@@ -683,6 +830,9 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         const int et = threadIdx.x - 64;         // 0..511
         const int row = quarter * 32 + lane;     // tensor-memory lane this thread reads
         constexpr int kChunks = BN / 32;
+        // normal orientation: columns a warp takes per step; 16 when the tile has only 64 channels, so that all four warps
+        // of a lane quarter have work
+        constexpr int CW = BN >= 128 ? 32 : 16;
         const bool has_bias = epi.bias != nullptr;
         const int act = epi.activation;
         for (int local = 0; local < my_tiles; ++local) {
@@ -719,33 +869,40 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             if (!SWAP) {
                 int m = m_tile * PIX + row;
                 bool live = m < kp.M_total;
-                if (kp.rows_segs) {
+                if (MODE == kModeRows) {
                     const int row_id = kp.d_segs.div(m_tile), ow = (m_tile - row_id * kp.rows_segs) * PIX + row;
                     live = ow < kp.OW;
                     m = row_id * kp.OW + ow;
                 }
+                if (MODE == kModePatch) {
+                    const int p_img = kp.d_tiles_hw.div(m_tile), p_rem = m_tile - p_img * kp.patch_tiles_hw;
+                    const int p_r = kp.d_tiles_w.div(p_rem), p_c = p_rem - p_r * kp.patch_tiles_w;
+                    const int oh = p_r * (PIX / 8) + (row >> 3), ow = p_c * 8 + (row & 7);
+                    live = oh < kp.OH && ow < kp.OW;
+                    m = p_img * kp.P + oh * kp.OW + ow;
+                }
                 const int img = live ? kp.d_P.div(m) : 0;
                 const int p = live ? m - img * kp.P : 0;
 #pragma unroll 1
-                for (int c = part; c < kChunks; c += 4) {
-                    const int col0 = c * 32;
-                    const bool full = o_base + col0 + 32 <= epi.O;
+                for (int c = part; c < BN / CW; c += 4) {
+                    const int col0 = c * CW;
+                    const bool full = o_base + col0 + CW <= epi.O;
                     bool done = false;
                     if (full && kp.epi_mode != kEpiGeneric) {
-                        int v[32];
-                        tmem_ld32(taddr0 + (uint32_t)col0, v);
+                        int v[CW];
+                        tmem_ldw(taddr0 + (uint32_t)col0, v);
                         tmem_ld_wait();
                         if (kp.epi_mode == kEpiF32Nchw) {
                             if (live) {
                                 float *dst = epi.out_f32 + ((size_t)(img * epi.O + o_base + col0) * (size_t)epi.P + (size_t)p);
-                                TSB_EPI_DISPATCH(, store_f32_nchw_t, v, t_dq + col0, t_bias + col0, epi.leaky, dst, (uint32_t)epi.P);
+                                TSB_EPI_DISPATCH_W(, store_f32_nchw_t, CW, v, t_dq + col0, t_bias + col0, epi.leaky, dst, (uint32_t)epi.P);
                             }
                             done = true;
                         } else if (kp.epi_mode == kEpiI8Nhwc) {
                             const float rs = epi.nscales == 1 ? epi.rq_scales[0] : epi.rq_scales[img];
                             int8_t *dst = epi.out_i8 + (size_t)m * epi.out_cp + o_base + col0;
                             bool fine = true;
-                            if (live) TSB_EPI_DISPATCH(fine =, store_i8_nhwc_t, v, t_dq + col0, t_bias + col0, epi.leaky, rs, dst);
+                            if (live) TSB_EPI_DISPATCH_W(fine =, store_i8_nhwc_t, CW, v, t_dq + col0, t_bias + col0, epi.leaky, rs, dst);
                             done = !__any_sync(0xffffffffu, !fine);
                         } else {
                             const float rs = epi.nscales == 1 ? epi.rq_scales[0] : epi.rq_scales[img];
@@ -754,13 +911,13 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                             float *of = epi.out_f32 ? epi.out_f32 + f_off : nullptr;
                             int8_t *oi = epi.out_i8 ? epi.out_i8 + (size_t)m * epi.out_cp + o_base + col0 : nullptr;
                             bool fine = true;
-                            if (live) TSB_EPI_DISPATCH(fine =, store_nhwc_t, v, t_dq + col0, t_bias + col0, epi.leaky, res, of, oi, rs);
+                            if (live) TSB_EPI_DISPATCH_W(fine =, store_nhwc_t, CW, v, t_dq + col0, t_bias + col0, epi.leaky, res, of, oi, rs);
                             done = !__any_sync(0xffffffffu, !fine);
                         }
                     }
                     if (!done) {
                         // element by element: any combination of outputs, residual, partial channel chunks
-                        for (int j = 0; j < 32; ++j) {
+                        for (int j = 0; j < CW; ++j) {
                             const int a = tmem_ld1(taddr0 + (uint32_t)(col0 + j));
                             const int o = o_base + col0 + j;
                             if (!live) continue;
@@ -776,9 +933,52 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 const bool quarter_live = o_base + quarter * 32 < max(epi.O, epi.out_i8 && epi.i8_nhwc ? epi.out_cp : 0);
                 const float my_dq = ch_live ? epi.dq[o] : 0.0f;
                 const float my_bias = (ch_live && epi.bias) ? epi.bias[o] : 0.0f;
+                int p_img = 0, p_r = 0, p_c = 0;
+                if (MODE == kModePatch) {
+                    p_img = kp.d_tiles_hw.div(m_tile);
+                    const int p_rem = m_tile - p_img * kp.patch_tiles_hw;
+                    p_r = kp.d_tiles_w.div(p_rem);
+                    p_c = p_rem - p_r * kp.patch_tiles_w;
+                }
 #pragma unroll 1
                 for (int c = part; c < kChunks && quarter_live; c += 4) {
                     const int col0 = c * 32;
+                    if (MODE == kModePatch) {
+                        // this chunk: tile rows col0/8 .. col0/8+3, 8 pixels each
+                        const int oh0 = p_r * (PIX / 8) + (col0 >> 3), ow0 = p_c * 8;
+                        if (oh0 >= kp.OH) break;                         // uniform over the warp; later chunks lie lower still
+                        const int rows_live = min(4, kp.OH - oh0), cols_live = min(8, kp.OW - ow0);
+                        const int p0 = oh0 * kp.OW + ow0;
+                        bool done = false;
+                        if (kp.epi_mode == kEpiF32Nchw || kp.epi_mode == kEpiI8Nhwc) {
+                            int v[32];
+                            tmem_ld32(taddr0 + (uint32_t)col0, v);
+                            tmem_ld_wait();
+                            if (kp.epi_mode == kEpiF32Nchw) {
+                                if (ch_live) {
+                                    float *dst = epi.out_f32 + ((size_t)(p_img * epi.O + o) * (size_t)epi.P + (size_t)p0);
+                                    TSB_EPI_DISPATCH(, patch_f32_run, v, my_dq, my_bias, epi.leaky, dst, (uint32_t)kp.OW, rows_live, cols_live);
+                                }
+                                done = true;
+                            } else {
+                                const float rs = epi.nscales == 1 ? epi.rq_scales[0] : epi.rq_scales[p_img];
+                                int8_t *dst = epi.out_i8 + ((size_t)p_img * epi.P + p0) * epi.out_cp + o;
+                                TSB_EPI_DISPATCH(done =, patch_i8_run, v, my_dq, my_bias, epi.leaky, rs, o < epi.out_cp, dst, (uint32_t)epi.out_cp,
+                                                 (uint32_t)(kp.OW * epi.out_cp), rows_live, cols_live);
+                            }
+                        }
+                        if (!done) {
+                            for (int j = 0; j < 32; ++j) {
+                                if ((j >> 3) >= rows_live || (j & 7) >= cols_live) continue;   // uniform over the warp
+                                const int a = tmem_ld1(taddr0 + (uint32_t)(col0 + j));
+                                const int pj = p0 + (j >> 3) * kp.OW + (j & 7);
+                                if (ch_live) epilogue_store_one(epi, p_img, o, pj, a);
+                                else if (epi.out_i8 && epi.i8_nhwc && o < epi.out_cp)
+                                    epi.out_i8[((size_t)p_img * epi.P + pj) * epi.out_cp + o] = 0;
+                            }
+                        }
+                        continue;
+                    }
                     const int mfirst = m_tile * PIX + col0;              // first pixel of this chunk
                     if (mfirst >= kp.M_total) break;                     // uniform over the warp
                     const int npix = min(32, kp.M_total - mfirst);
@@ -871,11 +1071,11 @@ CUtensorMapSwizzle swizzle_for(int bk) {
     return bk == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (bk == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
 }
 
-template <int BN, int BK, bool SWAP>
+template <int BN, int BK, bool SWAP, int MODE>
 int launch(const Config &cfg, const CUtensorMap &ma, const CUtensorMap &mb, const KernelParams &kp, const EpiParams &epi,
            cudaStream_t stream) {
     static bool configured = false;
-    auto kernel = conv_i8_tc_kernel<BN, BK, SWAP>;
+    auto kernel = conv_i8_tc_kernel<BN, BK, SWAP, MODE>;
     if (!configured) {
         TSB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynamicSmem));
         configured = true;
@@ -940,6 +1140,9 @@ bool make_view(const ConvGeom &g, View *view, const char **why) {
     }
     v.a_tiled = (!v.fold && g.KH == 1 && g.KW == 1 && g.sh == 1 && g.sw == 1 && g.pad_t == 0 && g.pad_l == 0 &&
                  g.OH == g.H && g.OW == g.W && !getenv("TSB_NO_TILED_A")) ? 1 : 0;
+    const char *force_patch = getenv("TSB_PATCH");
+    v.patch = (!v.fold && !v.a_tiled && g.sh == 1 && g.sw == 1 && g.KH * g.KW > 1 && (g.KW - 1) * g.dw + 8 <= 256 &&
+               (g.KH - 1) * g.dh + 32 <= 256 && !(force_patch && atoi(force_patch) == 0)) ? 1 : 0;
     const ConvGeom &t = v.g;
     v.weight_bytes = (size_t)t.O * t.KH * t.KW * t.Cp;
     // im2col tensor maps take box corners in [-128,127], filter offsets in [0,255] and traversal strides up to 8
@@ -968,9 +1171,26 @@ Config choose_config(const View &v, int sm_count, int orientation) {
     // 256 (or 128) pixels on N -- it halves the MMA count of narrow layers but its epilogue (one channel per thread)
     // is dearer, so it is taken where it measured faster: multi-tap filters with at most 64 output channels.
     const char *force = getenv("TSB_SWAP");
+    // patch mode under a given tile shape: most of each 8 x (pix/8) tile inside the image, and the whole weight tile
+    // in shared memory beside at least two patches (TSB_PATCH=1 drops the first condition)
+    const char *force_patch = getenv("TSB_PATCH");
+    auto patch_fits = [&](int pix, int ch) {
+        if (!v.patch) return false;
+        const int th = pix / 8;
+        const int tiles_w = ceil_div(g.OW, 8), tiles_h = ceil_div(g.OH, th);
+        const int pw = 8 + (g.KW - 1) * g.dw, ph = th + (g.KH - 1) * g.dh;
+        const double eff = (double)(g.OH * g.OW) / ((double)tiles_w * tiles_h * pix);
+        const uint64_t patch_bytes = (uint64_t)round_up(pw * ph * c.bk, 1024);
+        const uint64_t w_all = (uint64_t)g.KH * g.KW * g.Cp * (uint64_t)ch;
+        return (eff >= 0.7 || (force_patch && atoi(force_patch) != 0)) && w_all + 2 * patch_bytes <= kSmemBudget;
+    };
+    const int bn_normal = g.O > 128 ? 256 : (g.O > 64 ? 128 : 64);
     if (v.rows) c.swap = 0;
     else if (orientation >= 0) c.swap = orientation;
-    else c.swap = force ? (atoi(force) != 0 && g.O <= 128) : (g.O <= 64 && g.KH * g.KW >= 9 && !v.fold);
+    else if (force) c.swap = atoi(force) != 0 && g.O <= 128;
+    // narrow multi-tap layers: swapped fills the MMA's N, but where patch mode applies the normal orientation with its
+    // cheaper epilogue (16 warps, 16-byte stores) measured faster
+    else c.swap = g.O <= 64 && g.KH * g.KW >= 9 && !v.fold && !patch_fits(kBM, bn_normal);
     if (c.swap) {
         c.ch = kBM;
         c.bn = 256;
@@ -995,19 +1215,26 @@ Config choose_config(const View &v, int sm_count, int orientation) {
     }
     c.num_m_tiles = v.rows ? g.N * g.OH * v.rows_segs : (int)ceil_div64(M, c.pix);
     c.num_n_tiles = ceil_div(g.O, c.ch);
+    if (patch_fits(c.pix, c.ch)) {
+        const int th = c.pix / 8;
+        c.patch = 1;
+        c.patch_tiles_w = ceil_div(g.OW, 8); c.patch_tiles_h = ceil_div(g.OH, th);
+        c.patch_pw = 8 + (g.KW - 1) * g.dw; c.patch_ph = th + (g.KH - 1) * g.dh;
+        c.num_m_tiles = g.N * c.patch_tiles_w * c.patch_tiles_h;
+    }
     const int64_t tiles = (int64_t)c.num_m_tiles * c.num_n_tiles;
     c.grid = (int)(tiles < sm_count ? tiles : sm_count);
     // shared-memory plan: keep the CTA's whole weight tile resident when it is small enough to leave room for
     // at least four activation stages; otherwise stream activations and weights together
     // raw-row mode stages, per tile, the KH staged image rows under 128 sliding windows (127 pixel strides of 16 bytes
     // plus one window in the last row)
-    const uint32_t p_bytes = v.rows ? (uint32_t)round_up((g.KH - 1) * g.dh * (int)v.stride_h + (kBM - 1) * 16 + c.bk, 128)
+    const uint32_t p_bytes = c.patch ? (uint32_t)round_up(c.patch_pw * c.patch_ph * c.bk, 1024) : v.rows ? (uint32_t)round_up((g.KH - 1) * g.dh * (int)v.stride_h + (kBM - 1) * 16 + c.bk, 128)
                                     : (uint32_t)c.pix * c.bk;
     const uint32_t w_bytes = (uint32_t)c.ch * c.bk;
     const uint32_t k_iters = (uint32_t)g.KH * g.KW * (g.Cp / c.bk);
     const uint32_t w_total = k_iters * w_bytes;
-    const bool want_resident = v.rows || (!getenv("TSB_NO_RESIDENT_B") && tiles > c.grid);  // pays off only when a CTA runs several tiles
-    if (want_resident && w_total <= 128 * 1024 && (kSmemBudget - w_total) / p_bytes >= 4) {
+    const bool want_resident = v.rows || c.patch || (!getenv("TSB_NO_RESIDENT_B") && tiles > c.grid);  // pays off only when a CTA runs several tiles
+    if (c.patch || (want_resident && w_total <= 128 * 1024 && (kSmemBudget - w_total) / p_bytes >= 4)) {
         c.b_resident = 1;
         c.stage_bytes = p_bytes;
         c.stages = std::min<int>(kMaxStages, (int)((kSmemBudget - w_total) / p_bytes));
@@ -1046,6 +1273,17 @@ int encode_activation_map(const View &v, const Config &cfg, const int8_t *x, CUt
     if (st != TSB_OK) return st;
     if (reinterpret_cast<uintptr_t>(x) % 16) return fail(TSB_ERR_INVALID_ARGUMENT, "staged activations must be 16-byte aligned");
     const ConvGeom &g = v.g;
+    if (cfg.patch) {
+        cuuint64_t dims4[4] = {(cuuint64_t)g.Cp, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.N};
+        cuuint64_t strides4[3] = {v.stride_w, v.stride_h, v.stride_n};
+        cuuint32_t box4[4] = {(cuuint32_t)cfg.bk, (cuuint32_t)cfg.patch_pw, (cuuint32_t)cfg.patch_ph, 1};
+        cuuint32_t estr4[4] = {1, 1, 1, 1};
+        CUresult r4 = g_encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<int8_t *>(x), dims4, strides4, box4,
+                                     estr4, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(cfg.bk),
+                                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r4 != CUDA_SUCCESS) return fail(TSB_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled(activation patches) failed with %d", (int)r4);
+        return TSB_OK;
+    }
     if (v.a_tiled) {
         cuuint64_t dims2[2] = {(cuuint64_t)g.Cp, (cuuint64_t)g.N * g.H * g.W};
         cuuint64_t strides2[1] = {(cuuint64_t)g.Cp};
@@ -1178,6 +1416,11 @@ int launch_conv_tc(const View &v, const Config &cfg, const CUtensorMap &map_a, c
     kp.b_off = cfg.b_off; kp.bar_off = cfg.bar_off;
     kp.rows_segs = 0; kp.rows_OH = g.OH; kp.rows_H = g.H; kp.rows_bytes = 0; kp.rows_stride_h = 0; kp.rows_stride_n = 0;
     kp.rows_x = nullptr;
+    kp.patch = cfg.patch; kp.OH = g.OH;
+    kp.patch_tiles_w = std::max(1, cfg.patch_tiles_w); kp.patch_tiles_hw = std::max(1, cfg.patch_tiles_w * cfg.patch_tiles_h);
+    kp.patch_pw = cfg.patch_pw; kp.patch_bytes = (uint32_t)(cfg.patch_pw * cfg.patch_ph * cfg.bk);
+    kp.d_tiles_w = FastDiv((uint32_t)kp.patch_tiles_w); kp.d_tiles_hw = FastDiv((uint32_t)kp.patch_tiles_hw);
+    if (cfg.patch && !cfg.b_resident) return fail(TSB_ERR_UNSUPPORTED, "patch mode needs resident weights");
     if (v.rows) {
         if (cfg.swap || !cfg.b_resident || !x_staged) return fail(TSB_ERR_UNSUPPORTED, "raw-row mode needs the normal orientation and resident weights");
         kp.rows_segs = v.rows_segs;
@@ -1196,18 +1439,19 @@ int launch_conv_tc(const View &v, const Config &cfg, const CUtensorMap &map_a, c
     if (!epi.out_acc && (epi.out_f32 || epi.residual) && epi.f32_nhwc && i8_fast && (const void *)epi.residual != (const void *)epi.out_f32 &&
         (cfg.swap || (g.O % 4 == 0 && ((reinterpret_cast<uintptr_t>(epi.out_f32) | reinterpret_cast<uintptr_t>(epi.residual)) & 15) == 0)))
         kp.epi_mode = kEpiNhwc;
-#define TSB_TC_CASE(BN_, BK_, SWAP_) \
-    if (cfg.bn == BN_ && cfg.bk == BK_ && (cfg.swap != 0) == SWAP_) return launch<BN_, BK_, SWAP_>(cfg, map_a, map_b, kp, epi, stream)
-    TSB_TC_CASE(64, 64, false);
-    TSB_TC_CASE(128, 64, false);
-    TSB_TC_CASE(256, 64, false);
-    TSB_TC_CASE(64, 128, false);
-    TSB_TC_CASE(128, 128, false);
-    TSB_TC_CASE(256, 128, false);
-    TSB_TC_CASE(128, 64, true);
-    TSB_TC_CASE(256, 64, true);
-    TSB_TC_CASE(128, 128, true);
-    TSB_TC_CASE(256, 128, true);
+    const int mode = cfg.patch ? kModePatch : (v.rows ? kModeRows : kModeGeneral);
+#define TSB_TC_CASE(BN_, BK_, SWAP_, MODE_) \
+    if (cfg.bn == BN_ && cfg.bk == BK_ && (cfg.swap != 0) == SWAP_ && mode == MODE_) return launch<BN_, BK_, SWAP_, MODE_>(cfg, map_a, map_b, kp, epi, stream)
+#define TSB_TC_BOTH(BN_, BK_, MODE_) TSB_TC_CASE(BN_, BK_, false, MODE_); TSB_TC_CASE(BN_, BK_, true, MODE_)
+    TSB_TC_CASE(64, 64, false, kModeGeneral); TSB_TC_CASE(64, 128, false, kModeGeneral);
+    TSB_TC_BOTH(128, 64, kModeGeneral); TSB_TC_BOTH(256, 64, kModeGeneral);
+    TSB_TC_BOTH(128, 128, kModeGeneral); TSB_TC_BOTH(256, 128, kModeGeneral);
+    TSB_TC_CASE(64, 64, false, kModePatch); TSB_TC_CASE(64, 128, false, kModePatch);
+    TSB_TC_BOTH(128, 64, kModePatch); TSB_TC_BOTH(256, 64, kModePatch);
+    TSB_TC_BOTH(128, 128, kModePatch); TSB_TC_BOTH(256, 128, kModePatch);
+    TSB_TC_CASE(64, 64, false, kModeRows); TSB_TC_CASE(128, 64, false, kModeRows); TSB_TC_CASE(256, 64, false, kModeRows);
+    TSB_TC_CASE(64, 128, false, kModeRows); TSB_TC_CASE(128, 128, false, kModeRows); TSB_TC_CASE(256, 128, false, kModeRows);
+#undef TSB_TC_BOTH
 #undef TSB_TC_CASE
     return fail(TSB_ERR_UNSUPPORTED, "no tcgen05 kernel for tile %dx%d", cfg.bn, cfg.bk);
 }

@@ -18,11 +18,16 @@ namespace tc {
 //            is up to 128 consecutive pixels of one output row; per filter row the kernel copies the staged bytes under
 //            those pixels ONCE (about 2 KB instead of 128 windows of 64 B) and the MMA reads the overlapping windows
 //            straight out of that copy through a no-swizzle descriptor whose rows are 16 bytes apart.
+//  patch == 1 (NHWC_PAD input, stride 1, more than one filter tap): the configuration may use "patch" mode.  A tile is
+//            8 pixels wide and pix/8 pixels high; one tiled tensor-map load per channel block brings the input patch under
+//            it (halo included, zero-filled outside the image) and every filter tap reads its shifted window out of that
+//            patch, so an activation byte is loaded once per tile instead of once per tap.  Needs resident weights.
 struct View {
     ConvGeom g;          // geometry handed to the kernel and the tensor maps
     ConvGeom real;       // geometry of the operator
     int fold = 0;
     int rows = 0;        // raw-row mode
+    int patch = 0;       // patch mode is possible for this geometry
     int rows_segs = 0;   // tiles per output row in raw-row mode
     int a_tiled = 0;     // 1x1 / stride 1 / no padding: the activations are the [M][Cp] matrix itself, loaded as 2-D tiles
     int cpix = 0;        // bytes per pixel of the folded staging
@@ -37,6 +42,8 @@ struct Config {
     int swap = 0;                     // 1: channels on the MMA's M side and pixels on its N side
     int pix = 0, ch = 0;              // pixels and output channels per tile
     int num_m_tiles = 0, num_n_tiles = 0;
+    int patch = 0;                    // this configuration runs in patch mode
+    int patch_tiles_w = 0, patch_tiles_h = 0, patch_pw = 0, patch_ph = 0;   // tiles per image, patch extent in pixels
     int grid = 0;                     // persistent CTAs
     // shared-memory plan of the kernel
     int stages = 0, b_resident = 0;

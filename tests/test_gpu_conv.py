@@ -189,6 +189,39 @@ def test_raw_row_mode(checker, port, monkeypatch, case):
     assert np.array_equal(got["i8"], want)
 
 
+@pytest.mark.parametrize("swap", ["0", "1"])
+@pytest.mark.parametrize("case", [
+    (2, 64, 20, 20, 64, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1)),      # image edges inside tiles on both axes
+    (1, 128, 56, 56, 128, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1)),    # many tiles per image, 128-byte channel blocks
+    (3, 192, 14, 14, 96, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1)),     # three 64-byte channel blocks, one tile per image
+    (2, 256, 9, 17, 40, 3, 3, (1, 1, 1, 1), (1, 1), (2, 2)),      # dilated taps, ragged channels
+    (2, 64, 12, 12, 72, 5, 5, (2, 2, 2, 2), (1, 1), (1, 1)),      # 25 taps
+    (1, 64, 10, 30, 32, 3, 1, (1, 1, 0, 0), (1, 1), (1, 1)),      # a column filter
+    (2, 64, 11, 13, 64, 2, 3, (0, 1, 2, 0), (1, 1), (1, 1)),      # asymmetric padding, even filter height
+])
+def test_patch_mode(checker, port, monkeypatch, case, swap):
+    """Stride-1 filters with several taps: one tensor-map load brings the input patch under an 8-pixel-wide tile and
+    every tap reads its window out of it through a shifted shared-memory descriptor.  Forced on here regardless of how
+    well the tiles cover the image, in both MMA orientations."""
+    monkeypatch.setenv("TSB_PATCH", "1")
+    monkeypatch.setenv("TSB_SWAP", swap)
+    N, C, H, W, O, KH, KW, pad, stride, dil = case
+    rng = np.random.default_rng(N * 13 + C + O + H)
+    x = rng.integers(-128, 128, size=(N, C, H, W), dtype=np.int8)
+    w = rng.integers(-127, 128, size=(O, C, KH, KW), dtype=np.int8)
+    dq = rng.uniform(0.001, 0.01, size=O).astype(np.float32)
+    bias = (rng.standard_normal(O) * 0.1).astype(np.float32)
+    got = check_case(checker, port, x, w, pad, stride, dil, dq, bias, "relu", 0.0, 0.0, 2)               # fp32 NCHW
+    assert got["kernel"] == 2
+    rq = rng.uniform(0.5, 2.0, size=N).astype(np.float32)
+    check_case(checker, port, x, w, pad, stride, dil, dq, None, "leaky_relu", 0.1, 0.0, 2, want_acc=False,
+               x_layout="nhwc", rq=rq, i8_layout="nhwc", f32_layout="nhwc")                                # element by element
+    got = run_gpu(x, w, pad, stride, dil, dq, bias, "relu", 0.0, 0.0, 2, x_layout="nhwc", rq=rq, i8_layout="nhwc",
+                  want_acc=False, want_f32=False)                                                          # int8 NHWC
+    want = checker.quantize(checker.relu(checker.add_bias(checker.conv2d_quantized(x, w, pad, stride, dil, dq), bias)), rq)
+    assert np.array_equal(got["i8"], want)
+
+
 @pytest.mark.parametrize("swap", [None, "0", "1"])
 @pytest.mark.parametrize("case", [
     (5, 64, 7, 7, 256),      # 49 pixels per image: most 32-pixel chunks cross an image boundary
