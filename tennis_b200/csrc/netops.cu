@@ -53,27 +53,68 @@ global_avgpool_f32_nhwc_kernel(const float *__restrict__ x, float *__restrict__ 
     const int64_t total = (int64_t)N * C;
     for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < total; i += (int64_t)gridDim.x * kThreads) {
         const int c = (int)(i % C), n = (int)(i / C);
+        // eight loads in flight, added in pixel order (the sum is a plain left-to-right fp32 sum)
+        const float *col = x + (int64_t)n * P * C + c;
         float s = 0.0f;
-        for (int p = 0; p < P; ++p) s = __fadd_rn(s, x[((int64_t)n * P + p) * C + c]);
+        for (int p0 = 0; p0 < P; p0 += 8) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = p0 + j < P ? __ldg(col + (int64_t)(p0 + j) * C) : 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (p0 + j < P) s = __fadd_rn(s, v[j]);
+        }
         y[i] = __fdiv_rn(s, (float)P);
     }
 }
 
-// y[n][o] = sum_k x[n][k] * w[o][k] + bias[o]; one warp per output, lanes stride over k, tree reduction.
+// y[n][o] = sum_k x[n][k] * w[o][k] + bias[o].  A warp owns a block of kIpN images x kIpO outputs: per step of 32 k's it
+// loads kIpN + kIpO values and does kIpN * kIpO multiply-adds, so every loaded value is used several times.  Each output
+// is summed in a fixed order (lane l takes k = l, l+32, ... in sequence, then a butterfly over the lanes), whatever the
+// block shape.
+constexpr int kIpN = 8, kIpO = 4;
 __global__ void __launch_bounds__(kThreads)
 inner_prod_f32_kernel(const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
                       float *__restrict__ y, int N, int K, int O) {
     pdl_sync();
     const int warps_per_block = kThreads / 32;
     const int lane = threadIdx.x & 31;
-    const int64_t total = (int64_t)N * O;
+    const int n_blocks = (N + kIpN - 1) / kIpN, o_blocks = (O + kIpO - 1) / kIpO;
+    const int64_t total = (int64_t)n_blocks * o_blocks;
     for (int64_t i = (int64_t)blockIdx.x * warps_per_block + (threadIdx.x >> 5); i < total; i += (int64_t)gridDim.x * warps_per_block) {
-        const int o = (int)(i % O), n = (int)(i / O);
-        float s = 0.0f;
-        for (int k = lane; k < K; k += 32) s = fmaf(x[(int64_t)n * K + k], w[(int64_t)o * K + k], s);
+        const int ob = (int)(i % o_blocks), nb = (int)(i / o_blocks);
+        const float *xr[kIpN];
+        const float *wr[kIpO];
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-        if (lane == 0) y[i] = bias ? s + bias[o] : s;
+        for (int a = 0; a < kIpN; ++a) xr[a] = x + (int64_t)min(nb * kIpN + a, N - 1) * K;   // clamped: extra rows are not stored
+#pragma unroll
+        for (int b = 0; b < kIpO; ++b) wr[b] = w + (int64_t)min(ob * kIpO + b, O - 1) * K;
+        float s[kIpN][kIpO];
+#pragma unroll
+        for (int a = 0; a < kIpN; ++a)
+#pragma unroll
+            for (int b = 0; b < kIpO; ++b) s[a][b] = 0.0f;
+        for (int k = lane; k < K; k += 32) {
+            float xv[kIpN], wv[kIpO];
+#pragma unroll
+            for (int a = 0; a < kIpN; ++a) xv[a] = __ldg(xr[a] + k);
+#pragma unroll
+            for (int b = 0; b < kIpO; ++b) wv[b] = __ldg(wr[b] + k);
+#pragma unroll
+            for (int a = 0; a < kIpN; ++a)
+#pragma unroll
+                for (int b = 0; b < kIpO; ++b) s[a][b] = fmaf(xv[a], wv[b], s[a][b]);
+        }
+#pragma unroll
+        for (int a = 0; a < kIpN; ++a)
+#pragma unroll
+            for (int b = 0; b < kIpO; ++b) {
+                float t = s[a][b];
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
+                const int n = nb * kIpN + a, o = ob * kIpO + b;
+                if (lane == 0 && n < N && o < O) y[(int64_t)n * O + o] = bias ? t + bias[o] : t;
+            }
     }
 }
 
@@ -111,7 +152,7 @@ int global_avgpool_f32_nhwc(const float *x, float *y, int n, int pixels, int cha
 int inner_prod_f32(const float *x, const float *w, const float *bias, float *y, int n, int k, int o, cudaStream_t stream) {
     if (!x || !w || !y) return fail(TSB_ERR_INVALID_ARGUMENT, "inner_prod: null pointer");
     if (n < 1 || k < 1 || o < 1) return fail(TSB_ERR_INVALID_ARGUMENT, "inner_prod: bad shape");
-    TSB_CUDA(launch_pdl(inner_prod_f32_kernel, dim3(grid_for((int64_t)n * o, kThreads / 32)), dim3(kThreads), 0, stream, x, w, bias, y, n, k, o));
+    TSB_CUDA(launch_pdl(inner_prod_f32_kernel, dim3(grid_for((int64_t)((n + kIpN - 1) / kIpN) * ((o + kIpO - 1) / kIpO), kThreads / 32)), dim3(kThreads), 0, stream, x, w, bias, y, n, k, o));
     TSB_LAUNCHED("inner_prod_f32_kernel");
     return TSB_OK;
 }
