@@ -42,6 +42,7 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-resnet", action="store_true", help="skip the secondary ResNet-50-shaped network measurement")
+    ap.add_argument("--no-csp", action="store_true", help="skip the secondary CSPDarknet53-shaped backbone measurement")
     ap.add_argument("--cpu-budget-s", type=float, default=20.0, help="host seconds the cpu_baseline sample may take")
     return ap.parse_args()
 
@@ -84,7 +85,7 @@ def cpu_arm(layers):
     from tennis_b200 import workloads
     orc.build() if not os.path.exists(os.path.join(ROOT, "oracle", "liboracle.so")) else None
     checker = orc.best()
-    cores = os.cpu_count() or 1
+    cores = orc.usable_cpus()
     # the reference's int8 GEMM is serial inside one Workbench; all host cores are used by running one
     # Workbench per core on its own samples.  The C port parallelises inside one call with OpenMP.
     workers = cores if checker.kind == "reference" else 1
@@ -248,6 +249,57 @@ def run_resnet50(args, dev, rank, world, sharding):
             "e2e_images_per_sec": images / (e2e_max / 1e3), "e2e_ms_per_batch": e2e_max,
             "h2d_bytes_per_batch": hx.numel() * 4 * world, "d2h_bytes_per_batch": hout.numel() * 4 * world,
             "kernels_per_pass": 53 + 4, "logits_checksum": float(logits.double().abs().sum())}
+
+
+def run_cspdarknet(args, dev, rank, world, sharding):
+    """Images/s of the CSPDarknet53-shaped int8 backbone (72 convolutions, LeakyReLU(0.1), Darknet shortcuts added in fp32
+    after the activation, cross-stage routes joined by an int8 concatenation), batch 16 per GPU at 3x608x608, synthetic
+    U(0,1) input, whole forward pass captured in a CUDA graph and replayed."""
+    import torch
+    from tennis_b200 import nets
+    batch = 16
+    spec = nets.cspdarknet_spec()
+    params = nets.make_conv_params(spec, seed=0)
+    net = nets.QuantCSPDarknet(spec, params, batch, dev)
+    g = torch.Generator(device=dev).manual_seed(sharding.shard_seed(0, rank))
+    x = torch.rand((batch, 3, 608, 608), device=dev, generator=g)
+    t0 = time.perf_counter()
+    net.calibrate(x)
+    net.status()
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    net.forward(x)
+    torch.cuda.synchronize()
+    first = time.perf_counter() - t1
+    if first > 1.0 or t1 - t0 > 60.0:   # a secondary figure must never stall the benchmark
+        return {"error": "skipped: calibration took %.1f s, one eager pass %.3f s" % (t1 - t0, first)}
+    stream = torch.cuda.Stream(device=dev)
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        for _ in range(2):
+            net.forward(x)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            out = net.forward(x)
+    torch.cuda.current_stream().wait_stream(stream)
+    net.status()
+    reps = max(5, min(args.steps, 20))
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        graph.replay()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / reps
+    ms_max, images = sharding.aggregate(ms, batch, dev)
+    ops_batch = nets.conv_ops(spec, batch)
+    return {"workload": "config3: CSPDarknet53-shaped int8 backbone, batch 16 per GPU at 608x608, CUDA graph replay",
+            "batch_per_gpu": batch, "images_per_sec": images / (ms_max / 1e3), "ms_per_batch": ms_max,
+            "int8_conv_tops": ops_batch * world / (ms_max / 1e3) / 1e12, "kernels_per_pass": 72 + 1 + 5,
+            "features_checksum": int(out.to(torch.int64).abs().sum())}
 
 
 def run_ours(args):
@@ -442,6 +494,15 @@ def run_ours(args):
         except Exception as e:  # reported, never fatal for the primary metric
             resnet = {"error": repr(e)[:300]}
 
+    csp = None
+    if not args.no_csp:
+        try:
+            if resnet is not None:
+                torch.cuda.empty_cache()
+            csp = run_cspdarknet(args, dev, rank, world, sharding)
+        except Exception as e:
+            csp = {"error": repr(e)[:300]}
+
     sampler.stop_flag.set()
     sampler.join(timeout=2)
 
@@ -497,6 +558,8 @@ def run_ours(args):
         }
         if resnet is not None:
             line["resnet50"] = resnet
+        if csp is not None:
+            line["cspdarknet53"] = csp
         line["e2e"]["h2d_bytes_per_step"] = h2d * world
         line["e2e"]["d2h_bytes_per_step"] = d2h * world
         if world == 1:

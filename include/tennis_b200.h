@@ -144,6 +144,9 @@ typedef struct tsb_conv_epilogue {
     const float *requant_scales_host; /* [n_requant_scales] host; 1 scale, or one per sample */
     int n_requant_scales;
     int32_t *out_acc;               /* device or NULL: raw int32 accumulators, NCHW (parity checks) */
+    int residual_after_activation;  /* 0: act(conv + bias + residual), a ResNet block's tail;
+                                       1: act(conv + bias) + residual, a Darknet shortcut (operators
+                                          conv2d_quantized -> add_bias -> leaky_relu -> add) */
 } tsb_conv_epilogue;
 
 typedef struct tsb_conv_plan tsb_conv_plan;
@@ -233,6 +236,13 @@ TSB_API int tsb_maxpool_i8_nhwc(const int8_t *x, int8_t *y, int n, int h, int w,
                                 void *stream);
 TSB_API int tsb_global_avgpool_f32_nhwc(const float *x, float *y, int n, int pixels, int channels, void *stream);
 TSB_API int tsb_inner_prod_f32(const float *x, const float *w, const float *bias, float *y, int n, int k, int o,
+                               void *stream);
+/*
+ * Channel concatenation (operator "concat" on dim 1, src/kernels/gpu/concat.cu) of two int8 NHWC_PAD tensors with the
+ * same pixels: y[pixel] = [a's channels_a | b's channels_b | zero padding].  Both inputs must have been quantized with
+ * the scale of the consumer, which makes this equal to quantizing the concatenated fp32 tensors.
+ */
+TSB_API int tsb_concat_i8_nhwc(const int8_t *a, int channels_a, const int8_t *b, int channels_b, int8_t *y, int64_t pixels,
                                void *stream);
 
 /* Debugging aid: while a device buffer of 2048 bytes is set, CTA 0 of each tensor-core convolution launch records a

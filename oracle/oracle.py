@@ -19,6 +19,40 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _c_int_p = ctypes.POINTER(ctypes.c_int)
 
 
+def usable_cpus():
+    """Host threads this process may really use: the affinity mask, cut down by a cgroup CPU quota when there is one.
+    os.cpu_count() alone over-subscribes containers that see all of a big host's cores but may run on a few."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    for path in ("/sys/fs/cgroup/cpu.max", "/sys/fs/cgroup/cpu/cpu.cfs_quota_us"):
+        try:
+            text = open(path).read().split()
+            if path.endswith("cpu.max"):
+                quota, period = text[0], float(text[1])
+            else:
+                quota, period = text[0], float(open("/sys/fs/cgroup/cpu/cpu.cfs_period_us").read())
+            if quota not in ("max", "-1") and period > 0:
+                n = min(n, max(1, int(float(quota) / period)))
+            break
+        except (OSError, ValueError, IndexError):
+            continue
+    return max(1, n)
+
+
+def limit_openmp(max_threads=None):
+    """Keeps the OpenMP runtimes of the checker libraries from spawning one spinning thread per visible core."""
+    n = min(usable_cpus(), max_threads or 16)
+    os.environ.setdefault("OMP_NUM_THREADS", str(n))
+    os.environ.setdefault("OMP_WAIT_POLICY", "PASSIVE")
+    try:
+        ctypes.CDLL("libgomp.so.1").omp_set_num_threads(int(os.environ["OMP_NUM_THREADS"]))
+    except (OSError, AttributeError, ValueError):
+        pass
+    return n
+
+
 def _ptr(a, ctype):
     return a.ctypes.data_as(ctypes.POINTER(ctype))
 
@@ -52,6 +86,7 @@ class Port:
         path = os.path.join(_HERE, "liboracle.so")
         if not os.path.exists(path):
             build()
+        limit_openmp()
         self.lib = ctypes.CDLL(path)
         self.lib.orc_quantize_group_len.restype = ctypes.c_int
 
@@ -113,14 +148,17 @@ class Port:
         return y
 
     def conv_block(self, xq, w, pad, stride, dilation, dq, bias=None, act=0, leaky=0.0, residual=None,
-                   requant_scales=None, padding_value=0.0):
-        """conv2d_quantized -> add_bias -> [+ residual] -> relu|leaky_relu -> [quantize]."""
+                   requant_scales=None, padding_value=0.0, residual_after_activation=False):
+        """conv2d_quantized -> add_bias -> [+ residual] -> relu|leaky_relu -> [+ residual] -> [quantize]; the residual
+        (operator "add", fp32) comes before the activation (ResNet) or after it (Darknet shortcut)."""
         y = self.conv2d_quantized(xq, w, pad, stride, dilation, dq, padding_value)
         if bias is not None:
             y = self.add_bias(y, bias)
-        if residual is not None:
+        if residual is not None and not residual_after_activation:
             y = (y + np.asarray(residual, dtype=np.float32)).astype(np.float32)
         y = self.activation(y, act, leaky)
+        if residual is not None and residual_after_activation:
+            y = (y + np.asarray(residual, dtype=np.float32)).astype(np.float32)
         if requant_scales is not None:
             return y, self.quantize(y, requant_scales)
         return y
@@ -135,6 +173,7 @@ class Reference(Port):
         path = os.path.join(_HERE, "_ref", "libtsref.so")
         if not os.path.exists(path):
             raise FileNotFoundError(path)
+        limit_openmp()
         self.ref = ctypes.CDLL(path)
         self.ref.tsref_last_error.restype = ctypes.c_char_p
         self.threads = threads

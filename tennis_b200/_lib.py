@@ -41,6 +41,7 @@ class ConvEpilogue(ctypes.Structure):
         ("requant_scales_host", ctypes.POINTER(ctypes.c_float)),
         ("n_requant_scales", ctypes.c_int),
         ("out_acc", ctypes.c_void_p),
+        ("residual_after_activation", ctypes.c_int),
     ]
 
 
@@ -75,6 +76,7 @@ SYMBOLS = {
     "tsb_maxpool_i8_nhwc": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "tsb_global_avgpool_f32_nhwc": (_i, [_vp, _vp, _i, _i, _i, _vp]),
     "tsb_inner_prod_f32": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "tsb_concat_i8_nhwc": (_i, [_vp, _i, _vp, _i, _vp, _i64, _vp]),
     "tsb_debug_set_trace_buffer": (_i, [_vp]),
     "tsb_kernel_launch_count": (_i64, []),
 }

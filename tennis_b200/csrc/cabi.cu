@@ -28,6 +28,7 @@ int activation_f32(const float *, float *, int64_t, int, float, cudaStream_t);
 int maxpool_i8_nhwc(const int8_t *, int8_t *, int, int, int, int, int, int, int, cudaStream_t);
 int global_avgpool_f32_nhwc(const float *, float *, int, int, int, cudaStream_t);
 int inner_prod_f32(const float *, const float *, const float *, float *, int, int, int, cudaStream_t);
+int concat_i8_nhwc(const int8_t *, int, const int8_t *, int, int8_t *, int64_t, cudaStream_t);
 
 namespace {
 
@@ -121,6 +122,9 @@ int tsb_global_avgpool_f32_nhwc(const float *x, float *y, int n, int pixels, int
 }
 int tsb_inner_prod_f32(const float *x, const float *w, const float *bias, float *y, int n, int k, int o, void *stream) {
     return inner_prod_f32(x, w, bias, y, n, k, o, (cudaStream_t)stream);
+}
+int tsb_concat_i8_nhwc(const int8_t *a, int channels_a, const int8_t *b, int channels_b, int8_t *y, int64_t pixels, void *stream) {
+    return concat_i8_nhwc(a, channels_a, b, channels_b, y, pixels, (cudaStream_t)stream);
 }
 
 int tsb_conv2d_i8_plan_create(const tsb_conv_desc *d, tsb_conv_plan **out) {
@@ -241,6 +245,7 @@ static int build_epilogue(const tsb_conv_plan *plan, const tsb_conv_epilogue *e,
     p.out_acc = e->out_acc;
     p.activation = e->activation;
     p.leaky = e->leaky_scale;
+    p.res_after = (e->residual && e->residual_after_activation) ? 1 : 0;
     p.f32_nhwc = e->out_f32_layout == TSB_LAYOUT_NHWC_PAD;
     p.i8_nhwc = e->out_i8_layout == TSB_LAYOUT_NHWC_PAD;
     p.out_cp = tsb_padded_channels(g.O);
@@ -309,7 +314,9 @@ int tsb_conv2d_i8_run(tsb_conv_plan *plan, const int8_t *x, int x_layout, const 
     // Pixel-major fp32 tensors (a network's residuals and block outputs) are stored coalesced when a thread owns a
     // channel, i.e. in the swapped orientation; everything else follows the geometry heuristic.
     const bool want_swap = (epi.out_f32 || epi.residual) && epi.f32_nhwc && !epi.out_acc;
-    const bool use_alt = plan->alt_valid && !getenv("TSB_SWAP") && (want_swap != (plan->cfg.swap != 0)) && (want_swap ? plan->cfg_alt.swap : 0);
+    // (the swapped patch-mode kernel has no fast path for pixel-major fp32 tensors)
+    const bool use_alt = plan->alt_valid && !getenv("TSB_SWAP") && (want_swap != (plan->cfg.swap != 0)) && (want_swap ? plan->cfg_alt.swap : 0) &&
+                         !plan->cfg_alt.patch;
     if (use_alt) {
         if (plan->map_a_alt_ptr != x_tc) {
             st = tc::encode_activation_map(plan->view, plan->cfg_alt, x_tc, &plan->map_a_alt);

@@ -119,17 +119,18 @@ __device__ __forceinline__ int q8(float x, float scale, bool half_even) {
     return half_even ? q8_half_even(v) : q8_half_away(v);
 }
 
-// dequantize -> add_bias -> (+residual) -> activation, one rounding per step.
+// dequantize -> add_bias -> (+residual) -> activation (-> +residual when it follows the activation), one rounding per step.
 struct EpilogueMath {
     int activation;
     float leaky;
     __device__ __forceinline__ float operator()(int acc, float dq, float bias, bool has_bias, float residual,
-                                                bool has_residual) const {
+                                                bool has_residual, bool residual_after = false) const {
         float v = __fmul_rn(__int2float_rn(acc), dq);
         if (has_bias) v = __fadd_rn(v, bias);
-        if (has_residual) v = __fadd_rn(v, residual);
+        if (has_residual && !residual_after) v = __fadd_rn(v, residual);
         if (activation == TSB_ACT_RELU) v = v > 0.0f ? v : 0.0f;
         else if (activation == TSB_ACT_LEAKY_RELU) v = v > 0.0f ? v : __fmul_rn(v, leaky);
+        if (has_residual && residual_after) v = __fadd_rn(v, residual);
         return v;
     }
 };

@@ -27,6 +27,7 @@ struct EpiParams {
     int32_t *out_acc;
     int activation;
     float leaky;
+    int res_after;      // the residual is added after the activation instead of before it
     int f32_nhwc;       // out_f32 / residual are [N][P][O] instead of NCHW
     int i8_nhwc;        // out_i8 is NHWC_PAD with out_cp channels
     int out_cp;
@@ -48,7 +49,7 @@ __device__ __forceinline__ void epilogue_store_one(const EpiParams &e, int n, in
     EpilogueMath math{e.activation, e.leaky};
     const uint32_t fidx = e.f32_nhwc ? nhwc : nchw;
     const float v = math(acc, e.dq[o], e.bias ? e.bias[o] : 0.0f, e.bias != nullptr,
-                         e.residual ? e.residual[fidx] : 0.0f, e.residual != nullptr);
+                         e.residual ? e.residual[fidx] : 0.0f, e.residual != nullptr, e.res_after != 0);
     if (e.out_f32) e.out_f32[fidx] = v;
     if (e.out_i8) {
         const uint32_t g = e.nscales == 1 ? 0u : nchw / e.group_len;

@@ -263,7 +263,7 @@ __device__ __forceinline__ bool store_i8_nhwc_t(const int (&v)[W], const float *
 // Block-output epilogue of a residual network: v = act(dq*acc + bias + residual); fp32 copy for the next residual and
 // int8 copy for the next convolution.  Each pointer may be null.  All three tensors are pixel-major, so the thread's 32
 // channels are contiguous: 16-byte loads and stores.
-template <int ACT, bool HAS_BIAS, int W>
+template <int ACT, bool HAS_BIAS, int W, bool AFTER>
 __device__ __forceinline__ bool store_nhwc_t(const int (&v)[W], const float *__restrict__ dq, const float *__restrict__ bias,
                                              float leaky, const float *__restrict__ res, float *__restrict__ out_f32,
                                              int8_t *__restrict__ out_i8, float rs) {
@@ -281,9 +281,10 @@ __device__ __forceinline__ bool store_nhwc_t(const int (&v)[W], const float *__r
         for (int k = 0; k < 4; ++k) {
             float t = __fmul_rn(__int2float_rn(v[4 * j4 + k]), dd[k]);
             if (HAS_BIAS) t = __fadd_rn(t, bb[k]);
-            if (res) t = __fadd_rn(t, rr[k]);
+            if (res && !AFTER) t = __fadd_rn(t, rr[k]);
             if (ACT == TSB_ACT_RELU) t = fmaxf(t, 0.0f);
             if (ACT == TSB_ACT_LEAKY_RELU) t = t > 0.0f ? t : __fmul_rn(t, leaky);
+            if (res && AFTER) t = __fadd_rn(t, rr[k]);
             f[k] = t;
         }
         if (out_f32) reinterpret_cast<float4 *>(out_f32)[j4] = make_float4(f[0], f[1], f[2], f[3]);
@@ -401,7 +402,7 @@ __device__ __forceinline__ void patch_f32_run(const int (&v)[32], float dq, floa
 
 // Pixel-major fp32 tensors in the swapped orientation: for one pixel the warp's 32 lanes touch 32 consecutive floats
 // (residual read, fp32 write) and 32 consecutive int8 (requantized write): every access is one coalesced line.
-template <int ACT, bool HAS_BIAS>
+template <int ACT, bool HAS_BIAS, bool AFTER>
 __device__ __forceinline__ bool swap_nhwc_run(const int (&v)[32], float dq, float bias, float leaky,
                                               const float *__restrict__ res, float *__restrict__ out_f32,
                                               int8_t *__restrict__ out_i8, bool write_i8, float rs0, float rs1, int split,
@@ -417,9 +418,10 @@ __device__ __forceinline__ bool swap_nhwc_run(const int (&v)[32], float dq, floa
             const int j = j0 + k;
             float t = __fmul_rn(__int2float_rn(v[j]), dq);
             if (HAS_BIAS) t = __fadd_rn(t, bias);
-            if (res) t = __fadd_rn(t, r[k]);
+            if (res && !AFTER) t = __fadd_rn(t, r[k]);
             if (ACT == TSB_ACT_RELU) t = fmaxf(t, 0.0f);
             if (ACT == TSB_ACT_LEAKY_RELU) t = t > 0.0f ? t : __fmul_rn(t, leaky);
+            if (res && AFTER) t = __fadd_rn(t, r[k]);
             if (out_f32 && ch_live) out_f32[(uint32_t)j * O] = t;
             if (out_i8) {
                 const float u = __fmul_rn(t, j < split ? rs0 : rs1);
@@ -447,6 +449,18 @@ __device__ __forceinline__ bool swap_nhwc_run(const int (&v)[32], float dq, floa
             else if (act == TSB_ACT_LEAKY_RELU) RESULT FN<TSB_ACT_LEAKY_RELU, false, W_>(__VA_ARGS__);    \
             else RESULT FN<TSB_ACT_NONE, false, W_>(__VA_ARGS__);                                         \
         }                                                                                                 \
+    } while (0)
+// the two residual epilogues: a second instantiation for "residual after the activation"
+#define TSB_EPI_DISPATCH_RES_W(RESULT, FN, W_, ...)                                                       \
+    do {                                                                                                  \
+        if (epi.res_after) TSB_EPI_DISPATCH_W(RESULT, FN, W_ TSB_COMMA true, __VA_ARGS__);                \
+        else TSB_EPI_DISPATCH_W(RESULT, FN, W_ TSB_COMMA false, __VA_ARGS__);                             \
+    } while (0)
+#define TSB_COMMA ,
+#define TSB_EPI_DISPATCH_SWAPRES(RESULT, FN, ...)                                                         \
+    do {                                                                                                  \
+        if (epi.res_after) TSB_EPI_DISPATCH_W(RESULT, FN, true, __VA_ARGS__);                             \
+        else TSB_EPI_DISPATCH_W(RESULT, FN, false, __VA_ARGS__);                                          \
     } while (0)
 #define TSB_EPI_DISPATCH(RESULT, FN, ...)                                                                 \
     do {                                                                                                  \
@@ -911,7 +925,7 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                             float *of = epi.out_f32 ? epi.out_f32 + f_off : nullptr;
                             int8_t *oi = epi.out_i8 ? epi.out_i8 + (size_t)m * epi.out_cp + o_base + col0 : nullptr;
                             bool fine = true;
-                            if (live) TSB_EPI_DISPATCH_W(fine =, store_nhwc_t, CW, v, t_dq + col0, t_bias + col0, epi.leaky, res, of, oi, rs);
+                            if (live) TSB_EPI_DISPATCH_RES_W(fine =, store_nhwc_t, CW, v, t_dq + col0, t_bias + col0, epi.leaky, res, of, oi, rs);
                             done = !__any_sync(0xffffffffu, !fine);
                         }
                     }
@@ -1009,7 +1023,7 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                             const float *res = epi.residual ? epi.residual + f_off : nullptr;
                             float *of = epi.out_f32 ? epi.out_f32 + f_off : nullptr;
                             int8_t *oi = epi.out_i8 ? epi.out_i8 + (size_t)mfirst * epi.out_cp + o : nullptr;
-                            TSB_EPI_DISPATCH(done =, swap_nhwc_run, v, my_dq, my_bias, epi.leaky, res, of, oi, o < epi.out_cp, rs0, rs1, split,
+                            TSB_EPI_DISPATCH_SWAPRES(done =, swap_nhwc_run, v, my_dq, my_bias, epi.leaky, res, of, oi, o < epi.out_cp, rs0, rs1, split,
                                              (uint32_t)epi.O, (uint32_t)epi.out_cp, ch_live);
                         }
                     }

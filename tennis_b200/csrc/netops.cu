@@ -118,6 +118,35 @@ inner_prod_f32_kernel(const float *__restrict__ x, const float *__restrict__ w, 
     }
 }
 
+// y[pixel] = [a[pixel][0..ca) | b[pixel][0..cb) | zeros up to cy]; ca_p, cb_p, cy are the padded channel counts
+__global__ void __launch_bounds__(kThreads)
+concat_i8_nhwc_kernel(const int8_t *__restrict__ a, int ca, int ca_p, const int8_t *__restrict__ b, int cb, int cb_p,
+                      int8_t *__restrict__ y, int cy, int64_t pixels, int vec) {
+    pdl_sync();
+    if (vec) {   // ca and cb are multiples of 16: whole 16-byte units
+        const int units = cy / 16, ua = ca / 16, ub = cb / 16;
+        const int64_t total = pixels * units;
+        for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < total; i += (int64_t)gridDim.x * kThreads) {
+            const int u = (int)(i % units);
+            const int64_t px = i / units;
+            int4 v = make_int4(0, 0, 0, 0);
+            if (u < ua) v = __ldg(reinterpret_cast<const int4 *>(a + px * ca_p) + u);
+            else if (u < ua + ub) v = __ldg(reinterpret_cast<const int4 *>(b + px * cb_p) + (u - ua));
+            reinterpret_cast<int4 *>(y + px * cy)[u] = v;
+        }
+    } else {
+        const int64_t total = pixels * cy;
+        for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < total; i += (int64_t)gridDim.x * kThreads) {
+            const int c = (int)(i % cy);
+            const int64_t px = i / cy;
+            int8_t v = 0;
+            if (c < ca) v = a[px * ca_p + c];
+            else if (c < ca + cb) v = b[px * cb_p + (c - ca)];
+            y[i] = v;
+        }
+    }
+}
+
 int grid_for(int64_t items, int per_block) {
     int64_t blocks = (items + per_block - 1) / per_block;
     if (blocks < 1) blocks = 1;
@@ -154,6 +183,20 @@ int inner_prod_f32(const float *x, const float *w, const float *bias, float *y, 
     if (n < 1 || k < 1 || o < 1) return fail(TSB_ERR_INVALID_ARGUMENT, "inner_prod: bad shape");
     TSB_CUDA(launch_pdl(inner_prod_f32_kernel, dim3(grid_for((int64_t)((n + kIpN - 1) / kIpN) * ((o + kIpO - 1) / kIpO), kThreads / 32)), dim3(kThreads), 0, stream, x, w, bias, y, n, k, o));
     TSB_LAUNCHED("inner_prod_f32_kernel");
+    return TSB_OK;
+}
+
+int concat_i8_nhwc(const int8_t *a, int ca, const int8_t *b, int cb, int8_t *y, int64_t pixels, cudaStream_t stream) {
+    if (!a || !b || !y) return fail(TSB_ERR_INVALID_ARGUMENT, "concat: null pointer");
+    if (ca < 1 || cb < 1 || pixels < 1) return fail(TSB_ERR_INVALID_ARGUMENT, "concat: bad extents");
+    if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(y)) % 16)
+        return fail(TSB_ERR_INVALID_ARGUMENT, "concat: tensors must be 16-byte aligned");
+    const int ca_p = tsb_padded_channels(ca), cb_p = tsb_padded_channels(cb), cy = tsb_padded_channels(ca + cb);
+    const int vec = (ca % 16 == 0 && cb % 16 == 0) ? 1 : 0;
+    const int64_t items = vec ? pixels * (cy / 16) : pixels * cy;
+    TSB_CUDA(launch_pdl(concat_i8_nhwc_kernel, dim3(grid_for(items, kThreads)), dim3(kThreads), 0, stream, a, ca, ca_p, b, cb, cb_p, y, cy,
+                        pixels, vec));
+    TSB_LAUNCHED("concat_i8_nhwc_kernel");
     return TSB_OK;
 }
 

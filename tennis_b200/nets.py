@@ -109,16 +109,35 @@ class QuantResNet:
         return self.buffers[key]
 
     # ---- one convolution ----------------------------------------------------------------------------------------
-    def _conv(self, idx, x_i8, key, act, want_i8=True, want_f32=False, residual=None, staged=False):
+    def _conv(self, idx, x_i8, key, act, want_i8=True, want_f32=False, residual=None, staged=False, leaky=0.0,
+              residual_after=False):
         L = self.convs[idx]
         c = L["spec"]
         out_i8 = self._i8(key + ".i8", c["oh"], c["o"]) if want_i8 else None
         out_f32 = self._f32(key + ".f32", c["oh"], c["o"]) if want_f32 else None
         L["plan"].run(None if staged else x_i8, LAYOUT_STAGED if staged else LAYOUT_NHWC_PAD, L["dq"], bias=L["bias"],
-                      residual=residual, activation=act, out_f32=out_f32, out_f32_layout=LAYOUT_NHWC_PAD, out_i8=out_i8,
-                      out_i8_layout=LAYOUT_NHWC_PAD,
-                      requant_scales=L["out_scale_arr"] if want_i8 else None)
+                      residual=residual, activation=act, leaky=leaky, out_f32=out_f32, out_f32_layout=LAYOUT_NHWC_PAD,
+                      out_i8=out_i8, out_i8_layout=LAYOUT_NHWC_PAD,
+                      requant_scales=L["out_scale_arr"] if want_i8 else None, residual_after_activation=residual_after)
         return out_i8, out_f32
+
+    def _calibrate_conv(self, idx, x_i8, key, act, residual=None, staged=False, leaky=0.0, residual_after=False):
+        """Fixes the layer's folded-BatchNorm factor (the convolution's own output is brought to a maximum of 4, so that
+        activations stay bounded through the network whatever the synthetic weight scales are) and returns the maximum
+        magnitude of the layer's fp32 output."""
+        L = self.convs[idx]
+        c = L["spec"]
+        f = self._f32(key + ".cal", c["oh"], c["o"])
+        src, layout = (None, LAYOUT_STAGED) if staged else (x_i8, LAYOUT_NHWC_PAD)
+        L["plan"].run(src, layout, L["dq"], out_f32=f, out_f32_layout=LAYOUT_NHWC_PAD)
+        m0 = float(f.abs().max())
+        L["bn"] = np.float32(4.0 / m0) if m0 > 0 else np.float32(1.0)
+        self._set_in_scale(idx, L["in_scale"])
+        L["plan"].run(src, layout, L["dq"], bias=L["bias"], residual=residual, activation=act, leaky=leaky, out_f32=f,
+                      out_f32_layout=LAYOUT_NHWC_PAD, residual_after_activation=residual_after)
+        m = float(f.abs().max())
+        del self.buffers[key + ".cal"]
+        return m
 
     def _set_in_scale(self, idx, scale):
         L = self.convs[idx]
@@ -139,20 +158,7 @@ class QuantResNet:
         self._set_in_scale(0, self.input_scale)
 
         def out_scale_of(idx, x_i8, key, act, residual=None, staged=False):
-            L = self.convs[idx]
-            c = L["spec"]
-            f = self._f32(key + ".cal", c["oh"], c["o"])
-            # folded BatchNorm: one factor per layer that brings the convolution's own output to a maximum of 4, so
-            # that activations stay bounded through the 53 layers whatever the synthetic weight scales are
-            L["plan"].run(None if staged else x_i8, LAYOUT_STAGED if staged else LAYOUT_NHWC_PAD, L["dq"], out_f32=f,
-                          out_f32_layout=LAYOUT_NHWC_PAD)
-            m0 = float(f.abs().max())
-            L["bn"] = np.float32(4.0 / m0) if m0 > 0 else np.float32(1.0)
-            self._set_in_scale(idx, L["in_scale"])
-            L["plan"].run(None if staged else x_i8, LAYOUT_STAGED if staged else LAYOUT_NHWC_PAD, L["dq"], bias=L["bias"],
-                          residual=residual, activation=act, out_f32=f, out_f32_layout=LAYOUT_NHWC_PAD)
-            m = float(f.abs().max())
-            del self.buffers[key + ".cal"]
+            m = self._calibrate_conv(idx, x_i8, key, act, residual=residual, staged=staged)
             return np.float32(127.0) / np.float32(m if m > 0 else 1.0)
 
         self.input_scale_arr = _lib.float_array([float(self.input_scale)] * self.batch)
@@ -223,3 +229,136 @@ class QuantResNet:
     def status(self):
         for L in self.convs:
             L["plan"].status()
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# CSPDarknet53-shaped backbone (configuration 3): LeakyReLU(0.1), Darknet shortcuts (fp32 add after the activation),
+# cross-stage partial routes joined by a channel concatenation
+# ---------------------------------------------------------------------------------------------------------------------
+LEAKY = 0.1
+
+
+def cspdarknet_spec(image=608, widths=(64, 128, 256, 512, 1024), blocks=(1, 2, 8, 8, 4), stem_channels=32):
+    """Topology of the CSPDarknet53 backbone as plain data (72 convolutions with the defaults)."""
+    convs = []
+
+    def conv(name, cin, cout, k, stride, size_in):
+        pad = k // 2
+        size_out = (size_in + 2 * pad - k) // stride + 1
+        convs.append(dict(name=name, c=cin, o=cout, k=k, stride=stride, pad=pad, h=size_in, oh=size_out))
+        return len(convs) - 1, size_out
+
+    stem, size = conv("stem", 3, stem_channels, 3, 1, image)
+    stages = []
+    cin = stem_channels
+    for si, (width, nblocks) in enumerate(zip(widths, blocks)):
+        name = "s%d" % (si + 1)
+        half = width if si == 0 else width // 2
+        inner = width // 2 if si == 0 else half          # bottleneck width of the residual blocks
+        st = dict(name=name)
+        st["down"], size = conv(name + ".down", cin, width, 3, 2, size)
+        st["route_a"], _ = conv(name + ".route_a", width, half, 1, 1, size)
+        st["route_b"], _ = conv(name + ".route_b", width, half, 1, 1, size)
+        st["blocks"] = []
+        for bi in range(nblocks):
+            b = dict(name="%sb%d" % (name, bi + 1))
+            b["conv1"], _ = conv(b["name"] + ".conv1", half, inner, 1, 1, size)
+            b["conv2"], _ = conv(b["name"] + ".conv2", inner, half, 3, 1, size)
+            st["blocks"].append(b)
+        st["post"], _ = conv(name + ".post", half, half, 1, 1, size)
+        st["transition"], _ = conv(name + ".transition", 2 * half, width, 1, 1, size)
+        st["half"], st["size"], st["width"] = half, size, width
+        stages.append(st)
+        cin = width
+    return dict(image=image, convs=convs, stem=stem, stages=stages, features=cin, final_size=size)
+
+
+def make_conv_params(spec, seed=0):
+    """Seeded synthetic convolution parameters only (networks without a classifier)."""
+    rng = np.random.default_rng(seed)
+    params = []
+    for c in spec["convs"]:
+        w = rng.integers(-127, 128, size=(c["o"], c["c"], c["k"], c["k"]), dtype=np.int8)
+        sw = rng.uniform(0.001, 0.01, size=c["o"]).astype(np.float32)
+        bias = (rng.standard_normal(c["o"]) * 0.1).astype(np.float32)
+        params.append(dict(w=w, sw=sw, bias=bias))
+    return dict(convs=params, fc_w=np.zeros((1, 1), np.float32), fc_b=np.zeros(1, np.float32))
+
+
+class QuantCSPDarknet(QuantResNet):
+    """The backbone on one GPU.  Every convolution is, in TenniS operator terms,
+    ``quantize -> conv2d_quantized -> add_bias -> leaky_relu [-> add]``; the two routes of a stage are requantized with the
+    same scale (that of the transition convolution's input) and joined by tsb_concat_i8_nhwc."""
+
+    def _concat(self, a, ca, b, cb, key, size):
+        out = self._i8(key, size, ca + cb)
+        check(self.lib.tsb_concat_i8_nhwc(a.data_ptr(), ca, b.data_ptr(), cb, out.data_ptr(), self.batch * size * size,
+                                          ops._stream_ptr()))
+        return out
+
+    def _scale(self, m):
+        return np.float32(127.0) / np.float32(m if m > 0 else 1.0)
+
+    def _walk(self, x, calibrate):
+        """One pass over the network; with calibrate=True every layer's scales are fixed just before it runs."""
+        spec = self.spec
+        act = _lib.ACT_LEAKY_RELU
+
+        def run(idx, x_i8, key, in_scale, out_scale=None, want_f32=False, residual=None, staged=False, want_i8=True):
+            if calibrate:
+                self._set_in_scale(idx, in_scale)
+                m = self._calibrate_conv(idx, x_i8, key, act, residual=residual, staged=staged, leaky=LEAKY,
+                                         residual_after=residual is not None)
+                self._set_out_scale(idx, out_scale if out_scale is not None else self._scale(m))
+            return self._conv(idx, x_i8, key, act, want_i8=want_i8, want_f32=want_f32, residual=residual, staged=staged,
+                              leaky=LEAKY, residual_after=residual is not None)
+
+        def peek_max(idx, x_i8, key, in_scale):
+            self._set_in_scale(idx, in_scale)
+            return self._calibrate_conv(idx, x_i8, key, act, leaky=LEAKY)
+
+        i0 = spec["stem"]
+        if calibrate:
+            amax = float(x.abs().max())
+            self.input_scale = np.float32(127.0) / np.float32(amax if amax > 0 else 1.0)
+            self.input_scale_arr = _lib.float_array([float(self.input_scale)] * self.batch)
+        self.convs[i0]["plan"].quantize_input(x, self.input_scale_arr)
+        cur, _ = run(i0, None, "stem", self.input_scale, staged=True)
+        cur_scale = self.convs[i0]["out_scale"]
+        for st in spec["stages"]:
+            half, size = st["half"], st["size"]
+            cur, _ = run(st["down"], cur, st["name"] + ".down", cur_scale)
+            s_down = self.convs[st["down"]]["out_scale"]
+            # route b: 1x1, residual blocks, 1x1
+            xb_i8, xb_f32 = run(st["route_b"], cur, st["name"] + ".rb", s_down, want_f32=True)
+            sb = self.convs[st["route_b"]]["out_scale"]
+            for b in st["blocks"]:
+                h, _ = run(b["conv1"], xb_i8, b["name"] + ".h", sb)
+                xb_i8, xb_f32 = run(b["conv2"], h, b["name"] + ".y", self.convs[b["conv1"]]["out_scale"], want_f32=True,
+                                    residual=xb_f32)
+                sb = self.convs[b["conv2"]]["out_scale"]
+            # the two tensors that are concatenated share the scale of the transition's input
+            if calibrate:
+                m_post = peek_max(st["post"], xb_i8, st["name"] + ".post", sb)
+                m_a = peek_max(st["route_a"], cur, st["name"] + ".ra", s_down)
+                s_cat = self._scale(max(m_post, m_a))
+            else:
+                s_cat = None
+            post, _ = run(st["post"], xb_i8, st["name"] + ".post", sb, out_scale=s_cat)
+            ra, _ = run(st["route_a"], cur, st["name"] + ".ra", s_down, out_scale=s_cat)
+            cat = self._concat(post, half, ra, half, st["name"] + ".cat", size)
+            cur, _ = run(st["transition"], cat, st["name"] + ".out", self.convs[st["post"]]["out_scale"])
+            cur_scale = self.convs[st["transition"]]["out_scale"]
+        return cur
+
+    def calibrate(self, x):
+        out = self._walk(x, calibrate=True)
+        self.calibrated = True
+        torch.cuda.synchronize()
+        return dict(input=self.input_scale, convs=[(L["in_scale"], L["out_scale"]) for L in self.convs],
+                    bn=[L["bn"] for L in self.convs])
+
+    def forward(self, x):
+        """x: fp32 NCHW [batch, 3, image, image] on the device -> int8 NHWC_PAD feature map of the last stage."""
+        assert self.calibrated, "call calibrate() first"
+        return self._walk(x, calibrate=False)

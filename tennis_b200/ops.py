@@ -169,8 +169,9 @@ class ConvPlan:
 
     def run(self, x, x_layout, dq, bias=None, residual=None, activation=ACT_NONE, leaky=0.0, out_f32=None,
             out_f32_layout=LAYOUT_NCHW, out_i8=None, out_i8_layout=LAYOUT_NCHW, requant_scales=None, out_acc=None,
-            stream=None):
+            stream=None, residual_after_activation=False):
         e = ConvEpilogue()
+        e.residual_after_activation = 1 if residual_after_activation else 0
         e.dequantize_scales = dq.data_ptr()
         e.bias = bias.data_ptr() if bias is not None else None
         e.residual = residual.data_ptr() if residual is not None else None

@@ -12,8 +12,26 @@ if ROOT not in sys.path:
 GOLDEN = os.path.join(ROOT, "tests", "golden")
 
 
+# a container may see every core of a big host while being allowed a few: keep the OpenMP runtimes modest
+os.environ.setdefault("OMP_WAIT_POLICY", "PASSIVE")
+if "OMP_NUM_THREADS" not in os.environ:
+    try:
+        os.environ["OMP_NUM_THREADS"] = str(min(16, len(os.sched_getaffinity(0))))
+    except AttributeError:
+        os.environ["OMP_NUM_THREADS"] = "8"
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+
+
+@pytest.fixture(autouse=True)
+def _stack_dump_if_stuck():
+    """If a test sits in one call for two minutes, the Python stacks of all threads go to stderr (the run goes on)."""
+    import faulthandler
+    faulthandler.dump_traceback_later(120, exit=False)
+    yield
+    faulthandler.cancel_dump_traceback_later()
 
 
 def golden_cases(prefix):

@@ -14,7 +14,8 @@ ACT = {"none": 0, "relu": 1, "leaky_relu": 2}
 
 
 def run_gpu(x, w, pad, stride, dil, dq, bias=None, act="none", leaky=0.0, padding_value=0.0, kernel=0,
-            x_layout="nchw", residual=None, rq=None, i8_layout="nchw", f32_layout="nchw", want_acc=True, want_f32=True):
+            x_layout="nchw", residual=None, rq=None, i8_layout="nchw", f32_layout="nchw", want_acc=True, want_f32=True,
+            res_after=False):
     """x int8 NCHW numpy.  Returns dict(kernel, acc, f32, i8) as NCHW numpy arrays."""
     from tennis_b200 import _lib, ops
     dev = torch.device("cuda")
@@ -42,7 +43,7 @@ def run_gpu(x, w, pad, stride, dil, dq, bias=None, act="none", leaky=0.0, paddin
              residual=res, activation=ACT[act], leaky=leaky, out_f32=out_f32,
              out_f32_layout=_lib.LAYOUT_NHWC_PAD if f32_nhwc else _lib.LAYOUT_NCHW, out_i8=out_i8,
              out_i8_layout=_lib.LAYOUT_NHWC_PAD if i8_layout == "nhwc" else _lib.LAYOUT_NCHW,
-             requant_scales=None if rq is None else list(rq), out_acc=out_acc)
+             requant_scales=None if rq is None else list(rq), out_acc=out_acc, residual_after_activation=res_after)
     plan.status()
     torch.cuda.synchronize()
     r = dict(kernel=plan.kernel)
@@ -64,9 +65,11 @@ def check_case(checker, port, x, w, pad, stride, dil, dq, bias, act, leaky, pv, 
     _, want_acc = port.conv2d_quantized(x, w, pad, stride, dil, dq, pv, return_acc=True)
     yb = checker.add_bias(want, bias) if bias is not None else want
     residual = kw.get("residual")
-    if residual is not None:
+    if residual is not None and not kw.get("res_after"):
         yb = (yb + residual).astype(np.float32)
     ya = checker.activation(yb, act, leaky)
+    if residual is not None and kw.get("res_after"):
+        ya = (ya + residual).astype(np.float32)
     got = run_gpu(x, w, pad, stride, dil, dq, bias, act, leaky, pv, kernel, **kw)
     if kw.get("want_acc", True):
         assert np.array_equal(got["acc"], want_acc), "int32 accumulators differ"
@@ -285,6 +288,47 @@ def test_epilogue_variants(checker, port, kernel):
             check_case(checker, port, *args, bias, "relu", 0.0, 0.0, kernel, residual=residual, rq=np.array([8.0], np.float32),
                        f32_layout=f32_layout, i8_layout=i8_layout)
     check_case(checker, port, *args, None, "leaky_relu", 0.25, 0.0, kernel, rq=np.array([0.5], np.float32))
+
+
+@pytest.mark.parametrize("kernel", [1, 2])
+@pytest.mark.parametrize("swap", [None, "0", "1"])
+def test_residual_after_the_activation(checker, port, monkeypatch, kernel, swap):
+    """A Darknet shortcut: leaky_relu(conv + bias) + residual, every output layout, both kernels and orientations."""
+    if swap is None:
+        monkeypatch.delenv("TSB_SWAP", raising=False)
+    else:
+        monkeypatch.setenv("TSB_SWAP", swap)
+    rng = np.random.default_rng(7)
+    N, C, H, W, O = 2, 64, 12, 12, 96
+    x = rng.integers(-128, 128, size=(N, C, H, W), dtype=np.int8)
+    w = rng.integers(-127, 128, size=(O, C, 3, 3), dtype=np.int8)
+    dq = rng.uniform(0.001, 0.01, size=O).astype(np.float32)
+    bias = (rng.standard_normal(O) * 0.1).astype(np.float32)
+    residual = rng.standard_normal((N, O, H, W)).astype(np.float32)
+    rq = rng.uniform(0.5, 2.0, size=N).astype(np.float32)
+    args = (x, w, (1, 1, 1, 1), (1, 1), (1, 1), dq)
+    for f32_layout, i8_layout in (("nhwc", "nhwc"), ("nchw", "nhwc"), ("nchw", "nchw")):
+        check_case(checker, port, *args, bias, "leaky_relu", 0.1, 0.0, kernel, residual=residual, rq=rq, res_after=True,
+                   x_layout="nhwc", f32_layout=f32_layout, i8_layout=i8_layout, want_acc=False)
+    w1 = rng.integers(-127, 128, size=(O, C, 1, 1), dtype=np.int8)
+    check_case(checker, port, x, w1, (0, 0, 0, 0), (1, 1), (1, 1), dq, bias, "relu", 0.0, 0.0, kernel, residual=residual, rq=rq,
+               res_after=True, x_layout="nhwc", f32_layout="nhwc", i8_layout="nhwc", want_acc=False)
+
+
+def test_concat_of_two_int8_tensors():
+    from tennis_b200 import _lib, ops
+    lib = _lib.load()
+    rng = np.random.default_rng(3)
+    for ca, cb in ((64, 64), (128, 64), (32, 48), (20, 7)):
+        px = 2 * 5 * 7
+        a = np.zeros((px, ops.padded_channels(ca)), dtype=np.int8); a[:, :ca] = rng.integers(-128, 128, size=(px, ca))
+        b = np.zeros((px, ops.padded_channels(cb)), dtype=np.int8); b[:, :cb] = rng.integers(-128, 128, size=(px, cb))
+        ad, bd = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+        y = torch.full((px, ops.padded_channels(ca + cb)), 99, dtype=torch.int8, device="cuda")
+        _lib.check(lib.tsb_concat_i8_nhwc(ad.data_ptr(), ca, bd.data_ptr(), cb, y.data_ptr(), px, ops._stream_ptr()))
+        got = y.cpu().numpy()
+        assert np.array_equal(got[:, :ca], a[:, :ca]) and np.array_equal(got[:, ca:ca + cb], b[:, :cb])
+        assert not got[:, ca + cb:].any()
 
 
 def test_rounding_ties_in_fused_requantize(checker, port):
