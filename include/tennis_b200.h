@@ -158,6 +158,13 @@ TSB_API int tsb_conv2d_i8_output_shape(const tsb_conv_plan *plan, int shape[4]);
 /* TSB_KERNEL_DIRECT or TSB_KERNEL_TCGEN05: what the plan resolved to */
 TSB_API int tsb_conv2d_i8_kernel(const tsb_conv_plan *plan);
 /*
+ * One line of text saying how the plan will run (kernel, load mode, MMA orientation, tile shape, tile counts,
+ * pipeline stages, shared memory) for its primary configuration and, after " | alt: ", for the configuration of the
+ * other orientation when the plan keeps one.  For logs and tests; returns the length written (without the
+ * terminating zero) or a negative status.
+ */
+TSB_API int tsb_conv2d_i8_plan_describe(const tsb_conv_plan *plan, char *text, size_t text_bytes);
+/*
  * Scratch the caller provides to tsb_conv2d_i8_run (256-byte aligned device memory, >= this many bytes):
  * the repacked weights and, for NCHW input, the NHWC_PAD staging of the activations.  The library
  * allocates no device memory itself.

@@ -66,7 +66,11 @@ def build(force=False):
     lib = os.path.join(_HERE, "liboracle.so")
     if force or not os.path.exists(lib) or os.path.getmtime(lib) < os.path.getmtime(os.path.join(_HERE, "oracle.c")):
         subprocess.check_call(["make", "-C", _HERE, "oracle"], stdout=subprocess.DEVNULL)
-    if os.path.isdir("/root/reference/src"):
+    # the reference build (324 files) only where its sources are present and the library is missing or older than
+    # its driver; a prebuilt library is used as it is
+    ref_lib = os.path.join(_HERE, "_ref", "libtsref.so")
+    stale = not os.path.exists(ref_lib) or os.path.getmtime(ref_lib) < os.path.getmtime(os.path.join(_HERE, "ref_driver.cpp"))
+    if os.path.isdir("/root/reference/src") and (force or stale):
         subprocess.check_call(["make", "-C", _HERE, "-j8", "ref"], stdout=subprocess.DEVNULL)
 
 

@@ -62,6 +62,7 @@ SYMBOLS = {
     "tsb_conv2d_i8_plan_destroy": (_i, [_vp]),
     "tsb_conv2d_i8_output_shape": (_i, [_vp, ctypes.POINTER(_i)]),
     "tsb_conv2d_i8_kernel": (_i, [_vp]),
+    "tsb_conv2d_i8_plan_describe": (_i, [_vp, ctypes.c_char_p, _sz]),
     "tsb_conv2d_i8_workspace_bytes": (_sz, [_vp]),
     "tsb_conv2d_i8_set_weights": (_i, [_vp, _vp, _vp, _sz, _vp]),
     "tsb_conv2d_i8_quantize_input": (_i, [_vp, _vp, _fp, _i, _vp, _sz, _vp]),

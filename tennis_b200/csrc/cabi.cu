@@ -204,6 +204,28 @@ int tsb_conv2d_i8_output_shape(const tsb_conv_plan *plan, int shape[4]) {
 
 int tsb_conv2d_i8_kernel(const tsb_conv_plan *plan) { return plan ? plan->kernel : TSB_ERR_INVALID_ARGUMENT; }
 
+int tsb_conv2d_i8_plan_describe(const tsb_conv_plan *plan, char *text, size_t text_bytes) {
+    if (!plan || !text || text_bytes < 2) return fail(TSB_ERR_INVALID_ARGUMENT, "plan_describe: null pointer");
+    auto one = [&](const tc::Config &c, char *dst, size_t n) {
+        const char *mode = c.patch ? "patch" : (plan->view.rows ? "rows" : (plan->view.a_tiled ? "tiled" : (plan->view.fold ? "fold" : "im2col")));
+        return snprintf(dst, n, "mode=%s swap=%d bn=%d bk=%d pix=%d tiles=%dx%d grid=%d stages=%d resident=%d smem=%u", mode, c.swap,
+                        c.bn, c.bk, c.pix, c.num_m_tiles, c.num_n_tiles, c.grid, c.stages, c.b_resident, c.dyn_smem);
+    };
+    int len;
+    if (plan->kernel != TSB_KERNEL_TCGEN05) {
+        len = snprintf(text, text_bytes, "kernel=direct (%s)", plan->why_not_tc);
+    } else {
+        len = snprintf(text, text_bytes, "kernel=tcgen05 ");
+        if (len > 0 && (size_t)len < text_bytes) len += one(plan->cfg, text + len, text_bytes - len);
+        if (plan->alt_valid && len > 0 && (size_t)len < text_bytes) {
+            len += snprintf(text + len, text_bytes - len, " | alt: ");
+            if ((size_t)len < text_bytes) len += one(plan->cfg_alt, text + len, text_bytes - len);
+        }
+    }
+    if (len < 0) return fail(TSB_ERR_INVALID_ARGUMENT, "plan_describe: formatting failed");
+    return (size_t)len < text_bytes ? len : (int)text_bytes - 1;
+}
+
 size_t tsb_conv2d_i8_workspace_bytes(const tsb_conv_plan *plan) { return plan ? plan->ws_bytes : 0; }
 
 int tsb_conv2d_i8_set_weights(tsb_conv_plan *plan, const int8_t *w_oihw, void *workspace, size_t workspace_bytes,

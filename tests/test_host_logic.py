@@ -109,6 +109,38 @@ def test_plan_create_validates_and_selects_kernel():
         assert st == _lib.ERR_INVALID_ARGUMENT, over
 
 
+def describe(**over):
+    lib = _lib.load()
+    st, h = create(desc(**over))
+    assert st == 0
+    buf = ctypes.create_string_buffer(512)
+    n = lib.tsb_conv2d_i8_plan_describe(h, buf, 512)
+    assert n > 0
+    lib.tsb_conv2d_i8_plan_destroy(h)
+    return buf.value.decode()
+
+
+def test_load_mode_and_orientation_of_the_benchmark_layers():
+    """Which variant of the tensor-core kernel the plan picks, layer by layer (no device needed)."""
+    same = dict(pad_top=1, pad_bottom=1, pad_left=1, pad_right=1)
+    none = dict(pad_top=0, pad_bottom=0, pad_left=0, pad_right=0)
+    stem = describe(n=32, c=3, h=224, w=224, o=64, kh=7, kw=7, stride_h=2, stride_w=2, pad_top=3, pad_bottom=3, pad_left=3, pad_right=3)
+    assert "mode=rows swap=0 bn=64 bk=64" in stem and "resident=1" in stem and "alt:" not in stem
+    c56 = describe(n=64, c=64, h=56, w=56, o=64, kh=3, kw=3, **same)
+    assert c56.startswith("kernel=tcgen05 mode=patch swap=0 bn=64 bk=64 pix=128 tiles=1792x1")
+    c28 = describe(n=64, c=128, h=28, w=28, o=128, kh=3, kw=3, **same)
+    assert "mode=patch swap=0 bn=128 bk=128" in c28.split(" | ")[0]
+    c14 = describe(n=64, c=256, h=14, w=14, o=256, kh=3, kw=3, **same)     # 590 KB of weights: no patch mode
+    assert "mode=im2col swap=0 bn=256 bk=128" in c14.split(" | ")[0]
+    s2 = describe(n=32, c=256, h=28, w=28, o=512, kh=3, kw=3, stride_h=2, stride_w=2, **same)
+    assert "mode=im2col" in s2.split(" | ")[0]
+    p1 = describe(n=32, c=256, h=14, w=14, o=1024, kh=1, kw=1, **none)
+    assert "mode=tiled swap=0 bn=128" in p1.split(" | ")[0] and "alt: mode=tiled swap=1" in p1   # 49 pixel tiles: narrower N
+    csp_stem = describe(n=16, c=3, h=608, w=608, o=32, kh=3, kw=3, **same)
+    assert "mode=rows" in csp_stem and "tiles=48640x1" in csp_stem
+    assert describe(padding_value=3.0).startswith("kernel=direct (non-zero padding_value)")
+
+
 def test_run_rejects_bad_arguments_before_any_launch():
     lib = _lib.load()
     before = lib.tsb_kernel_launch_count()
