@@ -567,14 +567,6 @@ __device__ __forceinline__ void rows_span(const KernelParams &kp, int oh, int &k
     kh_hi = min(kp.KH - 1, kp.d_dh.div(kp.rows_H - 1 - top));
 }
 
-#ifndef TSB_FENCE_EVERY_STAGE
-#define TSB_FENCE_EVERY_STAGE 1
-#endif
-#if TSB_FENCE_EVERY_STAGE
-#define TSB_STAGE_FENCE() tc_fence_after()
-#else
-#define TSB_STAGE_FENCE() do {} while (0)
-#endif
 constexpr int kModeGeneral = 0, kModeRows = 1, kModePatch = 2;
 constexpr int kMaxStages = 24;
 constexpr uint32_t kMaxDynamicSmem = 227 * 1024;
@@ -770,7 +762,7 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                             ok = false;
                             break;
                         }
-                        TSB_STAGE_FENCE();
+                        tc_fence_after();
                         if (cbi == 0) TSB_TRACE(local, 3);
                         const uint32_t sp = base + stage * kp.stage_bytes;
                         const uint32_t group_stride = (uint32_t)kp.patch_pw * BK;   // next tile row = next patch row
@@ -797,7 +789,7 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                         if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 3); }
                         break;
                     }
-                    TSB_STAGE_FENCE();
+                    tc_fence_after();
                     TSB_TRACE(local, 3);
                     const uint32_t sp = base + stage * kp.stage_bytes;
                     for (int kh = kh_lo; kh <= kh_hi; ++kh) {
@@ -818,7 +810,7 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                         ok = false;
                         break;
                     }
-                    TSB_STAGE_FENCE();
+                    tc_fence_after();
                     if (it == 0) TSB_TRACE(local, 3);
                     const uint32_t sp = base + stage * kp.stage_bytes;
                     const uint32_t sw = kp.b_resident ? w_res + (uint32_t)it * kWgtBytes : sp + kPixBytes;
