@@ -415,6 +415,49 @@ def run_ours(args):
                               conv_bytes=workloads.layer_bytes(l), conv_gbs=workloads.layer_bytes(l) / ms / 1e6,
                               quantize_gbs=5 * n_in / qms / 1e6))
 
+    # ---- configuration 0: the single batch-1 layer the reference runs on its CPU today; latency of quantize + conv ----
+    config0 = None
+    try:
+        l0 = workloads.CONFIG0[0]
+        d0 = workloads.make_layer_data(l0, seed=0)
+        x0 = torch.from_numpy(d0["x"]).to(dev)
+        plan0 = ops.ConvPlan(x0.shape, d0["w"].shape, (l0["pad"],) * 4, (l0["stride"],) * 2, (l0["dilation"],) * 2, 0.0, _lib.KERNEL_AUTO, dev)
+        plan0.set_weights(torch.from_numpy(d0["w"]).to(dev))
+        dq0, b0 = torch.from_numpy(d0["dq"]).to(dev), torch.from_numpy(d0["bias"]).to(dev)
+        out0 = torch.empty(plan0.out_shape, dtype=torch.float32, device=dev)
+        s0 = _lib.float_array([float(d0["qscale"])])
+
+        def run0():
+            plan0.quantize_input(x0, s0)
+            plan0.run(None, _lib.LAYOUT_STAGED, dq0, bias=b0, activation=_lib.ACT_RELU, out_f32=out0)
+        for _ in range(5):
+            run0()
+        ev0 = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(20)]
+        for a, b in ev0:
+            flush_l2()
+            a.record()
+            run0()
+            b.record()
+        torch.cuda.synchronize()
+        plan0.status()
+        us0 = statistics.median(a.elapsed_time(b) for a, b in ev0) * 1e3
+        config0 = {"workload": "config0: 1x64x56x56, 3x3 64->64, quantize + conv + bias + ReLU, fp32 NCHW out",
+                   "gpu_us": us0, "gpu_tops": workloads.layer_ops(l0) / us0 / 1e6,
+                   "note": "two launches, event-timed after an L2 flush (an event pair around an empty kernel reads ~6 us)"}
+        if world == 1 and rank == 0:
+            try:
+                from oracle import oracle as orc
+                chk0 = orc.best()
+                if chk0.kind == "reference":
+                    sec0, _ = chk0.time_layer(d0["x"], d0["w"], (l0["pad"],) * 4, (l0["stride"],) * 2, (l0["dilation"],) * 2,
+                                              float(d0["qscale"]), d0["dq"], d0["bias"], act=1, workers=1, repeats=3)
+                    config0["cpu_reference_us"] = sec0 * 1e6
+                    config0["cpu_reference_note"] = "the reference's operators, one Workbench with 1 computing thread (its correct setting)"
+            except Exception as e:
+                config0["cpu_reference_error"] = repr(e)[:200]
+    except Exception as e:
+        config0 = {"error": repr(e)[:200]}
+
     # ---- how fast this kernel's main loop runs when nothing else binds: a GEMM-shaped layer with int8 output ----
     probe = None
     try:
@@ -556,6 +599,8 @@ def run_ours(args):
             "gpu_launches": int(launches), "wall_s_timed_region": wall,
             "clocks": sampler.summary(), "roofline": roofline, "layers": per_layer,
         }
+        if config0 is not None:
+            line["config0"] = config0
         if resnet is not None:
             line["resnet50"] = resnet
         if csp is not None:

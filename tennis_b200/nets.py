@@ -362,3 +362,36 @@ class QuantCSPDarknet(QuantResNet):
         """x: fp32 NCHW [batch, 3, image, image] on the device -> int8 NHWC_PAD feature map of the last stage."""
         assert self.calibrated, "call calibrate() first"
         return self._walk(x, calibrate=False)
+
+
+def _main():
+    """python -m tennis_b200.nets {resnet50,cspdarknet53} [--batch N] [--passes K]: builds the synthetic network,
+    calibrates it on one random batch and runs K eager forward passes (what a profiler is pointed at)."""
+    import argparse
+    ap = argparse.ArgumentParser(description=_main.__doc__)
+    ap.add_argument("net", choices=["resnet50", "cspdarknet53"])
+    ap.add_argument("--batch", type=int, default=None)
+    ap.add_argument("--passes", type=int, default=3)
+    args = ap.parse_args()
+    if args.net == "resnet50":
+        batch = args.batch or 64
+        spec = resnet_spec()
+        net = QuantResNet(spec, make_params(spec, 0), batch)
+        x = torch.randn((batch, 3, 224, 224), device="cuda")
+    else:
+        batch = args.batch or 16
+        spec = cspdarknet_spec()
+        net = QuantCSPDarknet(spec, make_conv_params(spec, 0), batch)
+        x = torch.rand((batch, 3, 608, 608), device="cuda")
+    net.calibrate(x)
+    out = None
+    for _ in range(args.passes):
+        out = net.forward(x)
+    torch.cuda.synchronize()
+    net.status()
+    print("%s batch %d: %d convolutions, %.1f GOP per pass, output checksum %.6g"
+          % (args.net, batch, len(spec["convs"]), conv_ops(spec, batch) / 1e9, float(out.double().abs().sum())))
+
+
+if __name__ == "__main__":
+    _main()
