@@ -687,22 +687,27 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                         if (++stage == kStages) { stage = 0; phase ^= 1u; }
                     }
                 } else if (MODE == kModeRows) {
-                    // one copy per tile: the staged bytes from the first to the last input row the filter meets
+                    // One copy per output row (per run of its segments that this CTA owns): the staged bytes from the
+                    // first to the last input row the filter meets, from this segment to the end of the row.  The
+                    // following tiles of the same output row read the same stage at +2048 bytes per segment.
                     const int row_id = kp.d_segs.div(m_tile), seg = m_tile - row_id * kp.rows_segs;
-                    const int r_img = kp.d_OH.div(row_id), r_oh = row_id - r_img * kp.rows_OH;
-                    int kh_lo, kh_hi;
-                    rows_span(kp, r_oh, kh_lo, kh_hi);
-                    if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) {
-                        if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 1); }
-                        break;
+                    if (seg == 0 || i == 0) {
+                        const int r_img = kp.d_OH.div(row_id), r_oh = row_id - r_img * kp.rows_OH;
+                        int kh_lo, kh_hi;
+                        rows_span(kp, r_oh, kh_lo, kh_hi);
+                        if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) {
+                            if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 1); }
+                            break;
+                        }
+                        const int ih_lo = r_oh * kp.sh - kp.pad_t + kh_lo * kp.dh;
+                        const uint32_t bytes = (uint32_t)((kh_hi - kh_lo) * kp.dh) * (uint32_t)kp.rows_stride_h +
+                                               (uint32_t)(kp.rows_segs - 1 - seg) * (PIX * 16) + kp.rows_bytes;
+                        mbar_arrive_expect_tx(bar_full + 8 * stage, bytes);
+                        bulk_load(base + stage * kp.stage_bytes,
+                                  kp.rows_x + r_img * kp.rows_stride_n + ih_lo * kp.rows_stride_h + (long long)seg * (PIX * 16),
+                                  bytes, bar_full + 8 * stage);
+                        if (++stage == kStages) { stage = 0; phase ^= 1u; }
                     }
-                    const int ih_lo = r_oh * kp.sh - kp.pad_t + kh_lo * kp.dh;
-                    const uint32_t bytes = (uint32_t)((kh_hi - kh_lo) * kp.dh) * (uint32_t)kp.rows_stride_h + kp.rows_bytes;
-                    mbar_arrive_expect_tx(bar_full + 8 * stage, bytes);
-                    bulk_load(base + stage * kp.stage_bytes,
-                              kp.rows_x + r_img * kp.rows_stride_n + ih_lo * kp.rows_stride_h + (long long)seg * (PIX * 16),
-                              bytes, bar_full + 8 * stage);
-                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 } else
                 for (int kh = 0; kh < kp.KH && ok; ++kh)
                     for (int kw = 0; kw < kp.KW && ok; ++kw)
@@ -733,6 +738,7 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
             int cur_n = -1, w_loads = 0;
+            int rows_seg_first = 0;
             for (int local = 0; local < my_tiles && ok; ++local) {
                 int m_tile, n_tile;
                 decode(local, m_tile, n_tile);
@@ -782,16 +788,19 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                         if (++stage == kStages) { stage = 0; phase ^= 1u; }
                     }
                 } else if (!SWAP && MODE == kModeRows) {
-                    const int row_id = kp.d_segs.div(m_tile);
+                    const int row_id = kp.d_segs.div(m_tile), seg = m_tile - row_id * kp.rows_segs;
                     int kh_lo, kh_hi;
                     rows_span(kp, row_id - kp.d_OH.div(row_id) * kp.rows_OH, kh_lo, kh_hi);
-                    if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
-                        if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 3); }
-                        break;
+                    if (seg == 0 || local == 0) {      // the stage of this output row: loaded once, used by all its segments
+                        if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
+                            if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 3); }
+                            break;
+                        }
+                        tc_fence_after();
+                        rows_seg_first = seg;
                     }
-                    tc_fence_after();
                     TSB_TRACE(local, 3);
-                    const uint32_t sp = base + stage * kp.stage_bytes;
+                    const uint32_t sp = base + stage * kp.stage_bytes + (uint32_t)(seg - rows_seg_first) * (PIX * 16);
                     for (int kh = kh_lo; kh <= kh_hi; ++kh) {
                         const uint64_t da = smem_desc_sliding(sp + (uint32_t)((kh - kh_lo) * kp.dh) * (uint32_t)kp.rows_stride_h);
                         const uint64_t db = smem_desc<BK>(w_res + (uint32_t)kh * kWgtBytes);
@@ -801,8 +810,10 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                             accumulate = 1u;
                         }
                     }
-                    tc_commit(bar_empty + 8 * stage);
-                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                    if (seg == kp.rows_segs - 1 || local == my_tiles - 1) {
+                        tc_commit(bar_empty + 8 * stage);
+                        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                    }
                 } else
                 for (int it = 0; it < k_iters; ++it) {
                     if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
@@ -900,6 +911,17 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 #pragma unroll 1
                 for (int c = part; c < BN / CW; c += 4) {
                     const int col0 = c * CW;
+                    if (o_base + col0 >= epi.O) {
+                        // nothing but channel padding in this step: no accumulators to read, only the zero bytes the
+                        // NHWC_PAD layout wants in its padding channels
+                        if (live && epi.out_i8 && epi.i8_nhwc) {
+#pragma unroll
+                            for (int u = 0; u < CW; u += 16)
+                                if (o_base + col0 + u < epi.out_cp)
+                                    *reinterpret_cast<int4 *>(epi.out_i8 + (size_t)m * epi.out_cp + o_base + col0 + u) = make_int4(0, 0, 0, 0);
+                        }
+                        continue;
+                    }
                     const bool full = o_base + col0 + CW <= epi.O;
                     bool done = false;
                     if (full && kp.epi_mode != kEpiGeneric) {
@@ -1128,7 +1150,7 @@ bool make_view(const ConvGeom &g, View *view, const char **why) {
         // raw-row mode: pixel stride of exactly one 16-byte unit, every output row meets at least one input row, and
         // output rows long enough to fill most of a 128-pixel tile (TSB_ROWS=1/0 forces it on/off where it is possible)
         bool rows_ok = v.stride_w == 16 && (size_t)g.KH * bkf * std::min(round_up(g.O, 64), 256) <= 96 * 1024 &&
-                       (size_t)(g.KH - 1) * g.dh * v.stride_h + 4096 <= 40 * 1024;
+                       (size_t)(g.KH - 1) * g.dh * v.stride_h + (size_t)ceil_div(g.OW, kBM) * kBM * 16 + 2048 <= 48 * 1024;
         for (int oh = 0; oh < g.OH && rows_ok; ++oh) {
             bool any = false;
             for (int kh = 0; kh < g.KH; ++kh) {
@@ -1240,9 +1262,9 @@ Config choose_config(const View &v, int sm_count, int orientation) {
     c.grid = (int)(tiles < sm_count ? tiles : sm_count);
     // shared-memory plan: keep the CTA's whole weight tile resident when it is small enough to leave room for
     // at least four activation stages; otherwise stream activations and weights together
-    // raw-row mode stages, per tile, the KH staged image rows under 128 sliding windows (127 pixel strides of 16 bytes
-    // plus one window in the last row)
-    const uint32_t p_bytes = c.patch ? (uint32_t)round_up(c.patch_pw * c.patch_ph * c.bk, 1024) : v.rows ? (uint32_t)round_up((g.KH - 1) * g.dh * (int)v.stride_h + (kBM - 1) * 16 + c.bk, 128)
+    // raw-row mode stages, per output row, the KH staged image rows under all its segments of 128 sliding windows
+    // (127 pixel strides of 16 bytes plus one window in the last segment)
+    const uint32_t p_bytes = c.patch ? (uint32_t)round_up(c.patch_pw * c.patch_ph * c.bk, 1024) : v.rows ? (uint32_t)round_up((g.KH - 1) * g.dh * (int)v.stride_h + (v.rows_segs - 1) * kBM * 16 + (kBM - 1) * 16 + c.bk, 128)
                                     : (uint32_t)c.pix * c.bk;
     const uint32_t w_bytes = (uint32_t)c.ch * c.bk;
     const uint32_t k_iters = (uint32_t)g.KH * g.KW * (g.Cp / c.bk);

@@ -170,6 +170,9 @@ def test_both_mma_orientations(checker, port, monkeypatch, case, swap):
     (3, 3, 33, 35, 16, 7, 7, (3, 3, 3, 3), (2, 2), (1, 1)),
     (1, 3, 6, 260, 300, 3, 3, (1, 1, 1, 1), (2, 2), (1, 1)),     # two channel tiles: resident weights are reloaded
     (1, 5, 9, 40, 8, 3, 3, (2, 2, 1, 1), (1, 1), (1, 2)),        # two padding rows above, dilated taps inside a row
+    (1, 3, 120, 700, 32, 3, 3, (1, 1, 1, 1), (2, 2), (1, 1)),    # three segments per output row, 180 tiles on 148 CTAs:
+                                                                 # CTAs that start in the middle of a row, shared stages
+    (2, 3, 50, 390, 24, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1)),     # 16 bytes per pixel, four segments, 400 tiles
 ])
 def test_raw_row_mode(checker, port, monkeypatch, case):
     """Few input channels with a pixel stride of 16 staged bytes: the kernel copies each staged image row once per
