@@ -1,4 +1,5 @@
-// Operator "conv2d_quantized" on TenniS's "gpu" device, over libtennis_b200.so.
+// Operator "conv2d_quantized" on TenniS's "gpu" device, over libtennis_b200.so, and the compile-time rewrite that
+// folds the add_bias and activation after it into the same launch.
 //
 // The shell (fields, init, infer, run, scratch frame) is ts::base::Conv2DQuantized
 // (src/backend/base/base_conv2d_quantized.cpp:13-219); the compute core below takes the place of
@@ -10,6 +11,10 @@
 #include <core/tensor_builder.h>
 #include <global/operator_factory.h>
 #include <kernels/gpu/operator_on_gpu.h>
+#include <compiler/option/zipper_option.h>
+#include <module/menu.h>
+
+#include <atomic>
 
 #include <cstring>
 
@@ -26,6 +31,15 @@ namespace ts {
             void conv2d(const Tensor &x, const Padding2D &padding, float padding_value, const Tensor &w,
                         const Stride2D &stride, const Dilation2D &dilation, Conv2DFormat format,
                         std::vector<float> dequantize_scales, Tensor &out, Stack &stack) override {
+                conv2d_fused(x, padding, padding_value, w, stride, dilation, format, dequantize_scales, out, stack, nullptr,
+                             TSB_ACT_NONE, 0.0f);
+            }
+
+            // conv2d_quantized -> add_bias -> relu | leaky_relu in one launch (bias: device pointer or null)
+            void conv2d_fused(const Tensor &x, const Padding2D &padding, float padding_value, const Tensor &w,
+                              const Stride2D &stride, const Dilation2D &dilation, Conv2DFormat format,
+                              std::vector<float> dequantize_scales, Tensor &out, Stack &stack, const float *bias,
+                              int activation, float leaky) {
                 (void) stack;
                 if (format != FORMAT_NCHW) {
                     TS_LOG_ERROR << "Conv2D_quantized only support NCHW" << eject;
@@ -67,7 +81,9 @@ namespace ts {
                 tsb_conv_epilogue epilogue;
                 std::memset(&epilogue, 0, sizeof(epilogue));
                 epilogue.dequantize_scales = m_scales.data<float>();
-                epilogue.activation = TSB_ACT_NONE;
+                epilogue.bias = bias;
+                epilogue.activation = activation;
+                epilogue.leaky_scale = leaky;
                 epilogue.out_f32 = out.data<float>();
                 epilogue.out_f32_layout = TSB_LAYOUT_NCHW;
                 check(tsb_conv2d_i8_run(m_plan, x.data<int8_t>(), TSB_LAYOUT_NCHW, &epilogue, m_workspace.data(),
@@ -84,9 +100,118 @@ namespace ts {
         };
 
         using Conv2DQuantized = base::Conv2DWithCore<gpu::OperatorOnGPU<base::Conv2DQuantized>, Conv2DQuantizedCore>;
+
+        // "b200_conv2d_quantized_fused": conv2d_quantized with the add_bias and relu / leaky_relu that follow it folded
+        // into the convolution's epilogue.  Same inputs (x int8, w int8), attributes and fp32 NCHW output as
+        // conv2d_quantized, plus the bias (a constant of the graph) and the activation as attributes.  Never written by
+        // hand: the zipper option below puts it into the graph when a module is compiled for the gpu device.
+        class Conv2DQuantizedFused : public gpu::OperatorOnGPU<base::Conv2DQuantized> {
+        public:
+            using self = Conv2DQuantizedFused;
+            using supper = gpu::OperatorOnGPU<base::Conv2DQuantized>;
+
+            Conv2DQuantizedFused() {
+                field(fused_bias(), OPTIONAL);
+                field(fused_activation(), OPTIONAL, tensor::from<int32_t>(TSB_ACT_NONE));
+                field(fused_leaky(), OPTIONAL, tensor::from<float>(0.0f));
+            }
+
+            static const std::string &op_name() { static const std::string n = "b200_conv2d_quantized_fused"; return n; }
+            static const std::string &fused_bias() { static const std::string n = "b200_bias"; return n; }
+            static const std::string &fused_activation() { static const std::string n = "b200_activation"; return n; }
+            static const std::string &fused_leaky() { static const std::string n = "b200_leaky_scale"; return n; }
+
+            void init() override {
+                supper::init();
+                m_activation = tensor::to_int(get(fused_activation()));
+                m_leaky = tensor::to_float(get(fused_leaky()));
+                m_has_bias = has(fused_bias());
+                if (m_has_bias) m_bias_host = tensor::cast(FLOAT32, get(fused_bias()));
+            }
+
+            void conv2d(const Tensor &x, const Padding2D &padding, float padding_value, const Tensor &w,
+                        const Stride2D &stride, const Dilation2D &dilation, Conv2DFormat format,
+                        std::vector<float> dequantize_scales, Tensor &out, Stack &stack) override {
+                const float *bias = nullptr;
+                if (m_has_bias) {
+                    if (m_bias_host.count() != w.size(0)) {
+                        TS_LOG_ERROR << op_name() << ": bias has " << m_bias_host.count() << " entries for " << w.size(0)
+                                     << " output channels" << eject;
+                    }
+                    if (m_bias_device.count() != m_bias_host.count()) m_bias_device = m_bias_host.view(out.device()).clone();
+                    bias = m_bias_device.data<float>();
+                }
+                m_core.conv2d_fused(x, padding, padding_value, w, stride, dilation, format, dequantize_scales, out, stack, bias,
+                                    m_activation, m_leaky);
+                fused_runs().fetch_add(1);
+            }
+
+            static std::atomic<long> &fused_runs() { static std::atomic<long> n(0); return n; }
+
+        private:
+            b200::Conv2DQuantizedCore m_core;   // the class above, not the base interface of the same name
+            int m_activation = TSB_ACT_NONE;
+            float m_leaky = 0.0f;
+            bool m_has_bias = false;
+            Tensor m_bias_host, m_bias_device;
+        };
+
+        // Graph rewrite at compile time (src/compiler/zipper.cpp:20-62 visits every node of the module once):
+        //   relu | leaky_relu ( add_bias ( conv2d_quantized(x, w), <const bias> ) )  ->  b200_conv2d_quantized_fused(x, w)
+        // on the gpu device, when the bias is a constant over the channel dimension of an NCHW tensor and neither
+        // intermediate result has another consumer.  The fused node keeps the name of the activation node, so the
+        // module's outputs are found as before.
+        class ConvBiasActivationZipper : public ZipperOption {
+        public:
+            bool zip(const ComputingDevice &device, Node node, Node &zipped_node) const override {
+                if (device.type() != GPU) return false;
+                const Bubble &act = node.bubble();
+                int activation;
+                float leaky = 0.0f;
+                if (act.op() == name::layer::relu()) activation = TSB_ACT_RELU;
+                else if (act.op() == "leaky_relu") {   // src/backend/base/base_leaky_relu.cpp registers it under this name
+                    activation = TSB_ACT_LEAKY_RELU;
+                    if (!act.has(name::scale)) return false;
+                    leaky = tensor::to_float(act.get(name::scale));
+                } else return false;
+                auto act_inputs = node.inputs();
+                if (act_inputs.size() != 1) return false;
+                Node biased = act_inputs[0];
+                if (biased.bubble().op() != name::layer::add_bias() || biased.outputs().size() != 1) return false;
+                if (biased.bubble().has(name::format)) {
+                    if (tensor::to_string(biased.bubble().get(name::format)) != name::NCHW) return false;
+                } else if (biased.bubble().has(name::dim)) {
+                    if (tensor::to_int(biased.bubble().get(name::dim)) != 1) return false;
+                } else return false;
+                auto biased_inputs = biased.inputs();
+                if (biased_inputs.size() != 2) return false;
+                Node conv = biased_inputs[0], bias = biased_inputs[1];
+                if (conv.bubble().op() != name::layer::conv2d_quantized() || conv.outputs().size() != 1) return false;
+                if (bias.bubble().op() != Bubble::Const || !bias.bubble().has(name::value)) return false;
+                if (conv.bubble().has(name::format) && tensor::to_string(conv.bubble().get(name::format)) != name::NCHW) return false;
+
+                Node fused = bubble::op(act.name(), Conv2DQuantizedFused::op_name(), conv.inputs());
+                for (auto &param : conv.bubble().params()) {
+                    if (!param.first.empty() && param.first[0] == Bubble::retention_param_sign) continue;   // #name, #op, ...
+                    fused.bubble().set(param.first, param.second);
+                }
+                fused.bubble().set(Conv2DQuantizedFused::fused_bias(), tensor::cast(FLOAT32, bias.bubble().get(name::value)));
+                fused.bubble().set(Conv2DQuantizedFused::fused_activation(), tensor::from<int32_t>(activation));
+                fused.bubble().set(Conv2DQuantizedFused::fused_leaky(), tensor::from<float>(leaky));
+                zipped_node = fused;
+                return true;
+            }
+        };
     }
+}
+
+// how many times the fused operator has run in this process (drop-in tests read it)
+extern "C" __attribute__((visibility("default"))) long tsb_plugin_fused_runs() {
+    return ts::b200::Conv2DQuantizedFused::fused_runs().load();
 }
 
 using namespace ts;
 using namespace b200;
 TS_REGISTER_OPERATOR(Conv2DQuantized, ts::GPU, name::layer::conv2d_quantized())
+TS_REGISTER_OPERATOR(Conv2DQuantizedFused, ts::GPU, Conv2DQuantizedFused::op_name())
+TS_REGISTER_ZIPPER_OPTION(ConvBiasActivationZipper)

@@ -1,7 +1,7 @@
 // Drop-in test driver (test infrastructure): runs the SAME TenniS graph -- quantize -> conv2d_quantized ->
 // add_bias -> relu, built with the reference's own graph API and loaded with Workbench::Load -- once on the
 // reference's CPU device and once on its "gpu" device, where tennis_b200/plugin has registered the B200
-// operators, and compares the outputs.  Also runs the two operators alone through offline_create/offline_run.
+// operators and the compile-time rewrite that folds add_bias and relu into the convolution, and compares the outputs.  Also runs the two operators alone through offline_create/offline_run.
 //
 // Built against the reference headers and linked to the CUDA host build of the reference
 // (oracle/_ref/libtennis_cuda.so) and to libtennis_b200_ops.so, whose static initialisers do the registration.
@@ -22,6 +22,8 @@
 #include <vector>
 
 #include "tennis_b200.h"
+
+extern "C" long tsb_plugin_fused_runs();   // tennis_b200/plugin/gpu_conv2d_quantized.cpp
 
 using namespace ts;
 
@@ -152,12 +154,16 @@ int tsplug_selftest(int n, int c, int h, int w, int o, int k, int stride, int pa
         long bad_y = mismatches_f32(y_cpu, y_gpu);
         const int64_t launches_ops = tsb_kernel_launch_count() - launches0;
         Tensor g_cpu = run_graph(CPU, cs, d);
+        const long fused0 = tsb_plugin_fused_runs();
         Tensor g_gpu = run_graph(GPU, cs, d);
+        // compiling for the gpu device folds add_bias and relu into the convolution (two runs of the graph)
+        const long fused = tsb_plugin_fused_runs() - fused0;
         long bad_g = mismatches_f32(g_cpu, g_gpu);
         const int64_t launches_all = tsb_kernel_launch_count() - launches0;
-        std::snprintf(msg, msglen, "quantize mismatch=%ld conv mismatches=%ld graph mismatches=%ld of %d; b200 kernel launches: ops=%lld total=%lld",
-                      bad_q, bad_y, bad_g, g_cpu.count(), (long long) launches_ops, (long long) launches_all);
+        std::snprintf(msg, msglen, "quantize mismatch=%ld conv mismatches=%ld graph mismatches=%ld of %d; b200 kernel launches: ops=%lld total=%lld; fused operator runs=%ld",
+                      bad_q, bad_y, bad_g, g_cpu.count(), (long long) launches_ops, (long long) launches_all, fused);
         if (launches_ops < 2) return 2;  // the gpu workbench did not reach the B200 operators (CPU fallback)
+        if (fused != 2) return 3;        // the graph rewrite did not happen
         return (bad_q == 0 && bad_y == 0 && bad_g == 0) ? 0 : 1;
     } catch (const std::exception &e) {
         std::snprintf(msg, msglen, "exception: %s", e.what());

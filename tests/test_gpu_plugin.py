@@ -34,3 +34,4 @@ def test_graph_runs_unchanged_on_gpu_device(driver, case):
     text = msg.value.decode(errors="replace")
     assert rc == 0, text
     assert "graph mismatches=0" in text
+    assert "fused operator runs=2" in text      # the compiled gpu program runs conv + bias + relu as one operator
