@@ -35,7 +35,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 15.2e6
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 15.7e6
 METRIC = "int8_conv_tops"
 UNIT = "TOPS"
 WORKLOAD = "config1: int8 conv2d shape sweep, batch 32 (1x1 256->1024@14, 3x3 128->128@28, 3x3/2 256->512@28, 1x1 2048->512@7, 7x7/2 3->64@224), fp32 NCHW out, bias+ReLU"
