@@ -11,6 +11,7 @@
 #include <core/tensor_builder.h>
 #include <global/operator_factory.h>
 #include <kernels/gpu/operator_on_gpu.h>
+#include <backend/common_function.h>
 #include <compiler/option/zipper_option.h>
 #include <module/menu.h>
 
@@ -39,13 +40,17 @@ namespace ts {
             void conv2d_fused(const Tensor &x, const Padding2D &padding, float padding_value, const Tensor &w,
                               const Stride2D &stride, const Dilation2D &dilation, Conv2DFormat format,
                               std::vector<float> dequantize_scales, Tensor &out, Stack &stack, const float *bias,
-                              int activation, float leaky) {
+                              int activation, float leaky, const std::vector<float> *quantize_scales = nullptr) {
                 (void) stack;
                 if (format != FORMAT_NCHW) {
                     TS_LOG_ERROR << "Conv2D_quantized only support NCHW" << eject;
                 }
-                if (x.dtype() != INT8) {
+                // quantize_scales given: x is the fp32 tensor the folded quantize operator would have read
+                if (quantize_scales == nullptr && x.dtype() != INT8) {
                     TS_LOG_ERROR << "Conv2D_quantized not support this data type: " << type_str(x.dtype()) << eject;
+                }
+                if (quantize_scales != nullptr && x.dtype() != FLOAT32) {
+                    TS_LOG_ERROR << "quantize not support data type(" << x.dtype() << "): " << type_str(x.dtype()) << eject;
                 }
                 const std::string op = "conv2d_quantized";
                 auto stream = stream_on_context();
@@ -86,6 +91,14 @@ namespace ts {
                 epilogue.leaky_scale = leaky;
                 epilogue.out_f32 = out.data<float>();
                 epilogue.out_f32_layout = TSB_LAYOUT_NCHW;
+                if (quantize_scales != nullptr) {
+                    // fp32 NCHW -> the plan's own staged int8 layout, then the convolution reads it in place
+                    check(tsb_conv2d_i8_quantize_input(m_plan, x.data<float>(), quantize_scales->data(), int(quantize_scales->size()),
+                                                       m_workspace.data(), m_workspace_bytes, stream), op);
+                    check(tsb_conv2d_i8_run(m_plan, nullptr, TSB_LAYOUT_STAGED, &epilogue, m_workspace.data(), m_workspace_bytes,
+                                            stream), op);
+                    return;
+                }
                 check(tsb_conv2d_i8_run(m_plan, x.data<int8_t>(), TSB_LAYOUT_NCHW, &epilogue, m_workspace.data(),
                                         m_workspace_bytes, stream), op);
             }
@@ -114,12 +127,16 @@ namespace ts {
                 field(fused_bias(), OPTIONAL);
                 field(fused_activation(), OPTIONAL, tensor::from<int32_t>(TSB_ACT_NONE));
                 field(fused_leaky(), OPTIONAL, tensor::from<float>(0.0f));
+                field(fused_quantize_scale(), OPTIONAL);
             }
 
             static const std::string &op_name() { static const std::string n = "b200_conv2d_quantized_fused"; return n; }
             static const std::string &fused_bias() { static const std::string n = "b200_bias"; return n; }
             static const std::string &fused_activation() { static const std::string n = "b200_activation"; return n; }
             static const std::string &fused_leaky() { static const std::string n = "b200_leaky_scale"; return n; }
+            // present when the quantize operator in front of the convolution was folded in: the operator's first input
+            // is then the fp32 tensor, and this is that operator's quantize_scale attribute (one scale per sample)
+            static const std::string &fused_quantize_scale() { static const std::string n = "b200_quantize_scale"; return n; }
 
             void init() override {
                 supper::init();
@@ -127,11 +144,68 @@ namespace ts {
                 m_leaky = tensor::to_float(get(fused_leaky()));
                 m_has_bias = has(fused_bias());
                 if (m_has_bias) m_bias_host = tensor::cast(FLOAT32, get(fused_bias()));
+                m_folded_quantize = has(fused_quantize_scale());
+                if (m_folded_quantize) {
+                    m_quantize_scales = tensor::array::to_float(get(fused_quantize_scale()));
+                    // the shell keeps its parsed attributes private; the folded path needs them again (the shell's init()
+                    // above has already validated them: src/backend/base/base_conv2d_quantized.cpp:36-117)
+                    if (tensor::to_string(get(name::format)) != name::NCHW) {
+                        TS_LOG_ERROR << op_name() << " folds quantize only for format NCHW" << eject;
+                    }
+                    auto padding = tensor::cast(INT32, get(name::padding));
+                    auto stride = tensor::cast(INT32, get(name::stride));
+                    auto dilation = tensor::cast(INT32, has(name::dilation) ? get(name::dilation) : get(name::typo::dialations));
+                    m_padding = Padding2D(padding.data<int32_t>(4), padding.data<int32_t>(5), padding.data<int32_t>(6), padding.data<int32_t>(7));
+                    m_stride = Stride2D(stride.data<int32_t>(2), stride.data<int32_t>(3));
+                    m_dilation = Dilation2D(dilation.data<int32_t>(2), dilation.data<int32_t>(3));
+                    m_padding_value = tensor::to_float(get(name::padding_value));
+                    m_dequantize_scales = tensor::array::to_float(get(name::dequantize_scales));
+                }
+            }
+
+            // With the quantize folded in, the first input is fp32: the shell's infer/run (which insist on int8) are
+            // replaced by the same steps on the fp32 tensor.
+            int infer(Stack &stack, std::vector<Tensor::Prototype> &output) override {
+                if (!m_folded_quantize) return supper::infer(stack, output);
+                TS_AUTO_CHECK(stack.size() == 2);
+                auto x = stack[0];
+                auto w = stack[1];
+                TS_AUTO_CHECK(x.dims() == 4);
+                TS_AUTO_CHECK(w.dims() == 4);
+                TS_AUTO_CHECK(x.dtype() == FLOAT32);
+                TS_AUTO_CHECK(w.dtype() == INT8);
+                TS_AUTO_CHECK(w.size(1) == x.size(1));
+                TS_AUTO_CHECK(int(m_quantize_scales.size()) == x.size(0));      // base_quantize.cpp:26
+                TS_AUTO_CHECK(int(m_dequantize_scales.size()) == w.size(0));
+                Size2D y = conv2d_forward(Size2D(x.size(2), x.size(3)), m_padding, Size2D(w.size(2), w.size(3)), m_stride, m_dilation);
+                output.resize(1);
+                output[0] = Tensor::Prototype(FLOAT32, {x.size(0), w.size(0), y.height, y.width});
+                return 1;
+            }
+
+            int run(Stack &stack) override {
+                if (!m_folded_quantize) return supper::run(stack);
+                std::vector<Tensor::Prototype> protos;
+                infer(stack, protos);
+                auto memory_device = running_memory_device();
+                Tensor x = stack[0].view(memory_device);
+                Tensor w = stack[1].view(memory_device);
+                Tensor out = *stack.push(protos[0], memory_device);
+                run_core(x, m_padding, m_padding_value, w, m_stride, m_dilation, FORMAT_NCHW, m_dequantize_scales, out, stack,
+                         &m_quantize_scales);
+                return 1;
             }
 
             void conv2d(const Tensor &x, const Padding2D &padding, float padding_value, const Tensor &w,
                         const Stride2D &stride, const Dilation2D &dilation, Conv2DFormat format,
                         std::vector<float> dequantize_scales, Tensor &out, Stack &stack) override {
+                run_core(x, padding, padding_value, w, stride, dilation, format, dequantize_scales, out, stack, nullptr);
+            }
+
+            void run_core(const Tensor &x, const Padding2D &padding, float padding_value, const Tensor &w,
+                          const Stride2D &stride, const Dilation2D &dilation, Conv2DFormat format,
+                          const std::vector<float> &dequantize_scales, Tensor &out, Stack &stack,
+                          const std::vector<float> *quantize_scales) {
                 const float *bias = nullptr;
                 if (m_has_bias) {
                     if (m_bias_host.count() != w.size(0)) {
@@ -142,11 +216,13 @@ namespace ts {
                     bias = m_bias_device.data<float>();
                 }
                 m_core.conv2d_fused(x, padding, padding_value, w, stride, dilation, format, dequantize_scales, out, stack, bias,
-                                    m_activation, m_leaky);
+                                    m_activation, m_leaky, quantize_scales);
                 fused_runs().fetch_add(1);
+                if (quantize_scales) folded_quantize_runs().fetch_add(1);
             }
 
             static std::atomic<long> &fused_runs() { static std::atomic<long> n(0); return n; }
+            static std::atomic<long> &folded_quantize_runs() { static std::atomic<long> n(0); return n; }
 
         private:
             b200::Conv2DQuantizedCore m_core;   // the class above, not the base interface of the same name
@@ -154,10 +230,17 @@ namespace ts {
             float m_leaky = 0.0f;
             bool m_has_bias = false;
             Tensor m_bias_host, m_bias_device;
+            bool m_folded_quantize = false;
+            std::vector<float> m_quantize_scales, m_dequantize_scales;
+            Padding2D m_padding;
+            Stride2D m_stride;
+            Dilation2D m_dilation;
+            float m_padding_value = 0.0f;
         };
 
         // Graph rewrite at compile time (src/compiler/zipper.cpp:20-62 visits every node of the module once):
         //   relu | leaky_relu ( add_bias ( conv2d_quantized(x, w), <const bias> ) )  ->  b200_conv2d_quantized_fused(x, w)
+        //   ... and with x = quantize(x32) read by nothing else                       ->  b200_conv2d_quantized_fused(x32, w)
         // on the gpu device, when the bias is a constant over the channel dimension of an NCHW tensor and neither
         // intermediate result has another consumer.  The fused node keeps the name of the activation node, so the
         // module's outputs are found as before.
@@ -190,7 +273,20 @@ namespace ts {
                 if (bias.bubble().op() != Bubble::Const || !bias.bubble().has(name::value)) return false;
                 if (conv.bubble().has(name::format) && tensor::to_string(conv.bubble().get(name::format)) != name::NCHW) return false;
 
-                Node fused = bubble::op(act.name(), Conv2DQuantizedFused::op_name(), conv.inputs());
+                // quantize(x) in front of the convolution, read by nothing else: the fused operator takes x itself and
+                // quantizes it straight into the layout its kernel reads
+                std::vector<Node> fused_inputs = conv.inputs();
+                if (fused_inputs.size() != 2) return false;
+                Tensor folded_scales;
+                {
+                    Node q = fused_inputs[0];
+                    if (q.bubble().op() == name::layer::quantize() && q.outputs().size() == 1 && q.inputs().size() == 1 &&
+                        q.bubble().has(name::quantize_scale)) {
+                        folded_scales = tensor::cast(FLOAT32, q.bubble().get(name::quantize_scale));
+                        fused_inputs[0] = q.input(0);
+                    }
+                }
+                Node fused = bubble::op(act.name(), Conv2DQuantizedFused::op_name(), fused_inputs);
                 for (auto &param : conv.bubble().params()) {
                     if (!param.first.empty() && param.first[0] == Bubble::retention_param_sign) continue;   // #name, #op, ...
                     fused.bubble().set(param.first, param.second);
@@ -198,6 +294,7 @@ namespace ts {
                 fused.bubble().set(Conv2DQuantizedFused::fused_bias(), tensor::cast(FLOAT32, bias.bubble().get(name::value)));
                 fused.bubble().set(Conv2DQuantizedFused::fused_activation(), tensor::from<int32_t>(activation));
                 fused.bubble().set(Conv2DQuantizedFused::fused_leaky(), tensor::from<float>(leaky));
+                if (!folded_scales.empty()) fused.bubble().set(Conv2DQuantizedFused::fused_quantize_scale(), folded_scales);
                 zipped_node = fused;
                 return true;
             }
@@ -208,6 +305,10 @@ namespace ts {
 // how many times the fused operator has run in this process (drop-in tests read it)
 extern "C" __attribute__((visibility("default"))) long tsb_plugin_fused_runs() {
     return ts::b200::Conv2DQuantizedFused::fused_runs().load();
+}
+// ... and how many of those runs had the quantize operator folded in
+extern "C" __attribute__((visibility("default"))) long tsb_plugin_folded_quantize_runs() {
+    return ts::b200::Conv2DQuantizedFused::folded_quantize_runs().load();
 }
 
 using namespace ts;

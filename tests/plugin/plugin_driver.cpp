@@ -23,7 +23,8 @@
 
 #include "tennis_b200.h"
 
-extern "C" long tsb_plugin_fused_runs();   // tennis_b200/plugin/gpu_conv2d_quantized.cpp
+extern "C" long tsb_plugin_fused_runs();             // tennis_b200/plugin/gpu_conv2d_quantized.cpp
+extern "C" long tsb_plugin_folded_quantize_runs();
 
 using namespace ts;
 
@@ -84,7 +85,8 @@ void set_conv_params(Bubble &b, const Case &cs, const Data &d) {
 }
 
 // the quantized layer as a TenniS graph, compiled and run on `device`
-Tensor run_graph(const std::string &device, const Case &cs, const Data &d) {
+// keep_q: the quantized tensor is a second output of the module, so the quantize operator has to stay in the program
+Tensor run_graph(const std::string &device, const Case &cs, const Data &d, bool keep_q = false) {
     Graph g;
     ctx::bind<Graph> _graph(g);
     auto x = bubble::param("x");
@@ -98,7 +100,8 @@ Tensor run_graph(const std::string &device, const Case &cs, const Data &d) {
     biased.bubble().set(name::format, tensor::from("NCHW"));
     auto y = bubble::op("y", name::layer::relu(), {biased});
     std::shared_ptr<Module> m = std::make_shared<Module>();
-    m->load(g, {"y"});
+    if (keep_q) m->load(g, std::vector<std::string>{"y", "q"});
+    else m->load(g, {"y"});
     ComputingDevice cd(device, 0);
     Workbench::shared bench = Workbench::Load(m, cd);
     if (device == CPU) bench->runtime().set_computing_thread_number(1);
@@ -155,15 +158,23 @@ int tsplug_selftest(int n, int c, int h, int w, int o, int k, int stride, int pa
         const int64_t launches_ops = tsb_kernel_launch_count() - launches0;
         Tensor g_cpu = run_graph(CPU, cs, d);
         const long fused0 = tsb_plugin_fused_runs();
+        const long folded_start = tsb_plugin_folded_quantize_runs();
         Tensor g_gpu = run_graph(GPU, cs, d);
         // compiling for the gpu device folds add_bias and relu into the convolution (two runs of the graph)
         const long fused = tsb_plugin_fused_runs() - fused0;
-        long bad_g = mismatches_f32(g_cpu, g_gpu);
+        const long folded0 = tsb_plugin_folded_quantize_runs();
+        // ... and, the quantize being read by the convolution alone, folds it in as well.  A module that also outputs
+        // the quantized tensor keeps its quantize operator for that output and must still give the same y.
+        Tensor g_gpu_q = run_graph(GPU, cs, d, true);
+        const long folded = folded0 - folded_start;   // the two runs of the first gpu graph
+        long bad_g = mismatches_f32(g_cpu, g_gpu) + mismatches_f32(g_cpu, g_gpu_q);
         const int64_t launches_all = tsb_kernel_launch_count() - launches0;
-        std::snprintf(msg, msglen, "quantize mismatch=%ld conv mismatches=%ld graph mismatches=%ld of %d; b200 kernel launches: ops=%lld total=%lld; fused operator runs=%ld",
-                      bad_q, bad_y, bad_g, g_cpu.count(), (long long) launches_ops, (long long) launches_all, fused);
+        std::snprintf(msg, msglen, "quantize mismatch=%ld conv mismatches=%ld graph mismatches=%ld of %d; b200 kernel launches: ops=%lld total=%lld; fused operator runs=%ld; quantize folded=%d",
+                      bad_q, bad_y, bad_g, g_cpu.count(), (long long) launches_ops, (long long) launches_all, fused,
+                      int(folded >= 2));
         if (launches_ops < 2) return 2;  // the gpu workbench did not reach the B200 operators (CPU fallback)
         if (fused != 2) return 3;        // the graph rewrite did not happen
+        if (folded < 2) return 4;
         return (bad_q == 0 && bad_y == 0 && bad_g == 0) ? 0 : 1;
     } catch (const std::exception &e) {
         std::snprintf(msg, msglen, "exception: %s", e.what());

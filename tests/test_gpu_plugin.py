@@ -35,3 +35,4 @@ def test_graph_runs_unchanged_on_gpu_device(driver, case):
     assert rc == 0, text
     assert "graph mismatches=0" in text
     assert "fused operator runs=2" in text      # the compiled gpu program runs conv + bias + relu as one operator
+    assert "quantize folded=1" in text          # ... and quantizes the fp32 input itself, straight into its staged layout
