@@ -86,7 +86,8 @@ void set_conv_params(Bubble &b, const Case &cs, const Data &d) {
 
 // the quantized layer as a TenniS graph, compiled and run on `device`
 // keep_q: the quantized tensor is a second output of the module, so the quantize operator has to stay in the program
-Tensor run_graph(const std::string &device, const Case &cs, const Data &d, bool keep_q = false) {
+// leaky > 0: the activation is leaky_relu with that scale instead of relu
+Tensor run_graph(const std::string &device, const Case &cs, const Data &d, bool keep_q = false, float leaky = 0.0f) {
     Graph g;
     ctx::bind<Graph> _graph(g);
     auto x = bubble::param("x");
@@ -98,7 +99,8 @@ Tensor run_graph(const std::string &device, const Case &cs, const Data &d, bool 
     set_conv_params(conv.bubble(), cs, d);
     auto biased = bubble::op("biased", name::layer::add_bias(), {conv, b});
     biased.bubble().set(name::format, tensor::from("NCHW"));
-    auto y = bubble::op("y", name::layer::relu(), {biased});
+    auto y = bubble::op("y", leaky > 0.0f ? std::string("leaky_relu") : name::layer::relu(), {biased});
+    if (leaky > 0.0f) y.bubble().set(name::scale, tensor::from<float>(leaky));
     std::shared_ptr<Module> m = std::make_shared<Module>();
     if (keep_q) m->load(g, std::vector<std::string>{"y", "q"});
     else m->load(g, {"y"});
@@ -167,14 +169,20 @@ int tsplug_selftest(int n, int c, int h, int w, int o, int k, int stride, int pa
         // the quantized tensor keeps its quantize operator for that output and must still give the same y.
         Tensor g_gpu_q = run_graph(GPU, cs, d, true);
         const long folded = folded0 - folded_start;   // the two runs of the first gpu graph
-        long bad_g = mismatches_f32(g_cpu, g_gpu) + mismatches_f32(g_cpu, g_gpu_q);
+        // the same layer with leaky_relu(0.1): the other activation the rewrite folds
+        Tensor l_cpu = run_graph(CPU, cs, d, false, 0.1f);
+        const long fused_l0 = tsb_plugin_fused_runs();
+        Tensor l_gpu = run_graph(GPU, cs, d, false, 0.1f);
+        const long fused_leaky = tsb_plugin_fused_runs() - fused_l0;
+        const long bad_l = mismatches_f32(l_cpu, l_gpu);
+        long bad_g = mismatches_f32(g_cpu, g_gpu) + mismatches_f32(g_cpu, g_gpu_q) + bad_l;
         const int64_t launches_all = tsb_kernel_launch_count() - launches0;
         std::snprintf(msg, msglen, "quantize mismatch=%ld conv mismatches=%ld graph mismatches=%ld of %d; b200 kernel launches: ops=%lld total=%lld; fused operator runs=%ld; quantize folded=%d",
                       bad_q, bad_y, bad_g, g_cpu.count(), (long long) launches_ops, (long long) launches_all, fused,
                       int(folded >= 2));
         if (launches_ops < 2) return 2;  // the gpu workbench did not reach the B200 operators (CPU fallback)
         if (fused != 2) return 3;        // the graph rewrite did not happen
-        if (folded < 2) return 4;
+        if (folded < 2 || fused_leaky != 2) return 4;
         return (bad_q == 0 && bad_y == 0 && bad_g == 0) ? 0 : 1;
     } catch (const std::exception &e) {
         std::snprintf(msg, msglen, "exception: %s", e.what());
