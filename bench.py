@@ -621,6 +621,7 @@ def run_ours(args):
                     "tensor_view": tensor_view, "hbm_view": hbm_view, "int8_gemm_probe": probe}
         if probe and "tops" in probe:
             probe["frac_of_peak"] = probe["tops"] / int8_peak
+            probe["frac_of_nominal_dense_int8"] = probe["tops"] / 4500.0   # NVIDIA's dense int8 figure for B200
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
             "ms_per_step": total_ms_max / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
