@@ -160,7 +160,8 @@ TSB_API int tsb_conv2d_i8_kernel(const tsb_conv_plan *plan);
 /*
  * One line of text saying how the plan will run (kernel, load mode, MMA orientation, tile shape, tile counts,
  * pipeline stages, shared memory) for its primary configuration and, after " | alt: ", for the configuration of the
- * other orientation when the plan keeps one.  For logs and tests; returns the length written (without the
+ * other orientation when the plan keeps one.  For logs and tests (no counterpart in the reference, whose operators
+ * have one code path); returns the length written (without the
  * terminating zero) or a negative status.
  */
 TSB_API int tsb_conv2d_i8_plan_describe(const tsb_conv_plan *plan, char *text, size_t text_bytes);
