@@ -69,6 +69,15 @@ TSB_API int tsb_quantize_f32_i8(const float *x, int8_t *y, int64_t count, const 
                         void *stream);
 
 /*
+ * quantize of an fp64 tensor: the FLOAT64 branch of ts::cpu::Quantize::quantize (src/kernels/cpu/quantize.cpp:134 ->
+ * the generic cpu_quantize_compute_run<double>, :38-67, with to_int8<double>, :30-36).  The product x[i] * scale is
+ * formed in double, rounded half away from zero for EVERY element (this path has no half-to-even vector body), then
+ * converted and clamped as above; scale groups as for fp32.
+ */
+TSB_API int tsb_quantize_f64_i8(const double *x, int8_t *y, int64_t count, const float *scales_host, int nscales,
+                        void *stream);
+
+/*
  * quantize without any allocation (this entry point has no counterpart in the reference).
  *
  * For callers that are not allowed to obtain device memory at call time: a serving process that handed the whole
@@ -85,7 +94,12 @@ TSB_API int tsb_quantize_f32_i8(const float *x, int8_t *y, int64_t count, const 
  *   - All calls on one GPU share the table, and each call overwrites the entries it uses.  Calls whose work may
  *     overlap on the GPU (different streams) therefore race: keep them on one stream or order them with events.
  *   - It calls no cudaMalloc/cudaFree (nor their async forms) and no allocating library routine; x, y and the
- *     host scale list are the caller's.  The host list may be reused as soon as the call returns.
+ *     host scale list are the caller's.
+ *   - The scale list reaches the table by a copy enqueued on `stream`.  A list in ordinary (pageable) host memory
+ *     has been read when the call returns and may be reused at once; a list in pinned or registered host memory
+ *     is read later, when the stream gets to the copy, and must stay unchanged until then.
+ *   - The remembered table address belongs to the device's current CUDA context: it does not survive a
+ *     cudaDeviceReset.
  */
 TSB_API int tsb_quantize_f32_i8_static(const float *x, int8_t *y, int64_t count, const float *scales_host,
                                        int nscales, void *stream);
@@ -117,7 +131,19 @@ typedef struct tsb_conv_desc {
     int dilation_h, dilation_w;
     float padding_value;
     int kernel;                                     /* TSB_KERNEL_* */
+    /*
+     * Overrides of the plan heuristics, each TSB_TUNE_AUTO (0: the library chooses -- what every caller outside the
+     * test-suite passes), TSB_TUNE_OFF or TSB_TUNE_ON.  They change speed only, never results; a mode that the
+     * geometry does not admit stays off.  Zero-initialise the descriptor and leave them alone.
+     */
+    int mma_orientation;                            /* OFF: pixels on the MMA's M side; ON: channels on M (O <= 128) */
+    int raw_row_mode;                               /* few-channel layers: one bulk copy of the staged rows per tile */
+    int patch_mode;                                 /* stride-1 multi-tap filters: one input patch per tile */
 } tsb_conv_desc;
+
+#define TSB_TUNE_AUTO 0
+#define TSB_TUNE_OFF 1
+#define TSB_TUNE_ON 2
 
 /*
  * What happens to the int32 accumulators.  In operator order:
@@ -142,12 +168,17 @@ typedef struct tsb_conv_epilogue {
     int8_t *out_i8;                 /* device or NULL */
     int out_i8_layout;              /* TSB_LAYOUT_NCHW or TSB_LAYOUT_NHWC_PAD */
     const float *requant_scales_host; /* [n_requant_scales] host; 1 scale, or one per sample */
-    int n_requant_scales;
+    int n_requant_scales;           /* at most TSB_MAX_REQUANT_SCALES: the scales travel as kernel arguments, so a
+                                       fused requantize serves batches up to that size; beyond it the call is
+                                       rejected with TSB_ERR_UNSUPPORTED and the caller runs tsb_quantize_f32_i8 on
+                                       the fp32 output instead */
     int32_t *out_acc;               /* device or NULL: raw int32 accumulators, NCHW (parity checks) */
     int residual_after_activation;  /* 0: act(conv + bias + residual), a ResNet block's tail;
                                        1: act(conv + bias) + residual, a Darknet shortcut (operators
                                           conv2d_quantized -> add_bias -> leaky_relu -> add) */
 } tsb_conv_epilogue;
+
+#define TSB_MAX_REQUANT_SCALES 128
 
 typedef struct tsb_conv_plan tsb_conv_plan;
 
@@ -155,7 +186,12 @@ TSB_API int tsb_conv2d_i8_plan_create(const tsb_conv_desc *desc, tsb_conv_plan *
 TSB_API int tsb_conv2d_i8_plan_destroy(tsb_conv_plan *plan);
 /* output extent {N,O,OH,OW} */
 TSB_API int tsb_conv2d_i8_output_shape(const tsb_conv_plan *plan, int shape[4]);
-/* TSB_KERNEL_DIRECT or TSB_KERNEL_TCGEN05: what the plan resolved to */
+/*
+ * TSB_KERNEL_DIRECT or TSB_KERNEL_TCGEN05: what the plan resolved to.  A TSB_KERNEL_AUTO plan takes the CUDA-core
+ * kernel only for what the tensor-core kernel cannot express (a non-zero padding_value, filters beyond the tensor
+ * map limits); it is many times slower, so a host should check this once per plan and say so in its log --
+ * tsb_conv2d_i8_plan_describe gives the reason.
+ */
 TSB_API int tsb_conv2d_i8_kernel(const tsb_conv_plan *plan);
 /*
  * One line of text saying how the plan will run (kernel, load mode, MMA orientation, tile shape, tile counts,
@@ -194,11 +230,20 @@ TSB_API int tsb_conv2d_i8_run(tsb_conv_plan *plan, const int8_t *x, int x_layout
                       void *workspace, size_t workspace_bytes, void *stream);
 
 /*
- * Reads back the status word the tensor-core kernel keeps in the workspace and synchronises the stream:
- * TSB_OK, or TSB_ERR_DEVICE_TIMEOUT when one of the kernel's bounded waits ran out (the run's outputs are
- * then invalid; the CUDA context stays usable).
+ * Failure detection.  Every wait inside the tensor-core kernel is bounded; a wait that runs out makes the kernel
+ * write a code (1..6, which wait) into the status word at the start of the workspace, release what it holds and
+ * return, so the CUDA context stays usable but that run's outputs are invalid.
+ *  - tsb_conv2d_i8_status: copies the word back, synchronises the stream and returns TSB_OK or
+ *    TSB_ERR_DEVICE_TIMEOUT (tsb_last_error names the wait); a reported time-out is cleared again.
+ *  - tsb_conv2d_i8_status_async: only enqueues the 4-byte copy into `status_word_host` (pinned memory) on the
+ *    stream -- no wait; the caller looks at the word once the stream has passed that point (an event, or its next
+ *    synchronisation) and turns it into a status and message with tsb_conv2d_i8_status_decode.  This is how the
+ *    TenniS operator checks without adding a synchronisation to the workbench's stream.
+ * tsb_conv2d_quantized_host (the waiting form) checks the word itself.
  */
 TSB_API int tsb_conv2d_i8_status(tsb_conv_plan *plan, void *workspace, void *stream);
+TSB_API int tsb_conv2d_i8_status_async(tsb_conv_plan *plan, void *workspace, int *status_word_host, void *stream);
+TSB_API int tsb_conv2d_i8_status_decode(int status_word);
 
 /*
  * Host-buffer convenience over the three calls above (what a CPU-resident TenniS tensor goes through):
@@ -232,16 +277,22 @@ TSB_API int tsb_leaky_relu_f32(const float *x, float *y, int64_t count, float sc
 
 /*
  * The operators around the convolutions of a quantized ResNet-style network, on the convolution path's layouts.
- *  - max pooling (operator "pooling2d", type max; src/kernels/gpu/pooling2d_core.cu) on int8 NHWC_PAD: because
- *    quantize is monotonic, pooling the int8 tensor equals quantizing the pooled fp32 tensor with the same scale;
- *    taps outside the image are ignored (identical to zero padding for post-ReLU inputs);
+ *  - max pooling (operator "pooling2d", type max; src/kernels/gpu/pooling2d_core.cu, src/kernels/cpu/pooling2d_core.cpp:47-93)
+ *    on int8 NHWC_PAD: because quantize is monotonic, pooling the int8 tensor equals quantizing the pooled fp32 tensor
+ *    with the same scale.  The output extent is the reference's: tsb_pool_out_dim = ceil((x + pad_lo + pad_hi - k) /
+ *    float(stride) + 1) (include/backend/common_function.h:13-20) -- CEIL, unlike the convolution's floor -- and every
+ *    window is clipped to the image, so padding never takes part in the maximum.  (A ResNet stem pool written for
+ *    floor semantics, 112 -> 56 with k 3, stride 2, reaches TenniS as padding {top 1, bottom 0, left 1, right 0}.)
+ *    Geometries in which a whole window falls into the padding are rejected: the reference's value there is whatever
+ *    lies at the clamped start index;
  *  - global average pooling ("global_pooling2d", type avg) on fp32 [N][pixels][C] -> [N][C];
  *  - inner product ("inner_prod"; the reference calls cuBLAS SGEMM) y[n][o] = sum_k x[n][k] * w[o][k] + bias[o].
  * The two fp32 reductions sum in a fixed order that differs from the CPU reference's, so they agree to rounding
  * (1e-5 relative), not bit for bit.
  */
-TSB_API int tsb_maxpool_i8_nhwc(const int8_t *x, int8_t *y, int n, int h, int w, int channels, int k, int stride, int pad,
-                                void *stream);
+TSB_API int tsb_pool_out_dim(int x, int pad_lo, int pad_hi, int k, int stride);
+TSB_API int tsb_maxpool_i8_nhwc(const int8_t *x, int8_t *y, int n, int h, int w, int channels, int k, int stride, int pad_top,
+                                int pad_bottom, int pad_left, int pad_right, void *stream);
 TSB_API int tsb_global_avgpool_f32_nhwc(const float *x, float *y, int n, int pixels, int channels, void *stream);
 TSB_API int tsb_inner_prod_f32(const float *x, const float *w, const float *bias, float *y, int n, int k, int o,
                                void *stream);
@@ -253,9 +304,12 @@ TSB_API int tsb_inner_prod_f32(const float *x, const float *w, const float *bias
 TSB_API int tsb_concat_i8_nhwc(const int8_t *a, int channels_a, const int8_t *b, int channels_b, int8_t *y, int64_t pixels,
                                void *stream);
 
-/* Debugging aid: while a device buffer of 2048 bytes is set, CTA 0 of each tensor-core convolution launch records a
- * timeline (eight nanosecond stamps per tile for its first 32 tiles) into it.  NULL (the default) switches it off. */
+#ifdef TSB_ENABLE_TRACE
+/* Profiling builds only (compile the library with -DTSB_ENABLE_TRACE; release builds carry neither this symbol nor the
+ * stamps): while a device buffer of 2048 bytes is set, CTA 0 of each tensor-core convolution launch records a
+ * timeline (eight nanosecond stamps per tile for its first 32 tiles) into it.  NULL switches it off. */
 TSB_API int tsb_debug_set_trace_buffer(void *device_buffer);
+#endif
 
 /* Number of kernels this library has launched on the calling process since load (bench bookkeeping). */
 TSB_API int64_t tsb_kernel_launch_count(void);

@@ -70,6 +70,73 @@ void orc_quantize_f32(const float *x, int count, const float *scales, int nscale
     }
 }
 
+/* to_int8<double>: src/kernels/cpu/quantize.cpp:30-36 -- int32_t(round(src)) on a double (cvttsd2si: out-of-range
+ * and NaN give INT32_MIN). */
+static int8_t to_int8_f64(double v) {
+    const double r = round(v);
+    if (!(r >= -2147483648.0 && r < 2147483648.0)) return clamp_i8(INT32_MIN);
+    return clamp_i8((int32_t)r);
+}
+
+/*
+ * cpu_quantize_compute_run<double> (the generic template): src/kernels/cpu/quantize.cpp:38-67, dispatched at :134.
+ * The product is double * float -> double; every element goes through to_int8<double> (half away), with one scale or
+ * with G groups of ceil(count/G) elements.
+ */
+void orc_quantize_f64(const double *x, int count, const float *scales, int nscales, int8_t *y) {
+    if (nscales == 1) {
+        const float s = scales[0];
+        for (int i = 0; i < count; ++i) y[i] = to_int8_f64(x[i] * s);
+    } else {
+        const int len = orc_quantize_group_len(count, nscales);
+        int index = 0;
+        for (int g = 0; g < nscales; ++g) {
+            const float s = scales[g];
+            int left = len;
+            while (index < count && left) {
+                y[index] = to_int8_f64(x[index] * s);
+                ++index;
+                --left;
+            }
+        }
+    }
+}
+
+/* pooling2d_forward: include/backend/common_function.h:13-20 -- ceil of an fp32 quotient. */
+int orc_pool_out_dim(int x, int pad_lo, int pad_hi, int k, int stride) {
+    return (int)ceilf((float)(x + pad_lo + pad_hi - k) / (float)stride + 1.0f);
+}
+
+/*
+ * cpu_max_pooling: src/kernels/cpu/pooling2d_core.cpp:47-93 (the generic kernel; the k3s2 / k2s2 special cases of
+ * pooling_algorithm.h compute the same maxima).  NCHW fp32; each window is clipped to the image and the maximum
+ * starts from the window's first element.  Windows that miss the image altogether are outside this restatement
+ * (the reference reads past the plane there); returns -1 for such a geometry.
+ */
+int orc_max_pooling2d(const float *x, int N, int C, int H, int W, int k, int stride, int pt, int pb, int pl, int pr,
+                      float *y) {
+    const int OH = orc_pool_out_dim(H, pt, pb, k, stride), OW = orc_pool_out_dim(W, pl, pr, k, stride);
+    if (OH < 1 || OW < 1 || (OH - 1) * stride - pt >= H || (OW - 1) * stride - pl >= W || k - pt < 1 || k - pl < 1) return -1;
+    for (int nc = 0; nc < N * C; ++nc) {
+        const float *in = x + (size_t)nc * H * W;
+        float *out = y + (size_t)nc * OH * OW;
+        for (int oh = 0; oh < OH; ++oh) {
+            int h0 = oh * stride - pt, h1 = h0 + k < H ? h0 + k : H;
+            if (h0 < 0) h0 = 0;
+            for (int ow = 0; ow < OW; ++ow) {
+                int w0 = ow * stride - pl, w1 = w0 + k < W ? w0 + k : W;
+                if (w0 < 0) w0 = 0;
+                float m = in[h0 * W + w0];
+                for (int ih = h0; ih < h1; ++ih)
+                    for (int iw = w0; iw < w1; ++iw)
+                        if (in[ih * W + iw] > m) m = in[ih * W + iw];
+                out[oh * OW + ow] = m;
+            }
+        }
+    }
+    return 0;
+}
+
 /* conv2d_forward: include/backend/common_function.h:30-40 (integer division, then floor of an integer). */
 int orc_conv_out_dim(int x, int pad_lo, int pad_hi, int k, int stride, int dilation) {
     return (x + pad_lo + pad_hi - (dilation * (k - 1) + 1)) / stride + 1;

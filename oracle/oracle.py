@@ -61,6 +61,17 @@ def _ints(values):
     return (ctypes.c_int * len(values))(*[int(v) for v in values])
 
 
+def reference_root():
+    """Where the reference's source tree lies, or None: $TENNIS_REFERENCE if set, else the Makefile's default REF."""
+    path = os.environ.get("TENNIS_REFERENCE")
+    if not path:
+        for line in open(os.path.join(_HERE, "Makefile")):
+            if line.startswith("REF") and "?=" in line:
+                path = line.split("?=", 1)[1].strip()
+                break
+    return path if path and os.path.isdir(os.path.join(path, "src")) else None
+
+
 def build(force=False):
     """Compile liboracle.so (and _ref/ when the reference sources are present)."""
     lib = os.path.join(_HERE, "liboracle.so")
@@ -70,8 +81,9 @@ def build(force=False):
     # its driver; a prebuilt library is used as it is
     ref_lib = os.path.join(_HERE, "_ref", "libtsref.so")
     stale = not os.path.exists(ref_lib) or os.path.getmtime(ref_lib) < os.path.getmtime(os.path.join(_HERE, "ref_driver.cpp"))
-    if os.path.isdir("/root/reference/src") and (force or stale):
-        subprocess.check_call(["make", "-C", _HERE, "-j8", "ref"], stdout=subprocess.DEVNULL)
+    ref = reference_root()
+    if ref and (force or stale):
+        subprocess.check_call(["make", "-C", _HERE, "-j8", "ref", "REF=" + ref], stdout=subprocess.DEVNULL)
 
 
 def conv_out_dim(x, pad_lo, pad_hi, k, stride, dilation):
@@ -100,6 +112,29 @@ class Port:
         y = np.zeros(x.shape, dtype=np.int8)
         self.lib.orc_quantize_f32(_ptr(x, ctypes.c_float), ctypes.c_int(x.size), _ptr(s, ctypes.c_float),
                                   ctypes.c_int(s.size), _ptr(y, ctypes.c_int8))
+        return y
+
+    def quantize_f64(self, x, scales):
+        """quantize of a FLOAT64 tensor (src/kernels/cpu/quantize.cpp:38-67,134)."""
+        x = np.ascontiguousarray(x, dtype=np.float64)
+        s = np.ascontiguousarray(scales, dtype=np.float32).reshape(-1)
+        y = np.zeros(x.shape, dtype=np.int8)
+        self.lib.orc_quantize_f64(_ptr(x, ctypes.c_double), ctypes.c_int(x.size), _ptr(s, ctypes.c_float),
+                                  ctypes.c_int(s.size), _ptr(y, ctypes.c_int8))
+        return y
+
+    def max_pooling2d(self, x, k, stride, pad):
+        """pooling2d, type max, NCHW fp32, pad = (top, bottom, left, right); the reference's ceil-mode extent."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        N, C, H, W = x.shape
+        self.lib.orc_pool_out_dim.restype = ctypes.c_int
+        OH = self.lib.orc_pool_out_dim(H, int(pad[0]), int(pad[1]), int(k), int(stride))
+        OW = self.lib.orc_pool_out_dim(W, int(pad[2]), int(pad[3]), int(k), int(stride))
+        y = np.zeros((N, C, max(OH, 0), max(OW, 0)), dtype=np.float32)
+        rc = self.lib.orc_max_pooling2d(_ptr(x, ctypes.c_float), N, C, H, W, int(k), int(stride), int(pad[0]), int(pad[1]),
+                                        int(pad[2]), int(pad[3]), _ptr(y, ctypes.c_float))
+        if rc != 0:
+            raise ValueError("a pooling window lies entirely in the padding")
         return y
 
     def conv2d_quantized(self, x, w, pad, stride, dilation, dq, padding_value=0.0, return_acc=False):
@@ -196,6 +231,24 @@ class Reference(Port):
         y = np.zeros(x.shape, dtype=np.int8)
         self._check(self.ref.tsref_quantize(_ptr(x, ctypes.c_float), _ints(x.shape), x.ndim, _ptr(s, ctypes.c_float),
                                             int(s.size), _ptr(y, ctypes.c_int8), self.threads))
+        return y
+
+    def quantize_f64(self, x, scales):
+        x = np.ascontiguousarray(x, dtype=np.float64)
+        s = np.ascontiguousarray(scales, dtype=np.float32).reshape(-1)
+        y = np.zeros(x.shape, dtype=np.int8)
+        self._check(self.ref.tsref_quantize_f64(_ptr(x, ctypes.c_double), _ints(x.shape), x.ndim, _ptr(s, ctypes.c_float),
+                                                int(s.size), _ptr(y, ctypes.c_int8), self.threads))
+        return y
+
+    def max_pooling2d(self, x, k, stride, pad):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        shape = _ints([0, 0, 0, 0])
+        self._check(self.ref.tsref_max_pooling2d(_ptr(x, ctypes.c_float), _ints(x.shape), int(k), int(stride), _ints(pad),
+                                                 None, shape, self.threads))
+        y = np.zeros(tuple(shape), dtype=np.float32)
+        self._check(self.ref.tsref_max_pooling2d(_ptr(x, ctypes.c_float), _ints(x.shape), int(k), int(stride), _ints(pad),
+                                                 _ptr(y, ctypes.c_float), shape, self.threads))
         return y
 
     def conv2d_quantized(self, x, w, pad, stride, dilation, dq, padding_value=0.0, return_acc=False):

@@ -92,6 +92,38 @@ int tsref_quantize(const float *x, const int *shape, int ndims, const float *sca
     TSREF_GUARD_END
 }
 
+// the same operator on a FLOAT64 tensor: the generic branch, src/kernels/cpu/quantize.cpp:38-67 and :134.
+__attribute__((visibility("default")))
+int tsref_quantize_f64(const double *x, const int *shape, int ndims, const float *scales, int nscales,
+                       int8_t *y, int threads) {
+    TSREF_GUARD_BEGIN
+    Workbench bench(ComputingDevice(CPU, 0), threads);
+    Tensor out = run1(bench, quantize_bubble(scales, nscales), {make_tensor(FLOAT64, shape, ndims, x)});
+    std::memcpy(y, out.data(), size_t(out.count()));
+    return 0;
+    TSREF_GUARD_END
+}
+
+// "pooling2d", type max, format NCHW, padding_type black (the default): src/backend/base/base_pooling2d.cpp:14-118,
+// src/kernels/cpu/pooling2d_core.cpp.  out_shape receives {N,C,OH,OW}; y may be null to ask for the shape only.
+__attribute__((visibility("default")))
+int tsref_max_pooling2d(const float *x, const int *shape, int k, int stride, const int *pad_tblr, float *y,
+                        int *out_shape, int threads) {
+    TSREF_GUARD_BEGIN
+    Workbench bench(ComputingDevice(CPU, 0), threads);
+    Bubble b(name::layer::pooling2d(), "pool", 1);
+    b.set(name::format, tensor::from("NCHW"));
+    b.set(name::type, tensor::from<int32_t>(0));
+    b.set(name::padding, int_tensor({0, 0, 0, 0, pad_tblr[0], pad_tblr[1], pad_tblr[2], pad_tblr[3]}, Shape({4, 2})));
+    b.set(name::ksize, int_tensor({1, 1, k, k}, Shape({4})));
+    b.set(name::stride, int_tensor({1, 1, stride, stride}, Shape({4})));
+    Tensor out = run1(bench, b, {make_tensor(FLOAT32, shape, 4, x)});
+    for (int i = 0; i < 4; ++i) out_shape[i] = out.size(i);
+    if (y) std::memcpy(y, out.data(), size_t(out.count()) * sizeof(float));
+    return 0;
+    TSREF_GUARD_END
+}
+
 // "conv2d_quantized": src/backend/base/base_conv2d_quantized.cpp:13-219,
 // src/kernels/cpu/quantized/conv2d_quantized_core.cpp:18-147.  out_shape receives {N,O,OH,OW}.
 __attribute__((visibility("default")))

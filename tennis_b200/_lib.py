@@ -18,13 +18,18 @@ ERR_DEVICE_TIMEOUT = -4
 ACT_NONE, ACT_RELU, ACT_LEAKY_RELU = 0, 1, 2
 LAYOUT_NCHW, LAYOUT_NHWC_PAD, LAYOUT_STAGED = 0, 1, 2
 KERNEL_AUTO, KERNEL_DIRECT, KERNEL_TCGEN05 = 0, 1, 2
+TUNE_AUTO, TUNE_OFF, TUNE_ON = 0, 1, 2
+MAX_REQUANT_SCALES = 128
 
 
 class ConvDesc(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int) for n in (
         "n", "c", "h", "w", "o", "kh", "kw", "pad_top", "pad_bottom", "pad_left", "pad_right",
         "stride_h", "stride_w", "dilation_h", "dilation_w")] + [("padding_value", ctypes.c_float),
-                                                                 ("kernel", ctypes.c_int)]
+                                                                 ("kernel", ctypes.c_int),
+                                                                 ("mma_orientation", ctypes.c_int),
+                                                                 ("raw_row_mode", ctypes.c_int),
+                                                                 ("patch_mode", ctypes.c_int)]
 
 
 class ConvEpilogue(ctypes.Structure):
@@ -54,6 +59,7 @@ SYMBOLS = {
     "tsb_version": (_i, []),
     "tsb_padded_channels": (_i, [_i]),
     "tsb_quantize_f32_i8": (_i, [_vp, _vp, _i64, _fp, _i, _vp]),
+    "tsb_quantize_f64_i8": (_i, [_vp, _vp, _i64, _fp, _i, _vp]),
     "tsb_quantize_f32_i8_static": (_i, [_vp, _vp, _i64, _fp, _i, _vp]),
     "tsb_quantize_f32_nchw_to_nhwc": (_i, [_vp, _vp, _i, _i, _i, _i, _fp, _i, _vp]),
     "tsb_repack_i8_nchw_to_nhwc": (_i, [_vp, _vp, _i, _i, _i, _i, _vp]),
@@ -68,17 +74,19 @@ SYMBOLS = {
     "tsb_conv2d_i8_quantize_input": (_i, [_vp, _vp, _fp, _i, _vp, _sz, _vp]),
     "tsb_conv2d_i8_run": (_i, [_vp, _vp, _i, ctypes.POINTER(ConvEpilogue), _vp, _sz, _vp]),
     "tsb_conv2d_i8_status": (_i, [_vp, _vp, _vp]),
+    "tsb_conv2d_i8_status_async": (_i, [_vp, _vp, _vp, _vp]),
+    "tsb_conv2d_i8_status_decode": (_i, [_i]),
     "tsb_conv2d_host_scratch_bytes": (_sz, [_vp]),
     "tsb_conv2d_quantized_host": (_i, [_vp, _vp, _fp, _i, _vp, _vp, _vp, _i, _f, _vp, _vp, _sz, _i, _vp]),
     "tsb_conv2d_quantized_host_async": (_i, [_vp, _vp, _fp, _i, _vp, _vp, _vp, _i, _f, _vp, _vp, _sz, _i, _vp]),
     "tsb_add_bias_f32_nchw": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp]),
     "tsb_relu_f32": (_i, [_vp, _vp, _i64, _vp]),
     "tsb_leaky_relu_f32": (_i, [_vp, _vp, _i64, _f, _vp]),
-    "tsb_maxpool_i8_nhwc": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
+    "tsb_pool_out_dim": (_i, [_i, _i, _i, _i, _i]),
+    "tsb_maxpool_i8_nhwc": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "tsb_global_avgpool_f32_nhwc": (_i, [_vp, _vp, _i, _i, _i, _vp]),
     "tsb_inner_prod_f32": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "tsb_concat_i8_nhwc": (_i, [_vp, _i, _vp, _i, _vp, _i64, _vp]),
-    "tsb_debug_set_trace_buffer": (_i, [_vp]),
     "tsb_kernel_launch_count": (_i64, []),
 }
 

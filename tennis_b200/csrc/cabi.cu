@@ -17,6 +17,7 @@ std::atomic<int64_t> g_launches{0};
 
 // quantize.cu
 int quantize_f32_i8(const float *, int8_t *, int64_t, const float *, int, cudaStream_t);
+int quantize_f64_i8(const double *, int8_t *, int64_t, const float *, int, cudaStream_t);
 int quantize_f32_i8_static(const float *, int8_t *, int64_t, const float *, int, cudaStream_t);
 int quantize_f32_nchw_to_nhwc(const float *, int8_t *, int, int, int, int, const float *, int, cudaStream_t);
 int quantize_stage(const float *, int8_t *, int, int, int, int, int, int, int, int, const float *, int, cudaStream_t);
@@ -25,7 +26,8 @@ int repack_i8_nhwc_to_nchw(const int8_t *, int8_t *, int, int, int, int, cudaStr
 int add_bias_f32_nchw(const float *, float *, int, int, int, const float *, cudaStream_t);
 int activation_f32(const float *, float *, int64_t, int, float, cudaStream_t);
 // netops.cu
-int maxpool_i8_nhwc(const int8_t *, int8_t *, int, int, int, int, int, int, int, cudaStream_t);
+int pool_out_dim(int, int, int, int, int);
+int maxpool_i8_nhwc(const int8_t *, int8_t *, int, int, int, int, int, int, int, int, int, int, cudaStream_t);
 int global_avgpool_f32_nhwc(const float *, float *, int, int, int, cudaStream_t);
 int inner_prod_f32(const float *, const float *, const float *, float *, int, int, int, cudaStream_t);
 int concat_i8_nhwc(const int8_t *, int, const int8_t *, int, int8_t *, int64_t, cudaStream_t);
@@ -41,6 +43,7 @@ struct tsb_conv_plan {
     tsb_conv_desc desc;
     tsb::ConvGeom geom;
     int kernel;                      // resolved TSB_KERNEL_*
+    tsb::tc::Tuning tune;            // heuristic overrides taken from the descriptor
     const char *why_not_tc;
     tsb::tc::View view;
     tsb::tc::Config cfg;             // orientation chosen by the geometry heuristic
@@ -76,19 +79,23 @@ int tsb_version(void) { return 100; }
 
 int tsb_padded_channels(int channels) {
     if (channels <= 16) return 16;
-    static const int unit = getenv("TSB_PAD128") ? 128 : 64;
-    return round_up(channels, unit);
+    return round_up(channels, 64);
 }
 
 int64_t tsb_kernel_launch_count(void) { return g_launches.load(); }
 
+#ifdef TSB_ENABLE_TRACE
 int tsb_debug_set_trace_buffer(void *device_buffer) {
     tc::set_trace_buffer(static_cast<unsigned long long *>(device_buffer));
     return TSB_OK;
 }
+#endif
 
 int tsb_quantize_f32_i8(const float *x, int8_t *y, int64_t count, const float *scales_host, int nscales, void *stream) {
     return quantize_f32_i8(x, y, count, scales_host, nscales, (cudaStream_t)stream);
+}
+int tsb_quantize_f64_i8(const double *x, int8_t *y, int64_t count, const float *scales_host, int nscales, void *stream) {
+    return quantize_f64_i8(x, y, count, scales_host, nscales, (cudaStream_t)stream);
 }
 int tsb_quantize_f32_i8_static(const float *x, int8_t *y, int64_t count, const float *scales_host, int nscales,
                                void *stream) {
@@ -114,8 +121,13 @@ int tsb_leaky_relu_f32(const float *x, float *y, int64_t count, float scale, voi
     return activation_f32(x, y, count, TSB_ACT_LEAKY_RELU, scale, (cudaStream_t)stream);
 }
 
-int tsb_maxpool_i8_nhwc(const int8_t *x, int8_t *y, int n, int h, int w, int channels, int k, int stride, int pad, void *stream) {
-    return maxpool_i8_nhwc(x, y, n, h, w, channels, k, stride, pad, (cudaStream_t)stream);
+int tsb_pool_out_dim(int x, int pad_lo, int pad_hi, int k, int stride) {
+    if (x < 1 || k < 1 || stride < 1 || pad_lo < 0 || pad_hi < 0) return fail(TSB_ERR_INVALID_ARGUMENT, "pool_out_dim: bad geometry");
+    return pool_out_dim(x, pad_lo, pad_hi, k, stride);
+}
+int tsb_maxpool_i8_nhwc(const int8_t *x, int8_t *y, int n, int h, int w, int channels, int k, int stride, int pad_top,
+                        int pad_bottom, int pad_left, int pad_right, void *stream) {
+    return maxpool_i8_nhwc(x, y, n, h, w, channels, k, stride, pad_top, pad_bottom, pad_left, pad_right, (cudaStream_t)stream);
 }
 int tsb_global_avgpool_f32_nhwc(const float *x, float *y, int n, int pixels, int channels, void *stream) {
     return global_avgpool_f32_nhwc(x, y, n, pixels, channels, (cudaStream_t)stream);
@@ -139,6 +151,9 @@ int tsb_conv2d_i8_plan_create(const tsb_conv_desc *d, tsb_conv_plan **out) {
         return fail(TSB_ERR_INVALID_ARGUMENT, "plan_create: negative padding");
     if (d->kernel < TSB_KERNEL_AUTO || d->kernel > TSB_KERNEL_TCGEN05)
         return fail(TSB_ERR_INVALID_ARGUMENT, "plan_create: unknown kernel selector %d", d->kernel);
+    if (d->mma_orientation < 0 || d->mma_orientation > 2 || d->raw_row_mode < 0 || d->raw_row_mode > 2 || d->patch_mode < 0 ||
+        d->patch_mode > 2)
+        return fail(TSB_ERR_INVALID_ARGUMENT, "plan_create: mma_orientation, raw_row_mode and patch_mode take TSB_TUNE_AUTO, _OFF or _ON");
     const int OH = conv_out_dim(d->h, d->pad_top, d->pad_bottom, d->kh, d->stride_h, d->dilation_h);
     const int OW = conv_out_dim(d->w, d->pad_left, d->pad_right, d->kw, d->stride_w, d->dilation_w);
     if (OH < 1 || OW < 1 || d->h + d->pad_top + d->pad_bottom < d->dilation_h * (d->kh - 1) + 1 ||
@@ -159,7 +174,10 @@ int tsb_conv2d_i8_plan_create(const tsb_conv_desc *d, tsb_conv_plan **out) {
     g.Cp = tsb_padded_channels(d->c);
     g.pad_value = (int)(int8_t)d->padding_value;  // T(padding_value) of the reference's im2col call
     p->why_not_tc = "";
-    const bool tc_ok = tc::make_view(g, &p->view, &p->why_not_tc);
+    p->tune.orientation = d->mma_orientation;
+    p->tune.rows = d->raw_row_mode;
+    p->tune.patch = d->patch_mode;
+    const bool tc_ok = tc::make_view(g, p->tune, &p->view, &p->why_not_tc);
     if (d->kernel == TSB_KERNEL_TCGEN05 && !tc_ok) {
         int st = fail(TSB_ERR_UNSUPPORTED, "plan_create: tcgen05 kernel not available: %s", p->why_not_tc);
         delete p;
@@ -172,9 +190,10 @@ int tsb_conv2d_i8_plan_create(const tsb_conv_desc *d, tsb_conv_plan **out) {
         int sms = 148, dev = 0;
         if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (sms <= 0) sms = 148;
-        p->cfg = tc::choose_config(p->view, sms, -1);
-        p->cfg_alt = tc::choose_config(p->view, sms, p->cfg.swap ? 0 : 1);
-        p->alt_valid = p->cfg_alt.swap != p->cfg.swap;
+        p->cfg = tc::choose_config(p->view, p->tune, sms, -1);
+        p->cfg_alt = tc::choose_config(p->view, p->tune, sms, p->cfg.swap ? 0 : 1);
+        // a forced orientation is final: the run-time choice by epilogue is only made between the library's own two plans
+        p->alt_valid = p->cfg_alt.swap != p->cfg.swap && p->tune.orientation == 0;
         end = p->off_weights + align256(p->view.weight_bytes);
     }
     p->off_stage = end;
@@ -337,7 +356,7 @@ int tsb_conv2d_i8_run(tsb_conv_plan *plan, const int8_t *x, int x_layout, const 
     // channel, i.e. in the swapped orientation; everything else follows the geometry heuristic.
     const bool want_swap = (epi.out_f32 || epi.residual) && epi.f32_nhwc && !epi.out_acc;
     // (the swapped patch-mode kernel has no fast path for pixel-major fp32 tensors)
-    const bool use_alt = plan->alt_valid && !getenv("TSB_SWAP") && (want_swap != (plan->cfg.swap != 0)) && (want_swap ? plan->cfg_alt.swap : 0) &&
+    const bool use_alt = plan->alt_valid && (want_swap != (plan->cfg.swap != 0)) && (want_swap ? plan->cfg_alt.swap : 0) &&
                          !plan->cfg_alt.patch;
     if (use_alt) {
         if (plan->map_a_alt_ptr != x_tc) {
@@ -355,14 +374,46 @@ int tsb_conv2d_i8_run(tsb_conv_plan *plan, const int8_t *x, int x_layout, const 
     return tc::launch_conv_tc(plan->view, plan->cfg, plan->map_a, plan->map_b, x_tc, epi, static_cast<int *>(workspace), stream);
 }
 
-int tsb_conv2d_i8_status(tsb_conv_plan *plan, void *workspace, void *stream_) {
-    cudaStream_t stream = (cudaStream_t)stream_;
-    if (!plan || !workspace) return fail(TSB_ERR_INVALID_ARGUMENT, "status: null pointer");
+// what each code of the status word means (the kernel's bounded waits, conv_tc.cu)
+static const char *wait_name(int code) {
+    switch (code) {
+        case 1: return "producer: pipeline stage free";
+        case 2: return "MMA issuer: accumulator buffer free";
+        case 3: return "MMA issuer: tile loaded";
+        case 4: return "epilogue: accumulator ready";
+        case 5: return "producer: resident weight tile free";
+        case 6: return "MMA issuer: resident weight tile loaded";
+        default: return "unknown wait";
+    }
+}
+
+// Reads the status word (after everything enqueued on the stream) and, when a wait ran out, clears it again so that
+// one reported time-out does not stick to later runs.
+static int read_status(void *workspace, cudaStream_t stream, const char *who) {
     int word = 0;
     TSB_CUDA(cudaMemcpyAsync(&word, workspace, sizeof(int), cudaMemcpyDeviceToHost, stream));
     TSB_CUDA(cudaStreamSynchronize(stream));
-    if (word != 0) return fail(TSB_ERR_DEVICE_TIMEOUT, "conv kernel: bounded wait %d ran out (1 stage-free, 2 accumulator-free, 3 tile-loaded, 4 accumulator-ready)", word);
+    if (word == 0) return TSB_OK;
+    TSB_CUDA(cudaMemsetAsync(workspace, 0, sizeof(int), stream));
+    return fail(TSB_ERR_DEVICE_TIMEOUT, "%s: conv kernel gave up on bounded wait %d (%s); the outputs of that run are invalid", who, word,
+                wait_name(word));
+}
+
+int tsb_conv2d_i8_status(tsb_conv_plan *plan, void *workspace, void *stream_) {
+    if (!plan || !workspace) return fail(TSB_ERR_INVALID_ARGUMENT, "status: null pointer");
+    return read_status(workspace, (cudaStream_t)stream_, "status");
+}
+
+int tsb_conv2d_i8_status_async(tsb_conv_plan *plan, void *workspace, int *status_word_host, void *stream_) {
+    if (!plan || !workspace || !status_word_host) return fail(TSB_ERR_INVALID_ARGUMENT, "status_async: null pointer");
+    TSB_CUDA(cudaMemcpyAsync(status_word_host, workspace, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream_));
     return TSB_OK;
+}
+
+int tsb_conv2d_i8_status_decode(int status_word) {
+    if (status_word == 0) return TSB_OK;
+    return fail(TSB_ERR_DEVICE_TIMEOUT, "conv kernel gave up on bounded wait %d (%s); the outputs of that run are invalid", status_word,
+                wait_name(status_word));
 }
 
 // ---- host-buffer convenience --------------------------------------------------------------------------
@@ -427,6 +478,9 @@ static int conv2d_quantized_host(tsb_conv_plan *plan, const float *x_host, const
     st = tsb_conv2d_i8_run(plan, nullptr, TSB_LAYOUT_STAGED, &e, ws, plan->ws_bytes, stream);
     if (st != TSB_OK) return st;
     TSB_CUDA(cudaMemcpyAsync(out_host, d_out, (size_t)g.N * g.O * g.OH * g.OW * 4, cudaMemcpyDeviceToHost, stream));
+    // the waiting form also reports a kernel that gave up on one of its bounded waits (the non-waiting form cannot:
+    // its caller asks tsb_conv2d_i8_status after synchronising)
+    if (wait && plan->kernel == TSB_KERNEL_TCGEN05) return read_status(ws, stream, "conv2d_quantized_host");
     if (wait) TSB_CUDA(cudaStreamSynchronize(stream));
     return TSB_OK;
 }

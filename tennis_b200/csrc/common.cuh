@@ -51,11 +51,10 @@ inline int cuda_fail(cudaError_t e, const char *what) {
 
 // Launch with programmatic stream serialization: the grid may start while the previous kernel of the stream is still
 // draining, so its prologue overlaps that kernel's tail.  Only for kernels whose every thread executes pdl_sync() before
-// its first access to global memory.  TSB_NO_PDL=1 switches back to plain launches.
+// its first access to global memory.
 #ifdef __CUDACC__
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args &&...args) {
-    static const bool off = getenv("TSB_NO_PDL") != nullptr;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -65,7 +64,7 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = off ? 0 : 1;
+    cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 // Waits until the kernels this grid depends on have completed and their writes are visible, then lets the next grid of
@@ -117,6 +116,15 @@ __device__ __forceinline__ int q8_half_away(float v) {
 __device__ __forceinline__ int q8(float x, float scale, bool half_even) {
     const float v = __fmul_rn(x, scale);  // one rounding, never contracted
     return half_even ? q8_half_even(v) : q8_half_away(v);
+}
+
+// fp64 input (src/kernels/cpu/quantize.cpp:30-36,38-67,134 of the reference): the product is formed in double (the
+// fp32 scale is promoted), rounded half away from zero and converted the x86 way -- for every element, whatever the
+// number of scales (the fp64 path has no half-to-even vector body).
+__device__ __forceinline__ int q8(double x, float scale, bool /*half_even*/) {
+    const double r = round(__dmul_rn(x, (double)scale));
+    if (!(fabs(r) < 2147483648.0)) return -128;    // NaN or beyond int32: "integer indefinite", then the clamp
+    return max(-128, min(127, (int)r));
 }
 
 // dequantize -> add_bias -> (+residual) -> activation (-> +residual when it follows the activation), one rounding per step.

@@ -6,7 +6,7 @@
 
 namespace tsb {
 
-constexpr int kMaxRequantScales = 128;
+constexpr int kMaxRequantScales = TSB_MAX_REQUANT_SCALES;
 
 struct ConvGeom {
     int N, C, H, W;

@@ -23,6 +23,7 @@
 #include <cudaTypedefs.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstdlib>
 
 namespace tsb {
@@ -547,7 +548,7 @@ struct KernelParams {
     int OH;
     FastDiv d_tiles_w, d_tiles_hw;
     int *status;     // device word: 0 ok, else the code of the wait that ran out
-    unsigned long long *trace;  // optional timeline of CTA 0 (debugging aid): 8 stamps per tile, 32 tiles
+    unsigned long long *trace;  // profiling builds: timeline of CTA 0, 8 stamps per tile, 32 tiles (null otherwise)
 };
 
 __device__ __forceinline__ unsigned long long global_ns() {
@@ -555,10 +556,14 @@ __device__ __forceinline__ unsigned long long global_ns() {
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
+#ifdef TSB_ENABLE_TRACE
 #define TSB_TRACE(tile_index, slot)                                                              \
     do {                                                                                         \
         if (kp.trace && blockIdx.x == 0 && (tile_index) < 32) kp.trace[(tile_index) * 8 + (slot)] = global_ns(); \
     } while (0)
+#else
+#define TSB_TRACE(tile_index, slot) do { } while (0)
+#endif
 
 // raw-row mode: the filter rows kh_lo..kh_hi that meet an input row for output row oh (a contiguous, non-empty range)
 __device__ __forceinline__ void rows_span(const KernelParams &kp, int oh, int &kh_lo, int &kh_hi) {
@@ -1086,7 +1091,9 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 // ---------------------------------------------------------------------------------------------------------
 namespace {
 
-unsigned long long *g_trace = nullptr;  // set through set_trace_buffer(); null in normal operation
+#ifdef TSB_ENABLE_TRACE
+unsigned long long *g_trace = nullptr;  // set through set_trace_buffer()
+#endif
 PFN_cuTensorMapEncodeTiled_v12000 g_encode_tiled = nullptr;
 PFN_cuTensorMapEncodeIm2col_v12000 g_encode_im2col = nullptr;
 
@@ -1110,11 +1117,16 @@ CUtensorMapSwizzle swizzle_for(int bk) {
 template <int BN, int BK, bool SWAP, int MODE>
 int launch(const Config &cfg, const CUtensorMap &ma, const CUtensorMap &mb, const KernelParams &kp, const EpiParams &epi,
            cudaStream_t stream) {
-    static bool configured = false;
+    // The shared-memory limit of a kernel is a per-device attribute: one process may drive several GPUs (one TenniS
+    // Workbench per device, each on its own thread), so the "already raised" note is kept per device.
+    static std::atomic<uint64_t> configured{0};
     auto kernel = conv_i8_tc_kernel<BN, BK, SWAP, MODE>;
-    if (!configured) {
+    int dev = 0;
+    TSB_CUDA(cudaGetDevice(&dev));
+    const uint64_t bit = dev >= 0 && dev < 64 ? 1ull << dev : 0;
+    if (!(configured.load(std::memory_order_acquire) & bit)) {
         TSB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynamicSmem));
-        configured = true;
+        configured.fetch_or(bit, std::memory_order_release);
     }
     TSB_CUDA(launch_pdl(kernel, dim3(cfg.grid), dim3(kThreads), cfg.dyn_smem, stream, ma, mb, kp, epi));
     TSB_LAUNCHED("conv_i8_tc_kernel");
@@ -1123,9 +1135,11 @@ int launch(const Config &cfg, const CUtensorMap &ma, const CUtensorMap &mb, cons
 
 }  // namespace
 
+#ifdef TSB_ENABLE_TRACE
 void set_trace_buffer(unsigned long long *device_buffer) { g_trace = device_buffer; }
+#endif
 
-bool make_view(const ConvGeom &g, View *view, const char **why) {
+bool make_view(const ConvGeom &g, const Tuning &tune, View *view, const char **why) {
     *why = "";
     View v;
     v.real = g;
@@ -1133,7 +1147,7 @@ bool make_view(const ConvGeom &g, View *view, const char **why) {
     if (g.pad_value != 0) { *why = "non-zero padding_value"; return false; }
     if (g.C <= 16) {
         // fold the filter row into the channel dimension
-        const int cpix = (g.C <= 8 && g.sw % 2 == 0 && !getenv("TSB_FOLD16")) ? 8 : 16;
+        const int cpix = (g.C <= 8 && g.sw % 2 == 0) ? 8 : 16;
         const int span = (g.KW - 1) * g.dw + 1;
         const int bkf = round_up(span * cpix, 64);
         if (bkf > 128) { *why = "filter row too wide to fold into one K block"; return false; }
@@ -1148,7 +1162,7 @@ bool make_view(const ConvGeom &g, View *view, const char **why) {
         v.stride_n = v.stride_h * g.H;
         v.stage_bytes = (size_t)v.stride_n * g.N;
         // raw-row mode: pixel stride of exactly one 16-byte unit, every output row meets at least one input row, and
-        // output rows long enough to fill most of a 128-pixel tile (TSB_ROWS=1/0 forces it on/off where it is possible)
+        // output rows long enough to fill most of a 128-pixel tile (tune.rows forces it on/off where it is possible)
         bool rows_ok = v.stride_w == 16 && (size_t)g.KH * bkf * std::min(round_up(g.O, 64), 256) <= 96 * 1024 &&
                        (size_t)(g.KH - 1) * g.dh * v.stride_h + (size_t)ceil_div(g.OW, kBM) * kBM * 16 + 2048 <= 48 * 1024;
         for (int oh = 0; oh < g.OH && rows_ok; ++oh) {
@@ -1160,9 +1174,8 @@ bool make_view(const ConvGeom &g, View *view, const char **why) {
             rows_ok = any;
         }
         const int segs = ceil_div(g.OW, kBM);
-        const char *force_rows = getenv("TSB_ROWS");
         const bool rows_pay = (double)g.OW / (double)(segs * kBM) >= 0.75;
-        if (rows_ok && (force_rows ? atoi(force_rows) != 0 : rows_pay)) {
+        if (rows_ok && (tune.rows ? tune.rows == 2 : rows_pay)) {
             v.rows = 1;
             v.rows_segs = segs;
             v.stage_bytes += (size_t)kBM * 16 + 256;   // the copy under the last tile of the last row runs past the row's end
@@ -1175,10 +1188,9 @@ bool make_view(const ConvGeom &g, View *view, const char **why) {
         v.stage_bytes = (size_t)v.stride_n * g.N;
     }
     v.a_tiled = (!v.fold && g.KH == 1 && g.KW == 1 && g.sh == 1 && g.sw == 1 && g.pad_t == 0 && g.pad_l == 0 &&
-                 g.OH == g.H && g.OW == g.W && !getenv("TSB_NO_TILED_A")) ? 1 : 0;
-    const char *force_patch = getenv("TSB_PATCH");
+                 g.OH == g.H && g.OW == g.W) ? 1 : 0;
     v.patch = (!v.fold && !v.a_tiled && g.sh == 1 && g.sw == 1 && g.KH * g.KW > 1 && (g.KW - 1) * g.dw + 8 <= 256 &&
-               (g.KH - 1) * g.dh + 32 <= 256 && !(force_patch && atoi(force_patch) == 0)) ? 1 : 0;
+               (g.KH - 1) * g.dh + 32 <= 256 && tune.patch != 1) ? 1 : 0;
     const ConvGeom &t = v.g;
     v.weight_bytes = (size_t)t.O * t.KH * t.KW * t.Cp;
     // im2col tensor maps take box corners in [-128,127], filter offsets in [0,255] and traversal strides up to 8
@@ -1197,7 +1209,7 @@ bool make_view(const ConvGeom &g, View *view, const char **why) {
     return true;
 }
 
-Config choose_config(const View &v, int sm_count, int orientation) {
+Config choose_config(const View &v, const Tuning &tune, int sm_count, int orientation) {
     const ConvGeom &g = v.g;
     Config c;
     c.bk = (g.Cp % 128 == 0) ? 128 : 64;
@@ -1206,10 +1218,8 @@ Config choose_config(const View &v, int sm_count, int orientation) {
     // Normal orientation: 128 pixels on M, up to 256 output channels on N.  Swapped orientation: channels on M,
     // 256 (or 128) pixels on N -- it halves the MMA count of narrow layers but its epilogue (one channel per thread)
     // is dearer, so it is taken where it measured faster: multi-tap filters with at most 64 output channels.
-    const char *force = getenv("TSB_SWAP");
     // patch mode under a given tile shape: most of each 8 x (pix/8) tile inside the image, and the whole weight tile
-    // in shared memory beside at least two patches (TSB_PATCH=1 drops the first condition)
-    const char *force_patch = getenv("TSB_PATCH");
+    // in shared memory beside at least two patches (tune.patch == 2 drops the first condition)
     auto patch_fits = [&](int pix, int ch) {
         if (!v.patch) return false;
         const int th = pix / 8;
@@ -1218,12 +1228,12 @@ Config choose_config(const View &v, int sm_count, int orientation) {
         const double eff = (double)(g.OH * g.OW) / ((double)tiles_w * tiles_h * pix);
         const uint64_t patch_bytes = (uint64_t)round_up(pw * ph * c.bk, 1024);
         const uint64_t w_all = (uint64_t)g.KH * g.KW * g.Cp * (uint64_t)ch;
-        return (eff >= 0.7 || (force_patch && atoi(force_patch) != 0)) && w_all + 2 * patch_bytes <= kSmemBudget;
+        return (eff >= 0.7 || tune.patch == 2) && w_all + 2 * patch_bytes <= kSmemBudget;
     };
     const int bn_normal = g.O > 128 ? 256 : (g.O > 64 ? 128 : 64);
     if (v.rows) c.swap = 0;
     else if (orientation >= 0) c.swap = orientation;
-    else if (force) c.swap = atoi(force) != 0 && g.O <= 128;
+    else if (tune.orientation) c.swap = tune.orientation == 2 && g.O <= 128;
     // narrow multi-tap layers: swapped fills the MMA's N, but where patch mode applies the normal orientation with its
     // cheaper epilogue (16 warps, 16-byte stores) measured faster
     else c.swap = g.O <= 64 && g.KH * g.KW >= 9 && !v.fold && !patch_fits(kBM, bn_normal);
@@ -1269,8 +1279,10 @@ Config choose_config(const View &v, int sm_count, int orientation) {
     const uint32_t w_bytes = (uint32_t)c.ch * c.bk;
     const uint32_t k_iters = (uint32_t)g.KH * g.KW * (g.Cp / c.bk);
     const uint32_t w_total = k_iters * w_bytes;
-    const bool want_resident = v.rows || c.patch || (!getenv("TSB_NO_RESIDENT_B") && tiles > c.grid);  // pays off only when a CTA runs several tiles
-    if (c.patch || (want_resident && w_total <= 128 * 1024 && (kSmemBudget - w_total) / p_bytes >= 4)) {
+    const bool want_resident = v.rows || c.patch || tiles > c.grid;  // pays off only when a CTA runs several tiles
+    // (raw-row mode always keeps its weights resident; make_view admitted it only where two row stages fit beside them)
+    const uint32_t min_stages = v.rows ? 2 : 4;
+    if (c.patch || (want_resident && w_total <= 128 * 1024 && (kSmemBudget - w_total) / p_bytes >= min_stages)) {
         c.b_resident = 1;
         c.stage_bytes = p_bytes;
         c.stages = std::min<int>(kMaxStages, (int)((kSmemBudget - w_total) / p_bytes));
@@ -1446,7 +1458,11 @@ int launch_conv_tc(const View &v, const Config &cfg, const CUtensorMap &map_a, c
     kp.d_segs = FastDiv((uint32_t)std::max(1, v.rows_segs)); kp.d_OH = FastDiv((uint32_t)g.OH); kp.d_dh = FastDiv((uint32_t)g.dh);
     kp.per_sample_scale = (epi.nscales > 1 && epi.nscales == g.N && epi.group_len == (uint32_t)(g.O * g.OH * g.OW)) ? 1 : 0;
     kp.status = status_word;
+#ifdef TSB_ENABLE_TRACE
     kp.trace = g_trace;
+#else
+    kp.trace = nullptr;
+#endif
     kp.a_tiled = v.a_tiled;
     kp.stages = cfg.stages; kp.stage_bytes = cfg.stage_bytes; kp.b_resident = cfg.b_resident;
     kp.b_off = cfg.b_off; kp.bar_off = cfg.bar_off;

@@ -50,10 +50,19 @@ struct Config {
     uint32_t stage_bytes = 0, b_off = 0, bar_off = 0, dyn_smem = 0;
 };
 
+// Overrides of the plan heuristics, from tsb_conv_desc (tests force every code path with them): 0 = the library
+// chooses, 1 = off / normal orientation, 2 = on / swapped orientation.
+struct Tuning {
+    int orientation = 0;   // TSB_TUNE_* of tsb_conv_desc::mma_orientation
+    int rows = 0;          // tsb_conv_desc::raw_row_mode
+    int patch = 0;         // tsb_conv_desc::patch_mode
+};
+
 // Whether the tensor-core kernel covers this geometry; *why names the reason when it does not.
-bool make_view(const ConvGeom &g, View *view, const char **why);
-// orientation: -1 = by heuristic, 0 = normal, 1 = swapped (any number of output channels, 128 per channel tile)
-Config choose_config(const View &v, int sm_count, int orientation);
+bool make_view(const ConvGeom &g, const Tuning &tune, View *view, const char **why);
+// orientation: -1 = by heuristic (or tune.orientation), 0 = normal, 1 = swapped (any number of output channels, 128
+// per channel tile)
+Config choose_config(const View &v, const Tuning &tune, int sm_count, int orientation);
 // w_packed: [O][KH][KW][Cp] int8 of the view's geometry
 int encode_weight_map(const View &v, const Config &cfg, const int8_t *w_packed, CUtensorMap *map);
 // x: the staged activations (NHWC_PAD or folded), 16-byte aligned
@@ -62,9 +71,11 @@ int encode_activation_map(const View &v, const Config &cfg, const int8_t *x, CUt
 int pack_weights(const View &v, const int8_t *w_oihw, int8_t *w_packed, cudaStream_t stream);
 // int8 input (NCHW, or NHWC_PAD when x_nhwc) -> folded staging (fold views only)
 int stage_folded(const View &v, const int8_t *x, int x_nhwc, int8_t *staged, cudaStream_t stream);
-// Debugging aid: CTA 0 of later launches writes 8 time stamps (ns) per tile for its first 32 tiles into this device
-// buffer of 256 x 8 bytes; null switches it off.
+#ifdef TSB_ENABLE_TRACE
+// Profiling builds only: CTA 0 of later launches writes 8 time stamps (ns) per tile for its first 32 tiles into this
+// device buffer of 256 x 8 bytes; null switches it off.
 void set_trace_buffer(unsigned long long *device_buffer);
+#endif
 // x_staged: the activations the map_a was encoded for (read directly in raw-row mode)
 int launch_conv_tc(const View &v, const Config &cfg, const CUtensorMap &map_a, const CUtensorMap &map_b,
                    const int8_t *x_staged, const EpiParams &epi, int *status_word, cudaStream_t stream);

@@ -5,17 +5,20 @@
 //   inner_prod             src/kernels/gpu/inner_prod.cu (cuBLAS SGEMM in the reference)
 #include "common.cuh"
 
+#include <cmath>
+
 namespace tsb {
 namespace {
 
 constexpr int kThreads = 256;
 
-// int8 NHWC_PAD max pooling; taps outside the image are ignored.  quantize is monotonic, so pooling the int8
-// tensor gives exactly quantize(pool(x)) for the same scale; for post-ReLU inputs ignoring the halo and padding it
-// with zeros are the same thing.  One thread produces 16 channels of one output pixel.
+// int8 NHWC_PAD max pooling; a window is clipped to the image, as the reference's kernels clip it
+// (src/kernels/cpu/pooling2d_core.cpp:47-93, src/kernels/gpu/pooling2d_core.cu), so taps in the padding never count.
+// quantize is monotonic, so pooling the int8 tensor gives exactly quantize(pool(x)) for the same scale.  One thread
+// produces 16 channels of one output pixel.
 __global__ void __launch_bounds__(kThreads)
 maxpool_i8_nhwc_kernel(const int8_t *__restrict__ x, int8_t *__restrict__ y, int N, int H, int W, int Cp, int OH, int OW,
-                       int K, int S, int pad) {
+                       int K, int S, int pad_t, int pad_l) {
     pdl_sync();
     const int units = Cp / 16;
     const int64_t total = (int64_t)N * OH * OW * units;
@@ -27,10 +30,10 @@ maxpool_i8_nhwc_kernel(const int8_t *__restrict__ x, int8_t *__restrict__ y, int
 #pragma unroll
         for (int b = 0; b < 16; ++b) best[b] = -128;
         for (int kh = 0; kh < K; ++kh) {
-            const int ih = oh * S - pad + kh;
+            const int ih = oh * S - pad_t + kh;
             if ((unsigned)ih >= (unsigned)H) continue;
             for (int kw = 0; kw < K; ++kw) {
-                const int iw = ow * S - pad + kw;
+                const int iw = ow * S - pad_l + kw;
                 if ((unsigned)iw >= (unsigned)W) continue;
                 const int4 v = *reinterpret_cast<const int4 *>(x + (((int64_t)n * H + ih) * W + iw) * Cp + u * 16);
                 const int8_t *b8 = reinterpret_cast<const int8_t *>(&v);
@@ -155,17 +158,30 @@ int grid_for(int64_t items, int per_block) {
 
 }  // namespace
 
-int maxpool_i8_nhwc(const int8_t *x, int8_t *y, int n, int h, int w, int channels, int k, int stride, int pad,
-                    cudaStream_t stream) {
+// Output extent of the reference's pooling2d: ceil((x + pad_lo + pad_hi - k) / float(stride) + 1), evaluated in fp32
+// (include/backend/common_function.h:13-20, src/runtime/inferer/factory.cpp:221-223).
+int pool_out_dim(int x, int pad_lo, int pad_hi, int k, int stride) {
+    return (int)std::ceil((float)(x + pad_lo + pad_hi - k) / (float)stride + 1.0f);
+}
+
+int maxpool_i8_nhwc(const int8_t *x, int8_t *y, int n, int h, int w, int channels, int k, int stride, int pad_top,
+                    int pad_bottom, int pad_left, int pad_right, cudaStream_t stream) {
     if (!x || !y) return fail(TSB_ERR_INVALID_ARGUMENT, "maxpool: null pointer");
-    if (n < 1 || h < 1 || w < 1 || channels < 1 || k < 1 || stride < 1 || pad < 0 || pad >= k)
+    if (n < 1 || h < 1 || w < 1 || channels < 1 || k < 1 || stride < 1 || pad_top < 0 || pad_bottom < 0 || pad_left < 0 ||
+        pad_right < 0)
         return fail(TSB_ERR_INVALID_ARGUMENT, "maxpool: bad geometry");
     const int cp = tsb_padded_channels(channels);
-    const int oh = (h + 2 * pad - k) / stride + 1, ow = (w + 2 * pad - k) / stride + 1;
+    const int oh = pool_out_dim(h, pad_top, pad_bottom, k, stride), ow = pool_out_dim(w, pad_left, pad_right, k, stride);
     if (oh < 1 || ow < 1) return fail(TSB_ERR_INVALID_ARGUMENT, "maxpool: empty output");
+    // Every window must meet the image.  Where the ceil-mode extent adds a window that starts at or beyond the image
+    // edge (or ends before it), the reference reads whatever lies at the clamped start index -- the next channel
+    // plane or memory past the tensor -- which no layout-independent kernel can reproduce.
+    if ((oh - 1) * stride - pad_top >= h || (ow - 1) * stride - pad_left >= w || k - pad_top < 1 || k - pad_left < 1)
+        return fail(TSB_ERR_UNSUPPORTED, "maxpool: a pooling window lies entirely in the padding (the reference's result there is undefined)");
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) % 16) return fail(TSB_ERR_INVALID_ARGUMENT, "maxpool: tensors must be 16-byte aligned");
     const int64_t items = (int64_t)n * oh * ow * (cp / 16);
-    TSB_CUDA(launch_pdl(maxpool_i8_nhwc_kernel, dim3(grid_for(items, kThreads)), dim3(kThreads), 0, stream, x, y, n, h, w, cp, oh, ow, k, stride, pad));
+    TSB_CUDA(launch_pdl(maxpool_i8_nhwc_kernel, dim3(grid_for(items, kThreads)), dim3(kThreads), 0, stream, x, y, n, h, w, cp, oh, ow, k, stride,
+                        pad_top, pad_left));
     TSB_LAUNCHED("maxpool_i8_nhwc_kernel");
     return TSB_OK;
 }

@@ -2,6 +2,7 @@
 // coalesced loads/stores, grid sized as a multiple of the SM count, no tensor cores.
 #include "common.cuh"
 
+#include <atomic>
 #include <cmath>
 #include <mutex>
 
@@ -39,9 +40,26 @@ namespace {
 
 constexpr int kThreads = 256;
 
-// 16 consecutive elements per thread: 4 x float4 in, one 16-byte store out.
+// 16 consecutive elements of this thread, streamed once
+__device__ __forceinline__ void load16(const float *src, float (&f)[16]) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float4 t = __ldcs(reinterpret_cast<const float4 *>(src) + k);
+        f[4 * k + 0] = t.x; f[4 * k + 1] = t.y; f[4 * k + 2] = t.z; f[4 * k + 3] = t.w;
+    }
+}
+__device__ __forceinline__ void load16(const double *src, double (&f)[16]) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const double2 t = __ldcs(reinterpret_cast<const double2 *>(src) + k);
+        f[2 * k + 0] = t.x; f[2 * k + 1] = t.y;
+    }
+}
+
+// 16 consecutive elements per thread: 4 x float4 (8 x double2) in, one 16-byte store out.
+template <typename TIn>
 __global__ void __launch_bounds__(kThreads)
-quantize_vec16_kernel(const float *__restrict__ x, int8_t *__restrict__ y, uint32_t count, QuantRule rule,
+quantize_vec16_kernel(const TIn *__restrict__ x, int8_t *__restrict__ y, uint32_t count, QuantRule rule,
                       ScaleArg scales) {
     const uint32_t nvec = count >> 4;
     const uint32_t rne_limit = (uint32_t)rule.rne_limit;
@@ -49,13 +67,8 @@ quantize_vec16_kernel(const float *__restrict__ x, int8_t *__restrict__ y, uint3
     const int nscales = rule.nscales;
     for (uint32_t v = blockIdx.x * kThreads + threadIdx.x; v < nvec; v += gridDim.x * kThreads) {
         const uint32_t i0 = v << 4;
-        const float4 *src = reinterpret_cast<const float4 *>(x + i0);
-        float f[16];
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            float4 t = __ldcs(src + k);  // streamed once
-            f[4 * k + 0] = t.x; f[4 * k + 1] = t.y; f[4 * k + 2] = t.z; f[4 * k + 3] = t.w;
-        }
+        TIn f[16];
+        load16(x + i0, f);
         uint32_t g0 = nscales == 1 ? 0u : i0 / group_len;
         uint32_t g1 = nscales == 1 ? 0u : (i0 + 15u) / group_len;
         uint32_t packed[4];
@@ -85,8 +98,9 @@ quantize_vec16_kernel(const float *__restrict__ x, int8_t *__restrict__ y, uint3
 }
 
 // element-at-a-time: misaligned tensors and the < 16 element tail
+template <typename TIn>
 __global__ void __launch_bounds__(kThreads)
-quantize_scalar_kernel(const float *__restrict__ x, int8_t *__restrict__ y, uint32_t begin, uint32_t count,
+quantize_scalar_kernel(const TIn *__restrict__ x, int8_t *__restrict__ y, uint32_t begin, uint32_t count,
                        QuantRule rule, ScaleArg scales) {
     const uint32_t rne_limit = (uint32_t)rule.rne_limit;
     const uint32_t group_len = (uint32_t)rule.group_len;
@@ -270,12 +284,16 @@ activation_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t co
     }
 }
 
+// SM count of the CURRENT device (one process may drive several GPUs; remembered per device)
 int sm_count() {
-    static int sms = 0;
+    constexpr int kMaxDevices = 64;
+    static std::atomic<int> cached[kMaxDevices] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+    int sms = cached[dev].load(std::memory_order_relaxed);
     if (!sms) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-            sms = 148;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+        cached[dev].store(sms, std::memory_order_relaxed);
     }
     return sms;
 }
@@ -305,8 +323,9 @@ int make_scale_arg(const float *scales_host, int nscales, cudaStream_t stream, S
     return TSB_OK;
 }
 
-int quantize_f32_i8(const float *x, int8_t *y, int64_t count, const float *scales_host, int nscales,
-                    cudaStream_t stream) {
+template <typename TIn>
+static int quantize_any_i8(const TIn *x, int8_t *y, int64_t count, const float *scales_host, int nscales,
+                           cudaStream_t stream) {
     if (!x || !y || !scales_host) return fail(TSB_ERR_INVALID_ARGUMENT, "quantize: null pointer");
     if (nscales < 1) return fail(TSB_ERR_INVALID_ARGUMENT, "quantize: needs at least one scale");
     if (count < 0 || count > INT32_MAX) return fail(TSB_ERR_INVALID_ARGUMENT, "quantize: count %lld out of range", (long long)count);
@@ -319,16 +338,24 @@ int quantize_f32_i8(const float *x, int8_t *y, int64_t count, const float *scale
     const bool aligned = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (reinterpret_cast<uintptr_t>(y) % 16 == 0);
     uint32_t done = 0;
     if (aligned && count >= 16) {
-        quantize_vec16_kernel<<<grid_for(count >> 4), kThreads, 0, stream>>>(x, y, (uint32_t)count, rule, arg);
+        quantize_vec16_kernel<TIn><<<grid_for(count >> 4), kThreads, 0, stream>>>(x, y, (uint32_t)count, rule, arg);
         TSB_LAUNCHED("quantize_vec16_kernel");
         done = (uint32_t)((count >> 4) << 4);
     }
     if (done < count) {
-        quantize_scalar_kernel<<<grid_for(count - done), kThreads, 0, stream>>>(x, y, done, (uint32_t)count, rule, arg);
+        quantize_scalar_kernel<TIn><<<grid_for(count - done), kThreads, 0, stream>>>(x, y, done, (uint32_t)count, rule, arg);
         TSB_LAUNCHED("quantize_scalar_kernel");
     }
     if (tmp) TSB_CUDA(cudaFreeAsync(tmp, stream));
     return TSB_OK;
+}
+
+int quantize_f32_i8(const float *x, int8_t *y, int64_t count, const float *scales_host, int nscales, cudaStream_t stream) {
+    return quantize_any_i8<float>(x, y, count, scales_host, nscales, stream);
+}
+
+int quantize_f64_i8(const double *x, int8_t *y, int64_t count, const float *scales_host, int nscales, cudaStream_t stream) {
+    return quantize_any_i8<double>(x, y, count, scales_host, nscales, stream);
 }
 
 static int check_nchw(const void *x, const void *y, int n, int c, int h, int w, const char *who) {
@@ -454,12 +481,12 @@ int quantize_f32_i8_static(const float *x, int8_t *y, int64_t count, const float
     const bool aligned = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (reinterpret_cast<uintptr_t>(y) % 16 == 0);
     uint32_t done = 0;
     if (aligned && count >= 16) {
-        quantize_vec16_kernel<<<grid_for(count >> 4), kThreads, 0, stream>>>(x, y, (uint32_t)count, rule, arg);
+        quantize_vec16_kernel<float><<<grid_for(count >> 4), kThreads, 0, stream>>>(x, y, (uint32_t)count, rule, arg);
         TSB_LAUNCHED("quantize_vec16_kernel");
         done = (uint32_t)((count >> 4) << 4);
     }
     if (done < count) {
-        quantize_scalar_kernel<<<grid_for(count - done), kThreads, 0, stream>>>(x, y, done, (uint32_t)count, rule, arg);
+        quantize_scalar_kernel<float><<<grid_for(count - done), kThreads, 0, stream>>>(x, y, done, (uint32_t)count, rule, arg);
         TSB_LAUNCHED("quantize_scalar_kernel");
     }
     return TSB_OK;

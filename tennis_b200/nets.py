@@ -29,7 +29,9 @@ def resnet_spec(image=224, widths=(64, 128, 256, 512), blocks=(3, 4, 6, 3), stem
         return size_out
 
     size = conv("stem", 3, stem_channels, 7, 2, 3, image)
-    pooled = (size + 2 * 1 - 3) // 2 + 1
+    # pooling2d 3x3/2 with padding {top 1, bottom 0, left 1, right 0}: under the reference's ceil-mode extent
+    # (include/backend/common_function.h:13-20) that is the usual floor-mode pool with padding 1
+    pooled = -(-(size + 1 + 0 - 3) // 2) + 1
     stages = []
     cin, size = stem_channels, pooled
     for si, (width, nblocks) in enumerate(zip(widths, blocks)):
@@ -199,7 +201,7 @@ class QuantResNet:
         s_i8, _ = self._conv(0, None, "stem", ACT_RELU, staged=True)
         c = L["spec"]
         pooled = self._i8("stem.pool", spec["stem_pooled"], c["o"])
-        check(self.lib.tsb_maxpool_i8_nhwc(s_i8.data_ptr(), pooled.data_ptr(), self.batch, c["oh"], c["oh"], c["o"], 3, 2, 1,
+        check(self.lib.tsb_maxpool_i8_nhwc(s_i8.data_ptr(), pooled.data_ptr(), self.batch, c["oh"], c["oh"], c["o"], 3, 2, 1, 0, 1, 0,
                                            ops._stream_ptr()))
         return pooled
 

@@ -112,21 +112,24 @@ class Quantize(Operator):
     def run(self, inputs, stream=None):
         self.infer(inputs)
         x = inputs[0]
-        if x.dtype != torch.float32:
+        if x.dtype not in (torch.float32, torch.float64):   # the reference's dispatch: src/kernels/cpu/quantize.cpp:130-141
             raise EjectionException("%s not support this data type: %s" % (self.op, str(x.dtype).replace("torch.", "")))
         x = x.contiguous()
         y = torch.empty(x.shape, dtype=torch.int8, device=x.device)
-        check(_lib.load().tsb_quantize_f32_i8(_ptr(x), _ptr(y), x.numel(), float_array(self.scales), len(self.scales),
-                                              _stream_ptr(stream)))
+        lib = _lib.load()
+        fn = lib.tsb_quantize_f32_i8 if x.dtype == torch.float32 else lib.tsb_quantize_f64_i8
+        check(fn(_ptr(x), _ptr(y), x.numel(), float_array(self.scales), len(self.scales), _stream_ptr(stream)))
         return y
 
 
 class ConvPlan:
     """Owner of a tsb_conv_plan, its workspace and the device copies of the per-channel vectors."""
 
-    def __init__(self, xshape, wshape, pad, stride, dilation, padding_value=0.0, kernel=KERNEL_AUTO, device="cuda"):
+    def __init__(self, xshape, wshape, pad, stride, dilation, padding_value=0.0, kernel=KERNEL_AUTO, device="cuda",
+                 mma_orientation=0, raw_row_mode=0, patch_mode=0):
         lib = _lib.load()
         d = ConvDesc()
+        d.mma_orientation, d.raw_row_mode, d.patch_mode = int(mma_orientation), int(raw_row_mode), int(patch_mode)
         d.n, d.c, d.h, d.w = [int(v) for v in xshape]
         d.o, _, d.kh, d.kw = [int(v) for v in wshape]
         d.pad_top, d.pad_bottom, d.pad_left, d.pad_right = [int(v) for v in pad]
@@ -192,6 +195,13 @@ class ConvPlan:
 
     def status(self, stream=None):
         check(_lib.load().tsb_conv2d_i8_status(self.handle, _ptr(self.workspace), _stream_ptr(stream)))
+
+    def describe(self):
+        buf = ctypes.create_string_buffer(512)
+        n = _lib.load().tsb_conv2d_i8_plan_describe(self.handle, buf, len(buf))
+        if n < 0:
+            check(n)
+        return buf.value.decode()
 
 
 def _to_string(arr):

@@ -26,7 +26,41 @@ namespace ts {
         class Conv2DQuantizedCore : public base::Conv2DQuantizedCore {
         public:
             ~Conv2DQuantizedCore() override {
+                // the last run's status word has not been looked at yet: wait for it and at least say so (a destructor
+                // cannot eject)
+                if (m_status_pending && m_status_event && cudaEventSynchronize(m_status_event) == cudaSuccess &&
+                    m_status_host && *m_status_host != 0 && tsb_conv2d_i8_status_decode(*m_status_host) != TSB_OK) {
+                    TS_LOG_ERROR << "conv2d_quantized: " << tsb_last_error();
+                }
+                if (m_status_event) cudaEventDestroy(m_status_event);
+                if (m_status_host) cudaFreeHost(m_status_host);
                 if (m_plan) tsb_conv2d_i8_plan_destroy(m_plan);
+            }
+
+            // Failure detection without a synchronisation on the workbench's stream: every run enqueues a 4-byte copy
+            // of the kernel's status word into pinned memory and records an event; the NEXT run (or the destructor)
+            // looks at the word once the event has passed.  A kernel that gave up on one of its bounded waits
+            // therefore ejects, with the name of the wait, instead of handing on invalid output silently.
+            void check_previous_run(cudaStream_t stream, const std::string &op) {
+                if (!m_status_pending || cudaEventQuery(m_status_event) != cudaSuccess) return;
+                m_status_pending = false;
+                if (*m_status_host == 0) return;
+                const int word = *m_status_host;
+                *m_status_host = 0;
+                if (m_plan) cudaMemsetAsync(m_workspace.data(), 0, sizeof(int), stream);   // reported once, then cleared
+                check(tsb_conv2d_i8_status_decode(word), op);
+            }
+
+            void note_run(cudaStream_t stream, const std::string &op) {
+                if (tsb_conv2d_i8_kernel(m_plan) != TSB_KERNEL_TCGEN05) return;
+                if (!m_status_host) {
+                    if (cudaMallocHost(reinterpret_cast<void **>(&m_status_host), sizeof(int)) != cudaSuccess) { m_status_host = nullptr; return; }
+                    *m_status_host = 0;
+                    if (cudaEventCreateWithFlags(&m_status_event, cudaEventDisableTiming) != cudaSuccess) { m_status_event = nullptr; return; }
+                }
+                if (!m_status_event) return;
+                check(tsb_conv2d_i8_status_async(m_plan, m_workspace.data(), m_status_host, stream), op);
+                if (cudaEventRecord(m_status_event, stream) == cudaSuccess) m_status_pending = true;
             }
 
             void conv2d(const Tensor &x, const Padding2D &padding, float padding_value, const Tensor &w,
@@ -71,10 +105,20 @@ namespace ts {
                 // packed weights and the device copy of the scales are built on the first run and kept while the
                 // geometry and the weight pointer stay the same.
                 const void *w_ptr = w.data();
+                check_previous_run(stream, op);
                 if (m_plan == nullptr || std::memcmp(&desc, &m_desc, sizeof(desc)) != 0 || w_ptr != m_weights) {
                     if (m_plan) tsb_conv2d_i8_plan_destroy(m_plan);
                     m_plan = nullptr;
+                    m_status_pending = false;
                     check(tsb_conv2d_i8_plan_create(&desc, &m_plan), op);
+                    if (tsb_conv2d_i8_kernel(m_plan) != TSB_KERNEL_TCGEN05) {
+                        // the CUDA-core kernel is a correctness path (non-zero padding_value, filters beyond the
+                        // tensor-map limits) and many times slower: say so once per plan
+                        char text[256];
+                        if (tsb_conv2d_i8_plan_describe(m_plan, text, sizeof(text)) > 0) {
+                            TS_LOG_INFO << op << ": this layer runs on the CUDA-core kernel, not on the tensor cores: " << text;
+                        }
+                    }
                     m_desc = desc;
                     m_weights = w_ptr;
                     m_workspace_bytes = tsb_conv2d_i8_workspace_bytes(m_plan);
@@ -97,10 +141,12 @@ namespace ts {
                                                        m_workspace.data(), m_workspace_bytes, stream), op);
                     check(tsb_conv2d_i8_run(m_plan, nullptr, TSB_LAYOUT_STAGED, &epilogue, m_workspace.data(), m_workspace_bytes,
                                             stream), op);
+                    note_run(stream, op);
                     return;
                 }
                 check(tsb_conv2d_i8_run(m_plan, x.data<int8_t>(), TSB_LAYOUT_NCHW, &epilogue, m_workspace.data(),
                                         m_workspace_bytes, stream), op);
+                note_run(stream, op);
             }
 
         private:
@@ -110,6 +156,9 @@ namespace ts {
             size_t m_workspace_bytes = 0;
             Tensor m_workspace;
             Tensor m_scales;
+            int *m_status_host = nullptr;          // pinned: the status word of the last run lands here
+            cudaEvent_t m_status_event = nullptr;
+            bool m_status_pending = false;
         };
 
         using Conv2DQuantized = base::Conv2DWithCore<gpu::OperatorOnGPU<base::Conv2DQuantized>, Conv2DQuantizedCore>;

@@ -18,13 +18,19 @@ namespace ts {
             using supper = gpu::OperatorOnGPU<base::Quantize>;
 
             void quantize(const Tensor &x, std::vector<float> quantize_scales, Tensor &out) override {
-                // all tensors live on the GPU, as given by running_memory_device()
-                if (x.dtype() != FLOAT32) {
+                // all tensors live on the GPU, as given by running_memory_device(); the same two input types as the CPU
+                // operator's dispatch (src/kernels/cpu/quantize.cpp:130-141) and its error text for the rest
+                if (x.dtype() == FLOAT32) {
+                    check(tsb_quantize_f32_i8(x.data<float>(), out.data<int8_t>(), int64_t(out.count()),
+                                              quantize_scales.data(), int(quantize_scales.size()), stream_on_context()),
+                          this->op());
+                } else if (x.dtype() == FLOAT64) {
+                    check(tsb_quantize_f64_i8(x.data<double>(), out.data<int8_t>(), int64_t(out.count()),
+                                              quantize_scales.data(), int(quantize_scales.size()), stream_on_context()),
+                          this->op());
+                } else {
                     TS_LOG_ERROR << this->op() << " not support this data type: " << x.dtype() << eject;
                 }
-                check(tsb_quantize_f32_i8(x.data<float>(), out.data<int8_t>(), int64_t(out.count()),
-                                          quantize_scales.data(), int(quantize_scales.size()), stream_on_context()),
-                      this->op());
             }
         };
     }

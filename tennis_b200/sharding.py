@@ -18,9 +18,19 @@ def shard_range(global_batch, world, rank):
     return start, count
 
 
-def shard_seed(base_seed, rank):
-    """Per-shard seed of the synthetic inputs."""
-    return base_seed + 1000 * rank
+def shard_seed(rank, base_seed=1000):
+    """Per-shard seed of the synthetic inputs: 1000 + rank (shard 0 draws from seed 1000, shard 1 from 1001, ...)."""
+    if rank < 0:
+        raise ValueError("negative rank")
+    return base_seed + rank
+
+
+def micro_batches(count, size):
+    """Sizes of the micro-batches a shard of `count` images is processed in: full ones of `size`, then the remainder."""
+    if count < 0 or size < 1:
+        raise ValueError("bad micro-batch request")
+    full, rest = divmod(count, size)
+    return [size] * full + ([rest] if rest else [])
 
 
 def aggregate(elapsed_ms, units, device=None):

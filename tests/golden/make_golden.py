@@ -28,6 +28,20 @@ QUANT_CASES = [
     ("q_weights_per_channel", (6, 4, 3, 3), 6),
 ]
 
+# quantize of FLOAT64 tensors: (name, shape, number of scales)
+QUANT64_CASES = [
+    ("d_one_scale", (1, 3, 5, 5), 1),
+    ("d_batch4", (4, 3, 5, 7), 4),
+]
+
+# pooling2d, type max: (name, N, C, H, W, k, stride, pad(t,b,l,r))
+POOL_CASES = [
+    ("p_k3s2_p1_ceil", 2, 3, 12, 12, 3, 2, (1, 1, 1, 1)),      # ceil mode adds a last window: 12 -> 7
+    ("p_k3s2_p1_0", 1, 4, 12, 14, 3, 2, (1, 0, 1, 0)),         # how a floor-mode pool reaches TenniS: 12 -> 6
+    ("p_k2s2", 2, 2, 9, 7, 2, 2, (0, 0, 0, 0)),                # odd extents, clipped last window
+    ("p_k3s1_p1", 1, 2, 6, 5, 3, 1, (1, 1, 1, 1)),
+]
+
 CONV_CASES = [
     # name, N, C, H, W, O, KH, KW, pad(t,b,l,r), stride, dilation, padding_value, act, leaky
     ("c_3x3_p1", 1, 8, 9, 9, 5, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1), 0.0, "relu", 0.0),
@@ -84,7 +98,19 @@ def main():
                             stride=np.array(stride), dilation=np.array(dil), padding_value=np.float32(pv),
                             act=np.array(act), leaky=np.float32(leaky), y_conv=y_conv, y_bias=y_bias, y_act=y_act,
                             rq=rq, y_q=y_q)
-    print("wrote", len(QUANT_CASES) + len(CONV_CASES), "fixtures to", HERE)
+    for name, shape, nscales in QUANT64_CASES:
+        x = tie_values(rng, shape).astype(np.float64)
+        x.reshape(-1)[1] = 0.49999999999999994     # just below a tie in double
+        x.reshape(-1)[2] = 3e9                      # beyond int32: -128
+        scales = np.ones(nscales, dtype=np.float32)
+        if nscales > 1:
+            scales[1:] = rng.uniform(0.5, 2.0, size=nscales - 1).astype(np.float32)
+        np.savez_compressed(os.path.join(HERE, name + ".npz"), x=x, scales=scales, y=ref.quantize_f64(x, scales))
+    for name, N, C, H, W, k, stride, pad in POOL_CASES:
+        x = rng.standard_normal((N, C, H, W)).astype(np.float32)
+        np.savez_compressed(os.path.join(HERE, name + ".npz"), x=x, k=np.int32(k), stride=np.int32(stride), pad=np.array(pad),
+                            y=ref.max_pooling2d(x, k, stride, pad))
+    print("wrote", len(QUANT_CASES) + len(CONV_CASES) + len(QUANT64_CASES) + len(POOL_CASES), "fixtures to", HERE)
 
 
 if __name__ == "__main__":

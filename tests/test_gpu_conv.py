@@ -15,13 +15,14 @@ ACT = {"none": 0, "relu": 1, "leaky_relu": 2}
 
 def run_gpu(x, w, pad, stride, dil, dq, bias=None, act="none", leaky=0.0, padding_value=0.0, kernel=0,
             x_layout="nchw", residual=None, rq=None, i8_layout="nchw", f32_layout="nchw", want_acc=True, want_f32=True,
-            res_after=False):
+            res_after=False, tune=None):
     """x int8 NCHW numpy.  Returns dict(kernel, acc, f32, i8) as NCHW numpy arrays."""
     from tennis_b200 import _lib, ops
     dev = torch.device("cuda")
     xd = torch.from_numpy(np.ascontiguousarray(x)).to(dev)
     wd = torch.from_numpy(np.ascontiguousarray(w)).to(dev)
-    plan = ops.ConvPlan(x.shape, w.shape, pad, stride, dil, padding_value, kernel, dev)
+    # tune: overrides of the plan heuristics (tsb_conv_desc.mma_orientation / raw_row_mode / patch_mode), 0 = automatic
+    plan = ops.ConvPlan(x.shape, w.shape, pad, stride, dil, padding_value, kernel, dev, **(tune or {}))
     plan.set_weights(wd)
     N, O, OH, OW = plan.out_shape
     if x_layout == "nhwc":
@@ -142,21 +143,21 @@ def test_tcgen05_kernel_cases(checker, port, case):
     (2, 3, 33, 35, 16, 7, 7, (3, 3, 3, 3), (2, 2), (1, 1)),       # folded input
     (4, 192, 14, 14, 100, 1, 1, (0, 0, 0, 0), (1, 1), (1, 1)),    # 1x1 with tiled activation loads
 ])
-def test_both_mma_orientations(checker, port, monkeypatch, case, swap):
+def test_both_mma_orientations(checker, port, case, swap):
     """Layers with at most 128 output channels can run with channels or with pixels on the MMA's M side; the
-    library picks one by a heuristic, the test forces each in turn (TSB_SWAP is read when the plan is created)."""
-    monkeypatch.setenv("TSB_SWAP", swap)
+    library picks one by a heuristic, the test forces each in turn (tsb_conv_desc.mma_orientation)."""
+    tune = dict(mma_orientation=2 if swap == "1" else 1)
     N, C, H, W, O, KH, KW, pad, stride, dil = case
     rng = np.random.default_rng(N * 100 + C + O + int(swap))
     x = rng.integers(-128, 128, size=(N, C, H, W), dtype=np.int8)
     w = rng.integers(-127, 128, size=(O, C, KH, KW), dtype=np.int8)
     dq = rng.uniform(0.001, 0.01, size=O).astype(np.float32)
     bias = (rng.standard_normal(O) * 0.1).astype(np.float32)
-    check_case(checker, port, x, w, pad, stride, dil, dq, bias, "relu", 0.0, 0.0, 2)                        # fp32 NCHW fast path
-    check_case(checker, port, x, w, pad, stride, dil, dq, None, "leaky_relu", 0.1, 0.0, 2, want_acc=False,
+    check_case(checker, port, x, w, pad, stride, dil, dq, bias, "relu", 0.0, 0.0, 2, tune=tune)             # fp32 NCHW fast path
+    check_case(checker, port, x, w, pad, stride, dil, dq, None, "leaky_relu", 0.1, 0.0, 2, want_acc=False, tune=tune,
                x_layout="nhwc", rq=np.full(N, 0.7, dtype=np.float32), i8_layout="nhwc", f32_layout="nhwc")  # generic path
     got = run_gpu(x, w, pad, stride, dil, dq, bias, "relu", 0.0, 0.0, 2, x_layout="nhwc", rq=np.full(N, 0.7, dtype=np.float32),
-                  i8_layout="nhwc", want_acc=False, want_f32=False)                                           # int8 NHWC fast path
+                  i8_layout="nhwc", want_acc=False, want_f32=False, tune=tune)                                # int8 NHWC fast path
     want = checker.quantize(checker.relu(checker.add_bias(checker.conv2d_quantized(x, w, pad, stride, dil, dq), bias)), np.full(N, 0.7, np.float32))
     assert np.array_equal(got["i8"], want)
 
@@ -174,23 +175,23 @@ def test_both_mma_orientations(checker, port, monkeypatch, case, swap):
                                                                  # CTAs that start in the middle of a row, shared stages
     (2, 3, 50, 390, 24, 3, 3, (1, 1, 1, 1), (1, 1), (1, 1)),     # 16 bytes per pixel, four segments, 400 tiles
 ])
-def test_raw_row_mode(checker, port, monkeypatch, case):
+def test_raw_row_mode(checker, port, case):
     """Few input channels with a pixel stride of 16 staged bytes: the kernel copies each staged image row once per
     tile and the MMA reads the overlapping windows through a sliding descriptor.  Forced on here for short rows too."""
-    monkeypatch.setenv("TSB_ROWS", "1")
+    tune = dict(raw_row_mode=2)
     N, C, H, W, O, KH, KW, pad, stride, dil = case
     rng = np.random.default_rng(N * 77 + C + O + W)
     x = rng.integers(-128, 128, size=(N, C, H, W), dtype=np.int8)
     w = rng.integers(-127, 128, size=(O, C, KH, KW), dtype=np.int8)
     dq = rng.uniform(0.001, 0.01, size=O).astype(np.float32)
     bias = (rng.standard_normal(O) * 0.1).astype(np.float32)
-    got = check_case(checker, port, x, w, pad, stride, dil, dq, bias, "relu", 0.0, 0.0, 2)
+    got = check_case(checker, port, x, w, pad, stride, dil, dq, bias, "relu", 0.0, 0.0, 2, tune=tune)
     assert got["kernel"] == 2
     rq = np.full(N, 0.7, dtype=np.float32)
-    check_case(checker, port, x, w, pad, stride, dil, dq, None, "leaky_relu", 0.1, 0.0, 2, want_acc=False,
+    check_case(checker, port, x, w, pad, stride, dil, dq, None, "leaky_relu", 0.1, 0.0, 2, want_acc=False, tune=tune,
                x_layout="nhwc", rq=rq, i8_layout="nhwc", f32_layout="nhwc")
     got = run_gpu(x, w, pad, stride, dil, dq, bias, "relu", 0.0, 0.0, 2, x_layout="nhwc", rq=rq, i8_layout="nhwc",
-                  want_acc=False, want_f32=False)
+                  want_acc=False, want_f32=False, tune=tune)
     want = checker.quantize(checker.relu(checker.add_bias(checker.conv2d_quantized(x, w, pad, stride, dil, dq), bias)), rq)
     assert np.array_equal(got["i8"], want)
 
@@ -205,25 +206,24 @@ def test_raw_row_mode(checker, port, monkeypatch, case):
     (1, 64, 10, 30, 32, 3, 1, (1, 1, 0, 0), (1, 1), (1, 1)),      # a column filter
     (2, 64, 11, 13, 64, 2, 3, (0, 1, 2, 0), (1, 1), (1, 1)),      # asymmetric padding, even filter height
 ])
-def test_patch_mode(checker, port, monkeypatch, case, swap):
+def test_patch_mode(checker, port, case, swap):
     """Stride-1 filters with several taps: one tensor-map load brings the input patch under an 8-pixel-wide tile and
     every tap reads its window out of it through a shifted shared-memory descriptor.  Forced on here regardless of how
     well the tiles cover the image, in both MMA orientations."""
-    monkeypatch.setenv("TSB_PATCH", "1")
-    monkeypatch.setenv("TSB_SWAP", swap)
+    tune = dict(patch_mode=2, mma_orientation=2 if swap == "1" else 1)
     N, C, H, W, O, KH, KW, pad, stride, dil = case
     rng = np.random.default_rng(N * 13 + C + O + H)
     x = rng.integers(-128, 128, size=(N, C, H, W), dtype=np.int8)
     w = rng.integers(-127, 128, size=(O, C, KH, KW), dtype=np.int8)
     dq = rng.uniform(0.001, 0.01, size=O).astype(np.float32)
     bias = (rng.standard_normal(O) * 0.1).astype(np.float32)
-    got = check_case(checker, port, x, w, pad, stride, dil, dq, bias, "relu", 0.0, 0.0, 2)               # fp32 NCHW
+    got = check_case(checker, port, x, w, pad, stride, dil, dq, bias, "relu", 0.0, 0.0, 2, tune=tune)    # fp32 NCHW
     assert got["kernel"] == 2
     rq = rng.uniform(0.5, 2.0, size=N).astype(np.float32)
-    check_case(checker, port, x, w, pad, stride, dil, dq, None, "leaky_relu", 0.1, 0.0, 2, want_acc=False,
+    check_case(checker, port, x, w, pad, stride, dil, dq, None, "leaky_relu", 0.1, 0.0, 2, want_acc=False, tune=tune,
                x_layout="nhwc", rq=rq, i8_layout="nhwc", f32_layout="nhwc")                                # element by element
     got = run_gpu(x, w, pad, stride, dil, dq, bias, "relu", 0.0, 0.0, 2, x_layout="nhwc", rq=rq, i8_layout="nhwc",
-                  want_acc=False, want_f32=False)                                                          # int8 NHWC
+                  want_acc=False, want_f32=False, tune=tune)                                               # int8 NHWC
     want = checker.quantize(checker.relu(checker.add_bias(checker.conv2d_quantized(x, w, pad, stride, dil, dq), bias)), rq)
     assert np.array_equal(got["i8"], want)
 
@@ -234,13 +234,10 @@ def test_patch_mode(checker, port, monkeypatch, case, swap):
     (3, 128, 14, 14, 160),   # 196 pixels per image
     (4, 64, 5, 5, 64),       # fewer than 32 pixels per image: several boundaries in one chunk
 ])
-def test_residual_tail_pixel_major_with_per_sample_scales(checker, port, monkeypatch, case, swap):
+def test_residual_tail_pixel_major_with_per_sample_scales(checker, port, case, swap):
     """1x1 convolution + residual + relu with pixel-major fp32 in/out and a fused requantize whose scale differs from
     sample to sample: a chunk of 32 pixels that crosses an image boundary must switch scales at the boundary."""
-    if swap is None:
-        monkeypatch.delenv("TSB_SWAP", raising=False)
-    else:
-        monkeypatch.setenv("TSB_SWAP", swap)
+    tune = dict(mma_orientation=0 if swap is None else (2 if swap == "1" else 1))
     N, C, H, W, O = case
     rng = np.random.default_rng(N * 31 + O)
     x = rng.integers(-128, 128, size=(N, C, H, W), dtype=np.int8)
@@ -249,9 +246,9 @@ def test_residual_tail_pixel_major_with_per_sample_scales(checker, port, monkeyp
     bias = (rng.standard_normal(O) * 0.1).astype(np.float32)
     residual = rng.standard_normal((N, O, H, W)).astype(np.float32)
     rq = rng.uniform(0.5, 4.0, size=N).astype(np.float32)
-    check_case(checker, port, x, w, (0, 0, 0, 0), (1, 1), (1, 1), dq, bias, "relu", 0.0, 0.0, 2, want_acc=False,
+    check_case(checker, port, x, w, (0, 0, 0, 0), (1, 1), (1, 1), dq, bias, "relu", 0.0, 0.0, 2, want_acc=False, tune=tune,
                x_layout="nhwc", residual=residual, rq=rq, f32_layout="nhwc", i8_layout="nhwc")
-    check_case(checker, port, x, w, (0, 0, 0, 0), (1, 1), (1, 1), dq, bias, "none", 0.0, 0.0, 2, want_acc=False,
+    check_case(checker, port, x, w, (0, 0, 0, 0), (1, 1), (1, 1), dq, bias, "none", 0.0, 0.0, 2, want_acc=False, tune=tune,
                x_layout="nhwc", rq=rq, f32_layout="nchw", i8_layout="nhwc")
 
 
@@ -295,12 +292,9 @@ def test_epilogue_variants(checker, port, kernel):
 
 @pytest.mark.parametrize("kernel", [1, 2])
 @pytest.mark.parametrize("swap", [None, "0", "1"])
-def test_residual_after_the_activation(checker, port, monkeypatch, kernel, swap):
+def test_residual_after_the_activation(checker, port, kernel, swap):
     """A Darknet shortcut: leaky_relu(conv + bias) + residual, every output layout, both kernels and orientations."""
-    if swap is None:
-        monkeypatch.delenv("TSB_SWAP", raising=False)
-    else:
-        monkeypatch.setenv("TSB_SWAP", swap)
+    tune = dict(mma_orientation=0 if swap is None else (2 if swap == "1" else 1))
     rng = np.random.default_rng(7)
     N, C, H, W, O = 2, 64, 12, 12, 96
     x = rng.integers(-128, 128, size=(N, C, H, W), dtype=np.int8)
@@ -312,10 +306,10 @@ def test_residual_after_the_activation(checker, port, monkeypatch, kernel, swap)
     args = (x, w, (1, 1, 1, 1), (1, 1), (1, 1), dq)
     for f32_layout, i8_layout in (("nhwc", "nhwc"), ("nchw", "nhwc"), ("nchw", "nchw")):
         check_case(checker, port, *args, bias, "leaky_relu", 0.1, 0.0, kernel, residual=residual, rq=rq, res_after=True,
-                   x_layout="nhwc", f32_layout=f32_layout, i8_layout=i8_layout, want_acc=False)
+                   x_layout="nhwc", f32_layout=f32_layout, i8_layout=i8_layout, want_acc=False, tune=tune)
     w1 = rng.integers(-127, 128, size=(O, C, 1, 1), dtype=np.int8)
     check_case(checker, port, x, w1, (0, 0, 0, 0), (1, 1), (1, 1), dq, bias, "relu", 0.0, 0.0, kernel, residual=residual, rq=rq,
-               res_after=True, x_layout="nhwc", f32_layout="nhwc", i8_layout="nhwc", want_acc=False)
+               res_after=True, x_layout="nhwc", f32_layout="nhwc", i8_layout="nhwc", want_acc=False, tune=tune)
 
 
 def test_concat_of_two_int8_tensors():

@@ -9,35 +9,9 @@ pytestmark = pytest.mark.gpu
 
 
 def reference_forward(spec, params, scales, x, chk):
+    from oracle import chains
     from tennis_b200 import nets
-    n = x.shape[0]
-    convs, P = spec["convs"], params["convs"]
-
-    def block(idx, xq, residual=None):
-        c, p = convs[idx], P[idx]
-        s_in, s_out = scales["convs"][idx]
-        dq = nets.dequantize_scales(p["sw"], scales["bn"][idx], s_in)
-        return chk.conv_block(xq, p["w"], (c["pad"],) * 4, (c["stride"],) * 2, (1, 1), dq, p["bias"], act="leaky_relu",
-                              leaky=nets.LEAKY, residual=residual, requant_scales=[float(s_out)] * n,
-                              residual_after_activation=residual is not None)
-
-    outs = {}
-    xq = chk.quantize(x, [float(scales["input"])] * n)
-    _, cur = block(spec["stem"], xq)
-    for st in spec["stages"]:
-        _, cur = block(st["down"], cur)
-        xb_f, xb_q = block(st["route_b"], cur)
-        for b in st["blocks"]:
-            _, h = block(b["conv1"], xb_q)
-            xb_f, xb_q = block(b["conv2"], h, residual=xb_f)
-            outs[b["name"]] = xb_q
-        _, post = block(st["post"], xb_q)
-        _, ra = block(st["route_a"], cur)
-        # concat of the fp32 tensors followed by one quantize == concat of the two int8 tensors (same scale)
-        assert scales["convs"][st["post"]][1] == scales["convs"][st["route_a"]][1]
-        _, cur = block(st["transition"], np.concatenate([post, ra], axis=1))
-        outs[st["name"]] = cur
-    return outs, cur
+    return chains.cspdarknet_forward(spec, params, scales, x, chk, leaky=nets.LEAKY)
 
 
 def test_small_cspdarknet_matches_the_operator_chain(checker):
@@ -78,6 +52,32 @@ def test_small_cspdarknet_matches_the_operator_chain(checker):
     graph.replay()
     torch.cuda.synchronize()
     assert torch.equal(res, out)
+
+
+def test_full_size_cspdarknet53_first_and_last_image(port):
+    """Configuration 3 at its full size (CSPDarknet53-shaped, batch 16 at 608 x 608): the first and the last image of
+    the batch against the operator chain run on those two images alone (per-sample scales make the slice exact)."""
+    from tennis_b200 import nets
+    spec = nets.cspdarknet_spec()
+    params = nets.make_conv_params(spec, seed=0)
+    n = 16
+    g = torch.Generator(device="cuda").manual_seed(0)
+    xd = torch.rand((n, 3, 608, 608), device="cuda", generator=g)
+    net = nets.QuantCSPDarknet(spec, params, n)
+    scales = net.calibrate(xd)
+    out = net.forward(xd).clone()
+    net.status()
+    torch.cuda.synchronize()
+    pick = [0, n - 1]
+    outs, last = reference_forward(spec, params, scales, xd[pick].cpu().numpy(), port)
+    for st in spec["stages"]:
+        for b in st["blocks"]:
+            got = net.buffers[b["name"] + ".y.i8"][pick].cpu().numpy()
+            o = spec["convs"][b["conv2"]]["o"]
+            assert np.array_equal(got[..., :o].transpose(0, 3, 1, 2), outs[b["name"]]), b["name"]
+        got = net.buffers[st["name"] + ".out.i8"][pick].cpu().numpy()
+        assert np.array_equal(got[..., :st["width"]].transpose(0, 3, 1, 2), outs[st["name"]]), st["name"]
+    assert np.array_equal(out[pick].cpu().numpy()[..., :spec["features"]].transpose(0, 3, 1, 2), last)
 
 
 def test_cspdarknet53_topology():

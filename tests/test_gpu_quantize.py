@@ -32,6 +32,32 @@ def test_quantize_golden(name):
     assert np.array_equal(gpu_quantize(g["x"], g["scales"]), g["y"])
 
 
+@pytest.mark.parametrize("name", golden_cases("d_"))
+def test_quantize_fp64_golden(name):
+    g = load_golden(name)
+    assert np.array_equal(gpu_quantize(g["x"], g["scales"]), g["y"])
+
+
+@pytest.mark.parametrize("shape", [(1, 1), (1, 9), (1, 17), (1, 1003), (3, 7), (4, 3, 5, 5), (200, 4, 3, 3), (2, 100003)])
+def test_fp64_input(checker, shape):
+    """FLOAT64 tensors take the reference's generic branch: a double product, half-away rounding for every element."""
+    rng = np.random.default_rng(sum(shape))
+    x = ties(rng, shape).astype(np.float64)
+    x.reshape(-1)[0] = 0.49999999999999994     # below a tie in double, a tie once narrowed to fp32
+    x.reshape(-1)[-1] = 2.5000000000000004
+    s = rng.uniform(0.5, 2.0, size=shape[0]).astype(np.float32)
+    s[0] = 1.0
+    assert np.array_equal(gpu_quantize(x, s), checker.quantize_f64(x, s))
+    # misaligned view: the element-at-a-time kernel
+    from tennis_b200 import _lib, ops
+    flat = torch.from_numpy(x.reshape(-1)).cuda()
+    if flat.numel() > 40:
+        y = torch.zeros(flat.numel(), dtype=torch.int8, device="cuda")
+        _lib.check(_lib.load().tsb_quantize_f64_i8(ops._ptr(flat[1:]), ops._ptr(y[1:]), flat.numel() - 1, _lib.float_array([1.0]), 1,
+                                                   ops._stream_ptr()))
+        assert np.array_equal(y[1:].cpu().numpy(), checker.quantize_f64(x.reshape(1, -1)[:, 1:], [1.0])[0])
+
+
 @pytest.mark.parametrize("count", [1, 7, 8, 9, 15, 16, 17, 24, 31, 32, 33, 255, 1000, 1003, 4099, 100003])
 def test_one_scale_tails_and_ties(checker, count):
     rng = np.random.default_rng(count)

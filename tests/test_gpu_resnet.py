@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 import torch
 
-from conftest import same_bits
+from conftest import golden_cases, load_golden, same_bits
 
 pytestmark = pytest.mark.gpu
 
@@ -23,34 +23,10 @@ def maxpool_f32(x, k=3, s=2, p=1):
 
 
 def reference_forward(spec, params, scales, x, chk):
-    """The network as a chain of reference operators.  Returns (int8 block outputs, fp32 last block output, logits)."""
-    from tennis_b200 import nets
-    n = x.shape[0]
-    convs, P = spec["convs"], params["convs"]
-
-    def block(idx, xq, act, residual=None, requant=True):
-        c, p = convs[idx], P[idx]
-        s_in, s_out = scales["convs"][idx]
-        dq = nets.dequantize_scales(p["sw"], scales["bn"][idx], s_in)
-        rq = [float(s_out)] * n if requant else None
-        return chk.conv_block(xq, p["w"], (c["pad"],) * 4, (c["stride"],) * 2, (1, 1), dq, p["bias"], act=act,
-                              residual=residual, requant_scales=rq)
-
-    xq = chk.quantize(x, [float(scales["input"])] * n)
-    y, _ = block(0, xq, "relu")
-    pooled = maxpool_f32(y)
-    x_i8 = chk.quantize(pooled, [float(scales["convs"][0][1])] * n)
-    x_f32, outs = None, []
-    for stage in spec["stages"]:
-        for b in stage:
-            _, a = block(b["conv1"], x_i8, "relu")
-            _, bb = block(b["conv2"], a, "relu")
-            sc = block(b["proj"], x_i8, "none", requant=False) if b["projection"] else x_f32
-            x_f32, x_i8 = block(b["conv3"], bb, "relu", residual=sc)
-            outs.append(x_i8)
-    feat = x_f32.reshape(n, x_f32.shape[1], -1).mean(axis=2, dtype=np.float64).astype(np.float32)
-    logits = (feat.astype(np.float64) @ params["fc_w"].T.astype(np.float64) + params["fc_b"]).astype(np.float32)
-    return outs, x_f32, logits
+    """The network as a chain of reference operators (oracle/chains.py); the stem pool is also checked against a plain
+    numpy floor-mode pooling, which the graph's padding {1,0,1,0} under the ceil-mode extent must equal."""
+    from oracle import chains
+    return chains.resnet_forward(spec, params, scales, x, chk)
 
 
 def test_small_resnet_matches_the_operator_chain(checker):
@@ -97,6 +73,54 @@ def test_small_resnet_matches_the_operator_chain(checker):
     assert torch.equal(out, logits)
 
 
+@pytest.mark.parametrize("name", golden_cases("p_"))
+def test_max_pooling_golden(name):
+    """pooling2d fixtures made by the reference's operator: quantize(pool(x)) == pool(quantize(x)) for the int8 kernel."""
+    from tennis_b200 import _lib, ops
+    lib = _lib.load()
+    g = load_golden(name)
+    x, k, st, pad = g["x"], int(g["k"]), int(g["stride"]), [int(v) for v in g["pad"]]
+    n, c, h, w = x.shape
+    scale = [float(127.0 / np.abs(x).max())] * n
+    xq = ops.quantize_nchw_to_nhwc(torch.from_numpy(x).cuda(), scale)
+    oh, ow = g["y"].shape[2:]
+    assert (oh, ow) == (lib.tsb_pool_out_dim(h, pad[0], pad[1], k, st), lib.tsb_pool_out_dim(w, pad[2], pad[3], k, st))
+    y = torch.zeros((n, oh, ow, xq.shape[3]), dtype=torch.int8, device="cuda")
+    _lib.check(lib.tsb_maxpool_i8_nhwc(xq.data_ptr(), y.data_ptr(), n, h, w, c, k, st, *pad, ops._stream_ptr()))
+    want = ops.quantize_nchw_to_nhwc(torch.from_numpy(g["y"]).cuda(), scale)
+    assert torch.equal(y, want)
+
+
+def test_full_size_resnet50_first_and_last_image(port):
+    """Configuration 2 at its full size (ResNet-50-shaped, batch 64, 224 x 224): the first and the last image of the
+    batch against the operator chain run on those two images alone.  Every scale is per sample, so a slice of the batch
+    is exact -- as long as the slice keeps more than one sample (a batch of one takes the operator's one-scale rounding)."""
+    from tennis_b200 import nets
+    spec = nets.resnet_spec()
+    params = nets.make_params(spec, seed=0)
+    n = 64
+    g = torch.Generator(device="cuda").manual_seed(0)
+    xd = torch.randn((n, 3, 224, 224), device="cuda", generator=g)
+    net = nets.QuantResNet(spec, params, n)
+    scales = net.calibrate(xd)
+    logits = net.forward(xd).clone()
+    net.status()
+    torch.cuda.synchronize()
+    pick = [0, n - 1]
+    outs, last_f32, want_logits = reference_forward(spec, params, scales, xd[pick].cpu().numpy(), port)
+    k = 0
+    for stage in spec["stages"]:
+        for b in stage:
+            got = net.buffers[b["name"] + ".y.i8"][pick].cpu().numpy()
+            o = spec["convs"][b["conv3"]]["o"]
+            assert np.array_equal(got[..., :o].transpose(0, 3, 1, 2), outs[k]), b["name"]
+            assert not got[..., o:].any()
+            k += 1
+    last = net.buffers[spec["stages"][-1][-1]["name"] + ".y.f32"][pick].cpu().numpy().transpose(0, 3, 1, 2)
+    assert same_bits(last, last_f32)
+    np.testing.assert_allclose(logits[pick].cpu().numpy(), want_logits, rtol=1e-5, atol=1e-5 * np.abs(want_logits).max())
+
+
 def test_resnet50_topology():
     from tennis_b200 import nets
     spec = nets.resnet_spec()
@@ -110,10 +134,14 @@ def test_pool_and_inner_product_kernels(checker):
     rng = np.random.default_rng(2)
     x = rng.integers(-128, 128, size=(2, 9, 11, 64), dtype=np.int8)
     xd = torch.from_numpy(x).cuda()
-    y = torch.empty((2, 5, 6, 64), dtype=torch.int8, device="cuda")
-    _lib.check(lib.tsb_maxpool_i8_nhwc(xd.data_ptr(), y.data_ptr(), 2, 9, 11, 64, 3, 2, 1, ops._stream_ptr()))
-    want = maxpool_f32(x.transpose(0, 3, 1, 2).astype(np.float32)).transpose(0, 2, 3, 1).astype(np.int8)
-    assert np.array_equal(y.cpu().numpy(), want)
+    # the reference's pooling2d: ceil-mode extent, windows clipped to the image
+    for (k, st, pad) in ((3, 2, (1, 1, 1, 1)), (3, 2, (1, 0, 1, 0)), (2, 2, (0, 0, 0, 0)), (3, 1, (1, 1, 1, 1)), (5, 3, (2, 2, 2, 1))):
+        want = checker.max_pooling2d(x.transpose(0, 3, 1, 2).astype(np.float32), k, st, pad)
+        oh, ow = lib.tsb_pool_out_dim(9, pad[0], pad[1], k, st), lib.tsb_pool_out_dim(11, pad[2], pad[3], k, st)
+        assert want.shape == (2, 64, oh, ow)
+        y = torch.full((2, oh, ow, 64), 99, dtype=torch.int8, device="cuda")
+        _lib.check(lib.tsb_maxpool_i8_nhwc(xd.data_ptr(), y.data_ptr(), 2, 9, 11, 64, k, st, *pad, ops._stream_ptr()))
+        assert np.array_equal(y.cpu().numpy(), want.transpose(0, 2, 3, 1).astype(np.int8)), (k, st, pad)
     f = rng.standard_normal((3, 49, 40)).astype(np.float32)
     fd = torch.from_numpy(f).cuda()
     g = torch.empty((3, 40), device="cuda")

@@ -1,6 +1,7 @@
 """Host-side behaviour that needs no GPU: attribute parsing and checks of the operator mirrors, argument
 validation of the C ABI (a rejected call launches nothing), kernel selection and the workload arithmetic."""
 import ctypes
+import os
 
 import numpy as np
 import pytest
@@ -139,6 +140,76 @@ def test_load_mode_and_orientation_of_the_benchmark_layers():
     csp_stem = describe(n=16, c=3, h=608, w=608, o=32, kh=3, kw=3, **same)
     assert "mode=rows" in csp_stem and "tiles=48640x1" in csp_stem
     assert describe(padding_value=3.0).startswith("kernel=direct (non-zero padding_value)")
+
+
+def test_raw_row_plans_keep_their_weights_resident():
+    """A wide few-channel layer with more than 128 output channels: raw-row mode is admitted where two row stages fit
+    beside the weight tile, and the plan must then keep the weights resident (the mode cannot stream them)."""
+    text = describe(n=1, c=3, h=64, w=700, o=192, kh=7, kw=7, stride_h=2, stride_w=2, pad_top=3, pad_bottom=3, pad_left=3, pad_right=3)
+    assert "mode=rows" in text and "resident=1" in text, text
+    stages = int(text.split("stages=")[1].split()[0])
+    assert 2 <= stages < 4, text
+    # forced off, the same layer takes the folded im2col loads
+    text = describe(n=1, c=3, h=64, w=700, o=192, kh=7, kw=7, stride_h=2, stride_w=2, pad_top=3, pad_bottom=3, pad_left=3, pad_right=3,
+                    raw_row_mode=_lib.TUNE_OFF)
+    assert "mode=fold" in text, text
+
+
+def test_heuristic_overrides_travel_in_the_descriptor():
+    same = dict(pad_top=1, pad_bottom=1, pad_left=1, pad_right=1)
+    auto = describe(n=2, c=64, h=20, w=20, o=64, kh=3, kw=3, **same)
+    normal = describe(n=2, c=64, h=20, w=20, o=64, kh=3, kw=3, mma_orientation=_lib.TUNE_OFF, **same)
+    swapped = describe(n=2, c=64, h=20, w=20, o=64, kh=3, kw=3, mma_orientation=_lib.TUNE_ON, **same)
+    assert "swap=0" in normal and "swap=1" in swapped and "alt:" not in normal and "alt:" not in swapped
+    assert "mode=patch" in describe(n=2, c=64, h=20, w=20, o=64, kh=3, kw=3, patch_mode=_lib.TUNE_ON, **same)
+    assert "mode=patch" not in describe(n=2, c=64, h=20, w=20, o=64, kh=3, kw=3, patch_mode=_lib.TUNE_OFF, **same)
+    assert auto.startswith("kernel=tcgen05")
+    st, _ = create(desc(mma_orientation=3))
+    assert st == _lib.ERR_INVALID_ARGUMENT and b"TSB_TUNE" in _lib.load().tsb_last_error()
+    # the environment no longer changes plans or layouts
+    import os
+    os.environ["TSB_SWAP"], os.environ["TSB_PAD128"] = "1", "1"
+    try:
+        assert describe(n=2, c=64, h=20, w=20, o=64, kh=3, kw=3, **same) == auto
+        assert _lib.load().tsb_padded_channels(65) == 128 and _lib.load().tsb_padded_channels(129) == 192
+    finally:
+        del os.environ["TSB_SWAP"], os.environ["TSB_PAD128"]
+
+
+def test_status_word_decoding_names_every_wait():
+    lib = _lib.load()
+    assert lib.tsb_conv2d_i8_status_decode(0) == 0
+    for code, word in ((1, b"stage free"), (2, b"accumulator buffer free"), (3, b"tile loaded"), (4, b"accumulator ready"),
+                       (5, b"weight tile free"), (6, b"weight tile loaded")):
+        assert lib.tsb_conv2d_i8_status_decode(code) == _lib.ERR_DEVICE_TIMEOUT
+        assert word in lib.tsb_last_error() and (b"wait %d" % code) in lib.tsb_last_error()
+
+
+def test_pool_extent_follows_the_reference():
+    lib = _lib.load()
+    assert lib.tsb_pool_out_dim(112, 1, 1, 3, 2) == 57 and lib.tsb_pool_out_dim(112, 1, 0, 3, 2) == 56
+    assert lib.tsb_pool_out_dim(9, 0, 0, 2, 2) == 5 and lib.tsb_pool_out_dim(6, 1, 1, 3, 1) == 6
+    assert lib.tsb_pool_out_dim(0, 0, 0, 2, 2) == _lib.ERR_INVALID_ARGUMENT
+    before = lib.tsb_kernel_launch_count()
+    # a window wholly inside the padding is refused before any launch
+    assert lib.tsb_maxpool_i8_nhwc(ctypes.c_void_p(256), ctypes.c_void_p(512), 1, 4, 4, 16, 2, 2, 0, 2, 0, 2, None) == _lib.ERR_UNSUPPORTED
+    assert lib.tsb_kernel_launch_count() == before
+
+
+def test_quantize_mirror_takes_fp32_and_fp64_only():
+    q = ops.Quantize()
+    q.set("quantize_scale", np.array([1.0], np.float32))
+    q.init()
+    with pytest.raises(ops.EjectionException, match="quantize not support this data type: float16"):
+        q.run([torch.zeros(1, 4, dtype=torch.float16)])
+    with pytest.raises(ops.EjectionException, match="not support this data type: int32"):
+        q.run([torch.zeros(1, 4, dtype=torch.int32)])
+
+
+def test_requantize_scale_limit_is_stated():
+    assert _lib.MAX_REQUANT_SCALES == 128
+    text = open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include", "tennis_b200.h")).read()
+    assert "#define TSB_MAX_REQUANT_SCALES 128" in text
 
 
 def test_run_rejects_bad_arguments_before_any_launch():

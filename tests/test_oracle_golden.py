@@ -24,6 +24,34 @@ def test_conv_golden(port, name):
     assert np.array_equal(port.quantize(ya, g["rq"]), g["y_q"])
 
 
+@pytest.mark.parametrize("name", golden_cases("d_"))
+def test_quantize_fp64_golden(port, name):
+    g = load_golden(name)
+    assert np.array_equal(port.quantize_f64(g["x"], g["scales"]), g["y"])
+
+
+@pytest.mark.parametrize("name", golden_cases("p_"))
+def test_max_pooling_golden(port, name):
+    g = load_golden(name)
+    y = port.max_pooling2d(g["x"], int(g["k"]), int(g["stride"]), g["pad"])
+    assert y.shape == g["y"].shape and np.array_equal(y, g["y"])
+
+
+def test_pooling_extent_is_ceil_mode(port):
+    # the ResNet stem pool: 112, k3, s2 -- padding 1 on both sides gives 57 under the reference's ceil rule,
+    # {1, 0} gives the familiar 56
+    x = np.zeros((1, 1, 112, 112), np.float32)
+    assert port.max_pooling2d(x, 3, 2, (1, 1, 1, 1)).shape == (1, 1, 57, 57)
+    assert port.max_pooling2d(x, 3, 2, (1, 0, 1, 0)).shape == (1, 1, 56, 56)
+    with pytest.raises(ValueError):      # a window that lies wholly in the padding
+        port.max_pooling2d(np.zeros((1, 1, 4, 4), np.float32), 2, 2, (0, 2, 0, 2))
+
+
+def test_fp64_rounds_half_away_everywhere(port):
+    x = np.array([[0.5, 2.5, 126.5, -0.5, -2.5, 1.5, 3.5, -1.5, 0.5, 2.5, 126.5, 3e9, np.nan]], dtype=np.float64)
+    assert port.quantize_f64(x, [1.0]).tolist() == [[1, 3, 127, -1, -3, 2, 4, -2, 1, 3, 127, -128, -128]]
+
+
 def test_known_rounding_answers(port):
     # one scale: the 8-wide body rounds half-to-even, the tail half-away-from-zero
     x = np.array([[0.5, 2.5, 126.5, -0.5, -2.5, 1.5, 3.5, -1.5, 0.5, 2.5, 126.5]], dtype=np.float32)
@@ -52,6 +80,16 @@ def test_port_matches_reference_live(port, reference):
         x = x[:nscales]
         s = rng.uniform(0.5, 2.0, size=nscales).astype(np.float32)
         assert np.array_equal(port.quantize(x, s), reference.quantize(x, s))
+    for count, nscales in [(9, 1), (1003, 1), (30, 3), (31, 4)]:
+        x = (rng.standard_normal((nscales, count)) * 50)
+        x[0, :4] = [0.5, 2.5, -0.5, 1e12]
+        s = rng.uniform(0.5, 2.0, size=nscales).astype(np.float32)
+        assert np.array_equal(port.quantize_f64(x, s), reference.quantize_f64(x, s))
+    for (shape, k, st, pad) in [((2, 3, 112, 112), 3, 2, (1, 1, 1, 1)), ((1, 2, 13, 9), 3, 2, (1, 0, 0, 1)), ((1, 1, 8, 8), 2, 2, (0, 0, 0, 0)),
+                                ((1, 2, 7, 7), 3, 1, (1, 1, 1, 1)), ((1, 2, 10, 11), 5, 3, (2, 2, 2, 2))]:
+        x = rng.standard_normal(shape).astype(np.float32)
+        a, b = port.max_pooling2d(x, k, st, pad), reference.max_pooling2d(x, k, st, pad)
+        assert a.shape == b.shape and np.array_equal(a, b), (shape, k, st, pad)
     cases = [(2, 5, 8, 8, 7, 3, 2, (1, 1, 0, 1), (1, 2), (1, 1)), (1, 6, 6, 6, 3, 1, 1, (1, 1, 1, 1), (1, 1), (3, 3)),
              (1, 3, 12, 12, 4, 5, 5, (2, 2, 2, 2), (3, 3), (1, 1))]
     for (N, C, H, W, O, KH, KW, pad, st, dl) in cases:

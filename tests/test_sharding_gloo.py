@@ -23,7 +23,11 @@ def test_shard_ranges_partition_the_batch():
     assert sharding.shard_range(2048, 8, 3) == (768, 256)
     with pytest.raises(ValueError):
         sharding.shard_range(8, 2, 2)
-    assert len({sharding.shard_seed(0, r) for r in range(8)}) == 8
+    assert [sharding.shard_seed(r) for r in range(8)] == list(range(1000, 1008))
+    # global batch 2048 in micro-batches of 64: 32 / 16 / 8 / 4 per replica at 1 / 2 / 4 / 8 replicas
+    for world, per in ((1, 32), (2, 16), (4, 8), (8, 4)):
+        assert sharding.micro_batches(sharding.shard_range(2048, world, world - 1)[1], 64) == [64] * per
+    assert sharding.micro_batches(130, 64) == [64, 64, 2] and sharding.micro_batches(0, 64) == []
 
 
 def _free_port():

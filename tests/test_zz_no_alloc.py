@@ -44,6 +44,20 @@ def test_static_table_quantize_matches_allocating_quantize_twice_in_a_row():
     x3 = torch.tensor([[0.5, 2.5, 126.5, -0.5, -2.5, 1.5, 3.5, -1.5, 0.5, 2.5, 126.5]], device="cuda")
     c_old, c_new = _both(lib, x3, [1.0])
     assert c_new.tolist() == [[0, 2, 126, 0, -2, 2, 4, -2, 1, 3, 127]] and torch.equal(c_old, c_new)
+    # the property the entry point exists for: no device memory is obtained by a call.  The allocating variant takes a
+    # stream-ordered temporary for 200 scales (the device's free memory drops while the pool holds it); the static
+    # variant must leave the free-memory figure of the driver exactly where it was.
+    torch.cuda.synchronize()
+    y = torch.zeros(x1.shape, dtype=torch.int8, device="cuda")
+    arr = _lib.float_array(s1)
+    from tennis_b200 import ops
+    free_before = torch.cuda.mem_get_info()[0]
+    for _ in range(3):
+        _lib.check(lib.tsb_quantize_f32_i8_static(ops._ptr(x1), ops._ptr(y), x1.numel(), arr, len(s1), ops._stream_ptr()))
+        assert torch.cuda.mem_get_info()[0] == free_before     # while the work may still be in flight
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    assert torch.equal(y, a_old)
     # beyond the table: refused, nothing launched, output untouched
     before = lib.tsb_kernel_launch_count()
     y = torch.full((8,), 7, dtype=torch.int8, device="cuda")
