@@ -227,8 +227,8 @@ int tsb_conv2d_i8_plan_describe(const tsb_conv_plan *plan, char *text, size_t te
     if (!plan || !text || text_bytes < 2) return fail(TSB_ERR_INVALID_ARGUMENT, "plan_describe: null pointer");
     auto one = [&](const tc::Config &c, char *dst, size_t n) {
         const char *mode = c.patch ? "patch" : (plan->view.rows ? "rows" : (plan->view.a_tiled ? "tiled" : (plan->view.fold ? "fold" : "im2col")));
-        return snprintf(dst, n, "mode=%s swap=%d bn=%d bk=%d pix=%d tiles=%dx%d grid=%d stages=%d resident=%d smem=%u", mode, c.swap,
-                        c.bn, c.bk, c.pix, c.num_m_tiles, c.num_n_tiles, c.grid, c.stages, c.b_resident, c.dyn_smem);
+        return snprintf(dst, n, "mode=%s swap=%d bn=%d bk=%d pix=%d tiles=%dx%d grid=%d stages=%d kgroup=%d resident=%d smem=%u", mode, c.swap,
+                        c.bn, c.bk, c.pix, c.num_m_tiles, c.num_n_tiles, c.grid, c.stages, c.kgroup, c.b_resident, c.dyn_smem);
     };
     int len;
     if (plan->kernel != TSB_KERNEL_TCGEN05) {

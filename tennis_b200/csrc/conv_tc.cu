@@ -24,14 +24,18 @@
 
 #include <algorithm>
 #include <atomic>
+#include <type_traits>
 #include <cstdlib>
 
 namespace tsb {
 namespace tc {
 
 constexpr int kBM = 128;
-constexpr int kThreads = 576;
+constexpr int kIssuers = 2;                              // warps that issue MMAs, on alternate tiles
+constexpr int kEpiWarp0 = 1 + kIssuers;                  // first epilogue warp
 constexpr int kEpiThreads = 512;
+constexpr int kThreads = 32 * kEpiWarp0 + kEpiThreads;   // producer warp, issuer warps, sixteen epilogue warps
+constexpr int kMaxAccBufs = 4;                           // accumulator buffers in tensor memory (512 columns / BN, at most 4)
 constexpr uint32_t kSmemBudget = 200 * 1024;  // stages; the rest holds barriers and epilogue tables
 
 // ---------------------------------------------------------------------------------------------------------
@@ -116,6 +120,18 @@ __device__ __forceinline__ void mma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t
         "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// The same, executed only when `on` is non-zero -- a predicated instruction, not a branch.  The issuing thread runs
+// alone in its warp and pays tens of cycles for every branch or dependent instruction, so its MMA sequences are
+// straight-line code in which inactive slots (a filter row outside the image, a k block beyond the group) are switched
+// off by predicate.
+__device__ __forceinline__ void mma_i8_if(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate, uint32_t on) {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.ne.b32 q, %5, 0;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(on));
+}
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, int (&v)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -156,6 +172,16 @@ __device__ __forceinline__ uint64_t smem_desc_strided(uint32_t saddr, uint32_t g
     d |= (uint64_t)1 << 46;
     d |= layout << 61;
     return d;
+}
+
+// The same descriptors split for the issuing thread's inner loops: everything but the 14-bit start-address field is
+// loop-invariant, so a loop keeps the invariant part in a register and ORs in (address >> 4) -- shared-memory addresses
+// stay below 2^18, so the field never overflows into its neighbours, and stepping along K inside a swizzle span or to
+// another filter tap is a plain add on that field.
+template <int BK>
+__device__ __forceinline__ constexpr uint64_t smem_desc_hi(uint32_t group_stride_bytes) {
+    return ((uint64_t)1 << 16) | ((uint64_t)(group_stride_bytes >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)(BK == 128 ? 2 : (BK == 64 ? 4 : 6)) << 61);
 }
 
 // Descriptor of a pixel operand whose rows OVERLAP in shared memory (raw-row mode): no swizzle, K-major.  In that canonical
@@ -527,7 +553,10 @@ struct KernelParams {
     int a_tiled;           // activations are a plain [M][Cp] matrix (1x1, stride 1, no padding): 2-D tile loads
     // shared-memory plan (bytes from the 1024-aligned base)
     int stages;            // pipeline stages (<= kMaxStages)
-    uint32_t stage_bytes;  // one stage: the pixel tile, followed by the weight tile unless the weights are resident
+    uint32_t stage_bytes;  // one stage: kgroup units of (pixel tile, followed by the weight tile unless the weights are resident)
+    int kgroup;            // general mode: K blocks per stage (1, 2 or 4; divides the K blocks of a tile): one barrier wait
+                           // and one commit of the MMA issuer serve kgroup * BK/32 MMAs
+    uint32_t unit_bytes;   // one K block inside a stage
     int b_resident;        // all K blocks of this CTA's weight tile stay in shared memory; only activations stream
     uint32_t b_off;        // offset of the resident weights
     uint32_t bar_off;      // offset of the mbarriers; tensor-memory slot, abort flag and epilogue tables follow
@@ -561,8 +590,28 @@ __device__ __forceinline__ unsigned long long global_ns() {
     do {                                                                                         \
         if (kp.trace && blockIdx.x == 0 && (tile_index) < 32) kp.trace[(tile_index) * 8 + (slot)] = global_ns(); \
     } while (0)
+// cycle accounting of the MMA issuer (profiling builds): where its time goes, summed over the CTA's tiles
+#define TSB_CYC_DECL long long cyc_full = 0, cyc_tempty = 0, cyc_issue = 0, cyc_commit = 0, cyc_t0 = clock64(), cyc_tmp = 0; int cyc_waits = 0
+#define TSB_CYC_START cyc_tmp = clock64()
+#define TSB_CYC_ADD(which) do { which += clock64() - cyc_tmp; } while (0)
+#define TSB_CYC_REPORT(ntiles)                                                                   \
+    do {                                                                                         \
+        if (kp.trace && blockIdx.x == 0) {                                                       \
+            kp.trace[31 * 8 + 0] = (unsigned long long)(clock64() - cyc_t0);                     \
+            kp.trace[31 * 8 + 1] = (unsigned long long)cyc_full;                                 \
+            kp.trace[31 * 8 + 2] = (unsigned long long)cyc_tempty;                               \
+            kp.trace[31 * 8 + 3] = (unsigned long long)(ntiles);                                 \
+            kp.trace[31 * 8 + 4] = (unsigned long long)cyc_waits;                                \
+            kp.trace[31 * 8 + 5] = (unsigned long long)cyc_issue;                                \
+            kp.trace[31 * 8 + 6] = (unsigned long long)cyc_commit;                               \
+        }                                                                                        \
+    } while (0)
 #else
 #define TSB_TRACE(tile_index, slot) do { } while (0)
+#define TSB_CYC_DECL do { } while (0)
+#define TSB_CYC_START do { } while (0)
+#define TSB_CYC_ADD(which) do { } while (0)
+#define TSB_CYC_REPORT(ntiles) do { } while (0)
 #endif
 
 // raw-row mode: the filter rows kh_lo..kh_hi that meet an input row for output row oh (a contiguous, non-empty range)
@@ -576,8 +625,8 @@ constexpr int kModeGeneral = 0, kModeRows = 1, kModePatch = 2;
 constexpr int kMaxStages = 24;
 constexpr uint32_t kMaxDynamicSmem = 227 * 1024;
 
-// barriers: full[stages], empty[stages], tmem_full[2], tmem_empty[2], b_full, b_free
-__host__ __device__ constexpr uint32_t num_barriers(int stages) { return 2u * (uint32_t)stages + 6u; }
+// barriers: full[stages], empty[stages], tmem_full[4], tmem_empty[4], b_full, b_free
+__host__ __device__ constexpr uint32_t num_barriers(int stages) { return 2u * (uint32_t)stages + 2u * kMaxAccBufs + 2u; }
 
 // PIX pixels x CH channels per tile.  Normal orientation: the pixel tile is the MMA's A operand (M = 128 pixels), the
 // weight tile its B operand (N = BN channels).  Swapped orientation: the weight tile is A (M = 128 channels, rows
@@ -593,7 +642,8 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     constexpr int PIX = SWAP ? BN : kBM;      // pixels per tile
     constexpr int CH = SWAP ? kBM : BN;       // output channels per tile
     constexpr uint32_t kPixBytes = PIX * BK, kWgtBytes = CH * BK;
-    constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // power of two for BN in {32,64,128,256}
+    constexpr int kBufs = 512 / BN < kMaxAccBufs ? 512 / BN : kMaxAccBufs;   // accumulator buffers: 2 for BN = 256, else 4
+    constexpr uint32_t kTmemCols = 512;                                       // one CTA per SM: all of tensor memory
     const int kStages = kp.stages;
 
     extern __shared__ uint8_t smem_raw[];
@@ -603,13 +653,15 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const uint32_t bar_full = base + kp.bar_off;
     const uint32_t bar_empty = bar_full + 8 * kStages;
     const uint32_t bar_tfull = bar_empty + 8 * kStages;
-    const uint32_t bar_tempty = bar_tfull + 16;
-    const uint32_t bar_bfull = bar_tempty + 16;
+    const uint32_t bar_tempty = bar_tfull + 8 * kMaxAccBufs;
+    const uint32_t bar_bfull = bar_tempty + 8 * kMaxAccBufs;
     const uint32_t bar_bfree = bar_bfull + 8;
     const uint32_t slot_off = kp.bar_off + 8 * num_barriers(kStages);
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + slot_off);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(base_ptr + slot_off + 4);
     float *table = reinterpret_cast<float *>(base_ptr + ((slot_off + 8 + 15) & ~15u));
+    // patch mode: (byte offset >> 4) of every filter tap's window inside a patch, for the MMA issuer
+    uint32_t *tap16 = reinterpret_cast<uint32_t *>(table + kMaxAccBufs * 2 * BN);
     const uint32_t w_res = base + kp.b_off;   // resident weights
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -621,6 +673,9 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const int tile_lo = kp.b_resident ? (int)((long long)blockIdx.x * total_tiles / gridDim.x) : 0;
     const int tile_hi = kp.b_resident ? (int)((long long)(blockIdx.x + 1) * total_tiles / gridDim.x) : 0;
     const int my_tiles = kp.b_resident ? tile_hi - tile_lo : (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    // Accumulator buffers in use = epilogue groups: as many as tensor memory holds (kBufs), but no more than this CTA has
+    // tiles -- a CTA with a single tile puts all sixteen epilogue warps on it.
+    const int nbuf = my_tiles >= 4 && kBufs >= 4 ? 4 : (my_tiles >= 2 ? 2 : 1);
     auto decode = [&](int i, int &m_tile, int &n_tile) {   // m_tile: pixel tile, n_tile: channel tile
         if (kp.b_resident) {
             const int t = tile_lo + i;
@@ -634,7 +689,7 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     if (threadIdx.x == 0) {
         TSB_TRACE(0, 7);
         for (int s = 0; s < kStages; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, kEpiThreads); }
+        for (int a = 0; a < kMaxAccBufs; ++a) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, kEpiThreads / nbuf); }
         mbar_init(bar_bfull, 1);
         mbar_init(bar_bfree, 1);
         *abort_flag = 0;
@@ -644,6 +699,12 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     if (warp == 1) {
         tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), kTmemCols);
         tmem_relinquish();
+    }
+    if (MODE == kModePatch && threadIdx.x >= 32 * kEpiWarp0) {
+        for (int t = (int)threadIdx.x - 32 * kEpiWarp0; t < kp.KH * kp.KW; t += kEpiThreads) {
+            const int kh = t / kp.KW, kw = t - kh * kp.KW;
+            tap16[t] = (uint32_t)((kh * kp.dh * kp.patch_pw + kw * kp.dw) * BK) >> 4;
+        }
     }
     tc_fence_before();
     __syncthreads();
@@ -713,48 +774,101 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                                   bytes, bar_full + 8 * stage);
                         if (++stage == kStages) { stage = 0; phase ^= 1u; }
                     }
-                } else
-                for (int kh = 0; kh < kp.KH && ok; ++kh)
-                    for (int kw = 0; kw < kp.KW && ok; ++kw)
-                        for (int cb = 0; cb < kp.Cp; cb += BK) {
-                            if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) {
-                                if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 1); }
-                                ok = false;
-                                break;
+                } else {
+                    int gk = 0;   // K block inside the current stage
+                    for (int kh = 0; kh < kp.KH && ok; ++kh)
+                        for (int kw = 0; kw < kp.KW && ok; ++kw)
+                            for (int cb = 0; cb < kp.Cp; cb += BK) {
+                                if (gk == 0) {
+                                    if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) {
+                                        if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 1); }
+                                        ok = false;
+                                        break;
+                                    }
+                                    mbar_arrive_expect_tx(bar_full + 8 * stage, (uint32_t)kp.kgroup * (kp.b_resident ? kPixBytes : kPixBytes + kWgtBytes));
+                                }
+                                const uint32_t sp = base + stage * kp.stage_bytes + (uint32_t)gk * kp.unit_bytes, sw = sp + kPixBytes;
+                                if (kp.a_tiled)
+                                    tma_load_2d(sp, &map_a, bar_full + 8 * stage, cb, m0);
+                                else
+                                    tma_load_im2col_4d(sp, &map_a, bar_full + 8 * stage, cb, wc, hc, img,
+                                                       (uint16_t)(kw * kp.dw), (uint16_t)(kh * kp.dh));
+                                if (!kp.b_resident)
+                                    tma_load_2d(sw, &map_b, bar_full + 8 * stage, (kh * kp.KW + kw) * kp.Cp + cb, n_tile * CH);
+                                if (++gk == kp.kgroup) {
+                                    gk = 0;
+                                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                                }
                             }
-                            const uint32_t sp = base + stage * kp.stage_bytes, sw = sp + kPixBytes;
-                            mbar_arrive_expect_tx(bar_full + 8 * stage, kp.b_resident ? kPixBytes : kPixBytes + kWgtBytes);
-                            if (kp.a_tiled)
-                                tma_load_2d(sp, &map_a, bar_full + 8 * stage, cb, m0);
-                            else
-                                tma_load_im2col_4d(sp, &map_a, bar_full + 8 * stage, cb, wc, hc, img,
-                                                   (uint16_t)(kw * kp.dw), (uint16_t)(kh * kp.dh));
-                            if (!kp.b_resident)
-                                tma_load_2d(sw, &map_b, bar_full + 8 * stage, (kh * kp.KW + kw) * kp.Cp + cb, n_tile * CH);
-                            if (++stage == kStages) { stage = 0; phase ^= 1u; }
-                        }
+                }
                 TSB_TRACE(i, 1);
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
+    } else if (warp <= kIssuers) {
+        // ------------------------------------------------------------------ MMA issuers
+        // One thread feeds the tensor core.  An MMA with N = 64 executes in 48 cycles, while a thread that runs alone in
+        // its warp pays tens of cycles for every branch, shared-memory load or dependent instruction (measured: a loop
+        // that computes a descriptor per MMA issues one every 80-180 cycles, straight-line code with the operands in
+        // registers one every 48-55).  So: the MMAs of a stage are straight-line code; descriptors are a loop-invariant
+        // high word plus a 14-bit address field (in 16-byte units) that takes one add; per-tap offsets sit in registers;
+        // slots that do not apply are switched off by predicate; and one barrier wait / one commit serve as many MMAs as
+        // the stage holds.
+        // Issuing costs the thread far more than an MMA with a small N takes to execute, and what it spends between two
+        // MMAs is not hidden behind the tensor core's work on the earlier one (measured: ~125 cycles per MMA at N = 64,
+        // ~190 at N = 256).  So kIssuers warps issue, each for every kIssuers-th tile of the CTA: while one computes
+        // descriptors, waits and commits, the tensor core runs the other's MMAs.  A tile's stages, accumulator buffer and
+        // barriers belong to the issuer of that tile alone.  Where tiles share state that one thread has to order -- a
+        // raw-row stage shared by the segments of an output row, or resident weights that are replaced inside this CTA's
+        // tile range -- the first issuer takes every tile.
         if (lane == 0) {
             constexpr uint32_t idesc = instr_desc<BN>();
-            int stage = 0; uint32_t phase = 0;
+            constexpr uint64_t dhi = smem_desc_hi<BK>(8 * BK);
+            constexpr uint32_t kWgt16 = kWgtBytes >> 4, kPix16 = kPixBytes >> 4;
+            constexpr int kMmaPerBlock = BK / 32;
+            const uint32_t base16 = base >> 4, stage16 = kp.stage_bytes >> 4, wres16 = w_res >> 4, unit16 = kp.unit_bytes >> 4;
+            const int resident = kp.b_resident;
             bool ok = true;
-            int cur_n = -1, w_loads = 0;
             int rows_seg_first = 0;
-            for (int local = 0; local < my_tiles && ok; ++local) {
+            int first_m = 0, first_n = 0, last_m = 0, last_n = 0;
+            if (my_tiles > 0) { decode(0, first_m, first_n); decode(my_tiles - 1, last_m, last_n); }
+            // pipeline stages a tile consumes
+            const int spt = MODE == kModePatch ? kp.Cp / BK : (MODE == kModeRows ? 1 : k_iters / kp.kgroup);
+            // A barrier wait names a phase by its parity only, so a waiter must never be two rounds of the stage ring away
+            // from the phase it means.  With several issuers that holds when the ring has room for one tile of each
+            // (kStages >= issuers * spt): the round before the one an issuer waits for then lies in tiles that were
+            // loaded before its own previous tile, whose loads it has seen complete.
+            const bool shared_state = (MODE == kModeRows && kp.rows_segs > 1) || (resident && first_n != last_n);
+            const int issuers = (shared_state || kStages < kIssuers * spt) ? 1 : kIssuers;
+            const int me = warp - 1;
+            int stage = 0; uint32_t phase = 0;
+            auto advance = [&](int n) {      // move n stages on (n >= 0)
+                stage += n;
+                while (stage >= kStages) { stage -= kStages; phase ^= 1u; }
+            };
+            advance(me * spt);
+            int w_loads = resident ? 1 : 0;   // without shared state the resident weights are loaded exactly once
+            int cur_n = -1;
+            // patch mode with up to nine filter taps (3x3, 1x3 ...): the taps' window offsets live in registers
+            const int taps = kp.KH * kp.KW;
+            uint32_t tapreg[9];
+#pragma unroll
+            for (int t = 0; t < 9; ++t) tapreg[t] = (MODE == kModePatch && t < taps) ? tap16[t] : 0u;
+            TSB_CYC_DECL;
+            for (int local = me; local < my_tiles && ok && me < issuers; local += issuers) {
                 int m_tile, n_tile;
                 decode(local, m_tile, n_tile);
-                const int acc = local & 1;
-                const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
+                uint32_t st16 = base16 + (uint32_t)stage * stage16;    // (address >> 4) of the current stage
+                const int acc = local & (nbuf - 1);
+                const uint32_t acc_phase = (uint32_t)(local / nbuf) & 1u;
+                TSB_CYC_START;
                 if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag)) {
                     if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 2); }
                     break;
                 }
-                if (kp.b_resident && n_tile != cur_n) {
-                    if (!mbar_wait(bar_bfull, (uint32_t)w_loads & 1u, abort_flag)) {
+                TSB_CYC_ADD(cyc_tempty);
+                if (resident && n_tile != cur_n) {
+                    // the (w_loads)-th load of resident weights: completes phase (w_loads - 1) of its barrier
+                    if (!mbar_wait(bar_bfull, (uint32_t)(w_loads - 1) & 1u, abort_flag)) {
                         if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 6); }
                         break;
                     }
@@ -762,118 +876,186 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     ++w_loads;
                 }
                 tc_fence_after();
-                TSB_TRACE(local, 2);
+                if (me == 0) TSB_TRACE(local, 2);
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
                 uint32_t accumulate = 0;
                 if (MODE == kModePatch) {
                     const int n_cb = kp.Cp / BK;
+                    const uint64_t dhi_patch = smem_desc_hi<BK>((uint32_t)kp.patch_pw * BK);   // next tile row = next patch row
+                    const uint32_t wtap16 = (uint32_t)n_cb * kWgt16;                          // next tap of the resident weights
                     for (int cbi = 0; cbi < n_cb && ok; ++cbi) {
+                        TSB_CYC_START;
                         if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
                             if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 3); }
                             ok = false;
                             break;
                         }
+                        TSB_CYC_ADD(cyc_full);
                         tc_fence_after();
-                        if (cbi == 0) TSB_TRACE(local, 3);
-                        const uint32_t sp = base + stage * kp.stage_bytes;
-                        const uint32_t group_stride = (uint32_t)kp.patch_pw * BK;   // next tile row = next patch row
-                        for (int kh = 0; kh < kp.KH; ++kh)
-                            for (int kw = 0; kw < kp.KW; ++kw) {
-                                const uint32_t shift = (uint32_t)(kh * kp.dh * kp.patch_pw + kw * kp.dw) * BK;
-                                const uint64_t dp = smem_desc_strided<BK>(sp + shift, group_stride);
-                                const uint64_t dw = smem_desc<BK>(w_res + (uint32_t)((kh * kp.KW + kw) * n_cb + cbi) * kWgtBytes);
+                        if (cbi == 0 && me == 0) TSB_TRACE(local, 3);
+                        uint32_t w16 = wres16 + (uint32_t)cbi * kWgt16;
+                        TSB_CYC_START;
+                        if (taps <= 9) {
+#pragma unroll
+                            for (int t = 0; t < 9; ++t) {
+                                const uint64_t dp = dhi_patch | (uint64_t)(st16 + tapreg[t]);
+                                const uint64_t dw = dhi | (uint64_t)w16;
+                                const uint64_t da = SWAP ? dw : dp, db = SWAP ? dp : dw;
+                                const uint32_t on = t < taps ? 1u : 0u;
+#pragma unroll
+                                for (int k = 0; k < kMmaPerBlock; ++k)
+                                    mma_i8_if(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (t | k) ? 1u : accumulate, on);
+                                w16 += wtap16;
+                            }
+                            accumulate = 1u;
+                        } else {
+                            for (int t = 0; t < taps; ++t) {
+                                const uint64_t dp = dhi_patch | (uint64_t)(st16 + tap16[t]);
+                                const uint64_t dw = dhi | (uint64_t)w16;
                                 const uint64_t da = SWAP ? dw : dp, db = SWAP ? dp : dw;
 #pragma unroll
-                                for (int k = 0; k < BK / 32; ++k) {
+                                for (int k = 0; k < kMmaPerBlock; ++k) {
                                     mma_i8(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, accumulate);
                                     accumulate = 1u;
                                 }
+                                w16 += wtap16;
                             }
+                        }
+                        TSB_CYC_ADD(cyc_issue);
+                        TSB_CYC_START;
                         tc_commit(bar_empty + 8 * stage);
-                        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                        TSB_CYC_ADD(cyc_commit);
+                        st16 += stage16;
+                        if (++stage == kStages) { stage = 0; phase ^= 1u; st16 = base16; }
                     }
                 } else if (!SWAP && MODE == kModeRows) {
                     const int row_id = kp.d_segs.div(m_tile), seg = m_tile - row_id * kp.rows_segs;
                     int kh_lo, kh_hi;
                     rows_span(kp, row_id - kp.d_OH.div(row_id) * kp.rows_OH, kh_lo, kh_hi);
-                    if (seg == 0 || local == 0) {      // the stage of this output row: loaded once, used by all its segments
+                    if (seg == 0 || local == me) {     // the stage of this output row: loaded once, used by all its segments
+                        TSB_CYC_START;
                         if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
                             if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 3); }
                             break;
                         }
+                        TSB_CYC_ADD(cyc_full);
                         tc_fence_after();
                         rows_seg_first = seg;
                     }
-                    TSB_TRACE(local, 3);
-                    const uint32_t sp = base + stage * kp.stage_bytes + (uint32_t)(seg - rows_seg_first) * (PIX * 16);
-                    for (int kh = kh_lo; kh <= kh_hi; ++kh) {
-                        const uint64_t da = smem_desc_sliding(sp + (uint32_t)((kh - kh_lo) * kp.dh) * (uint32_t)kp.rows_stride_h);
-                        const uint64_t db = smem_desc<BK>(w_res + (uint32_t)kh * kWgtBytes);
+                    if (me == 0) TSB_TRACE(local, 3);
+                    // sliding descriptor (no swizzle, LBO 16, SBO 128): only its address field changes from row to row
+                    const uint64_t dslide = smem_desc_sliding(0);
+                    const uint32_t row16 = (uint32_t)kp.dh * (uint32_t)(kp.rows_stride_h >> 4);
+                    // filter row kh reads the staged row (kh - kh_lo); rows outside [kh_lo, kh_hi] meet no input row
+                    const uint32_t a16_0 = st16 + (uint32_t)(seg - rows_seg_first) * PIX - (uint32_t)kh_lo * row16;
+                    if (kp.KH <= 8) {
 #pragma unroll
-                        for (int k = 0; k < BK / 32; ++k) {
-                            mma_i8(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, accumulate);
-                            accumulate = 1u;
+                        for (int kh = 0; kh < 8; ++kh) {
+                            const uint64_t da = dslide | (uint64_t)((a16_0 + (uint32_t)kh * row16) & 0x3FFFu);
+                            const uint64_t db = dhi | (uint64_t)(wres16 + (uint32_t)kh * kWgt16);
+                            const uint32_t on = (kh >= kh_lo && kh <= kh_hi) ? 1u : 0u;
+#pragma unroll
+                            for (int k = 0; k < kMmaPerBlock; ++k)
+                                mma_i8_if(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kh > kh_lo || k > 0) ? 1u : 0u, on);
+                        }
+                    } else {
+                        for (int kh = kh_lo; kh <= kh_hi; ++kh) {
+                            const uint64_t da = dslide | (uint64_t)(a16_0 + (uint32_t)kh * row16);
+                            const uint64_t db = dhi | (uint64_t)(wres16 + (uint32_t)kh * kWgt16);
+#pragma unroll
+                            for (int k = 0; k < kMmaPerBlock; ++k) {
+                                mma_i8(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, accumulate);
+                                accumulate = 1u;
+                            }
                         }
                     }
                     if (seg == kp.rows_segs - 1 || local == my_tiles - 1) {
                         tc_commit(bar_empty + 8 * stage);
-                        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                        advance(1);
                     }
-                } else
-                for (int it = 0; it < k_iters; ++it) {
-                    if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
-                        if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 3); }
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after();
-                    if (it == 0) TSB_TRACE(local, 3);
-                    const uint32_t sp = base + stage * kp.stage_bytes;
-                    const uint32_t sw = kp.b_resident ? w_res + (uint32_t)it * kWgtBytes : sp + kPixBytes;
-                    const uint64_t dp = smem_desc<BK>(sp), dw = smem_desc<BK>(sw);
-                    const uint64_t da = SWAP ? dw : dp, db = SWAP ? dp : dw;
+                } else {
+                    // general mode: a stage holds kgroup K blocks; one wait, kgroup * BK/32 MMAs in a row, one commit
+                    uint32_t w16 = wres16;
+                    const int G = kp.kgroup;
+                    auto issue_stage = [&](auto group) {      // the MMAs of one stage as straight-line code
+                        constexpr int kG = decltype(group)::value;
 #pragma unroll
-                    for (int k = 0; k < BK / 32; ++k) {
-                        // +32 bytes along K = +2 in the descriptor's 16-byte address units (inside the swizzle span, or
-                        // along the raw row)
-                        mma_i8(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, accumulate);
+                        for (int g = 0; g < kG; ++g) {
+                            const uint32_t a16 = st16 + (uint32_t)g * unit16;
+                            const uint64_t dp = dhi | (uint64_t)a16;
+                            const uint64_t dw = dhi | (uint64_t)(resident ? w16 + (uint32_t)g * kWgt16 : a16 + kPix16);
+                            const uint64_t da = SWAP ? dw : dp, db = SWAP ? dp : dw;
+#pragma unroll
+                            for (int k = 0; k < kMmaPerBlock; ++k)
+                                // +32 bytes along K = +2 in the descriptor's 16-byte address units (inside the swizzle span)
+                                mma_i8(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (g | k) ? 1u : accumulate);
+                        }
+                    };
+                    for (int it = 0; it < k_iters; it += G) {
+                        TSB_CYC_START;
+                        if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
+                            if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 3); }
+                            ok = false;
+                            break;
+                        }
+                        TSB_CYC_ADD(cyc_full);
+                        tc_fence_after();
+                        if (it == 0 && me == 0) TSB_TRACE(local, 3);
+                        TSB_CYC_START;
+                        if (G == 4) issue_stage(std::integral_constant<int, 4>());
+                        else if (G == 2) issue_stage(std::integral_constant<int, 2>());
+                        else issue_stage(std::integral_constant<int, 1>());
+                        TSB_CYC_ADD(cyc_issue);
                         accumulate = 1u;
+                        TSB_CYC_START;
+                        tc_commit(bar_empty + 8 * stage);  // frees the stage once these MMAs have read it
+                        TSB_CYC_ADD(cyc_commit);
+                        w16 += (uint32_t)G * kWgt16;
+                        st16 += stage16;
+                        if (++stage == kStages) { stage = 0; phase ^= 1u; st16 = base16; }
                     }
-                    tc_commit(bar_empty + 8 * stage);  // frees the stage once these MMAs have read it
-                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
+                TSB_CYC_START;
                 if (ok) tc_commit(bar_tfull + 8 * acc);  // accumulator complete
-                if (ok && kp.b_resident) {
-                    int nm, nn = -1;
+                TSB_CYC_ADD(cyc_commit);
+                if (ok && resident && issuers == 1) {
+                    int nm = 0, nn = -1;
                     if (local + 1 < my_tiles) decode(local + 1, nm, nn);
                     if (nn != cur_n) tc_commit(bar_bfree);  // the resident weights may be replaced
                 }
-                TSB_TRACE(local, 4);
+                advance((issuers - 1) * spt);             // skip the stages of the other issuers' tiles
+                if (me == 0) TSB_TRACE(local, 4);
             }
+            if (me == 0) TSB_CYC_REPORT((my_tiles + issuers - 1) / issuers);
         }
     } else {
-        // ------------------------------------------------------------------ epilogue (warps 2..17)
+        // ------------------------------------------------------------------ epilogue (the last sixteen warps)
         // A warp may read only the 32 tensor-memory lanes of its quarter (warp id mod 4); four warps share a
         // quarter and split the tile's columns between them in chunks of 32.
+        // The sixteen warps form nbuf groups (of four, eight or all sixteen warps); group g owns accumulator buffer g and
+        // takes the tiles local = g, g + nbuf, ...  One tile's epilogue is a chain of latencies (barrier, tensor-memory
+        // load, arithmetic, stores); with the groups on different tiles those chains overlap.
+        const int group_warps = 16 / nbuf;                       // 4, 8 or 16
+        const int group_threads = 32 * group_warps;
+        const int parts = group_warps / 4;                       // warps of a group per lane quarter: 1, 2 or 4
         const int quarter = warp & 3;
-        const int part = (warp - 2) >> 2;        // 0..3
-        const int et = threadIdx.x - 64;         // 0..511
+        const int group = (warp - kEpiWarp0) / group_warps;
+        const int part = ((warp - kEpiWarp0) % group_warps) >> 2;        // 0 .. parts-1
+        const int et = (int)threadIdx.x - 32 * kEpiWarp0 - group * group_threads;   // thread index inside the group
         const int row = quarter * 32 + lane;     // tensor-memory lane this thread reads
         constexpr int kChunks = BN / 32;
-        // normal orientation: columns a warp takes per step; 16 when the tile has only 64 channels, so that all four warps
-        // of a lane quarter have work
-        constexpr int CW = BN >= 128 ? 32 : 16;
+        constexpr int CW = 32;                   // normal orientation: columns a warp takes per step
         const bool has_bias = epi.bias != nullptr;
         const int act = epi.activation;
-        for (int local = 0; local < my_tiles; ++local) {
-            const int acc = local & 1;
-            const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
+        for (int local = group; local < my_tiles; local += nbuf) {
+            const int acc = group;
+            const uint32_t acc_phase = (uint32_t)(local / nbuf) & 1u;
             int m_tile, n_tile;
             decode(local, m_tile, n_tile);
             const int o_base = n_tile * CH;
             float *t_dq = table + acc * 2 * BN, *t_bias = t_dq + BN;
             if (!SWAP) {
-                for (int j = et; j < BN; j += kEpiThreads) {
+                for (int j = et; j < BN; j += group_threads) {
                     const int o = o_base + j;
                     t_dq[j] = o < epi.O ? epi.dq[o] : 0.0f;
                     t_bias[j] = (o < epi.O && epi.bias) ? epi.bias[o] : 0.0f;
@@ -886,15 +1068,20 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             asm volatile(
                 "{\n\t.reg .pred p, q;\n\t"
                 "setp.ne.b32 p, %1, 0;\n\t"
-                "bar.red.and.pred q, 1, %2, p;\n\t"
+                "bar.red.and.pred q, %3, %2, p;\n\t"       // named barrier 1 + group, over the group's threads
                 "selp.u32 %0, 1, 0, q;\n\t}"
-                : "=r"(all_ok) : "r"(ok), "n"(kEpiThreads) : "memory");
+                : "=r"(all_ok) : "r"(ok), "r"(group_threads), "r"(1 + group) : "memory");
             if (!all_ok) {
                 if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 4); }
                 break;
             }
             tc_fence_after();
-            if (et == 0) TSB_TRACE(local, 5);
+            if (et == 0 && local < 32) TSB_TRACE(local, 5);
+#ifdef TSB_ENABLE_TRACE
+            // profiling experiment: with trace[255] set, the epilogue warps hand the accumulator back without touching it
+            // (outputs are then garbage) -- shows how fast the other two roles run when left alone
+            if (kp.trace && kp.trace[255] != 0) { tc_fence_before(); mbar_arrive(bar_tempty + 8 * acc); continue; }
+#endif
             const uint32_t taddr0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
             if (!SWAP) {
                 int m = m_tile * PIX + row;
@@ -914,7 +1101,7 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 const int img = live ? kp.d_P.div(m) : 0;
                 const int p = live ? m - img * kp.P : 0;
 #pragma unroll 1
-                for (int c = part; c < BN / CW; c += 4) {
+                for (int c = part; c < BN / CW; c += parts) {
                     const int col0 = c * CW;
                     if (o_base + col0 >= epi.O) {
                         // nothing but channel padding in this step: no accumulators to read, only the zero bytes the
@@ -982,7 +1169,7 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     p_c = p_rem - p_r * kp.patch_tiles_w;
                 }
 #pragma unroll 1
-                for (int c = part; c < kChunks && quarter_live; c += 4) {
+                for (int c = part; c < kChunks && quarter_live; c += parts) {
                     const int col0 = c * 32;
                     if (MODE == kModePatch) {
                         // this chunk: tile rows col0/8 .. col0/8+3, 8 pixels each
@@ -1282,20 +1469,34 @@ Config choose_config(const View &v, const Tuning &tune, int sm_count, int orient
     const bool want_resident = v.rows || c.patch || tiles > c.grid;  // pays off only when a CTA runs several tiles
     // (raw-row mode always keeps its weights resident; make_view admitted it only where two row stages fit beside them)
     const uint32_t min_stages = v.rows ? 2 : 4;
+    // K blocks per stage (im2col / tiled loads only): the MMA issuer pays a barrier wait and a commit per stage, which
+    // costs it more than the MMAs of one K block take when N is small, so short K blocks are grouped -- as long as the
+    // group divides the K blocks of a tile, stays within 48 KB and leaves at least three stages.
+    auto group_for = [&](uint32_t unit, uint32_t room) {
+        if (c.patch || v.rows) return 1;
+        for (int gsz = 4; gsz >= 2; gsz /= 2)
+            if (k_iters % (uint32_t)gsz == 0 && (uint32_t)gsz * unit <= 48 * 1024 && room / ((uint32_t)gsz * unit) >= 3) return gsz;
+        return 1;
+    };
     if (c.patch || (want_resident && w_total <= 128 * 1024 && (kSmemBudget - w_total) / p_bytes >= min_stages)) {
         c.b_resident = 1;
-        c.stage_bytes = p_bytes;
-        c.stages = std::min<int>(kMaxStages, (int)((kSmemBudget - w_total) / p_bytes));
+        c.unit_bytes = p_bytes;
+        c.kgroup = group_for(p_bytes, kSmemBudget - w_total);
+        c.stage_bytes = (uint32_t)c.kgroup * p_bytes;
+        c.stages = std::min<int>(kMaxStages, (int)((kSmemBudget - w_total) / c.stage_bytes));
         c.b_off = (uint32_t)c.stages * c.stage_bytes;
         c.bar_off = c.b_off + w_total;
     } else {
         c.b_resident = 0;
-        c.stage_bytes = p_bytes + w_bytes;
+        c.unit_bytes = p_bytes + w_bytes;
+        c.kgroup = group_for(c.unit_bytes, kSmemBudget);
+        c.stage_bytes = (uint32_t)c.kgroup * c.unit_bytes;
         c.stages = std::min<int>(kMaxStages, (int)(kSmemBudget / c.stage_bytes));
         c.b_off = 0;
         c.bar_off = (uint32_t)c.stages * c.stage_bytes;
     }
-    const uint32_t tables = ((c.bar_off + 8 * num_barriers(c.stages) + 8 + 15) & ~15u) + 2 * 2 * (uint32_t)c.bn * 4;
+    const uint32_t tables = ((c.bar_off + 8 * num_barriers(c.stages) + 8 + 15) & ~15u) + kMaxAccBufs * 2 * (uint32_t)c.bn * 4 +
+                            (c.patch ? 4 * (uint32_t)(g.KH * g.KW) : 0);   // epilogue tables, then patch mode's tap table
     c.dyn_smem = tables + 1024;  // slack to align the tiles to 1024 bytes
     return c;
 }
@@ -1465,6 +1666,7 @@ int launch_conv_tc(const View &v, const Config &cfg, const CUtensorMap &map_a, c
 #endif
     kp.a_tiled = v.a_tiled;
     kp.stages = cfg.stages; kp.stage_bytes = cfg.stage_bytes; kp.b_resident = cfg.b_resident;
+    kp.kgroup = cfg.kgroup; kp.unit_bytes = cfg.unit_bytes;
     kp.b_off = cfg.b_off; kp.bar_off = cfg.bar_off;
     kp.rows_segs = 0; kp.rows_OH = g.OH; kp.rows_H = g.H; kp.rows_bytes = 0; kp.rows_stride_h = 0; kp.rows_stride_n = 0;
     kp.rows_x = nullptr;

@@ -47,6 +47,8 @@ struct Config {
     int grid = 0;                     // persistent CTAs
     // shared-memory plan of the kernel
     int stages = 0, b_resident = 0;
+    int kgroup = 1;                   // K blocks per pipeline stage (im2col / tiled loads; 1 in patch and raw-row mode)
+    uint32_t unit_bytes = 0;          // one K block of a stage
     uint32_t stage_bytes = 0, b_off = 0, bar_off = 0, dyn_smem = 0;
 };
 
