@@ -46,16 +46,18 @@ struct tsb_conv_plan {
     tsb::tc::Tuning tune;            // heuristic overrides taken from the descriptor
     const char *why_not_tc;
     tsb::tc::View view;
-    tsb::tc::Config cfg;             // orientation chosen by the geometry heuristic
-    tsb::tc::Config cfg_alt;         // the other orientation (alt_valid): taken when the epilogue is pixel-major fp32
-    int alt_valid;
+    tsb::tc::Config cfg;             // configuration with all shared memory given to the pipeline
+    tsb::tc::Config cfg_alt;         // the other orientation (alt_valid): taken when the epilogue is pixel-major fp32 and no
+    int alt_valid;                   // staged configuration fits
+    tsb::tc::Config cfg_stg[3];      // [1], [2]: configurations that set shared memory aside for the staged epilogue
+    int stg_valid[3];
     size_t off_weights, off_stage, ws_bytes;
     // state bound by set_weights / run
     const int8_t *weights_oihw;      // direct kernel reads the caller's tensor
     const void *weights_ws;          // workspace the packed weights live in
-    CUtensorMap map_b, map_b_alt;
-    const int8_t *map_a_ptr, *map_a_alt_ptr;
-    CUtensorMap map_a, map_a_alt;
+    CUtensorMap map_b, map_b_alt, map_b_stg[3];
+    const int8_t *map_a_ptr, *map_a_alt_ptr, *map_a_stg_ptr[3];
+    CUtensorMap map_a, map_a_alt, map_a_stg[3];
 };
 
 using namespace tsb;
@@ -194,6 +196,12 @@ int tsb_conv2d_i8_plan_create(const tsb_conv_desc *d, tsb_conv_plan **out) {
         p->cfg_alt = tc::choose_config(p->view, p->tune, sms, p->cfg.swap ? 0 : 1);
         // a forced orientation is final: the run-time choice by epilogue is only made between the library's own two plans
         p->alt_valid = p->cfg_alt.swap != p->cfg.swap && p->tune.orientation == 0;
+        for (int level = 1; level <= 2; ++level) {
+            p->cfg_stg[level] = tc::choose_config(p->view, p->tune, sms, -1, level);
+            const tc::Config &c = p->cfg_stg[level];
+            p->stg_valid[level] = c.staging == level && c.stages >= 2 && c.dyn_smem <= 227u * 1024u && (!p->view.rows || c.b_resident);
+            p->map_a_stg_ptr[level] = nullptr;
+        }
         end = p->off_weights + align256(p->view.weight_bytes);
     }
     p->off_stage = end;
@@ -206,6 +214,7 @@ int tsb_conv2d_i8_plan_create(const tsb_conv_desc *d, tsb_conv_plan **out) {
     p->weights_ws = nullptr;
     p->map_a_ptr = nullptr;
     p->map_a_alt_ptr = nullptr;
+    if (p->kernel != TSB_KERNEL_TCGEN05) p->stg_valid[1] = p->stg_valid[2] = 0;
     *out = p;
     return TSB_OK;
 }
@@ -240,6 +249,11 @@ int tsb_conv2d_i8_plan_describe(const tsb_conv_plan *plan, char *text, size_t te
             len += snprintf(text + len, text_bytes - len, " | alt: ");
             if ((size_t)len < text_bytes) len += one(plan->cfg_alt, text + len, text_bytes - len);
         }
+        for (int level = 1; level <= 2; ++level)
+            if (plan->stg_valid[level] && len > 0 && (size_t)len < text_bytes) {
+                len += snprintf(text + len, text_bytes - len, " | staged%d: ", level);
+                if ((size_t)len < text_bytes) len += one(plan->cfg_stg[level], text + len, text_bytes - len);
+            }
     }
     if (len < 0) return fail(TSB_ERR_INVALID_ARGUMENT, "plan_describe: formatting failed");
     return (size_t)len < text_bytes ? len : (int)text_bytes - 1;
@@ -266,6 +280,11 @@ int tsb_conv2d_i8_set_weights(tsb_conv_plan *plan, const int8_t *w_oihw, void *w
             st = tc::encode_weight_map(plan->view, plan->cfg_alt, wp, &plan->map_b_alt);
             if (st != TSB_OK) return st;
         }
+        for (int level = 1; level <= 2; ++level)
+            if (plan->stg_valid[level]) {
+                st = tc::encode_weight_map(plan->view, plan->cfg_stg[level], wp, &plan->map_b_stg[level]);
+                if (st != TSB_OK) return st;
+            }
     }
     return TSB_OK;
 }
@@ -352,8 +371,20 @@ int tsb_conv2d_i8_run(tsb_conv_plan *plan, const int8_t *x, int x_layout, const 
         if (st != TSB_OK) return st;
         x_tc = stage;
     }
-    // Pixel-major fp32 tensors (a network's residuals and block outputs) are stored coalesced when a thread owns a
-    // channel, i.e. in the swapped orientation; everything else follows the geometry heuristic.
+    // Outputs that can go through shared-memory tiles and tensor-map stores (int8 NHWC_PAD, pixel-major fp32 with or
+    // without a residual) take the configuration that sets the tiles' shared memory aside.
+    const int level = tc::staging_level(plan->view, epi);
+    if (level != 0 && plan->stg_valid[level]) {
+        if (plan->map_a_stg_ptr[level] != x_tc) {
+            st = tc::encode_activation_map(plan->view, plan->cfg_stg[level], x_tc, &plan->map_a_stg[level]);
+            if (st != TSB_OK) return st;
+            plan->map_a_stg_ptr[level] = x_tc;
+        }
+        return tc::launch_conv_tc(plan->view, plan->cfg_stg[level], plan->map_a_stg[level], plan->map_b_stg[level], x_tc, epi,
+                                  static_cast<int *>(workspace), stream);
+    }
+    // Otherwise pixel-major fp32 tensors (a network's residuals and block outputs) are stored coalesced when a thread owns
+    // a channel, i.e. in the swapped orientation; everything else follows the geometry heuristic.
     const bool want_swap = (epi.out_f32 || epi.residual) && epi.f32_nhwc && !epi.out_acc;
     // (the swapped patch-mode kernel has no fast path for pixel-major fp32 tensors)
     const bool use_alt = plan->alt_valid && (want_swap != (plan->cfg.swap != 0)) && (want_swap ? plan->cfg_alt.swap : 0) &&
@@ -383,6 +414,7 @@ static const char *wait_name(int code) {
         case 4: return "epilogue: accumulator ready";
         case 5: return "producer: resident weight tile free";
         case 6: return "MMA issuer: resident weight tile loaded";
+        case 7: return "epilogue: staged residual tile loaded";
         default: return "unknown wait";
     }
 }

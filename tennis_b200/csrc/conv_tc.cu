@@ -91,12 +91,48 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map
         "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n) : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c, int w, int h) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c), "r"(w), "r"(h) : "memory");
+}
+// tile stores shared -> global (bulk async group of the issuing thread); out-of-range parts of the box are not written
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, uint32_t src, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap *map, uint32_t src, int x, int y, int z, int w) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// the stores of this thread's groups have finished READING shared memory (the source may be overwritten)
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// generic-proxy writes to shared memory become visible to the async proxy (TMA) of this CTA
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// named barrier over `threads` threads that also ORs a predicate over them
+__device__ __forceinline__ bool bar_or(int id, int threads, bool pred) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 p, %1, 0;\n\t"
+        "bar.red.or.pred q, %2, %3, p;\n\t"
+        "selp.u32 %0, 1, 0, q;\n\t}"
+        : "=r"(r) : "r"((uint32_t)pred), "r"(id), "r"(threads) : "memory");
+    return r != 0;
+}
 __device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c, int w,
                                                    int h, int n, uint16_t off_w, uint16_t off_h) {
     asm volatile(
         "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes"
         " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
         ::"r"(dst), "l"(map), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h) : "memory");
+}
+
+// Brings a box of a tensor into L2 without a destination in shared memory (no barrier, nothing to wait for).
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap *map, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
 }
 
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
@@ -184,6 +220,12 @@ __device__ __forceinline__ constexpr uint64_t smem_desc_hi(uint32_t group_stride
            ((uint64_t)(BK == 128 ? 2 : (BK == 64 ? 4 : 6)) << 61);
 }
 
+// A descriptor from its two 32-bit halves (a register pair: no instruction).  The issuing thread keeps the high half and
+// the leading-offset bits of the low half loop-invariant and steps only the 14-bit address field: `lo` below is
+// (address >> 4) | (1 << 16), and adding a few 16-byte units to it never carries out of the field.
+__device__ __forceinline__ uint64_t desc_pair(uint32_t hi, uint32_t lo) { return ((uint64_t)hi << 32) | (uint64_t)lo; }
+constexpr uint32_t kDescLbo = 1u << 16;   // leading byte offset 16 (unused for swizzled K-major operands, set as before)
+
 // Descriptor of a pixel operand whose rows OVERLAP in shared memory (raw-row mode): no swizzle, K-major.  In that canonical
 // layout row r, 16-byte K chunk j sits at (r % 8) * 16 + (r / 8) * SBO + j * LBO; with SBO = 128 and LBO = 16 that is
 // r * 16 + j * 16: pixel r reads the bytes that start 16 bytes after pixel r-1's, which is exactly a convolution window
@@ -211,6 +253,10 @@ constexpr int kEpiGeneric = 0;   // any combination of outputs, element by eleme
 constexpr int kEpiF32Nchw = 1;   // fp32 NCHW output only (the operator's own output)
 constexpr int kEpiI8Nhwc = 2;    // requantized int8 NHWC_PAD output only, half-away rounding, one scale per sample
 constexpr int kEpiNhwc = 3;      // fp32 [N][P][O] residual in and/or fp32 [N][P][O] out and/or int8 NHWC_PAD out (normal orientation)
+constexpr int kEpiStaged = 4;    // the same outputs through shared-memory tiles and tensor-map loads / stores (normal orientation)
+constexpr uint32_t kStageF32Bytes = kBM * 32 * 4;   // one staged fp32 tile: 128 pixels x 32 channels, 128-byte rows, swizzle 128B
+constexpr uint32_t kStageI8Bytes = kBM * 32;        // one staged int8 tile: 128 pixels x 32 channels, 32-byte rows
+constexpr int kQuads = 4;                           // the sixteen epilogue warps form four quads of one warp per lane quarter
 
 template <int ACT, bool HAS_BIAS>
 __device__ __forceinline__ float epi_value(int acc, float dq, float bias, float leaky) {
@@ -325,6 +371,51 @@ __device__ __forceinline__ bool store_nhwc_t(const int (&v)[W], const float *__r
         if (!(worst < 2147483648.0f)) return false;
 #pragma unroll
         for (int h = 0; h < W / 16; ++h) *reinterpret_cast<int4 *>(out_i8 + 16 * h) = make_int4(q[4 * h], q[4 * h + 1], q[4 * h + 2], q[4 * h + 3]);
+    }
+    return true;
+}
+
+// Staged form of the same block epilogue: the thread's 32 channels of residual come from its row of a shared-memory tile
+// that a tensor-map load filled (128-byte rows, 128B swizzle: 16-byte chunk i of row r sits at chunk i ^ (r & 7)), the
+// fp32 results go back into the same places and the int8 results into the thread's 32-byte row of a second tile; tensor-
+// map stores carry both tiles to global memory.  No global address arithmetic, every shared-memory access 16 bytes wide.
+template <int ACT, bool HAS_BIAS, bool AFTER>
+__device__ __forceinline__ bool staged_chunk_t(const int (&v)[32], const float *__restrict__ dq, const float *__restrict__ bias,
+                                               float leaky, float4 *__restrict__ r_row, int key, bool has_res, bool has_f32,
+                                               int4 *__restrict__ q_row, bool has_i8, float rs) {
+    uint32_t q[8];
+    float worst = 0.0f;
+#pragma unroll
+    for (int j4 = 0; j4 < 8; ++j4) {
+        const float4 d4 = *reinterpret_cast<const float4 *>(dq + 4 * j4);
+        const float4 b4 = *reinterpret_cast<const float4 *>(bias + 4 * j4);
+        float4 r4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (has_res) r4 = r_row[j4 ^ key];
+        float f[4];
+        const float dd[4] = {d4.x, d4.y, d4.z, d4.w}, bb[4] = {b4.x, b4.y, b4.z, b4.w}, rr[4] = {r4.x, r4.y, r4.z, r4.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float t = __fmul_rn(__int2float_rn(v[4 * j4 + k]), dd[k]);
+            if (HAS_BIAS) t = __fadd_rn(t, bb[k]);
+            // without a residual rr is zero: adding it changes nothing but the sign of a negative zero, which the
+            // operators' results are compared up to anyway (relu and leaky_relu do not pin it either)
+            if (!AFTER) t = __fadd_rn(t, rr[k]);
+            if (ACT == TSB_ACT_RELU) t = fmaxf(t, 0.0f);
+            if (ACT == TSB_ACT_LEAKY_RELU) t = t > 0.0f ? t : __fmul_rn(t, leaky);
+            if (AFTER) t = __fadd_rn(t, rr[k]);
+            f[k] = t;
+        }
+        if (has_f32) r_row[j4 ^ key] = make_float4(f[0], f[1], f[2], f[3]);
+        if (has_i8) {
+            const float t0 = __fmul_rn(f[0], rs), t1 = __fmul_rn(f[1], rs), t2 = __fmul_rn(f[2], rs), t3 = __fmul_rn(f[3], rs);
+            worst = max_nan(max_nan(worst, fabsf(t0)), max_nan(fabsf(t1), max_nan(fabsf(t2), fabsf(t3))));
+            q[j4] = pack_sat_s8(half_away_s32(t0), half_away_s32(t1), half_away_s32(t2), half_away_s32(t3));
+        }
+    }
+    if (has_i8) {
+        if (!(worst < 2147483648.0f)) return false;
+        q_row[0] = make_int4(q[0], q[1], q[2], q[3]);
+        q_row[1] = make_int4(q[4], q[5], q[6], q[7]);
     }
     return true;
 }
@@ -560,6 +651,8 @@ struct KernelParams {
     int b_resident;        // all K blocks of this CTA's weight tile stay in shared memory; only activations stream
     uint32_t b_off;        // offset of the resident weights
     uint32_t bar_off;      // offset of the mbarriers; tensor-memory slot, abort flag and epilogue tables follow
+    uint32_t stg_off;      // staged epilogue: offset of the four quads' tiles (1024-aligned); per quad an fp32 tile (when
+    int stg_f32;           // stg_f32) followed by an int8 tile
     // raw-row mode (rows_segs > 0): a tile is up to 128 consecutive pixels of ONE output row; per filter row the
     // producer copies the staged bytes under those pixels once, and the MMA reads them through a sliding descriptor
     int rows_segs;         // tiles per output row (0: mode off)
@@ -576,6 +669,8 @@ struct KernelParams {
     uint32_t patch_bytes;                     // bytes of one patch (one channel block)
     int OH;
     FastDiv d_tiles_w, d_tiles_hw;
+    int res_prefetch;      // the residual tensor has a tensor map (map_r): the epilogue prefetches its boxes into L2 two
+                           // chunks ahead of the loads, so that those find the data on chip
     int *status;     // device word: 0 ok, else the code of the wait that ran out
     unsigned long long *trace;  // profiling builds: timeline of CTA 0, 8 stamps per tile, 32 tiles (null otherwise)
 };
@@ -625,8 +720,8 @@ constexpr int kModeGeneral = 0, kModeRows = 1, kModePatch = 2;
 constexpr int kMaxStages = 24;
 constexpr uint32_t kMaxDynamicSmem = 227 * 1024;
 
-// barriers: full[stages], empty[stages], tmem_full[4], tmem_empty[4], b_full, b_free
-__host__ __device__ constexpr uint32_t num_barriers(int stages) { return 2u * (uint32_t)stages + 2u * kMaxAccBufs + 2u; }
+// barriers: full[stages], empty[stages], tmem_full[4], tmem_empty[4], b_full, b_free, staged_residual[4]
+__host__ __device__ constexpr uint32_t num_barriers(int stages) { return 2u * (uint32_t)stages + 2u * kMaxAccBufs + 2u + 4u; }
 
 // PIX pixels x CH channels per tile.  Normal orientation: the pixel tile is the MMA's A operand (M = 128 pixels), the
 // weight tile its B operand (N = BN channels).  Swapped orientation: the weight tile is A (M = 128 channels, rows
@@ -638,7 +733,9 @@ __host__ __device__ constexpr uint32_t num_barriers(int stages) { return 2u * (u
 template <int BN, int BK, bool SWAP, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                  const __grid_constant__ KernelParams kp, const __grid_constant__ EpiParams epi) {
+                  const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_of,
+                  const __grid_constant__ CUtensorMap map_oi, const __grid_constant__ KernelParams kp,
+                  const __grid_constant__ EpiParams epi) {
     constexpr int PIX = SWAP ? BN : kBM;      // pixels per tile
     constexpr int CH = SWAP ? kBM : BN;       // output channels per tile
     constexpr uint32_t kPixBytes = PIX * BK, kWgtBytes = CH * BK;
@@ -656,6 +753,7 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const uint32_t bar_tempty = bar_tfull + 8 * kMaxAccBufs;
     const uint32_t bar_bfull = bar_tempty + 8 * kMaxAccBufs;
     const uint32_t bar_bfree = bar_bfull + 8;
+    const uint32_t bar_stg = bar_bfree + 8;     // one per epilogue quad: a staged residual tile has landed
     const uint32_t slot_off = kp.bar_off + 8 * num_barriers(kStages);
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + slot_off);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(base_ptr + slot_off + 4);
@@ -692,6 +790,7 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         for (int a = 0; a < kMaxAccBufs; ++a) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, kEpiThreads / nbuf); }
         mbar_init(bar_bfull, 1);
         mbar_init(bar_bfree, 1);
+        for (int q = 0; q < kQuads; ++q) mbar_init(bar_stg + 8 * q, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -882,6 +981,7 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 if (MODE == kModePatch) {
                     const int n_cb = kp.Cp / BK;
                     const uint64_t dhi_patch = smem_desc_hi<BK>((uint32_t)kp.patch_pw * BK);   // next tile row = next patch row
+                    const uint32_t hi_patch = (uint32_t)(dhi_patch >> 32), hi_plain = (uint32_t)(dhi >> 32);
                     const uint32_t wtap16 = (uint32_t)n_cb * kWgt16;                          // next tap of the resident weights
                     for (int cbi = 0; cbi < n_cb && ok; ++cbi) {
                         TSB_CYC_START;
@@ -895,7 +995,20 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                         if (cbi == 0 && me == 0) TSB_TRACE(local, 3);
                         uint32_t w16 = wres16 + (uint32_t)cbi * kWgt16;
                         TSB_CYC_START;
-                        if (taps <= 9) {
+                        if (taps == 9) {
+                            // 3x3: eighteen or thirty-six MMAs, two adds each
+                            const uint32_t p_lo = st16 | kDescLbo;
+#pragma unroll
+                            for (int t = 0; t < 9; ++t) {
+                                const uint32_t a_lo = p_lo + tapreg[t], w_lo = (w16 | kDescLbo) + (uint32_t)t * wtap16;
+#pragma unroll
+                                for (int k = 0; k < kMmaPerBlock; ++k) {
+                                    const uint64_t dp = desc_pair(hi_patch, a_lo + 2u * k), dw = desc_pair(hi_plain, w_lo + 2u * k);
+                                    mma_i8(d_tmem, SWAP ? dw : dp, SWAP ? dp : dw, idesc, (t | k) ? 1u : accumulate);
+                                }
+                            }
+                            accumulate = 1u;
+                        } else if (taps < 9) {
 #pragma unroll
                             for (int t = 0; t < 9; ++t) {
                                 const uint64_t dp = dhi_patch | (uint64_t)(st16 + tapreg[t]);
@@ -977,18 +1090,19 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     // general mode: a stage holds kgroup K blocks; one wait, kgroup * BK/32 MMAs in a row, one commit
                     uint32_t w16 = wres16;
                     const int G = kp.kgroup;
+                    const uint32_t hi_plain = (uint32_t)(dhi >> 32);
                     auto issue_stage = [&](auto group) {      // the MMAs of one stage as straight-line code
                         constexpr int kG = decltype(group)::value;
 #pragma unroll
                         for (int g = 0; g < kG; ++g) {
-                            const uint32_t a16 = st16 + (uint32_t)g * unit16;
-                            const uint64_t dp = dhi | (uint64_t)a16;
-                            const uint64_t dw = dhi | (uint64_t)(resident ? w16 + (uint32_t)g * kWgt16 : a16 + kPix16);
-                            const uint64_t da = SWAP ? dw : dp, db = SWAP ? dp : dw;
+                            const uint32_t a_lo = (st16 | kDescLbo) + (uint32_t)g * unit16;
+                            const uint32_t w_lo = resident ? (w16 | kDescLbo) + (uint32_t)g * kWgt16 : a_lo + kPix16;
 #pragma unroll
-                            for (int k = 0; k < kMmaPerBlock; ++k)
+                            for (int k = 0; k < kMmaPerBlock; ++k) {
                                 // +32 bytes along K = +2 in the descriptor's 16-byte address units (inside the swizzle span)
-                                mma_i8(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (g | k) ? 1u : accumulate);
+                                const uint64_t dp = desc_pair(hi_plain, a_lo + 2u * k), dw = desc_pair(hi_plain, w_lo + 2u * k);
+                                mma_i8(d_tmem, SWAP ? dw : dp, SWAP ? dp : dw, idesc, (g | k) ? 1u : accumulate);
+                            }
                         }
                     };
                     for (int it = 0; it < k_iters; it += G) {
@@ -1047,6 +1161,7 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         constexpr int CW = 32;                   // normal orientation: columns a warp takes per step
         const bool has_bias = epi.bias != nullptr;
         const int act = epi.activation;
+        uint32_t stg_phase[1] = {0u};            // staged epilogue: phase of this quad's residual barrier
         for (int local = group; local < my_tiles; local += nbuf) {
             const int acc = group;
             const uint32_t acc_phase = (uint32_t)(local / nbuf) & 1u;
@@ -1100,9 +1215,119 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 }
                 const int img = live ? kp.d_P.div(m) : 0;
                 const int p = live ? m - img * kp.P : 0;
+                if (kp.epi_mode == kEpiStaged) {
+                    // ---- staged epilogue: residual in by tensor-map load, fp32 / int8 tiles out by tensor-map stores.
+                    // A quad (the four warps of this group that share `part`, one per lane quarter = the tile's 128
+                    // pixels) owns one fp32 tile and one int8 tile in shared memory and works through its 32-channel
+                    // chunks; the warp of lane quarter 0 issues the quad's copies.
+                    const int quad = group * parts + part;
+                    const int bar_id = 5 + quad;                                   // named barriers 1..4 belong to the groups
+                    const uint32_t stg = base + kp.stg_off + (uint32_t)quad * ((kp.stg_f32 ? kStageF32Bytes : 0u) + kStageI8Bytes);
+                    float4 *r_tile = reinterpret_cast<float4 *>(base_ptr + (stg - base));
+                    int4 *q_tile = reinterpret_cast<int4 *>(base_ptr + (stg - base) + (kp.stg_f32 ? kStageF32Bytes : 0u));
+                    const uint32_t q_addr = stg + (kp.stg_f32 ? kStageF32Bytes : 0u);
+                    const uint32_t rbar = bar_stg + 8 * quad;
+                    const bool leader = quarter == 0 && lane == 0;
+                    const bool has_res = epi.residual != nullptr, has_f32 = epi.out_f32 != nullptr, has_i8 = epi.out_i8 != nullptr;
+                    // tile coordinates of the three tensor maps (innermost coordinate: the channel)
+                    int c1 = m_tile * PIX, c2 = 0, c3 = 0;                          // general: [pixel][channel]
+                    if (MODE == kModeRows) {                                      // [image row][ow][channel]
+                        const int row_id = kp.d_segs.div(m_tile);
+                        c1 = (m_tile - row_id * kp.rows_segs) * PIX; c2 = row_id;
+                    }
+                    if (MODE == kModePatch) {                                     // [image][oh][ow][channel]
+                        const int p_img = kp.d_tiles_hw.div(m_tile), p_rem = m_tile - p_img * kp.patch_tiles_hw;
+                        const int p_r = kp.d_tiles_w.div(p_rem), p_c = p_rem - p_r * kp.patch_tiles_w;
+                        c1 = p_c * 8; c2 = p_r * (PIX / 8); c3 = p_img;
+                    }
+                    auto load_res = [&](int ch) {
+                        mbar_arrive_expect_tx(rbar, kStageF32Bytes);
+                        if (MODE == kModePatch) tma_load_4d(stg, &map_r, rbar, ch, c1, c2, c3);
+                        else if (MODE == kModeRows) tma_load_3d(stg, &map_r, rbar, ch, c1, c2);
+                        else tma_load_2d(stg, &map_r, rbar, ch, c1);
+                    };
+                    auto store_tile = [&](const CUtensorMap *map, uint32_t src, int ch) {
+                        if (MODE == kModePatch) tma_store_4d(map, src, ch, c1, c2, c3);
+                        else if (MODE == kModeRows) tma_store_3d(map, src, ch, c1, c2);
+                        else tma_store_2d(map, src, ch, c1);
+                    };
+                    // channels this tile has to cover: the real ones, and for an int8 output its zero padding as well
+                    const int ch_end = min(o_base + BN, max(epi.O, has_i8 ? epi.out_cp : 0));
+                    const int nchunks = ch_end > o_base ? (ch_end - o_base + 31) >> 5 : 0;
+                    const float rs = epi.nscales == 1 ? epi.rq_scales[0] : epi.rq_scales[min(img, epi.nscales - 1)];
+                    const int key = row & 7;
+                    float4 *r_row = r_tile + row * 8;
+                    int4 *q_row = q_tile + row * 2;
+                    if (leader && has_res && part < nchunks && o_base + part * 32 < epi.O) {
+                        load_res(o_base + part * 32);
+                        if (MODE == kModeGeneral && part + parts < nchunks && o_base + (part + parts) * 32 < epi.O)
+                            tma_prefetch_l2_2d(&map_r, o_base + (part + parts) * 32, c1);
+                    }
+                    bool stg_ok = true;
+#pragma unroll 1
+                    for (int c = part; c < nchunks; c += parts) {
+                        const int col0 = c * 32;
+                        const bool real = o_base + col0 < epi.O;      // false: nothing but the int8 output's channel padding
+                        int v[32];
+                        if (real) tmem_ld32(taddr0 + (uint32_t)col0, v);
+                        else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = 0;
+                        }
+                        if (real && has_res) {
+                            if (!mbar_wait(rbar, stg_phase[0], abort_flag)) { stg_ok = false; }
+                            stg_phase[0] ^= 1u;
+                        }
+                        if (real) tmem_ld_wait();
+                        bool fine = true;
+                        if (stg_ok) {
+                            if (epi.res_after) TSB_EPI_DISPATCH_W(fine =, staged_chunk_t, true, v, t_dq + col0, t_bias + col0, epi.leaky, r_row, key, real && has_res, has_f32, q_row, has_i8, rs);
+                            else TSB_EPI_DISPATCH_W(fine =, staged_chunk_t, false, v, t_dq + col0, t_bias + col0, epi.leaky, r_row, key, real && has_res, has_f32, q_row, has_i8, rs);
+                        }
+                        fence_async_smem();
+                        // all four warps have written their rows; the OR says whether any value needs the exact slow path
+                        const bool redo = bar_or(bar_id, 128, !fine || !stg_ok);
+                        if (leader) {
+                            if (!redo) {
+                                if (has_f32 && real) store_tile(&map_of, stg, o_base + col0);
+                                if (has_i8) store_tile(&map_oi, q_addr, o_base + col0);
+                                bulk_commit();
+                            }
+                            bulk_wait_read();                                        // the tiles may be overwritten
+                            const int cn = c + parts;
+                            if (has_res && cn < nchunks && o_base + cn * 32 < epi.O) load_res(o_base + cn * 32);
+                            // and the residual box after that one on its way into L2
+                            const int cp = cn + parts;
+                            if (has_res && MODE == kModeGeneral && cp < nchunks && o_base + cp * 32 < epi.O) tma_prefetch_l2_2d(&map_r, o_base + cp * 32, c1);
+                        }
+                        if (redo) {
+                            // NaN or a value beyond the int32 range (they quantize to -128 in the reference), or a load that
+                            // did not arrive: this chunk goes element by element, straight to global memory
+                            for (int j = 0; j < 32; ++j) {
+                                const int o = o_base + col0 + j;
+                                const int a = real ? tmem_ld1(taddr0 + (uint32_t)(col0 + j)) : 0;
+                                if (!live) continue;
+                                if (o < epi.O) epilogue_store_one(epi, img, o, p, a);
+                                else if (has_i8 && epi.i8_nhwc && o < epi.out_cp) epi.out_i8[(size_t)m * epi.out_cp + o] = 0;
+                            }
+                        }
+                        // the next chunk's writes must not overtake the leader's wait above; with a residual the load it
+                        // issues afterwards orders them, otherwise a second barrier does
+                        if (!(has_res && c + parts < nchunks && o_base + (c + parts) * 32 < epi.O)) asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+                    }
+                    if (!stg_ok && !*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 7); }
+                } else {
+                // residual boxes of this thread quad ({32 channels, 128 pixels} each), two chunks ahead of their use
+                const bool prefetcher = kp.res_prefetch && MODE != kModePatch && MODE != kModeRows && quarter == 0 && lane == 0;
+                if (prefetcher) {
+                    if (o_base + part * CW < epi.O) tma_prefetch_l2_2d(&map_r, o_base + part * CW, m_tile * PIX);
+                    if (part + parts < BN / CW && o_base + (part + parts) * CW < epi.O) tma_prefetch_l2_2d(&map_r, o_base + (part + parts) * CW, m_tile * PIX);
+                }
 #pragma unroll 1
                 for (int c = part; c < BN / CW; c += parts) {
                     const int col0 = c * CW;
+                    if (prefetcher && c + 2 * parts < BN / CW && o_base + (c + 2 * parts) * CW < epi.O)
+                        tma_prefetch_l2_2d(&map_r, o_base + (c + 2 * parts) * CW, m_tile * PIX);
                     if (o_base + col0 >= epi.O) {
                         // nothing but channel padding in this step: no accumulators to read, only the zero bytes the
                         // NHWC_PAD layout wants in its padding channels
@@ -1154,6 +1379,7 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                         }
                     }
                 }
+                }   // not staged
             } else {
                 // this thread's channel; its scale and bias live in registers
                 const int o = o_base + row;
@@ -1168,9 +1394,17 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     p_r = kp.d_tiles_w.div(p_rem);
                     p_c = p_rem - p_r * kp.patch_tiles_w;
                 }
+                // residual boxes of this thread quad ({128 channels, 32 pixels} each), two chunks ahead of their use
+                const bool prefetcher = kp.res_prefetch && MODE != kModePatch && quarter == 0 && lane == 0;
+                if (prefetcher) {
+                    if (m_tile * PIX + part * 32 < kp.M_total) tma_prefetch_l2_2d(&map_r, o_base, m_tile * PIX + part * 32);
+                    if (part + parts < kChunks && m_tile * PIX + (part + parts) * 32 < kp.M_total) tma_prefetch_l2_2d(&map_r, o_base, m_tile * PIX + (part + parts) * 32);
+                }
 #pragma unroll 1
                 for (int c = part; c < kChunks && quarter_live; c += parts) {
                     const int col0 = c * 32;
+                    if (prefetcher && c + 2 * parts < kChunks && m_tile * PIX + (c + 2 * parts) * 32 < kp.M_total)
+                        tma_prefetch_l2_2d(&map_r, o_base, m_tile * PIX + (c + 2 * parts) * 32);
                     if (MODE == kModePatch) {
                         // this chunk: tile rows col0/8 .. col0/8+3, 8 pixels each
                         const int oh0 = p_r * (PIX / 8) + (col0 >> 3), ow0 = p_c * 8;
@@ -1302,8 +1536,8 @@ CUtensorMapSwizzle swizzle_for(int bk) {
 }
 
 template <int BN, int BK, bool SWAP, int MODE>
-int launch(const Config &cfg, const CUtensorMap &ma, const CUtensorMap &mb, const KernelParams &kp, const EpiParams &epi,
-           cudaStream_t stream) {
+int launch(const Config &cfg, const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mr, const CUtensorMap &mof,
+           const CUtensorMap &moi, const KernelParams &kp, const EpiParams &epi, cudaStream_t stream) {
     // The shared-memory limit of a kernel is a per-device attribute: one process may drive several GPUs (one TenniS
     // Workbench per device, each on its own thread), so the "already raised" note is kept per device.
     static std::atomic<uint64_t> configured{0};
@@ -1315,7 +1549,7 @@ int launch(const Config &cfg, const CUtensorMap &ma, const CUtensorMap &mb, cons
         TSB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynamicSmem));
         configured.fetch_or(bit, std::memory_order_release);
     }
-    TSB_CUDA(launch_pdl(kernel, dim3(cfg.grid), dim3(kThreads), cfg.dyn_smem, stream, ma, mb, kp, epi));
+    TSB_CUDA(launch_pdl(kernel, dim3(cfg.grid), dim3(kThreads), cfg.dyn_smem, stream, ma, mb, mr, mof, moi, kp, epi));
     TSB_LAUNCHED("conv_i8_tc_kernel");
     return TSB_OK;
 }
@@ -1396,11 +1630,31 @@ bool make_view(const ConvGeom &g, const Tuning &tune, View *view, const char **w
     return true;
 }
 
-Config choose_config(const View &v, const Tuning &tune, int sm_count, int orientation) {
+int staging_level(const View &v, const EpiParams &epi) {
+    const ConvGeom &g = v.real;
+    if (epi.out_acc) return 0;
+    const bool per_sample = epi.nscales > 1 && epi.nscales == g.N && epi.group_len == (uint32_t)(g.O * g.OH * g.OW);
+    if (epi.out_i8 && !(epi.i8_nhwc && epi.rne_limit == 0 && (epi.nscales == 1 || per_sample))) return 0;
+    if (epi.out_i8 && reinterpret_cast<uintptr_t>(epi.out_i8) % 16) return 0;
+    const bool f32_tiles = (epi.out_f32 || epi.residual) && epi.f32_nhwc;
+    if (f32_tiles) {
+        // tensor maps over [pixels][O] fp32: rows must be whole 16-byte units, the tensors 16-byte aligned and distinct
+        if (g.O % 4 != 0 || (const void *)epi.residual == (const void *)epi.out_f32) return 0;
+        if ((reinterpret_cast<uintptr_t>(epi.out_f32) | reinterpret_cast<uintptr_t>(epi.residual)) % 16) return 0;
+        return 2;
+    }
+    // fp32 NCHW output, or int8 NHWC_PAD alone: the direct paths (a thread's 32 int8 channels are one 32-byte sector,
+    // which two 16-byte stores write as well as a tile store would)
+    return 0;
+}
+
+Config choose_config(const View &v, const Tuning &tune, int sm_count, int orientation, int staging) {
     const ConvGeom &g = v.g;
     Config c;
     c.bk = (g.Cp % 128 == 0) ? 128 : 64;
     const int64_t M = (int64_t)g.N * g.OH * g.OW;
+    const uint32_t stg_bytes = staging == 2 ? kQuads * (kStageF32Bytes + kStageI8Bytes) : (staging == 1 ? kQuads * kStageI8Bytes : 0u);
+    const uint32_t budget = kSmemBudget - stg_bytes;
     // An MMA instruction costs the same 128 cycles for any N up to 256, so N should be 256 whenever possible.
     // Normal orientation: 128 pixels on M, up to 256 output channels on N.  Swapped orientation: channels on M,
     // 256 (or 128) pixels on N -- it halves the MMA count of narrow layers but its epilogue (one channel per thread)
@@ -1415,7 +1669,7 @@ Config choose_config(const View &v, const Tuning &tune, int sm_count, int orient
         const double eff = (double)(g.OH * g.OW) / ((double)tiles_w * tiles_h * pix);
         const uint64_t patch_bytes = (uint64_t)round_up(pw * ph * c.bk, 1024);
         const uint64_t w_all = (uint64_t)g.KH * g.KW * g.Cp * (uint64_t)ch;
-        return (eff >= 0.7 || tune.patch == 2) && w_all + 2 * patch_bytes <= kSmemBudget;
+        return (eff >= 0.7 || tune.patch == 2) && w_all + 2 * patch_bytes <= budget;
     };
     const int bn_normal = g.O > 128 ? 256 : (g.O > 64 ? 128 : 64);
     if (v.rows) c.swap = 0;
@@ -1478,22 +1732,28 @@ Config choose_config(const View &v, const Tuning &tune, int sm_count, int orient
             if (k_iters % (uint32_t)gsz == 0 && (uint32_t)gsz * unit <= 48 * 1024 && room / ((uint32_t)gsz * unit) >= 3) return gsz;
         return 1;
     };
-    if (c.patch || (want_resident && w_total <= 128 * 1024 && (kSmemBudget - w_total) / p_bytes >= min_stages)) {
+    if (c.patch || (want_resident && w_total <= 128 * 1024 && w_total < budget && (budget - w_total) / p_bytes >= min_stages)) {
         c.b_resident = 1;
         c.unit_bytes = p_bytes;
-        c.kgroup = group_for(p_bytes, kSmemBudget - w_total);
+        c.kgroup = group_for(p_bytes, budget - w_total);
         c.stage_bytes = (uint32_t)c.kgroup * p_bytes;
-        c.stages = std::min<int>(kMaxStages, (int)((kSmemBudget - w_total) / c.stage_bytes));
+        c.stages = std::min<int>(kMaxStages, (int)((budget - w_total) / c.stage_bytes));
         c.b_off = (uint32_t)c.stages * c.stage_bytes;
         c.bar_off = c.b_off + w_total;
     } else {
         c.b_resident = 0;
         c.unit_bytes = p_bytes + w_bytes;
-        c.kgroup = group_for(c.unit_bytes, kSmemBudget);
+        c.kgroup = group_for(c.unit_bytes, budget);
         c.stage_bytes = (uint32_t)c.kgroup * c.unit_bytes;
-        c.stages = std::min<int>(kMaxStages, (int)(kSmemBudget / c.stage_bytes));
+        c.stages = std::min<int>(kMaxStages, (int)(budget / c.stage_bytes));
         c.b_off = 0;
         c.bar_off = (uint32_t)c.stages * c.stage_bytes;
+    }
+    // the staged epilogue's tiles (1024-byte aligned for the 128B swizzle) sit between the pipeline and the barriers
+    c.staging = c.swap ? 0 : staging;
+    if (c.staging) {
+        c.stg_off = (c.bar_off + 1023u) & ~1023u;
+        c.bar_off = c.stg_off + stg_bytes;
     }
     const uint32_t tables = ((c.bar_off + 8 * num_barriers(c.stages) + 8 + 15) & ~15u) + kMaxAccBufs * 2 * (uint32_t)c.bn * 4 +
                             (c.patch ? 4 * (uint32_t)(g.KH * g.KW) : 0);   // epilogue tables, then patch mode's tap table
@@ -1694,8 +1954,72 @@ int launch_conv_tc(const View &v, const Config &cfg, const CUtensorMap &map_a, c
         (cfg.swap || (g.O % 4 == 0 && ((reinterpret_cast<uintptr_t>(epi.out_f32) | reinterpret_cast<uintptr_t>(epi.residual)) & 15) == 0)))
         kp.epi_mode = kEpiNhwc;
     const int mode = cfg.patch ? kModePatch : (v.rows ? kModeRows : kModeGeneral);
+    // Pixel-major fp32 residual (the shortcut of a residual block, as large as the output): a tensor map over it lets the
+    // epilogue prefetch the boxes it is about to read into L2.  The map is not used for loads, so a failure to encode one
+    // only switches the prefetch off.
+    CUtensorMap map_r = map_b;
+    kp.res_prefetch = 0;
+    if (kp.epi_mode == kEpiNhwc && epi.residual && mode == kModeGeneral && g.O % 4 == 0 && reinterpret_cast<uintptr_t>(epi.residual) % 16 == 0 &&
+        load_driver() == TSB_OK) {
+        cuuint64_t dims[2] = {(cuuint64_t)g.O, (cuuint64_t)kp.M_total};
+        cuuint64_t strides[1] = {(cuuint64_t)g.O * 4};
+        cuuint32_t box[2] = {cfg.swap ? (cuuint32_t)std::min(g.O, kBM) : 32u, cfg.swap ? 32u : (cuuint32_t)kBM};
+        cuuint32_t estr[2] = {1, 1};
+        if (g_encode_tiled(&map_r, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(epi.residual), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
+            kp.res_prefetch = 1;
+        else
+            map_r = map_b;
+    }
+    // Staged epilogue (normal orientation, shared memory set aside by the configuration): tensor maps over the residual,
+    // the fp32 output and the int8 output whose boxes are one quad's tile -- 32 channels x the tile's 128 pixels, shaped
+    // like the pixel tile of the load mode (a run of pixels, a run inside one output row, or an 8 x 16 block).
+    CUtensorMap map_of = map_b, map_oi = map_b;
+    kp.stg_off = cfg.stg_off;
+    kp.stg_f32 = cfg.staging == 2 ? 1 : 0;
+    const int want_staging = cfg.swap ? 0 : staging_level(v, epi);
+    if (want_staging != 0 && cfg.staging >= want_staging && load_driver() == TSB_OK) {
+        const ConvGeom &r = v.real;
+        auto encode = [&](CUtensorMap *map, const void *ptr, bool is_f32, uint64_t channels) -> bool {
+            const uint64_t es = is_f32 ? 4 : 1;
+            const CUtensorMapDataType dt = is_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+            const CUtensorMapSwizzle sw = is_f32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE;
+            cuuint32_t estr[4] = {1, 1, 1, 1};
+            CUresult rc;
+            if (mode == kModePatch) {
+                cuuint64_t dims[4] = {channels, (cuuint64_t)r.OW, (cuuint64_t)r.OH, (cuuint64_t)r.N};
+                cuuint64_t strides[3] = {channels * es, channels * es * r.OW, channels * es * r.OW * r.OH};
+                cuuint32_t box[4] = {32, 8, (cuuint32_t)(kBM / 8), 1};
+                rc = g_encode_tiled(map, dt, 4, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            } else if (mode == kModeRows) {
+                cuuint64_t dims[3] = {channels, (cuuint64_t)r.OW, (cuuint64_t)r.N * r.OH};
+                cuuint64_t strides[2] = {channels * es, channels * es * r.OW};
+                cuuint32_t box[3] = {32, (cuuint32_t)kBM, 1};
+                rc = g_encode_tiled(map, dt, 3, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            } else {
+                cuuint64_t dims[2] = {channels, (cuuint64_t)kp.M_total};
+                cuuint64_t strides[1] = {channels * es};
+                cuuint32_t box[2] = {32, (cuuint32_t)kBM};
+                rc = g_encode_tiled(map, dt, 2, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            }
+            return rc == CUDA_SUCCESS;
+        };
+        bool ok_maps = true;
+        if (epi.residual) ok_maps = ok_maps && encode(&map_r, epi.residual, true, (uint64_t)r.O);
+        if (epi.out_f32) ok_maps = ok_maps && encode(&map_of, epi.out_f32, true, (uint64_t)r.O);
+        if (epi.out_i8) ok_maps = ok_maps && encode(&map_oi, epi.out_i8, false, (uint64_t)epi.out_cp);
+        if (ok_maps) {
+            kp.epi_mode = kEpiStaged;
+            kp.res_prefetch = 0;
+            kp.stg_f32 = cfg.staging == 2 ? 1 : 0;
+        }
+    }
 #define TSB_TC_CASE(BN_, BK_, SWAP_, MODE_) \
-    if (cfg.bn == BN_ && cfg.bk == BK_ && (cfg.swap != 0) == SWAP_ && mode == MODE_) return launch<BN_, BK_, SWAP_, MODE_>(cfg, map_a, map_b, kp, epi, stream)
+    if (cfg.bn == BN_ && cfg.bk == BK_ && (cfg.swap != 0) == SWAP_ && mode == MODE_) return launch<BN_, BK_, SWAP_, MODE_>(cfg, map_a, map_b, map_r, map_of, map_oi, kp, epi, stream)
 #define TSB_TC_BOTH(BN_, BK_, MODE_) TSB_TC_CASE(BN_, BK_, false, MODE_); TSB_TC_CASE(BN_, BK_, true, MODE_)
     TSB_TC_CASE(64, 64, false, kModeGeneral); TSB_TC_CASE(64, 128, false, kModeGeneral);
     TSB_TC_BOTH(128, 64, kModeGeneral); TSB_TC_BOTH(256, 64, kModeGeneral);

@@ -50,6 +50,8 @@ struct Config {
     int kgroup = 1;                   // K blocks per pipeline stage (im2col / tiled loads; 1 in patch and raw-row mode)
     uint32_t unit_bytes = 0;          // one K block of a stage
     uint32_t stage_bytes = 0, b_off = 0, bar_off = 0, dyn_smem = 0;
+    int staging = 0;                  // shared memory set aside for the staged epilogue: 0 none, 1 int8 tiles, 2 fp32 + int8 tiles
+    uint32_t stg_off = 0;
 };
 
 // Overrides of the plan heuristics, from tsb_conv_desc (tests force every code path with them): 0 = the library
@@ -64,7 +66,12 @@ struct Tuning {
 bool make_view(const ConvGeom &g, const Tuning &tune, View *view, const char **why);
 // orientation: -1 = by heuristic (or tune.orientation), 0 = normal, 1 = swapped (any number of output channels, 128
 // per channel tile)
-Config choose_config(const View &v, const Tuning &tune, int sm_count, int orientation);
+// staging: shared memory to set aside for the staged epilogue (see Config::staging); only normal-orientation
+// configurations use it
+Config choose_config(const View &v, const Tuning &tune, int sm_count, int orientation, int staging = 0);
+// Which staged epilogue these outputs can take with this view: 0 none (direct stores), 1 int8 NHWC_PAD tile only,
+// 2 pixel-major fp32 residual / output (and int8) tiles.
+int staging_level(const View &v, const EpiParams &epi);
 // w_packed: [O][KH][KW][Cp] int8 of the view's geometry
 int encode_weight_map(const View &v, const Config &cfg, const int8_t *w_packed, CUtensorMap *map);
 // x: the staged activations (NHWC_PAD or folded), 16-byte aligned
