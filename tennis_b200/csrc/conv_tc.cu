@@ -291,6 +291,13 @@ __device__ __forceinline__ float max_nan(float a, float b) {
     return r;
 }
 
+// the same over three values (one instruction on this architecture)
+__device__ __forceinline__ float max3_nan(float a, float b, float c) {
+    float r;
+    asm("max.NaN.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
 // ---- fast paths, normal orientation: the thread owns one PIXEL (its tensor-memory lane) and 32 consecutive channels
 template <int ACT, bool HAS_BIAS, int W>
 __device__ __forceinline__ void store_f32_nchw_t(const int (&v)[W], const float *__restrict__ dq,
@@ -324,7 +331,7 @@ __device__ __forceinline__ bool store_i8_nhwc_t(const int (&v)[W], const float *
         const float t1 = __fmul_rn(epi_value<ACT, HAS_BIAS>(v[4 * j4 + 1], d4.y, b4.y, leaky), rs);
         const float t2 = __fmul_rn(epi_value<ACT, HAS_BIAS>(v[4 * j4 + 2], d4.z, b4.z, leaky), rs);
         const float t3 = __fmul_rn(epi_value<ACT, HAS_BIAS>(v[4 * j4 + 3], d4.w, b4.w, leaky), rs);
-        worst = max_nan(max_nan(worst, fabsf(t0)), max_nan(fabsf(t1), max_nan(fabsf(t2), fabsf(t3))));
+        worst = max3_nan(max3_nan(worst, fabsf(t0), fabsf(t1)), fabsf(t2), fabsf(t3));
         q[j4] = pack_sat_s8(half_away_s32(t0), half_away_s32(t1), half_away_s32(t2), half_away_s32(t3));
     }
     if (!(worst < 2147483648.0f)) return false;
@@ -363,7 +370,7 @@ __device__ __forceinline__ bool store_nhwc_t(const int (&v)[W], const float *__r
         if (out_f32) reinterpret_cast<float4 *>(out_f32)[j4] = make_float4(f[0], f[1], f[2], f[3]);
         if (out_i8) {
             const float t0 = __fmul_rn(f[0], rs), t1 = __fmul_rn(f[1], rs), t2 = __fmul_rn(f[2], rs), t3 = __fmul_rn(f[3], rs);
-            worst = max_nan(max_nan(worst, fabsf(t0)), max_nan(fabsf(t1), max_nan(fabsf(t2), fabsf(t3))));
+            worst = max3_nan(max3_nan(worst, fabsf(t0), fabsf(t1)), fabsf(t2), fabsf(t3));
             q[j4] = pack_sat_s8(half_away_s32(t0), half_away_s32(t1), half_away_s32(t2), half_away_s32(t3));
         }
     }
@@ -408,7 +415,7 @@ __device__ __forceinline__ bool staged_chunk_t(const int (&v)[32], const float *
         if (has_f32) r_row[j4 ^ key] = make_float4(f[0], f[1], f[2], f[3]);
         if (has_i8) {
             const float t0 = __fmul_rn(f[0], rs), t1 = __fmul_rn(f[1], rs), t2 = __fmul_rn(f[2], rs), t3 = __fmul_rn(f[3], rs);
-            worst = max_nan(max_nan(worst, fabsf(t0)), max_nan(fabsf(t1), max_nan(fabsf(t2), fabsf(t3))));
+            worst = max3_nan(max3_nan(worst, fabsf(t0), fabsf(t1)), fabsf(t2), fabsf(t3));
             q[j4] = pack_sat_s8(half_away_s32(t0), half_away_s32(t1), half_away_s32(t2), half_away_s32(t3));
         }
     }
@@ -1162,6 +1169,7 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         const bool has_bias = epi.bias != nullptr;
         const int act = epi.activation;
         uint32_t stg_phase[1] = {0u};            // staged epilogue: phase of this quad's residual barrier
+        int table_n = -1;                        // channel tile this group's scale / bias table holds
         for (int local = group; local < my_tiles; local += nbuf) {
             const int acc = group;
             const uint32_t acc_phase = (uint32_t)(local / nbuf) & 1u;
@@ -1169,24 +1177,21 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             decode(local, m_tile, n_tile);
             const int o_base = n_tile * CH;
             float *t_dq = table + acc * 2 * BN, *t_bias = t_dq + BN;
-            if (!SWAP) {
+            if (!SWAP && n_tile != table_n) {
+                // this group's table of per-channel scales and biases: rebuilt only when the channel tile changes (never, for
+                // layers of at most BN channels), between two barriers of the group
+                if (table_n >= 0) asm volatile("bar.sync %0, %1;" ::"r"(1 + group), "r"(group_threads) : "memory");
                 for (int j = et; j < BN; j += group_threads) {
                     const int o = o_base + j;
                     t_dq[j] = o < epi.O ? epi.dq[o] : 0.0f;
                     t_bias[j] = (o < epi.O && epi.bias) ? epi.bias[o] : 0.0f;
                 }
+                asm volatile("bar.sync %0, %1;" ::"r"(1 + group), "r"(group_threads) : "memory");
+                table_n = n_tile;
             }
-            // One collective decision per tile: the wait result is AND-reduced over the epilogue threads, so either
-            // all warps go on or all leave (the reduction is also the barrier that publishes the tables).
-            int ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag) ? 1 : 0;
-            int all_ok;
-            asm volatile(
-                "{\n\t.reg .pred p, q;\n\t"
-                "setp.ne.b32 p, %1, 0;\n\t"
-                "bar.red.and.pred q, %3, %2, p;\n\t"       // named barrier 1 + group, over the group's threads
-                "selp.u32 %0, 1, 0, q;\n\t}"
-                : "=r"(all_ok) : "r"(ok), "r"(group_threads), "r"(1 + group) : "memory");
-            if (!all_ok) {
+            // every warp waits for the accumulator on its own; one that gives up raises the CTA's abort flag, which ends
+            // the other warps' waits as well
+            if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) {
                 if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 4); }
                 break;
             }

@@ -96,6 +96,7 @@ class QuantResNet:
         self.fc_b = torch.from_numpy(params["fc_b"]).to(dev)
         self.buffers = {}
         self.calibrated = False
+        self.launch_log = None
 
     # ---- buffers ------------------------------------------------------------------------------------------------
     def _i8(self, key, pixels_hw, channels):
@@ -117,10 +118,21 @@ class QuantResNet:
         c = L["spec"]
         out_i8 = self._i8(key + ".i8", c["oh"], c["o"]) if want_i8 else None
         out_f32 = self._f32(key + ".f32", c["oh"], c["o"]) if want_f32 else None
-        L["plan"].run(None if staged else x_i8, LAYOUT_STAGED if staged else LAYOUT_NHWC_PAD, L["dq"], bias=L["bias"],
-                      residual=residual, activation=act, leaky=leaky, out_f32=out_f32, out_f32_layout=LAYOUT_NHWC_PAD,
-                      out_i8=out_i8, out_i8_layout=LAYOUT_NHWC_PAD,
-                      requant_scales=L["out_scale_arr"] if want_i8 else None, residual_after_activation=residual_after)
+
+        def launch():
+            L["plan"].run(None if staged else x_i8, LAYOUT_STAGED if staged else LAYOUT_NHWC_PAD, L["dq"], bias=L["bias"],
+                          residual=residual, activation=act, leaky=leaky, out_f32=out_f32, out_f32_layout=LAYOUT_NHWC_PAD,
+                          out_i8=out_i8, out_i8_layout=LAYOUT_NHWC_PAD,
+                          requant_scales=L["out_scale_arr"] if want_i8 else None, residual_after_activation=residual_after)
+        launch()
+        if self.launch_log is not None:      # layer_times(): every convolution launch of a pass, replayable
+            out_bytes = (out_i8.numel() if want_i8 else 0) + (4 * self.batch * c["oh"] * c["oh"] * c["o"] if want_f32 else 0)
+            in_bytes = self.batch * c["h"] * c["h"] * ops.padded_channels(c["c"]) + c["o"] * c["c"] * c["k"] * c["k"] + 8 * c["o"]
+            if residual is not None:
+                in_bytes += 4 * self.batch * c["oh"] * c["oh"] * c["o"]
+            self.launch_log.append(dict(name=c["name"], launch=launch, ops=2 * self.batch * c["o"] * c["oh"] * c["oh"] * c["c"] * c["k"] * c["k"],
+                                        bytes=in_bytes + out_bytes, k=c["k"], c=c["c"], o=c["o"], size=c["oh"], stride=c["stride"],
+                                        residual=residual is not None, fp32_out=bool(want_f32), int8_out=bool(want_i8)))
         return out_i8, out_f32
 
     def _calibrate_conv(self, idx, x_i8, key, act, residual=None, staged=False, leaky=0.0, residual_after=False):
@@ -231,6 +243,40 @@ class QuantResNet:
     def status(self):
         for L in self.convs:
             L["plan"].status()
+
+    def layer_times(self, x, reps=20):
+        """Device time of every convolution launch of one forward pass, each on its own: `reps` back-to-back launches
+        replayed from a CUDA graph, inputs as the pass left them (warm L2 for small layers, as inside the pass).
+        Returns a list of dicts (name, us, ops, bytes, shape fields)."""
+        self.launch_log = []
+        try:
+            self.forward(x)
+        finally:
+            log, self.launch_log = self.launch_log, None
+        torch.cuda.synchronize()
+        out = []
+        side = torch.cuda.Stream(device=self.dev)
+        for item in log:
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                item["launch"]()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    for _ in range(reps):
+                        item["launch"]()
+            torch.cuda.current_stream().wait_stream(side)
+            g.replay()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            g.replay()
+            b.record()
+            torch.cuda.synchronize()
+            d = {k: v for k, v in item.items() if k != "launch"}
+            d["us"] = a.elapsed_time(b) * 1e3 / reps
+            out.append(d)
+            del g
+        return out
 
 
 # ---------------------------------------------------------------------------------------------------------------------
