@@ -35,7 +35,28 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 15.7e6
+TRAFFIC_RECORD = os.path.join(ROOT, "profiles", "conv_i8_tc_kernel_config1.md")
+
+
+def ncu_traffic_record():
+    """DRAM bytes per convolution launch from the ncu capture summarised under profiles/, valid only for the kernel source
+    it was captured with: the summary carries the SHA-256 of tennis_b200/csrc/conv_tc.cu at capture time.  Returns
+    (bytes or None, stale flag, note)."""
+    import hashlib
+    import re
+    try:
+        text = open(TRAFFIC_RECORD).read()
+        m_bytes = re.search(r"dram_bytes_per_launch\s*=\s*([0-9.eE+]+)", text)
+        m_hash = re.search(r"conv_tc_sha256\s*=\s*([0-9a-f]{64})", text)
+        if not m_bytes or not m_hash:
+            return None, True, "no traffic record in %s" % os.path.relpath(TRAFFIC_RECORD, ROOT)
+        now = hashlib.sha256(open(os.path.join(ROOT, "tennis_b200", "csrc", "conv_tc.cu"), "rb").read()).hexdigest()
+        if now != m_hash.group(1):
+            return None, True, "the kernel source changed since the ncu capture in %s" % os.path.relpath(TRAFFIC_RECORD, ROOT)
+        return float(m_bytes.group(1)), False, "ncu capture summarised in %s" % os.path.relpath(TRAFFIC_RECORD, ROOT)
+    except OSError as e:
+        return None, True, repr(e)
+
 METRIC = "int8_conv_tops"
 UNIT = "TOPS"
 WORKLOAD = "config1: int8 conv2d shape sweep, batch 32 (1x1 256->1024@14, 3x3 128->128@28, 3x3/2 256->512@28, 1x1 2048->512@7, 7x7/2 3->64@224), fp32 NCHW out, bias+ReLU"
@@ -181,7 +202,61 @@ class ClockSampler(threading.Thread):
         return d
 
 
-def run_resnet50(args, dev, rank, world, sharding):
+
+def layer_table(times, peaks):
+    """Per-convolution figures of one network pass: time, TOPS, GB/s, which roofline binds the layer and the fraction of it."""
+    int8_peak = 2.0 * peaks["bf16_tflops"]
+    out = []
+    for t in times:
+        tops, gbs = t["ops"] / t["us"] / 1e6, t["bytes"] / t["us"] / 1e3
+        floor_tensor, floor_hbm = t["ops"] / (int8_peak * 1e6), t["bytes"] / (peaks["hbm_gbs"] * 1e3)
+        bound = "hbm" if floor_hbm >= floor_tensor else "tensor"
+        out.append({"name": t["name"], "shape": "%dx%d%s %d->%d @%d" % (t["k"], t["k"], "/2" if t["stride"] == 2 else "", t["c"], t["o"], t["size"]),
+                    "outputs": "+".join(x for x, on in (("residual", t["residual"]), ("f32", t["fp32_out"]), ("i8", t["int8_out"])) if on),
+                    "us": round(t["us"], 2), "tops": round(tops, 1), "gbs": round(gbs, 1), "bound": bound,
+                    "frac": round(max(floor_tensor, floor_hbm) / t["us"], 4)})
+    return out
+
+
+def pass_roofline(times, ms_pass, peaks, extra_bytes=0):
+    """The whole pass against both rooflines: algorithmic ops and bytes of its convolutions (plus the glue kernels' bytes)."""
+    int8_peak = 2.0 * peaks["bf16_tflops"]
+    ops = sum(t["ops"] for t in times)
+    nbytes = sum(t["bytes"] for t in times) + extra_bytes
+    floor_tensor_ms, floor_hbm_ms = ops / (int8_peak * 1e9), nbytes / (peaks["hbm_gbs"] * 1e6)
+    # a pass is a sequence of kernels, each bound by its own roofline: the floor is the sum of the per-layer floors
+    floor_sum_ms = sum(max(t["ops"] / (int8_peak * 1e9), t["bytes"] / (peaks["hbm_gbs"] * 1e6)) for t in times) + extra_bytes / (peaks["hbm_gbs"] * 1e6)
+    return {"algorithmic_gop": ops / 1e9, "algorithmic_mb": nbytes / 1e6, "min_ms_tensor": floor_tensor_ms, "min_ms_hbm": floor_hbm_ms,
+            "min_ms_per_layer_bounds": floor_sum_ms, "measured_ms": ms_pass, "frac": floor_sum_ms / ms_pass,
+            "sum_of_layer_times_ms": sum(t["us"] for t in times) / 1e3,
+            "peaks": "int8 tensor = 2 x %s bf16 (%.0f TOPS), HBM %s %.0f GB/s" % (peaks["source"], int8_peak, peaks["source"], peaks["hbm_gbs"])}
+
+
+def resnet_parity(net, spec, params, scales, x, logits):
+    """First and last image of the batch against the reference operator chain run on those two images (the C port of the
+    reference's arithmetic, OpenMP).  Test infrastructure used as the checker; returns the parity object of the bench line."""
+    from oracle import chains, oracle as orc
+    chk = orc.Port()
+    picks = [0, x.shape[0] - 1]
+    t0 = time.perf_counter()
+    outs, last_f32, want = chains.resnet_forward(spec, params, scales, x[picks].cpu().numpy(), chk)
+    bad = chains.resnet_mismatches(spec, net.buffers, logits, picks, outs, last_f32, want)
+    return {"images_checked": len(picks), "mismatches": bad, "checker": "C port of the reference operators, block outputs int8 bit-exact, last fp32 tensor bit-exact up to the sign of zero, logits 1e-5",
+            "host_s": round(time.perf_counter() - t0, 2)}
+
+
+def csp_parity(net, spec, params, scales, x, out):
+    from oracle import chains, oracle as orc
+    from tennis_b200 import nets
+    chk = orc.Port()
+    picks = [0, x.shape[0] - 1]
+    t0 = time.perf_counter()
+    outs, last = chains.cspdarknet_forward(spec, params, scales, x[picks].cpu().numpy(), chk, leaky=nets.LEAKY)
+    bad = chains.cspdarknet_mismatches(spec, net.buffers, out, picks, outs, last)
+    return {"images_checked": len(picks), "mismatches": bad, "checker": "C port of the reference operators, every block / stage output int8 bit-exact",
+            "host_s": round(time.perf_counter() - t0, 2)}
+
+def run_resnet50(args, dev, rank, world, sharding, peaks):
     """Images/s of the ResNet-50-shaped int8 network (53 convolutions with folded BN, fused ReLU / residual / requantize,
     int8 max pool, fp32 average pool and inner product), batch 64 per GPU, synthetic N(0,1) input, whole forward pass
     captured once in a CUDA graph and replayed.  The pass touches ~3 GB, far more than L2, so no flush is needed."""
@@ -191,9 +266,19 @@ def run_resnet50(args, dev, rank, world, sharding):
     spec = nets.resnet_spec()
     params = nets.make_params(spec, seed=0)
     net = nets.QuantResNet(spec, params, batch, dev)
-    g = torch.Generator(device=dev).manual_seed(sharding.shard_seed(0, rank))
+    g = torch.Generator(device=dev).manual_seed(0 if world == 1 else sharding.shard_seed(rank))
     x = torch.randn((batch, 3, 224, 224), device=dev, generator=g)
-    net.calibrate(x)
+    scales = net.calibrate(x)
+    parity = None
+    if rank == 0:
+        try:
+            first = net.forward(x).clone()
+            net.status()
+            torch.cuda.synchronize()
+            parity = resnet_parity(net, spec, params, scales, x, first)
+        except Exception as e:
+            parity = {"images_checked": 0, "mismatches": None, "error": repr(e)[:200]}
+    layer_times = net.layer_times(x) if rank == 0 else []
     stream = torch.cuda.Stream(device=dev)
     stream.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(stream):
@@ -251,14 +336,96 @@ def run_resnet50(args, dev, rank, world, sharding):
     ms_max, images = sharding.aggregate(ms, batch, dev)
     e2e_max, _ = sharding.aggregate(e2e_ms, batch, dev)
     ops_batch = nets.conv_ops(spec, batch)
+    # bytes of the four glue kernels: stem quantize (5 B per input element), max pool (int8 in + out), average pool, inner product
+    c0 = spec["convs"][0]
+    glue_bytes = (5 * x.numel() + batch * c0["oh"] * c0["oh"] * 64 + batch * spec["stem_pooled"] ** 2 * 64
+                  + 4 * batch * spec["final_size"] ** 2 * spec["features"] + 4 * spec["classes"] * spec["features"])
+    config4 = None
+    try:
+        config4 = run_config4(args, dev, rank, world, sharding, net, graph, x, logits, spec, params, scales)
+    except Exception as e:
+        config4 = {"error": repr(e)[:300]}
     return {"workload": "config2: ResNet-50-shaped int8 network, batch 64 per GPU, CUDA graph replay", "batch_per_gpu": batch,
             "images_per_sec": images / (ms_max / 1e3), "ms_per_batch": ms_max, "int8_conv_tops": ops_batch * world / (ms_max / 1e3) / 1e12,
             "e2e_images_per_sec": images / (e2e_max / 1e3), "e2e_ms_per_batch": e2e_max,
             "h2d_bytes_per_batch": hx.numel() * 4 * world, "d2h_bytes_per_batch": hout.numel() * 4 * world,
-            "kernels_per_pass": 53 + 4, "logits_checksum": float(logits.double().abs().sum())}
+            "kernels_per_pass": 53 + 4, "parity": parity,
+            "pass_roofline": pass_roofline(layer_times, ms_max, peaks, extra_bytes=glue_bytes) if layer_times else None,
+            "layers": layer_table(layer_times, peaks),
+            "config4": config4}
 
 
-def run_cspdarknet(args, dev, rank, world, sharding):
+
+def run_config4(args, dev, rank, world, sharding, net, graph, x_static, logits, spec, params, scales):
+    """Configuration 4: the ResNet-50-shaped network over a global batch of 2048 images split evenly over the replicas
+    (shard_range), each replica working through its shard in micro-batches of 64 with inputs drawn from its own seed
+    1000 + rank.  Device figure: shard resident in HBM, events around the shard's micro-batches.  End to end: the shard in
+    pinned host memory, every micro-batch uploaded (double-buffered on a copy stream) and its logits read back, all inside
+    the timed region.  Replica 0 also checks two images of its first micro-batch against the operator chain."""
+    import torch
+    start, count = sharding.shard_range(2048, world, rank)
+    sizes = sharding.micro_batches(count, 64)
+    full = [n for n in sizes if n == 64]          # the network is planned for micro-batches of 64 (2048 / N is a multiple for N <= 32)
+    g = torch.Generator(device=dev).manual_seed(sharding.shard_seed(rank))
+    shard = torch.randn((len(full) * 64, 3, 224, 224), device=dev, generator=g)
+    # parity of this seed's inputs: first micro-batch, first and last image (replica 0)
+    parity = None
+    if rank == 0:
+        x_static.copy_(shard[:64])
+        graph.replay()
+        torch.cuda.synchronize()
+        parity = resnet_parity(net, spec, params, scales, x_static, logits)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for i in range(min(2, len(full))):
+        x_static.copy_(shard[i * 64:(i + 1) * 64]); graph.replay()
+    torch.cuda.synchronize()
+    a.record()
+    for i in range(len(full)):
+        x_static.copy_(shard[i * 64:(i + 1) * 64], non_blocking=True)
+        graph.replay()
+    b.record()
+    torch.cuda.synchronize()
+    dev_ms = a.elapsed_time(b)
+    # end to end from pinned host memory
+    host = shard.cpu().pin_memory()
+    del shard
+    houts = torch.empty((len(full), 64, logits.shape[1]), dtype=torch.float32).pin_memory()
+    stage = [torch.empty_like(x_static) for _ in range(2)]
+    copied = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
+    copy_stream = torch.cuda.Stream(device=dev)
+    main = torch.cuda.current_stream()
+
+    def upload(i):
+        with torch.cuda.stream(copy_stream):
+            if i >= 2:
+                copy_stream.wait_event(consumed[i % 2])
+            stage[i % 2].copy_(host[i * 64:(i + 1) * 64], non_blocking=True)
+            copied[i % 2].record(copy_stream)
+
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    upload(0)
+    for i in range(len(full)):
+        if i + 1 < len(full):
+            upload(i + 1)
+        main.wait_event(copied[i % 2])
+        x_static.copy_(stage[i % 2], non_blocking=True)
+        consumed[i % 2].record(main)
+        graph.replay()
+        houts[i].copy_(logits, non_blocking=True)
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+    images = len(full) * 64
+    dev_max, images_all = sharding.aggregate(dev_ms, images, dev)
+    e2e_max, _ = sharding.aggregate(e2e_ms, images, dev)
+    return {"workload": "config4: ResNet-50-shaped int8 network, global batch 2048 split over %d replica(s), micro-batches of 64, inputs N(0,1) from seed 1000 + rank" % world,
+            "global_batch": int(images_all), "images_per_replica": images, "micro_batches_per_replica": len(full), "shard_of_rank0": [start, count],
+            "images_per_sec": images_all / (dev_max / 1e3), "ms_per_shard": dev_max,
+            "e2e_images_per_sec": images_all / (e2e_max / 1e3), "e2e_ms_per_shard": e2e_max,
+            "h2d_bytes": int(host.numel() * 4 * world), "d2h_bytes": int(houts.numel() * 4 * world), "parity": parity}
+
+def run_cspdarknet(args, dev, rank, world, sharding, peaks):
     """Images/s of the CSPDarknet53-shaped int8 backbone (72 convolutions, LeakyReLU(0.1), Darknet shortcuts added in fp32
     after the activation, cross-stage routes joined by an int8 concatenation), batch 16 per GPU at 3x608x608, synthetic
     U(0,1) input, whole forward pass captured in a CUDA graph and replayed."""
@@ -268,16 +435,23 @@ def run_cspdarknet(args, dev, rank, world, sharding):
     spec = nets.cspdarknet_spec()
     params = nets.make_conv_params(spec, seed=0)
     net = nets.QuantCSPDarknet(spec, params, batch, dev)
-    g = torch.Generator(device=dev).manual_seed(sharding.shard_seed(0, rank))
+    g = torch.Generator(device=dev).manual_seed(0 if world == 1 else sharding.shard_seed(rank))
     x = torch.rand((batch, 3, 608, 608), device=dev, generator=g)
     t0 = time.perf_counter()
-    net.calibrate(x)
+    scales = net.calibrate(x)
     net.status()
     torch.cuda.synchronize()
     t1 = time.perf_counter()
-    net.forward(x)
+    first_out = net.forward(x)
     torch.cuda.synchronize()
     first = time.perf_counter() - t1
+    parity = None
+    if rank == 0:
+        try:
+            parity = csp_parity(net, spec, params, scales, x, first_out.clone())
+        except Exception as e:
+            parity = {"images_checked": 0, "mismatches": None, "error": repr(e)[:200]}
+    layer_times = net.layer_times(x) if rank == 0 else []
     if first > 1.0 or t1 - t0 > 60.0:   # a secondary figure must never stall the benchmark
         return {"error": "skipped: calibration took %.1f s, one eager pass %.3f s" % (t1 - t0, first)}
     stream = torch.cuda.Stream(device=dev)
@@ -306,8 +480,54 @@ def run_cspdarknet(args, dev, rank, world, sharding):
     return {"workload": "config3: CSPDarknet53-shaped int8 backbone, batch 16 per GPU at 608x608, CUDA graph replay",
             "batch_per_gpu": batch, "images_per_sec": images / (ms_max / 1e3), "ms_per_batch": ms_max,
             "int8_conv_tops": ops_batch * world / (ms_max / 1e3) / 1e12, "kernels_per_pass": 72 + 1 + 5,
-            "features_checksum": int(out.to(torch.int64).abs().sum())}
+            "parity": parity, "pass_roofline": pass_roofline(layer_times, ms_max, peaks) if layer_times else None,
+            "layers": layer_table(layer_times, peaks)}
 
+
+
+def run_elementwise(dev, peaks):
+    """Achieved HBM bandwidth of the standalone elementwise operators on tensors far larger than L2 (CUDA events around
+    five launches each, best time): the operator-visible quantize with 1 and 64 scales on 64 Mi fp32 elements, the staging
+    quantize on the two network inputs, add_bias and relu on 64 Mi elements.  Algorithmic bytes: 5 per element for
+    quantize (4 read + 1 written), 8 for add_bias / relu."""
+    import torch
+    from tennis_b200 import _lib, ops
+    lib = _lib.load()
+    out = []
+
+    def timed(fn, nbytes, name):
+        for _ in range(2):
+            fn()
+        best = None
+        for _ in range(5):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b)
+            best = ms if best is None or ms < best else best
+        gbs = nbytes / best / 1e6
+        out.append({"kernel": name, "mb": round(nbytes / 1e6, 1), "us": round(best * 1e3, 1), "gbs": round(gbs, 1),
+                    "frac_of_hbm": round(gbs / peaks["hbm_gbs"], 4)})
+
+    n = 64 * 1024 * 1024
+    x = torch.randn(n, device=dev)
+    y8 = torch.empty(n, dtype=torch.int8, device=dev)
+    yf = torch.empty(n, device=dev)
+    sp = ops._stream_ptr
+    one, many = _lib.float_array([31.0]), _lib.float_array([31.0] * 64)
+    timed(lambda: _lib.check(lib.tsb_quantize_f32_i8(x.data_ptr(), y8.data_ptr(), n, one, 1, sp())), 5 * n, "tsb_quantize_f32_i8, 1 scale, 64 Mi elements")
+    timed(lambda: _lib.check(lib.tsb_quantize_f32_i8(x.data_ptr(), y8.data_ptr(), n, many, 64, sp())), 5 * n, "tsb_quantize_f32_i8, 64 scales, 64 Mi elements")
+    bias = torch.randn(64, device=dev)
+    timed(lambda: _lib.check(lib.tsb_add_bias_f32_nchw(x.data_ptr(), yf.data_ptr(), 1024, 64, 1024, bias.data_ptr(), sp())), 8 * n, "tsb_add_bias_f32_nchw, 1024x64x1024")
+    timed(lambda: _lib.check(lib.tsb_relu_f32(x.data_ptr(), yf.data_ptr(), n, sp())), 8 * n, "tsb_relu_f32, 64 Mi elements")
+    del y8, yf
+    for (nb, hw, o, k, st, pad, label) in ((64, 224, 64, 7, 2, 3, "ResNet stem input 64x3x224x224"), (16, 608, 32, 3, 1, 1, "CSPDarknet stem input 16x3x608x608")):
+        xi = torch.randn((nb, 3, hw, hw), device=dev)
+        plan = ops.ConvPlan(xi.shape, (o, 3, k, k), (pad,) * 4, (st, st), (1, 1), 0.0, _lib.KERNEL_TCGEN05, dev)
+        sc = _lib.float_array([31.0] * nb)
+        timed(lambda: plan.quantize_input(xi, sc), 5 * xi.numel(), "tsb_conv2d_i8_quantize_input (staging quantize), " + label)
+        del plan, xi
+    return out
 
 def run_ours(args):
     import numpy as np
@@ -332,7 +552,7 @@ def run_ours(args):
     # ---- resident state: inputs, weights, plans, outputs ----
     state = []
     for layer in layers:
-        d = workloads.make_layer_data(layer, seed=sharding.shard_seed(0, rank))  # per-shard seed
+        d = workloads.make_layer_data(layer, seed=0 if world == 1 else sharding.shard_seed(rank))  # seed 0 alone, 1000 + rank per shard
         x = torch.from_numpy(d["x"]).to(dev)
         w = torch.from_numpy(d["w"]).to(dev)
         pad = (layer["pad"],) * 4
@@ -566,7 +786,7 @@ def run_ours(args):
     resnet = None
     if not args.no_resnet:
         try:
-            resnet = run_resnet50(args, dev, rank, world, sharding)
+            resnet = run_resnet50(args, dev, rank, world, sharding, peaks)
         except Exception as e:  # reported, never fatal for the primary metric
             resnet = {"error": repr(e)[:300]}
 
@@ -575,9 +795,17 @@ def run_ours(args):
         try:
             if resnet is not None:
                 torch.cuda.empty_cache()
-            csp = run_cspdarknet(args, dev, rank, world, sharding)
+            csp = run_cspdarknet(args, dev, rank, world, sharding, peaks)
         except Exception as e:
             csp = {"error": repr(e)[:300]}
+
+    elementwise = None
+    if rank == 0:
+        try:
+            torch.cuda.empty_cache()
+            elementwise = run_elementwise(dev, peaks)
+        except Exception as e:
+            elementwise = {"error": repr(e)[:300]}
 
     sampler.stop_flag.set()
     sampler.join(timeout=2)
@@ -607,15 +835,16 @@ def run_ours(args):
         hbm_view = {"achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"], "min_ms": floor_hbm_ms,
                     "peak_source": "%s copy bandwidth" % peaks["source"]}
         bound = "hbm" if floor_hbm_ms >= floor_tensor_ms else "tensor"
+        traffic, traffic_stale, traffic_note = ncu_traffic_record()
         main_view = hbm_view if bound == "hbm" else tensor_view
         roofline = {"kernel": "conv_i8_tc_kernel", "bound": bound, "achieved": main_view["achieved"], "peak": main_view["peak"],
                     "unit": main_view["unit"], "frac": main_view["frac"], "peak_source": main_view["peak_source"],
                     "why_this_bound": "minimum time of the step's conv launches: %.1f us on the HBM roofline, %.1f us on the tensor roofline; measured %.1f us"
                                       % (floor_hbm_ms * 1e3, floor_tensor_ms * 1e3, tc_ms * 1e3),
                     # dram__bytes_read.sum + dram__bytes_write.sum per conv launch, averaged over the launches of one
-                    # step, from the ncu capture summarised in profiles/conv_i8_tc_kernel_config1.md
-                    "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
-                    "traffic_unit": "bytes per launch (ncu capture of this workload; part of the fp32 output is still in L2 when the kernel ends)",
+                    # step, from the ncu capture summarised under profiles/ (null when the kernel changed since)
+                    "traffic": traffic, "traffic_stale": traffic_stale, "traffic_source": traffic_note,
+                    "traffic_unit": "bytes per launch (part of the fp32 output is still in L2 when the kernel ends)",
                     "algorithmic_bytes_per_launch": tc_bytes / n_tc, "algorithmic_ops_per_launch": tc_ops / n_tc,
                     "avg_launch_ms": tc_ms / n_tc,
                     "tensor_view": tensor_view, "hbm_view": hbm_view, "int8_gemm_probe": probe}
@@ -639,6 +868,8 @@ def run_ours(args):
             line["resnet50"] = resnet
         if csp is not None:
             line["cspdarknet53"] = csp
+        if elementwise is not None:
+            line["elementwise"] = elementwise
         line["e2e"]["h2d_bytes_per_step"] = h2d * world
         line["e2e"]["d2h_bytes_per_step"] = d2h * world
         if world == 1:
