@@ -1577,7 +1577,8 @@ bool make_view(const ConvGeom &g, const Tuning &tune, View *view, const char **w
         const int span = (g.KW - 1) * g.dw + 1;
         const int bkf = round_up(span * cpix, 64);
         if (bkf > 128) { *why = "filter row too wide to fold into one K block"; return false; }
-        const int unit = 16 / cpix;  // pixels per 16 bytes: rows of the staging are whole 16-byte units
+        const int unit = 32 / cpix;  // pixels per 32 bytes: rows of the staging are whole 32-byte units (what one thread of
+                                     // the staging quantize writes)
         const int need = std::max(g.W + g.pad_l, (g.OW - 1) * g.sw + bkf / cpix);
         v.fold = 1;
         v.cpix = cpix;

@@ -2,6 +2,7 @@
 // coalesced loads/stores, grid sized as a multiple of the SM count, no tensor cores.
 #include "common.cuh"
 
+#include <algorithm>
 #include <atomic>
 #include <cmath>
 #include <mutex>
@@ -265,12 +266,94 @@ quantize_stage_kernel(const float *__restrict__ x, int8_t *__restrict__ y, Stage
     }
 }
 
+// Folded staging of inputs with at most four channels (the RGB stems of the benchmark networks): a thread produces 32
+// consecutive output bytes -- four staged pixels of 8 bytes, or two of 16 -- from exactly the CC x pixels values that are
+// live, so no load is wasted on padding channels; loads of a warp cover consecutive pixels of each channel plane, stores are
+// two 16-byte vectors per thread, contiguous over the warp.  One scale per tensor or per sample (the host checks).
+template <int CC, int CPIX>
+__global__ void __launch_bounds__(kThreads)
+quantize_stage_small_kernel(const float *__restrict__ x, int8_t *__restrict__ y, StageDesc d, uint32_t units, QuantRule rule,
+                            ScaleArg scales) {
+    pdl_sync();
+    constexpr int PPT = 32 / CPIX;                       // pixels per thread
+    const uint32_t rne_limit = (uint32_t)rule.rne_limit;
+    const uint32_t HW = (uint32_t)(d.H * d.W);
+    const uint32_t upr = (uint32_t)(d.Wp * CPIX) / 32u;  // 32-byte units per staged row (Wp * CPIX is a multiple of 32 here)
+    (void)units;
+    // block: 64 units x 4 rows; grid: x over the units of a row, y over (a stride of) the rows -- no division per unit
+    for (uint32_t row = blockIdx.y * 4 + threadIdx.y; row < (uint32_t)(d.N * d.H); row += gridDim.y * 4)
+    for (uint32_t ur = blockIdx.x * 64 + threadIdx.x; ur < upr; ur += gridDim.x * 64) {
+        const uint32_t t = row * upr + ur;
+        const uint32_t n = row / (uint32_t)d.H, h = row - n * (uint32_t)d.H;
+        const int w0 = (int)(ur * PPT) - d.pad_l;
+        const uint32_t base = (n * (uint32_t)CC * (uint32_t)d.H + h) * (uint32_t)d.W;
+        float val[PPT][CC];
+#pragma unroll
+        for (int p = 0; p < PPT; ++p) {
+            const int w = w0 + p;
+            const bool in = (unsigned)w < (unsigned)d.W;
+#pragma unroll
+            for (int c = 0; c < CC; ++c) val[p][c] = in ? __ldg(x + base + (uint32_t)c * HW + (uint32_t)w) : 0.0f;
+        }
+        const float s = scales.get(rule.nscales == 1 ? 0 : (int)n);
+        uint32_t word[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+        for (int p = 0; p < PPT; ++p) {
+            const int w = w0 + p;
+            if ((unsigned)w < (unsigned)d.W) {
+#pragma unroll
+                for (int c = 0; c < CC; ++c) {
+                    const uint32_t idx = base + (uint32_t)c * HW + (uint32_t)w;
+                    const int q = q8(val[p][c], s, idx < rne_limit);
+                    word[(p * CPIX + c) >> 2] |= (uint32_t)(q & 0xff) << (8 * (c & 3));
+                }
+            }
+        }
+        int4 *dst = reinterpret_cast<int4 *>(y + (size_t)t * 32);
+        dst[0] = make_int4(word[0], word[1], word[2], word[3]);
+        dst[1] = make_int4(word[4], word[5], word[6], word[7]);
+    }
+}
+
 __global__ void __launch_bounds__(kThreads)
 add_bias_nchw_kernel(const float *__restrict__ x, float *__restrict__ y, int C, int HW, int64_t count,
                      const float *__restrict__ bias) {
     for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < count; i += (int64_t)gridDim.x * kThreads) {
         const int c = (int)((i / HW) % C);
         y[i] = __fadd_rn(x[i], bias[c]);
+    }
+}
+
+// The same with 16-byte accesses: a block works inside one (sample, channel) plane, so the bias is a per-block scalar
+// and no index arithmetic is left in the loop.  planes = N*C, vec = HW/4 float4 per plane, chunks = blocks per plane.
+__global__ void __launch_bounds__(kThreads)
+add_bias_nchw_vec4_kernel(const float4 *__restrict__ x, float4 *__restrict__ y, int C, int vec, int chunks, int planes,
+                          const float *__restrict__ bias) {
+    for (int blk = blockIdx.x; blk < planes * chunks; blk += gridDim.x) {
+        const int plane = blk / chunks, chunk = blk - plane * chunks;
+        const float b = bias[plane % C];
+        const float4 *src = x + (size_t)plane * vec;
+        float4 *dst = y + (size_t)plane * vec;
+        for (int i = chunk * kThreads + threadIdx.x; i < vec; i += chunks * kThreads) {
+            float4 v = __ldcs(src + i);
+            v.x = __fadd_rn(v.x, b); v.y = __fadd_rn(v.y, b); v.z = __fadd_rn(v.z, b); v.w = __fadd_rn(v.w, b);
+            __stcs(dst + i, v);
+        }
+    }
+}
+
+// 16-byte accesses for the activations as well (count a multiple of 4, both tensors 16-byte aligned)
+__global__ void __launch_bounds__(kThreads)
+activation_vec4_kernel(const float4 *__restrict__ x, float4 *__restrict__ y, int64_t vec, int activation, float leaky) {
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < vec; i += (int64_t)gridDim.x * kThreads) {
+        float4 v = __ldcs(x + i);
+        float *f = reinterpret_cast<float *>(&v);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (activation == TSB_ACT_RELU) f[k] = f[k] > 0.0f ? f[k] : 0.0f;
+            else if (activation == TSB_ACT_LEAKY_RELU) f[k] = f[k] > 0.0f ? f[k] : __fmul_rn(f[k], leaky);
+        }
+        __stcs(y + i, v);
     }
 }
 
@@ -390,6 +473,23 @@ int quantize_stage(const float *x, int8_t *y, int n, int c, int h, int w, int fo
     const int64_t units = folded ? (int64_t)n * h * (wp * cpix / 16)
                                  : ceil_div64((int64_t)n * h * w, 32) * 32 * (d.Cp / 16);
     if (units > (int64_t)UINT32_MAX) return fail(TSB_ERR_UNSUPPORTED, "quantize_stage: tensor too large");
+    // few input channels, one scale per tensor or per sample, rows made of whole 32-byte units: the lean kernel
+    const bool per_sample = rule.nscales > 1 && rule.nscales == n && rule.group_len == (int64_t)c * h * w;
+    if (folded && c <= 4 && (wp * cpix) % 32 == 0 && (rule.nscales == 1 || per_sample)) {
+        const uint32_t units32 = (uint32_t)((int64_t)n * h * (wp * cpix / 32));
+        cudaError_t e = cudaSuccess;
+        const dim3 small_grid((unsigned)ceil_div(wp * cpix / 32, 64), (unsigned)std::min(ceil_div(n * h, 4), 65535));
+#define TSB_STAGE_SMALL(CC_, CPIX_)                                                                                       \
+        if (c == CC_ && cpix == CPIX_)                                                                                    \
+            e = launch_pdl(quantize_stage_small_kernel<CC_, CPIX_>, small_grid, dim3(64, 4), 0, stream, x, y, d, units32, rule, arg)
+        TSB_STAGE_SMALL(1, 8); TSB_STAGE_SMALL(2, 8); TSB_STAGE_SMALL(3, 8); TSB_STAGE_SMALL(4, 8);
+        TSB_STAGE_SMALL(1, 16); TSB_STAGE_SMALL(2, 16); TSB_STAGE_SMALL(3, 16); TSB_STAGE_SMALL(4, 16);
+#undef TSB_STAGE_SMALL
+        TSB_CUDA(e);
+        TSB_LAUNCHED("quantize_stage_small_kernel");
+        if (tmp) TSB_CUDA(cudaFreeAsync(tmp, stream));
+        return TSB_OK;
+    }
     TSB_CUDA(launch_pdl(quantize_stage_kernel, dim3(grid_for(units)), dim3(kThreads), 0, stream, x, y, d, (uint32_t)units, rule, arg));
     TSB_LAUNCHED("quantize_stage_kernel");
     if (tmp) TSB_CUDA(cudaFreeAsync(tmp, stream));
@@ -427,6 +527,17 @@ int add_bias_f32_nchw(const float *x, float *y, int n, int c, int hw, const floa
     if (!x || !y || !bias) return fail(TSB_ERR_INVALID_ARGUMENT, "add_bias: null pointer");
     if (n < 1 || c < 1 || hw < 1) return fail(TSB_ERR_INVALID_ARGUMENT, "add_bias: bad shape");
     const int64_t count = (int64_t)n * c * hw;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) % 16) == 0;
+    if (aligned && hw % 4 == 0 && (int64_t)n * c <= INT32_MAX / 64) {
+        const int vec = hw / 4, planes = n * c;
+        // enough blocks per plane to fill the GPU even when there are few planes, at most one per 256 float4
+        const int chunks = std::max(1, std::min(ceil_div(vec, kThreads), ceil_div(sm_count() * 8, planes)));
+        const int blocks = (int)std::min<int64_t>((int64_t)planes * chunks, (int64_t)sm_count() * 16);
+        add_bias_nchw_vec4_kernel<<<blocks, kThreads, 0, stream>>>(reinterpret_cast<const float4 *>(x), reinterpret_cast<float4 *>(y), c, vec,
+                                                                    chunks, planes, bias);
+        TSB_LAUNCHED("add_bias_nchw_vec4_kernel");
+        return TSB_OK;
+    }
     add_bias_nchw_kernel<<<grid_for(count), kThreads, 0, stream>>>(x, y, c, hw, count, bias);
     TSB_LAUNCHED("add_bias_nchw_kernel");
     return TSB_OK;
@@ -436,6 +547,12 @@ int activation_f32(const float *x, float *y, int64_t count, int activation, floa
     if (!x || !y) return fail(TSB_ERR_INVALID_ARGUMENT, "activation: null pointer");
     if (count < 0) return fail(TSB_ERR_INVALID_ARGUMENT, "activation: negative count");
     if (count == 0) return TSB_OK;
+    if (count % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) % 16) == 0) {
+        activation_vec4_kernel<<<grid_for(count / 4), kThreads, 0, stream>>>(reinterpret_cast<const float4 *>(x), reinterpret_cast<float4 *>(y),
+                                                                             count / 4, activation, leaky);
+        TSB_LAUNCHED("activation_vec4_kernel");
+        return TSB_OK;
+    }
     activation_kernel<<<grid_for(count), kThreads, 0, stream>>>(x, y, count, activation, leaky);
     TSB_LAUNCHED("activation_kernel");
     return TSB_OK;
