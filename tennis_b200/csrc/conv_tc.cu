@@ -314,6 +314,31 @@ __device__ __forceinline__ void store_f32_nchw_t(const int (&v)[W], const float 
     }
 }
 
+// The same with an fp32 NCHW residual (operator "add" between add_bias and the activation, or after the activation): the
+// residual is read where the result is written, so a warp's 32 pixels make one coalesced line per channel either way.
+template <int ACT, bool HAS_BIAS, int W, bool AFTER>
+__device__ __forceinline__ void store_f32_nchw_res_t(const int (&v)[W], const float *__restrict__ dq,
+                                                     const float *__restrict__ bias, float leaky, const float *__restrict__ res,
+                                                     float *__restrict__ dst, uint32_t stride) {
+#pragma unroll
+    for (int j8 = 0; j8 < W / 8; ++j8) {
+        float r[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) r[k] = __ldg(res + (uint32_t)(8 * j8 + k) * stride);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int j = 8 * j8 + k;
+            float t = __fmul_rn(__int2float_rn(v[j]), dq[j]);
+            if (HAS_BIAS) t = __fadd_rn(t, bias[j]);
+            if (!AFTER) t = __fadd_rn(t, r[k]);
+            if (ACT == TSB_ACT_RELU) t = fmaxf(t, 0.0f);
+            if (ACT == TSB_ACT_LEAKY_RELU) t = t > 0.0f ? t : __fmul_rn(t, leaky);
+            if (AFTER) t = __fadd_rn(t, r[k]);
+            dst[(uint32_t)j * stride] = t;
+        }
+    }
+}
+
 // Requantized int8 output.  Returns false when a scaled value was NaN or beyond the int32 range -- those quantize to
 // -128 in the reference (x86 integer-indefinite), which the saturating fast path does not reproduce; the caller
 // then redoes the chunk element by element.
@@ -1352,8 +1377,10 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                         tmem_ld_wait();
                         if (kp.epi_mode == kEpiF32Nchw) {
                             if (live) {
-                                float *dst = epi.out_f32 + ((size_t)(img * epi.O + o_base + col0) * (size_t)epi.P + (size_t)p);
-                                TSB_EPI_DISPATCH_W(, store_f32_nchw_t, CW, v, t_dq + col0, t_bias + col0, epi.leaky, dst, (uint32_t)epi.P);
+                                const size_t off = (size_t)(img * epi.O + o_base + col0) * (size_t)epi.P + (size_t)p;
+                                float *dst = epi.out_f32 + off;
+                                if (epi.residual) TSB_EPI_DISPATCH_RES_W(, store_f32_nchw_res_t, CW, v, t_dq + col0, t_bias + col0, epi.leaky, epi.residual + off, dst, (uint32_t)epi.P);
+                                else TSB_EPI_DISPATCH_W(, store_f32_nchw_t, CW, v, t_dq + col0, t_bias + col0, epi.leaky, dst, (uint32_t)epi.P);
                             }
                             done = true;
                         } else if (kp.epi_mode == kEpiI8Nhwc) {
@@ -1953,6 +1980,9 @@ int launch_conv_tc(const View &v, const Config &cfg, const CUtensorMap &map_a, c
     const bool plain = !epi.out_acc && !epi.residual;
     kp.epi_mode = kEpiGeneric;
     if (plain && epi.out_f32 && !epi.f32_nhwc && !epi.out_i8) kp.epi_mode = kEpiF32Nchw;
+    // ... and with an fp32 NCHW residual (a shortcut folded into the convolution by the graph rewrite), where a thread owns a pixel
+    if (!cfg.swap && !epi.out_acc && epi.residual && epi.out_f32 && !epi.f32_nhwc && !epi.out_i8 && (const void *)epi.residual != (const void *)epi.out_f32)
+        kp.epi_mode = kEpiF32Nchw;
     const bool i8_fast = !epi.out_i8 || (epi.i8_nhwc && epi.rne_limit == 0 && (epi.nscales == 1 || kp.per_sample_scale));
     if (plain && epi.out_i8 && !epi.out_f32 && i8_fast) kp.epi_mode = kEpiI8Nhwc;
     // pixel-major fp32 tensors (block outputs and residuals of a network): 16-byte accesses need O % 4 == 0

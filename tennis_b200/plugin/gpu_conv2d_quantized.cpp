@@ -14,8 +14,10 @@
 #include <backend/common_function.h>
 #include <compiler/option/zipper_option.h>
 #include <module/menu.h>
+#include <runtime/inferer.h>
 
 #include <atomic>
+#include <memory>
 
 #include <cstring>
 
@@ -70,16 +72,33 @@ namespace ts {
                              TSB_ACT_NONE, 0.0f);
             }
 
+            // What the compile-time rewrite can ask of one launch beyond bias and activation.
+            struct Extras {
+                const std::vector<float> *quantize_scales = nullptr;   // x is fp32 NCHW: quantize it into the staged layout first
+                bool x_nhwc = false;                                   // x is int8 NHWC_PAD [N,H,W,Cp], written by another fused node
+                const std::vector<float> *out_scales = nullptr;        // out is int8 NHWC_PAD [N,OH,OW,Cp]: the consumer's quantize
+                const float *residual = nullptr;                       // fp32 NCHW shortcut (operator "add"), device pointer
+                bool residual_after = false;                           // added after the activation instead of before it
+            };
+
             // conv2d_quantized -> add_bias -> relu | leaky_relu in one launch (bias: device pointer or null)
             void conv2d_fused(const Tensor &x, const Padding2D &padding, float padding_value, const Tensor &w,
                               const Stride2D &stride, const Dilation2D &dilation, Conv2DFormat format,
                               std::vector<float> dequantize_scales, Tensor &out, Stack &stack, const float *bias,
-                              int activation, float leaky, const std::vector<float> *quantize_scales = nullptr) {
+                              int activation, float leaky, const std::vector<float> *quantize_scales = nullptr,
+                              const Extras *extras = nullptr) {
                 (void) stack;
+                Extras ex;
+                if (extras) ex = *extras;
+                if (quantize_scales) ex.quantize_scales = quantize_scales;
+                quantize_scales = ex.quantize_scales;
                 if (format != FORMAT_NCHW) {
                     TS_LOG_ERROR << "Conv2D_quantized only support NCHW" << eject;
                 }
                 // quantize_scales given: x is the fp32 tensor the folded quantize operator would have read
+                if (ex.x_nhwc && (x.dtype() != INT8 || x.size(3) != tsb_padded_channels(w.size(1)))) {
+                    TS_LOG_ERROR << "b200_conv2d_quantized_fused: the int8 NHWC_PAD input does not match the weights" << eject;
+                }
                 if (quantize_scales == nullptr && x.dtype() != INT8) {
                     TS_LOG_ERROR << "Conv2D_quantized not support this data type: " << type_str(x.dtype()) << eject;
                 }
@@ -92,7 +111,8 @@ namespace ts {
 
                 tsb_conv_desc desc;
                 std::memset(&desc, 0, sizeof(desc));
-                desc.n = x.size(0); desc.c = x.size(1); desc.h = x.size(2); desc.w = x.size(3);
+                if (ex.x_nhwc) { desc.n = x.size(0); desc.c = w.size(1); desc.h = x.size(1); desc.w = x.size(2); }
+                else { desc.n = x.size(0); desc.c = x.size(1); desc.h = x.size(2); desc.w = x.size(3); }
                 desc.o = w.size(0); desc.kh = w.size(2); desc.kw = w.size(3);
                 desc.pad_top = padding.top; desc.pad_bottom = padding.bottom;
                 desc.pad_left = padding.left; desc.pad_right = padding.right;
@@ -133,8 +153,24 @@ namespace ts {
                 epilogue.bias = bias;
                 epilogue.activation = activation;
                 epilogue.leaky_scale = leaky;
-                epilogue.out_f32 = out.data<float>();
-                epilogue.out_f32_layout = TSB_LAYOUT_NCHW;
+                if (ex.out_scales != nullptr) {
+                    // int8 NHWC_PAD for the next fused convolution: the requantize of the epilogue with that layer's scales
+                    epilogue.out_i8 = out.data<int8_t>();
+                    epilogue.out_i8_layout = TSB_LAYOUT_NHWC_PAD;
+                    epilogue.requant_scales_host = ex.out_scales->data();
+                    epilogue.n_requant_scales = int(ex.out_scales->size());
+                } else {
+                    epilogue.out_f32 = out.data<float>();
+                    epilogue.out_f32_layout = TSB_LAYOUT_NCHW;
+                }
+                epilogue.residual = ex.residual;
+                epilogue.residual_after_activation = ex.residual_after ? 1 : 0;
+                if (ex.x_nhwc) {
+                    check(tsb_conv2d_i8_run(m_plan, x.data<int8_t>(), TSB_LAYOUT_NHWC_PAD, &epilogue, m_workspace.data(),
+                                            m_workspace_bytes, stream), op);
+                    note_run(stream, op);
+                    return;
+                }
                 if (quantize_scales != nullptr) {
                     // fp32 NCHW -> the plan's own staged int8 layout, then the convolution reads it in place
                     check(tsb_conv2d_i8_quantize_input(m_plan, x.data<float>(), quantize_scales->data(), int(quantize_scales->size()),
@@ -177,6 +213,9 @@ namespace ts {
                 field(fused_activation(), OPTIONAL, tensor::from<int32_t>(TSB_ACT_NONE));
                 field(fused_leaky(), OPTIONAL, tensor::from<float>(0.0f));
                 field(fused_quantize_scale(), OPTIONAL);
+                field(fused_in_nhwc(), OPTIONAL, tensor::from<int32_t>(0));
+                field(fused_out_scale(), OPTIONAL);
+                field(fused_residual(), OPTIONAL, tensor::from<int32_t>(0));
             }
 
             static const std::string &op_name() { static const std::string n = "b200_conv2d_quantized_fused"; return n; }
@@ -186,6 +225,15 @@ namespace ts {
             // present when the quantize operator in front of the convolution was folded in: the operator's first input
             // is then the fp32 tensor, and this is that operator's quantize_scale attribute (one scale per sample)
             static const std::string &fused_quantize_scale() { static const std::string n = "b200_quantize_scale"; return n; }
+            // 1: the first input is the int8 NHWC_PAD tensor [N,H,W,Cp] another fused node wrote (the quantize between the
+            // two layers was folded into that node's epilogue)
+            static const std::string &fused_in_nhwc() { static const std::string n = "b200_input_nhwc"; return n; }
+            // present: the output is int8 NHWC_PAD [N,OH,OW,Cp], requantized with these scales (the quantize_scale attribute of
+            // the quantize operator that followed this layer and fed the next convolution alone)
+            static const std::string &fused_out_scale() { static const std::string n = "b200_output_quantize_scale"; return n; }
+            // 1: a third input, fp32 NCHW of the output's shape, is added between add_bias and the activation (a ResNet
+            // shortcut); 2: it is added after the activation (a Darknet shortcut)
+            static const std::string &fused_residual() { static const std::string n = "b200_residual"; return n; }
 
             void init() override {
                 supper::init();
@@ -194,8 +242,13 @@ namespace ts {
                 m_has_bias = has(fused_bias());
                 if (m_has_bias) m_bias_host = tensor::cast(FLOAT32, get(fused_bias()));
                 m_folded_quantize = has(fused_quantize_scale());
-                if (m_folded_quantize) {
-                    m_quantize_scales = tensor::array::to_float(get(fused_quantize_scale()));
+                m_in_nhwc = tensor::to_int(get(fused_in_nhwc())) != 0;
+                m_residual = tensor::to_int(get(fused_residual()));
+                m_has_out_scale = has(fused_out_scale());
+                if (m_has_out_scale) m_out_scales = tensor::array::to_float(get(fused_out_scale()));
+                m_extended = m_folded_quantize || m_in_nhwc || m_residual != 0 || m_has_out_scale;
+                if (m_extended) {
+                    if (m_folded_quantize) m_quantize_scales = tensor::array::to_float(get(fused_quantize_scale()));
                     // the shell keeps its parsed attributes private; the folded path needs them again (the shell's init()
                     // above has already validated them: src/backend/base/base_conv2d_quantized.cpp:36-117)
                     if (tensor::to_string(get(name::format)) != name::NCHW) {
@@ -215,46 +268,135 @@ namespace ts {
             // With the quantize folded in, the first input is fp32: the shell's infer/run (which insist on int8) are
             // replaced by the same steps on the fp32 tensor.
             int infer(Stack &stack, std::vector<Tensor::Prototype> &output) override {
-                if (!m_folded_quantize) return supper::infer(stack, output);
-                TS_AUTO_CHECK(stack.size() == 2);
+                if (!m_extended) return supper::infer(stack, output);
+                TS_AUTO_CHECK(stack.size() == (m_residual ? 3 : 2));
                 auto x = stack[0];
                 auto w = stack[1];
                 TS_AUTO_CHECK(x.dims() == 4);
                 TS_AUTO_CHECK(w.dims() == 4);
-                TS_AUTO_CHECK(x.dtype() == FLOAT32);
                 TS_AUTO_CHECK(w.dtype() == INT8);
-                TS_AUTO_CHECK(w.size(1) == x.size(1));
-                TS_AUTO_CHECK(int(m_quantize_scales.size()) == x.size(0));      // base_quantize.cpp:26
+                int height, width;
+                if (m_in_nhwc) {
+                    TS_AUTO_CHECK(x.dtype() == INT8);
+                    TS_AUTO_CHECK(x.size(3) == tsb_padded_channels(w.size(1)));
+                    height = x.size(1); width = x.size(2);
+                } else {
+                    TS_AUTO_CHECK(x.dtype() == (m_folded_quantize ? FLOAT32 : INT8));
+                    TS_AUTO_CHECK(w.size(1) == x.size(1));
+                    height = x.size(2); width = x.size(3);
+                }
+                if (m_folded_quantize) TS_AUTO_CHECK(int(m_quantize_scales.size()) == x.size(0));      // base_quantize.cpp:26
+                if (m_has_out_scale) TS_AUTO_CHECK(int(m_out_scales.size()) == x.size(0));
                 TS_AUTO_CHECK(int(m_dequantize_scales.size()) == w.size(0));
-                Size2D y = conv2d_forward(Size2D(x.size(2), x.size(3)), m_padding, Size2D(w.size(2), w.size(3)), m_stride, m_dilation);
+                Size2D y = conv2d_forward(Size2D(height, width), m_padding, Size2D(w.size(2), w.size(3)), m_stride, m_dilation);
+                Shape y_shape = {x.size(0), w.size(0), y.height, y.width};
+                DTYPE y_dtype = FLOAT32;
+                if (m_residual && !shortcut_fits(stack[2], y_shape)) {
+                    // operator "add" broadcasts and up-casts (src/backend/base/element_wise_reduce.cpp:21-138): such a
+                    // shortcut goes through the device's own add operator after the convolution, see run()
+                    std::vector<Tensor::Prototype> sum;
+                    stack.push(Tensor::Prototype(FLOAT32, y_shape), MemoryDevice(CPU));
+                    stack.push(stack[2]);
+                    InferOperator(reference_add(), stack, 2, sum);      // takes its two arguments off the stack
+                    TS_AUTO_CHECK(sum.size() == 1);
+                    y_shape = sum[0].sizes();
+                    y_dtype = sum[0].dtype();
+                }
                 output.resize(1);
-                output[0] = Tensor::Prototype(FLOAT32, {x.size(0), w.size(0), y.height, y.width});
+                if (m_has_out_scale) {
+                    TS_AUTO_CHECK(y_shape.size() == 4 && y_dtype == FLOAT32);
+                    output[0] = Tensor::Prototype(INT8, {y_shape[0], y_shape[2], y_shape[3], tsb_padded_channels(y_shape[1])});
+                } else {
+                    output[0] = Tensor::Prototype(y_dtype, y_shape);
+                }
                 return 1;
             }
 
+            // the shortcut can go into the convolution's epilogue: fp32 and of the convolution's own output shape
+            static bool shortcut_fits(const Tensor &r, const Shape &y_shape) {
+                return r.dtype() == FLOAT32 && r.has_shape(y_shape);
+            }
+
             int run(Stack &stack) override {
-                if (!m_folded_quantize) return supper::run(stack);
+                if (!m_extended) return supper::run(stack);
                 std::vector<Tensor::Prototype> protos;
                 infer(stack, protos);
                 auto memory_device = running_memory_device();
                 Tensor x = stack[0].view(memory_device);
                 Tensor w = stack[1].view(memory_device);
+                b200::Conv2DQuantizedCore::Extras extras;
+                extras.quantize_scales = m_folded_quantize ? &m_quantize_scales : nullptr;
+                extras.x_nhwc = m_in_nhwc;
+                const int height = m_in_nhwc ? x.size(1) : x.size(2), width = m_in_nhwc ? x.size(2) : x.size(3);
+                Size2D y = conv2d_forward(Size2D(height, width), m_padding, Size2D(w.size(2), w.size(3)), m_stride, m_dilation);
+                const Shape y_shape = {x.size(0), w.size(0), y.height, y.width};
+                if (m_residual && !shortcut_fits(stack[2], y_shape)) return run_with_reference_add(stack, x, w, y_shape, protos[0], extras);
+                Tensor shortcut;
+                if (m_residual) shortcut = stack[2].view(memory_device);
                 Tensor out = *stack.push(protos[0], memory_device);
+                extras.out_scales = m_has_out_scale ? &m_out_scales : nullptr;
+                extras.residual = m_residual ? shortcut.data<float>() : nullptr;
+                extras.residual_after = m_residual == 2;
                 run_core(x, m_padding, m_padding_value, w, m_stride, m_dilation, FORMAT_NCHW, m_dequantize_scales, out, stack,
-                         &m_quantize_scales);
+                         &extras, m_activation);
                 return 1;
+            }
+
+            // A shortcut the epilogue cannot take (another shape: "add" broadcasts; another type: it up-casts).  The graph
+            // was rewritten before any shape was known (the compiler strips "#shape" from the module's inputs), so the
+            // decision falls here, per run: the convolution with its bias (and the activation, where the shortcut comes
+            // after it) runs fused, then the gpu device's own add -- and activation -- operators finish the layer.
+            int run_with_reference_add(Stack &stack, const Tensor &x, const Tensor &w, const Shape &y_shape,
+                                       const Tensor::Prototype &result, b200::Conv2DQuantizedCore::Extras extras) {
+                auto memory_device = running_memory_device();
+                Tensor conv_out = *stack.push(Tensor::Prototype(FLOAT32, y_shape), memory_device);
+                run_core(x, m_padding, m_padding_value, w, m_stride, m_dilation, FORMAT_NCHW, m_dequantize_scales, conv_out, stack,
+                         &extras, m_residual == 2 ? m_activation : TSB_ACT_NONE);
+                stack.push(stack[2]);
+                RunOperator(reference_add(), stack, 2);
+                if (m_residual == 1 && m_activation != TSB_ACT_NONE) RunOperator(reference_activation(), stack, 1);
+                reference_add_runs().fetch_add(1);
+                if (!m_has_out_scale) return 1;
+                Tensor sum = stack[-1].view(memory_device);
+                Tensor out = *stack.push(result, memory_device);
+                check(tsb_quantize_f32_nchw_to_nhwc(sum.data<float>(), out.data<int8_t>(), sum.size(0), sum.size(1), sum.size(2),
+                                                    sum.size(3), m_out_scales.data(), int(m_out_scales.size()), stream_on_context()),
+                      op_name());
+                return 1;
+            }
+
+            Operator::shared reference_add() {
+                if (!m_add) {
+                    m_add = OperatorCreator::Create(GPU, name::layer::add(), false);
+                    m_add->set(Bubble::RetentionParam::op, tensor::from(name::layer::add()));
+                    m_add->set(Bubble::RetentionParam::name, tensor::from(name() + ".add"));
+                    m_add->init();
+                }
+                return m_add;
+            }
+
+            Operator::shared reference_activation() {
+                if (!m_act) {
+                    const std::string act = m_activation == TSB_ACT_RELU ? name::layer::relu() : std::string("leaky_relu");
+                    m_act = OperatorCreator::Create(GPU, act, false);
+                    m_act->set(Bubble::RetentionParam::op, tensor::from(act));
+                    m_act->set(Bubble::RetentionParam::name, tensor::from(name() + ".activation"));
+                    if (m_activation == TSB_ACT_LEAKY_RELU) m_act->set(name::scale, tensor::from<float>(m_leaky));
+                    m_act->init();
+                }
+                return m_act;
             }
 
             void conv2d(const Tensor &x, const Padding2D &padding, float padding_value, const Tensor &w,
                         const Stride2D &stride, const Dilation2D &dilation, Conv2DFormat format,
                         std::vector<float> dequantize_scales, Tensor &out, Stack &stack) override {
-                run_core(x, padding, padding_value, w, stride, dilation, format, dequantize_scales, out, stack, nullptr);
+                run_core(x, padding, padding_value, w, stride, dilation, format, dequantize_scales, out, stack, nullptr, m_activation);
             }
 
             void run_core(const Tensor &x, const Padding2D &padding, float padding_value, const Tensor &w,
                           const Stride2D &stride, const Dilation2D &dilation, Conv2DFormat format,
                           const std::vector<float> &dequantize_scales, Tensor &out, Stack &stack,
-                          const std::vector<float> *quantize_scales) {
+                          const b200::Conv2DQuantizedCore::Extras *extras, int activation) {
                 const float *bias = nullptr;
                 if (m_has_bias) {
                     if (m_bias_host.count() != w.size(0)) {
@@ -265,13 +407,18 @@ namespace ts {
                     bias = m_bias_device.data<float>();
                 }
                 m_core.conv2d_fused(x, padding, padding_value, w, stride, dilation, format, dequantize_scales, out, stack, bias,
-                                    m_activation, m_leaky, quantize_scales);
+                                    activation, m_leaky, nullptr, extras);
                 fused_runs().fetch_add(1);
-                if (quantize_scales) folded_quantize_runs().fetch_add(1);
+                if (extras && extras->quantize_scales) folded_quantize_runs().fetch_add(1);
+                if (extras && extras->x_nhwc) int8_handover_runs().fetch_add(1);
+                if (extras && extras->residual) residual_runs().fetch_add(1);
             }
 
             static std::atomic<long> &fused_runs() { static std::atomic<long> n(0); return n; }
             static std::atomic<long> &folded_quantize_runs() { static std::atomic<long> n(0); return n; }
+            static std::atomic<long> &int8_handover_runs() { static std::atomic<long> n(0); return n; }
+            static std::atomic<long> &residual_runs() { static std::atomic<long> n(0); return n; }
+            static std::atomic<long> &reference_add_runs() { static std::atomic<long> n(0); return n; }
 
         private:
             b200::Conv2DQuantizedCore m_core;   // the class above, not the base interface of the same name
@@ -279,71 +426,200 @@ namespace ts {
             float m_leaky = 0.0f;
             bool m_has_bias = false;
             Tensor m_bias_host, m_bias_device;
-            bool m_folded_quantize = false;
-            std::vector<float> m_quantize_scales, m_dequantize_scales;
+            Operator::shared m_add, m_act;      // the device's own operators, for a shortcut the epilogue cannot take
+            bool m_folded_quantize = false, m_in_nhwc = false, m_has_out_scale = false, m_extended = false;
+            int m_residual = 0;
+            std::vector<float> m_quantize_scales, m_dequantize_scales, m_out_scales;
             Padding2D m_padding;
             Stride2D m_stride;
             Dilation2D m_dilation;
             float m_padding_value = 0.0f;
         };
 
-        // Graph rewrite at compile time (src/compiler/zipper.cpp:20-62 visits every node of the module once):
-        //   relu | leaky_relu ( add_bias ( conv2d_quantized(x, w), <const bias> ) )  ->  b200_conv2d_quantized_fused(x, w)
-        //   ... and with x = quantize(x32) read by nothing else                       ->  b200_conv2d_quantized_fused(x32, w)
-        // on the gpu device, when the bias is a constant over the channel dimension of an NCHW tensor and neither
-        // intermediate result has another consumer.  The fused node keeps the name of the activation node, so the
-        // module's outputs are found as before.
+        // Graph rewrite at compile time.  src/compiler/zipper.cpp:20-62 walks the module from its outputs towards its
+        // inputs, offers every node to the registered options once, and goes on with the inputs of what an option returned.
+        // On the gpu device this option turns a quantized layer -- as a TenniS graph spells it -- into ONE node:
+        //
+        //   relu | leaky_relu ( add_bias ( conv2d_quantized(x, w), <const bias> ) )                      plain layer
+        //   relu | leaky_relu ( add ( add_bias(conv2d_quantized(x, w), <const bias>), shortcut ) )       ResNet block tail
+        //   add ( relu | leaky_relu ( add_bias(conv2d_quantized(x, w), <const bias>) ), shortcut )       Darknet shortcut
+        //                                                            ->  b200_conv2d_quantized_fused(x, w [, shortcut])
+        //
+        // with NCHW tensors, a constant per-channel bias, and no other reader of the intermediate results.  No shape is
+        // known here (the compiler strips "#shape" from the module's inputs before this pass), so whether a shortcut has
+        // the layer's own output shape -- "add" broadcasts -- is settled by the fused operator at run time: it folds the
+        // shortcut into its epilogue when the shapes agree and finishes the layer with the device's add operator when not.
+        // Around the fused node the quantize operators go as well:
+        //   * x = quantize(x32), read by this convolution alone: the node takes x32 and quantizes it straight into the layout
+        //     its kernel reads;
+        //   * x = quantize(y) where y is the top of another such layer that nothing else reads: that layer's node writes int8
+        //     in the convolution path's own layout, requantized in its epilogue with this quantize's scales, and this node
+        //     reads it as it is -- int8 travels between the layers and no fp32 tensor is written or read in between.
+        // Both ends of a hand-over are decided by the same test on the unchanged graph, whichever node is visited first.
+        // The fused node keeps the name of the node it replaces, so the module's outputs are found as before.
         class ConvBiasActivationZipper : public ZipperOption {
         public:
-            bool zip(const ComputingDevice &device, Node node, Node &zipped_node) const override {
-                if (device.type() != GPU) return false;
-                const Bubble &act = node.bubble();
-                int activation;
+            struct Chain {           // (ts::Node has no empty state: the nodes are held by pointer until they are known)
+                std::shared_ptr<Node> conv, bias;         // the conv2d_quantized node and the constant of its add_bias
+                int activation = TSB_ACT_NONE;
                 float leaky = 0.0f;
-                if (act.op() == name::layer::relu()) activation = TSB_ACT_RELU;
-                else if (act.op() == "leaky_relu") {   // src/backend/base/base_leaky_relu.cpp registers it under this name
+                int residual = 0;        // 0 none, 1 added before the activation, 2 after it
+                std::shared_ptr<Node> shortcut;
+            };
+
+            // The readers of a node in the graph as the module gave it: fused nodes this option has already created (the
+            // walk goes from the outputs inwards, so a consumer is rewritten before its producer) read the same tensor in
+            // place of the quantize -> convolution pair they replace, and are not counted a second time.
+            static std::vector<Node> users(const Node &n) {
+                std::vector<Node> out;
+                for (auto &u : n.outputs())
+                    if (u.bubble().op() != Conv2DQuantizedFused::op_name()) out.push_back(u);
+                return out;
+            }
+
+            static bool is_activation(const Node &n, int &activation, float &leaky) {
+                const Bubble &b = n.bubble();
+                leaky = 0.0f;
+                if (b.op() == name::layer::relu()) { activation = TSB_ACT_RELU; return n.inputs().size() == 1; }
+                if (b.op() == "leaky_relu") {     // src/backend/base/base_leaky_relu.cpp registers it under this name
+                    if (!b.has(name::scale) || n.inputs().size() != 1) return false;
                     activation = TSB_ACT_LEAKY_RELU;
-                    if (!act.has(name::scale)) return false;
-                    leaky = tensor::to_float(act.get(name::scale));
-                } else return false;
-                auto act_inputs = node.inputs();
-                if (act_inputs.size() != 1) return false;
-                Node biased = act_inputs[0];
+                    leaky = tensor::to_float(b.get(name::scale));
+                    return true;
+                }
+                return false;
+            }
+
+            // add_bias(conv2d_quantized(x, w), const) over the channel dimension of NCHW tensors, each read by one node
+            static bool is_biased_conv(const Node &biased, Chain &m) {
                 if (biased.bubble().op() != name::layer::add_bias() || biased.outputs().size() != 1) return false;
                 if (biased.bubble().has(name::format)) {
                     if (tensor::to_string(biased.bubble().get(name::format)) != name::NCHW) return false;
                 } else if (biased.bubble().has(name::dim)) {
                     if (tensor::to_int(biased.bubble().get(name::dim)) != 1) return false;
                 } else return false;
-                auto biased_inputs = biased.inputs();
-                if (biased_inputs.size() != 2) return false;
-                Node conv = biased_inputs[0], bias = biased_inputs[1];
+                auto in = biased.inputs();
+                if (in.size() != 2) return false;
+                Node conv = in[0], bias = in[1];
                 if (conv.bubble().op() != name::layer::conv2d_quantized() || conv.outputs().size() != 1) return false;
+                if (conv.inputs().size() != 2) return false;
                 if (bias.bubble().op() != Bubble::Const || !bias.bubble().has(name::value)) return false;
                 if (conv.bubble().has(name::format) && tensor::to_string(conv.bubble().get(name::format)) != name::NCHW) return false;
+                m.conv = std::make_shared<Node>(conv);
+                m.bias = std::make_shared<Node>(bias);
+                return true;
+            }
 
-                // quantize(x) in front of the convolution, read by nothing else: the fused operator takes x itself and
-                // quantizes it straight into the layout its kernel reads
-                std::vector<Node> fused_inputs = conv.inputs();
-                if (fused_inputs.size() != 2) return false;
+            // act(...) with the chain below it; with_add: the activation may sit on add(add_bias(conv), shortcut)
+            static bool match_activation(const Node &act, Chain &m, bool with_add) {
+                if (!is_activation(act, m.activation, m.leaky)) return false;
+                Node in = act.input(0);
+                if (with_add && in.bubble().op() == name::layer::add() && in.outputs().size() == 1 && in.inputs().size() == 2) {
+                    for (int i = 0; i < 2; ++i) {
+                        Node biased = in.input(i), other = in.input(1 - i);
+                        Chain t = m;
+                        if (is_biased_conv(biased, t)) {
+                            m = t; m.residual = 1; m.shortcut = std::make_shared<Node>(other);
+                            return true;
+                        }
+                    }
+                    return false;
+                }
+                m.residual = 0;
+                return is_biased_conv(in, m);
+            }
+
+            // `top` is the last node of a quantized layer this option replaces
+            static bool match(const Node &top, Chain &m) {
+                if (top.bubble().op() == name::layer::add() && top.inputs().size() == 2) {
+                    for (int i = 0; i < 2; ++i) {
+                        Node act = top.input(i), other = top.input(1 - i);
+                        Chain t;
+                        if (act.outputs().size() == 1 && match_activation(act, t, false)) {
+                            m = t; m.residual = 2; m.shortcut = std::make_shared<Node>(other);
+                            return true;
+                        }
+                    }
+                    return false;
+                }
+                // an activation that a Darknet-style add absorbs is not a layer top of its own
+                Chain t;
+                if (!match_activation(top, t, true)) return false;
+                if (users(top).size() == 1) {
+                    Node user = users(top)[0];
+                    Chain u;
+                    if (user.bubble().op() == name::layer::add() && match(user, u) && *u.conv == *t.conv) return false;
+                }
+                m = t;
+                return true;
+            }
+
+            // the top node of the layer whose convolution is `conv`, if that layer is one this option replaces
+            static bool layer_top(const Node &conv) {
+                if (conv.outputs().size() != 1) return false;
+                Node biased = conv.outputs()[0];
+                if (biased.outputs().size() != 1) return false;
+                Node next = biased.outputs()[0];
+                std::vector<Node> candidates;
+                if (next.bubble().op() == name::layer::add()) {
+                    if (next.outputs().size() == 1) candidates.push_back(next.outputs()[0]);     // act(add(...))
+                } else {
+                    if (next.outputs().size() == 1) candidates.push_back(next.outputs()[0]);     // add(act(...), s)
+                    candidates.push_back(next);                                                   // act(...)
+                }
+                for (auto &c : candidates) {
+                    Chain m;
+                    if (match(c, m) && *m.conv == conv) return true;
+                }
+                return false;
+            }
+
+            // y -> quantize q -> convolution `consumer`, nothing else reading y or q, both layers replaced by fused nodes:
+            // int8 can travel from the first node to the second
+            static bool handover(const Node &producer_top, const Node &q, const Node &consumer) {
+                if (q.bubble().op() != name::layer::quantize() || !q.bubble().has(name::quantize_scale)) return false;
+                if (q.inputs().size() != 1 || q.outputs().size() != 1 || users(producer_top).size() != 1) return false;
+                if (q.input(0) != producer_top || q.outputs()[0] != consumer) return false;
+                if (consumer.bubble().op() != name::layer::conv2d_quantized() || consumer.input(0) != q) return false;
+                Chain pm;
+                return match(producer_top, pm) && layer_top(consumer);
+            }
+
+            bool zip(const ComputingDevice &device, Node node, Node &zipped_node) const override {
+                if (device.type() != GPU) return false;
+                Chain m;
+                if (!match(node, m)) return false;
+                std::vector<Node> fused_inputs = m.conv->inputs();       // x (int8), w
                 Tensor folded_scales;
+                bool in_nhwc = false;
                 {
                     Node q = fused_inputs[0];
                     if (q.bubble().op() == name::layer::quantize() && q.outputs().size() == 1 && q.inputs().size() == 1 &&
                         q.bubble().has(name::quantize_scale)) {
-                        folded_scales = tensor::cast(FLOAT32, q.bubble().get(name::quantize_scale));
+                        if (handover(q.input(0), q, *m.conv)) in_nhwc = true;    // the producer writes what this kernel reads
+                        else folded_scales = tensor::cast(FLOAT32, q.bubble().get(name::quantize_scale));
                         fused_inputs[0] = q.input(0);
                     }
                 }
-                Node fused = bubble::op(act.name(), Conv2DQuantizedFused::op_name(), fused_inputs);
-                for (auto &param : conv.bubble().params()) {
+                Tensor out_scales;
+                if (users(node).size() == 1) {
+                    Node q = users(node)[0];
+                    if (q.outputs().size() == 1 && handover(node, q, q.outputs()[0]))
+                        out_scales = tensor::cast(FLOAT32, q.bubble().get(name::quantize_scale));
+                }
+                if (m.residual) fused_inputs.push_back(*m.shortcut);
+                Node fused = bubble::op(node.bubble().name(), Conv2DQuantizedFused::op_name(), fused_inputs);
+                for (auto &param : m.conv->bubble().params()) {
                     if (!param.first.empty() && param.first[0] == Bubble::retention_param_sign) continue;   // #name, #op, ...
                     fused.bubble().set(param.first, param.second);
                 }
-                fused.bubble().set(Conv2DQuantizedFused::fused_bias(), tensor::cast(FLOAT32, bias.bubble().get(name::value)));
-                fused.bubble().set(Conv2DQuantizedFused::fused_activation(), tensor::from<int32_t>(activation));
-                fused.bubble().set(Conv2DQuantizedFused::fused_leaky(), tensor::from<float>(leaky));
+                fused.bubble().set(Conv2DQuantizedFused::fused_bias(), tensor::cast(FLOAT32, m.bias->bubble().get(name::value)));
+                fused.bubble().set(Conv2DQuantizedFused::fused_activation(), tensor::from<int32_t>(m.activation));
+                fused.bubble().set(Conv2DQuantizedFused::fused_leaky(), tensor::from<float>(m.leaky));
                 if (!folded_scales.empty()) fused.bubble().set(Conv2DQuantizedFused::fused_quantize_scale(), folded_scales);
+                if (in_nhwc) fused.bubble().set(Conv2DQuantizedFused::fused_in_nhwc(), tensor::from<int32_t>(1));
+                if (!out_scales.empty()) fused.bubble().set(Conv2DQuantizedFused::fused_out_scale(), out_scales);
+                if (m.residual) fused.bubble().set(Conv2DQuantizedFused::fused_residual(), tensor::from<int32_t>(m.residual));
                 zipped_node = fused;
                 return true;
             }
@@ -358,6 +634,17 @@ extern "C" __attribute__((visibility("default"))) long tsb_plugin_fused_runs() {
 // ... and how many of those runs had the quantize operator folded in
 extern "C" __attribute__((visibility("default"))) long tsb_plugin_folded_quantize_runs() {
     return ts::b200::Conv2DQuantizedFused::folded_quantize_runs().load();
+}
+// ... how many took their input as int8 from another fused node, and how many had a shortcut folded in
+extern "C" __attribute__((visibility("default"))) long tsb_plugin_int8_handover_runs() {
+    return ts::b200::Conv2DQuantizedFused::int8_handover_runs().load();
+}
+extern "C" __attribute__((visibility("default"))) long tsb_plugin_residual_runs() {
+    return ts::b200::Conv2DQuantizedFused::residual_runs().load();
+}
+// ... and how many finished a shortcut of another shape or type with the device's own add operator
+extern "C" __attribute__((visibility("default"))) long tsb_plugin_reference_add_runs() {
+    return ts::b200::Conv2DQuantizedFused::reference_add_runs().load();
 }
 
 using namespace ts;

@@ -25,6 +25,9 @@
 
 extern "C" long tsb_plugin_fused_runs();             // tennis_b200/plugin/gpu_conv2d_quantized.cpp
 extern "C" long tsb_plugin_folded_quantize_runs();
+extern "C" long tsb_plugin_int8_handover_runs();
+extern "C" long tsb_plugin_residual_runs();
+extern "C" long tsb_plugin_reference_add_runs();
 
 using namespace ts;
 
@@ -144,7 +147,100 @@ long mismatches_f32(const Tensor &a, const Tensor &b) {
     return bad;
 }
 
+// One quantized layer of a larger graph: quantize -> conv2d_quantized -> add_bias [-> add shortcut] -> relu | leaky_relu
+// [-> add shortcut], as a model converter writes it.  shortcut_mode: 0 none, 1 before the activation, 2 after it.
+Node quantized_layer(const std::string &name, Node in, const Case &cs, const Data &d, float in_scale, float leaky, int shortcut_mode,
+                     const Node *shortcut) {
+    auto q = bubble::op(name + ".q", name::layer::quantize(), {in});
+    q.bubble().set(name::quantize_scale, float_vector(std::vector<float>(cs.n, in_scale)));
+    auto conv = bubble::op(name + ".conv", name::layer::conv2d_quantized(), {q, bubble::data(name + ".w", d.w)});
+    set_conv_params(conv.bubble(), cs, d);
+    auto biased = bubble::op(name + ".biased", name::layer::add_bias(), {conv, bubble::data(name + ".b", d.bias)});
+    biased.bubble().set(name::format, tensor::from("NCHW"));
+    Node pre = biased;
+    if (shortcut_mode == 1) pre = bubble::op(name + ".sum", name::layer::add(), {biased, *shortcut});
+    auto act = bubble::op(name + ".act", leaky > 0.0f ? std::string("leaky_relu") : name::layer::relu(), {pre});
+    if (leaky > 0.0f) act.bubble().set(name::scale, tensor::from<float>(leaky));
+    if (shortcut_mode == 2) return bubble::op(name + ".sum", name::layer::add(), {act, *shortcut});
+    return act;
+}
+
+// A bottleneck block with a shortcut -- 1x1 c->m, 3x3 m->m, 1x1 m->c, the sum with the block's input before the last
+// relu (darknet: after a leaky_relu) -- as ONE TenniS graph, loaded with Workbench::Load.
+// broadcast: the shortcut is a second input of shape [1, c, 1, 1] instead, which operator "add" broadcasts;
+// tail: a fourth layer (1x1 c->m) reads the block's result, so the block's last node hands int8 on as well.
+Tensor run_block(const std::string &device, int n, int c, int m, int h, int w, const Data d[4], const float scales[4], bool darknet,
+                 bool broadcast, bool tail, const Tensor &side) {
+    Graph g;
+    ctx::bind<Graph> _graph(g);
+    auto x = bubble::param("x", FLOAT32, Shape({n, c, h, w}));
+    auto s = broadcast ? bubble::param("s", FLOAT32, Shape({1, c, 1, 1})) : x;
+    const float leaky = darknet ? 0.1f : 0.0f;
+    Case c1{n, c, h, w, m, 1, 1, 0}, c2{n, m, h, w, m, 3, 1, 1}, c3{n, m, h, w, c, 1, 1, 0};
+    Node y1 = quantized_layer("l1", x, c1, d[0], scales[0], leaky, 0, nullptr);
+    Node y2 = quantized_layer("l2", y1, c2, d[1], scales[1], leaky, 0, nullptr);
+    Node y3 = quantized_layer("l3", y2, c3, d[2], scales[2], leaky, darknet ? 2 : 1, &s);
+    Node top = tail ? quantized_layer("l4", y3, c1, d[3], scales[3], leaky, 0, nullptr) : y3;
+    std::shared_ptr<Module> mod = std::make_shared<Module>();
+    mod->load(g, {top.bubble().name()});
+    ComputingDevice cd(device, 0);
+    Workbench::shared bench = Workbench::Load(mod, cd);
+    if (device == CPU) bench->runtime().set_computing_thread_number(1);
+    Tensor input(FLOAT32, Shape({n, c, h, w}));
+    std::memcpy(input.data(), d[0].x.data(), size_t(input.count()) * sizeof(float));
+    bench->input("x", input);
+    if (broadcast) bench->input("s", side);
+    bench->run();
+    bench->run();
+    return bench->output(0).view(MemoryDevice(CPU)).clone();
+}
+
 }  // namespace
+
+// The bottleneck block on the cpu and on the gpu device.  On the gpu device the layers must become fused nodes that pass
+// int8 between them: per run one staging quantize of the block's input and one convolution launch per layer, nothing
+// else from this library.  variant: bit 0 Darknet-style shortcut, bit 1 broadcast shortcut (the fused node then finishes
+// the layer with the device's own add), bit 2 a fourth layer behind the block.
+extern "C" __attribute__((visibility("default")))
+int tsplug_block(int n, int c, int m, int h, int w, int variant, unsigned seed, char *msg, int msglen) {
+    const char *phase = "setup";
+    try {
+        const bool darknet = variant & 1, broadcast = variant & 2, tail = variant & 4;
+        const int layers = tail ? 4 : 3;
+        Data d[4] = {make_data(Case{n, c, h, w, m, 1, 1, 0}, seed), make_data(Case{n, m, h, w, m, 3, 1, 1}, seed + 1),
+                     make_data(Case{n, m, h, w, c, 1, 1, 0}, seed + 2), make_data(Case{n, c, h, w, m, 1, 1, 0}, seed + 3)};
+        // activation scales between the layers: 127 / (a plausible maximum of the previous layer's output)
+        const float scales[4] = {d[0].qscales[0], 127.0f / 3.0f, 127.0f / 2.5f, 127.0f / 4.0f};
+        for (int l = 1; l < 4; ++l)
+            for (auto &v : d[l].dq) v = v * d[l].qscales[0] / scales[l];      // weight scale / this layer's input scale
+        Tensor side(FLOAT32, Shape({1, c, 1, 1}));
+        for (int i = 0; i < c; ++i) side.data<float>()[i] = 0.25f * float((i * 7) % 11) - 1.0f;
+        phase = "cpu device";
+        Tensor y_cpu = run_block(CPU, n, c, m, h, w, d, scales, darknet, broadcast, tail, side);
+        const long fused0 = tsb_plugin_fused_runs(), hand0 = tsb_plugin_int8_handover_runs(), res0 = tsb_plugin_residual_runs();
+        const long folded0 = tsb_plugin_folded_quantize_runs(), ref0 = tsb_plugin_reference_add_runs();
+        const int64_t launches0 = tsb_kernel_launch_count();
+        phase = "gpu device";
+        Tensor y_gpu = run_block(GPU, n, c, m, h, w, d, scales, darknet, broadcast, tail, side);
+        const long fused = tsb_plugin_fused_runs() - fused0, hand = tsb_plugin_int8_handover_runs() - hand0;
+        const long res = tsb_plugin_residual_runs() - res0, folded = tsb_plugin_folded_quantize_runs() - folded0;
+        const long ref_add = tsb_plugin_reference_add_runs() - ref0;
+        const int64_t launches = tsb_kernel_launch_count() - launches0;
+        const long bad = mismatches_f32(y_cpu, y_gpu);
+        std::snprintf(msg, msglen, "block mismatches=%ld of %d; per 2 runs: fused nodes=%ld int8 hand-overs=%ld shortcuts folded=%ld shortcuts by the add operator=%ld input quantizes folded=%ld kernel launches=%lld",
+                      bad, y_cpu.count(), fused, hand, res, ref_add, folded, (long long) launches);
+        // the rewrite must have produced the chain of fused nodes
+        if (fused != 2 * layers || hand != 2 * (layers - 1) || folded != 2) return 3;
+        if (res != (broadcast ? 0 : 2) || ref_add != (broadcast ? 2 : 0)) return 3;
+        // two runs x (1 staging quantize + the convolutions [+ the quantize behind a shortcut the add operator took]),
+        // plus the weight repacks of the first run
+        if (launches != 2 * (1 + layers + (broadcast && tail ? 1 : 0)) + layers) return 4;
+        return bad == 0 ? 0 : 1;
+    } catch (const std::exception &e) {
+        std::snprintf(msg, msglen, "exception (%s): %s", phase, e.what());
+        return -1;
+    }
+}
 
 extern "C" __attribute__((visibility("default")))
 int tsplug_selftest(int n, int c, int h, int w, int o, int k, int stride, int pad, unsigned seed, char *msg, int msglen) {

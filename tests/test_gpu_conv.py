@@ -290,6 +290,23 @@ def test_epilogue_variants(checker, port, kernel):
     check_case(checker, port, *args, None, "leaky_relu", 0.25, 0.0, kernel, rq=np.array([0.5], np.float32))
 
 
+@pytest.mark.parametrize("tune", [dict(), dict(mma_orientation=1), dict(mma_orientation=2), dict(patch_mode=1)])
+def test_nchw_residual_with_nchw_output(checker, port, tune):
+    """What the graph rewrite produces when it folds a shortcut into the convolution: fp32 NCHW residual in, fp32 NCHW
+    out, no int8 output -- residual before the activation (ResNet) and after it (Darknet)."""
+    rng = np.random.default_rng(11)
+    N, C, H, W, O = 2, 64, 13, 11, 160
+    x = rng.integers(-128, 128, size=(N, C, H, W), dtype=np.int8)
+    dq = rng.uniform(0.001, 0.01, size=O).astype(np.float32)
+    bias = (rng.standard_normal(O) * 0.1).astype(np.float32)
+    residual = rng.standard_normal((N, O, H, W)).astype(np.float32)
+    for k, pad in ((1, (0, 0, 0, 0)), (3, (1, 1, 1, 1))):
+        w = rng.integers(-127, 128, size=(O, C, k, k), dtype=np.int8)
+        check_case(checker, port, x, w, pad, (1, 1), (1, 1), dq, bias, "relu", 0.0, 0.0, 2, residual=residual, want_acc=False, tune=tune)
+        check_case(checker, port, x, w, pad, (1, 1), (1, 1), dq, bias, "leaky_relu", 0.1, 0.0, 2, residual=residual, res_after=True,
+                   want_acc=False, x_layout="nhwc", tune=tune)
+
+
 @pytest.mark.parametrize("kernel", [1, 2])
 @pytest.mark.parametrize("swap", [None, "0", "1"])
 def test_residual_after_the_activation(checker, port, kernel, swap):

@@ -19,6 +19,7 @@ def driver():
         pytest.skip("tests/plugin/libplugin_driver.so was not built (needs the reference sources at build time)")
     lib = ctypes.CDLL(DRIVER)
     lib.tsplug_selftest.argtypes = [ctypes.c_int] * 8 + [ctypes.c_uint, ctypes.c_char_p, ctypes.c_int]
+    lib.tsplug_block.argtypes = [ctypes.c_int] * 6 + [ctypes.c_uint, ctypes.c_char_p, ctypes.c_int]
     return lib
 
 
@@ -36,3 +37,34 @@ def test_graph_runs_unchanged_on_gpu_device(driver, case):
     assert "graph mismatches=0" in text
     assert "fused operator runs=2" in text      # the compiled gpu program runs conv + bias + relu as one operator
     assert "quantize folded=1" in text          # ... and quantizes the fp32 input itself, straight into its staged layout
+
+
+@pytest.mark.parametrize("variant", [0, 1, 4, 5])
+@pytest.mark.parametrize("case", [
+    (2, 256, 64, 14, 14),     # a ResNet-50 bottleneck at 14 x 14: 1x1 256->64, 3x3 64->64, 1x1 64->256 + identity shortcut
+    (3, 128, 32, 9, 11),      # odd extents, 32 channels in the middle
+])
+def test_bottleneck_block_passes_int8_between_fused_nodes(driver, case, variant):
+    """A three-convolution block with a shortcut, loaded from ONE graph: on the gpu device the rewrite must leave three
+    fused nodes that hand int8 to one another (no quantize or layout kernel between the layers) and fold the shortcut into
+    the last one; the result must equal the cpu device's bit for bit.  variant bit 0: the shortcut is added after a
+    leaky_relu (Darknet) instead of before a relu (ResNet); bit 2: a fourth layer reads the block's result, so the node
+    with the shortcut hands int8 on too."""
+    msg = ctypes.create_string_buffer(512)
+    rc = driver.tsplug_block(*case, variant, 11, msg, 512)
+    text = msg.value.decode(errors="replace")
+    assert rc == 0, text
+    hand = 6 if variant & 4 else 4
+    assert "block mismatches=0" in text and f"int8 hand-overs={hand}" in text and "shortcuts folded=2" in text
+
+
+@pytest.mark.parametrize("variant", [2, 3, 6, 7])
+def test_broadcast_shortcut_is_left_to_the_add_operator(driver, variant):
+    """Operator "add" broadcasts; no shape is known when the graph is rewritten.  A shortcut of shape [1, C, 1, 1] must
+    therefore still give the cpu device's result: the fused node runs convolution and bias (and the activation, Darknet
+    style) itself and finishes with the gpu device's own add -- and still hands int8 to a layer behind it."""
+    msg = ctypes.create_string_buffer(512)
+    rc = driver.tsplug_block(2, 128, 32, 10, 12, variant, 5, msg, 512)
+    text = msg.value.decode(errors="replace")
+    assert rc == 0, text
+    assert "block mismatches=0" in text and "shortcuts folded=0" in text and "shortcuts by the add operator=2" in text
