@@ -256,6 +256,37 @@ def csp_parity(net, spec, params, scales, x, out):
     return {"images_checked": len(picks), "mismatches": bad, "checker": "C port of the reference operators, every block / stage output int8 bit-exact",
             "host_s": round(time.perf_counter() - t0, 2)}
 
+def run_workbench_resnet(reps):
+    """The same ResNet-50 shape as a TenniS graph inside the reference's own runtime (Workbench::Load / Workbench::run on
+    its "gpu" device, with this repo's operators and graph rewrite registered there): what the runtime around the
+    kernels costs.  Needs tennis_b200/libtennis_b200_workbench.so, which is built against the reference's sources and
+    its CUDA host library; without them the object says so."""
+    import ctypes
+    path = os.path.join(ROOT, "tennis_b200", "libtennis_b200_workbench.so")
+    if not os.path.exists(path):
+        return {"unavailable": "libtennis_b200_workbench.so was not built (needs the reference's sources at build time)"}
+    lib = ctypes.CDLL(path)
+    lib.tsb_workbench_resnet50.argtypes = [ctypes.c_int] * 4 + [ctypes.c_uint, ctypes.POINTER(ctypes.c_double), ctypes.c_char_p,
+                                           ctypes.c_int]
+    res = {"graph": "53 quantize -> conv2d_quantized -> add_bias [-> add] -> relu layers, pooling2d, global_pooling2d, flatten, "
+                    "inner_prod; built with the reference's graph API, compiled by Workbench::Load for device gpu",
+           "timing": "wall clock around reps x (Workbench::input, Workbench::run, output view on the host), device idle at both ends"}
+    for key, batch, mode in (("batch64_host_input", 64, 0), ("batch64_resident_input", 64, -1), ("batch1_resident_input", 1, -1)):
+        out = (ctypes.c_double * 6)()
+        msg = ctypes.create_string_buffer(512)
+        rc = lib.tsb_workbench_resnet50(batch, 224, reps, mode, 3, out, msg, 512)
+        if rc != 0:
+            res[key] = {"error": msg.value.decode(errors="replace")[:300]}
+            continue
+        res[key] = {"ms_per_pass": out[0], "images_per_sec": batch / (out[0] / 1e3), "library_kernel_launches_per_pass": out[1],
+                    "fused_nodes_per_pass": out[2], "int8_handovers_per_pass": out[3], "shortcuts_in_epilogue_per_pass": out[4]}
+    one = res.get("batch1_resident_input", {})
+    if "ms_per_pass" in one:
+        # 53 fused nodes + pooling2d + global_pooling2d + flatten + inner_prod = 57 operator instructions per pass
+        res["host_us_per_operator_upper_bound"] = one["ms_per_pass"] * 1e3 / 57
+    return res
+
+
 def run_resnet50(args, dev, rank, world, sharding, peaks):
     """Images/s of the ResNet-50-shaped int8 network (53 convolutions with folded BN, fused ReLU / residual / requantize,
     int8 max pool, fp32 average pool and inner product), batch 64 per GPU, synthetic N(0,1) input, whole forward pass
@@ -345,6 +376,12 @@ def run_resnet50(args, dev, rank, world, sharding, peaks):
         config4 = run_config4(args, dev, rank, world, sharding, net, graph, x, logits, spec, params, scales)
     except Exception as e:
         config4 = {"error": repr(e)[:300]}
+    workbench = None
+    if rank == 0:
+        try:
+            workbench = run_workbench_resnet(max(5, min(args.steps, 20)))
+        except Exception as e:
+            workbench = {"error": repr(e)[:300]}
     return {"workload": "config2: ResNet-50-shaped int8 network, batch 64 per GPU, CUDA graph replay", "batch_per_gpu": batch,
             "images_per_sec": images / (ms_max / 1e3), "ms_per_batch": ms_max, "int8_conv_tops": ops_batch * world / (ms_max / 1e3) / 1e12,
             "e2e_images_per_sec": images / (e2e_max / 1e3), "e2e_ms_per_batch": e2e_max,
@@ -352,7 +389,7 @@ def run_resnet50(args, dev, rank, world, sharding, peaks):
             "kernels_per_pass": 53 + 4, "parity": parity,
             "pass_roofline": pass_roofline(layer_times, ms_max, peaks, extra_bytes=glue_bytes) if layer_times else None,
             "layers": layer_table(layer_times, peaks),
-            "config4": config4}
+            "config4": config4, "workbench": workbench}
 
 
 

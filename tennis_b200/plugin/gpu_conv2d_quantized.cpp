@@ -441,6 +441,7 @@ namespace ts {
         // On the gpu device this option turns a quantized layer -- as a TenniS graph spells it -- into ONE node:
         //
         //   relu | leaky_relu ( add_bias ( conv2d_quantized(x, w), <const bias> ) )                      plain layer
+        //   add_bias ( conv2d_quantized(x, w), <const bias> )       with no activation behind it: projection shortcut
         //   relu | leaky_relu ( add ( add_bias(conv2d_quantized(x, w), <const bias>), shortcut ) )       ResNet block tail
         //   add ( relu | leaky_relu ( add_bias(conv2d_quantized(x, w), <const bias>) ), shortcut )       Darknet shortcut
         //                                                            ->  b200_conv2d_quantized_fused(x, w [, shortcut])
@@ -490,9 +491,14 @@ namespace ts {
                 return false;
             }
 
-            // add_bias(conv2d_quantized(x, w), const) over the channel dimension of NCHW tensors, each read by one node
-            static bool is_biased_conv(const Node &biased, Chain &m) {
-                if (biased.bubble().op() != name::layer::add_bias() || biased.outputs().size() != 1) return false;
+            static bool is_add(const Node &n) {
+                return n.bubble().op() == name::layer::add() && n.inputs().size() == 2 && n.input(0) != n.input(1);
+            }
+
+            // add_bias(conv2d_quantized(x, w), const) over the channel dimension of NCHW tensors; the convolution's result
+            // is read by the add_bias alone
+            static bool is_biased_conv(const Node &biased) {
+                if (biased.bubble().op() != name::layer::add_bias()) return false;
                 if (biased.bubble().has(name::format)) {
                     if (tensor::to_string(biased.bubble().get(name::format)) != name::NCHW) return false;
                 } else if (biased.bubble().has(name::dim)) {
@@ -501,77 +507,101 @@ namespace ts {
                 auto in = biased.inputs();
                 if (in.size() != 2) return false;
                 Node conv = in[0], bias = in[1];
-                if (conv.bubble().op() != name::layer::conv2d_quantized() || conv.outputs().size() != 1) return false;
+                if (conv.bubble().op() != name::layer::conv2d_quantized() || users(conv).size() != 1) return false;
                 if (conv.inputs().size() != 2) return false;
                 if (bias.bubble().op() != Bubble::Const || !bias.bubble().has(name::value)) return false;
                 if (conv.bubble().has(name::format) && tensor::to_string(conv.bubble().get(name::format)) != name::NCHW) return false;
+                return true;
+            }
+
+            // ... read by one node only / an activation on such a node, itself read by one node only
+            static bool is_biased_chain(const Node &n) { return is_biased_conv(n) && users(n).size() == 1; }
+            static bool is_activated_chain(const Node &n) {
+                int activation; float leaky;
+                return is_activation(n, activation, leaky) && users(n).size() == 1 && is_biased_chain(n.input(0));
+            }
+
+            // An "add" goes into ONE layer: style 1, act(add(add_bias(conv), other)), for its first operand that is a biased
+            // convolution when an activation alone reads the sum; else style 2, add(act(add_bias(conv)), other), for its
+            // first operand that is an activated layer.
+            static bool add_owner(const Node &sum, int &operand, int &style) {
+                if (!is_add(sum)) return false;
+                auto readers = users(sum);
+                int activation; float leaky;
+                if (readers.size() == 1 && is_activation(readers[0], activation, leaky)) {
+                    for (int i = 0; i < 2; ++i) if (is_biased_chain(sum.input(i))) { operand = i; style = 1; return true; }
+                }
+                for (int i = 0; i < 2; ++i) if (is_activated_chain(sum.input(i))) { operand = i; style = 2; return true; }
+                return false;
+            }
+
+            // The layer around one conv2d_quantized node, read off the graph as the module gave it: what follows the
+            // convolution up to the layer's last node `top` (the add_bias itself where no activation follows: a projection
+            // shortcut).  Every question about a layer -- is this node a top, will that convolution be replaced -- goes
+            // through here, so all nodes of the walk agree.
+            static bool layer_of(const Node &conv, Chain &m, std::shared_ptr<Node> &top) {
+                if (conv.bubble().op() != name::layer::conv2d_quantized()) return false;
+                auto readers = users(conv);
+                if (readers.size() != 1 || !is_biased_conv(readers[0]) || readers[0].input(0) != conv) return false;
+                Node biased = readers[0];
+                m = Chain();
                 m.conv = std::make_shared<Node>(conv);
-                m.bias = std::make_shared<Node>(bias);
+                m.bias = std::make_shared<Node>(biased.input(1));
+                top = std::make_shared<Node>(biased);
+                readers = users(biased);
+                if (readers.size() != 1) return true;
+                Node next = readers[0];
+                int operand, style;
+                if (is_activation(next, m.activation, m.leaky)) {
+                    top = std::make_shared<Node>(next);
+                    readers = users(next);
+                    if (readers.size() == 1 && add_owner(readers[0], operand, style) && style == 2 && readers[0].input(operand) == next) {
+                        m.residual = 2;
+                        m.shortcut = std::make_shared<Node>(readers[0].input(1 - operand));
+                        top = std::make_shared<Node>(readers[0]);
+                    }
+                    return true;
+                }
+                m.activation = TSB_ACT_NONE;
+                m.leaky = 0.0f;
+                if (add_owner(next, operand, style) && style == 1 && next.input(operand) == biased) {
+                    Node act = users(next)[0];
+                    is_activation(act, m.activation, m.leaky);
+                    m.residual = 1;
+                    m.shortcut = std::make_shared<Node>(next.input(1 - operand));
+                    top = std::make_shared<Node>(act);
+                }
                 return true;
             }
 
-            // act(...) with the chain below it; with_add: the activation may sit on add(add_bias(conv), shortcut)
-            static bool match_activation(const Node &act, Chain &m, bool with_add) {
-                if (!is_activation(act, m.activation, m.leaky)) return false;
-                Node in = act.input(0);
-                if (with_add && in.bubble().op() == name::layer::add() && in.outputs().size() == 1 && in.inputs().size() == 2) {
-                    for (int i = 0; i < 2; ++i) {
-                        Node biased = in.input(i), other = in.input(1 - i);
-                        Chain t = m;
-                        if (is_biased_conv(biased, t)) {
-                            m = t; m.residual = 1; m.shortcut = std::make_shared<Node>(other);
-                            return true;
-                        }
-                    }
-                    return false;
+            // `node` is the last node of a quantized layer this option replaces
+            static bool match(const Node &node, Chain &m) {
+                std::vector<Node> convs;        // the convolutions whose layer could end in this node
+                auto below_bias = [&](const Node &n) { if (n.bubble().op() == name::layer::add_bias() && n.inputs().size() == 2) convs.push_back(n.input(0)); };
+                int activation; float leaky;
+                if (node.bubble().op() == name::layer::add_bias()) {
+                    below_bias(node);
+                } else if (is_activation(node, activation, leaky)) {
+                    Node in = node.input(0);
+                    below_bias(in);
+                    if (is_add(in)) for (int i = 0; i < 2; ++i) below_bias(in.input(i));
+                } else if (is_add(node)) {
+                    for (int i = 0; i < 2; ++i)
+                        if (is_activation(node.input(i), activation, leaky)) below_bias(node.input(i).input(0));
                 }
-                m.residual = 0;
-                return is_biased_conv(in, m);
-            }
-
-            // `top` is the last node of a quantized layer this option replaces
-            static bool match(const Node &top, Chain &m) {
-                if (top.bubble().op() == name::layer::add() && top.inputs().size() == 2) {
-                    for (int i = 0; i < 2; ++i) {
-                        Node act = top.input(i), other = top.input(1 - i);
-                        Chain t;
-                        if (act.outputs().size() == 1 && match_activation(act, t, false)) {
-                            m = t; m.residual = 2; m.shortcut = std::make_shared<Node>(other);
-                            return true;
-                        }
-                    }
-                    return false;
-                }
-                // an activation that a Darknet-style add absorbs is not a layer top of its own
-                Chain t;
-                if (!match_activation(top, t, true)) return false;
-                if (users(top).size() == 1) {
-                    Node user = users(top)[0];
-                    Chain u;
-                    if (user.bubble().op() == name::layer::add() && match(user, u) && *u.conv == *t.conv) return false;
-                }
-                m = t;
-                return true;
-            }
-
-            // the top node of the layer whose convolution is `conv`, if that layer is one this option replaces
-            static bool layer_top(const Node &conv) {
-                if (conv.outputs().size() != 1) return false;
-                Node biased = conv.outputs()[0];
-                if (biased.outputs().size() != 1) return false;
-                Node next = biased.outputs()[0];
-                std::vector<Node> candidates;
-                if (next.bubble().op() == name::layer::add()) {
-                    if (next.outputs().size() == 1) candidates.push_back(next.outputs()[0]);     // act(add(...))
-                } else {
-                    if (next.outputs().size() == 1) candidates.push_back(next.outputs()[0]);     // add(act(...), s)
-                    candidates.push_back(next);                                                   // act(...)
-                }
-                for (auto &c : candidates) {
-                    Chain m;
-                    if (match(c, m) && *m.conv == conv) return true;
+                for (auto &conv : convs) {
+                    Chain t;
+                    std::shared_ptr<Node> top;
+                    if (layer_of(conv, t, top) && *top == node) { m = t; return true; }
                 }
                 return false;
+            }
+
+            // the convolution `conv` belongs to a layer this option replaces
+            static bool layer_top(const Node &conv) {
+                Chain m;
+                std::shared_ptr<Node> top;
+                return layer_of(conv, m, top);
             }
 
             // y -> quantize q -> convolution `consumer`, nothing else reading y or q, both layers replaced by fused nodes:

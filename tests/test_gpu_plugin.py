@@ -68,3 +68,24 @@ def test_broadcast_shortcut_is_left_to_the_add_operator(driver, variant):
     text = msg.value.decode(errors="replace")
     assert rc == 0, text
     assert "block mismatches=0" in text and "shortcuts folded=0" in text and "shortcuts by the add operator=2" in text
+
+
+def test_resnet50_graph_on_gpu_device_equals_cpu_device():
+    """53 convolutions, 16 shortcuts (4 of them projections), one max pool, as ONE TenniS graph: every quantized layer
+    becomes a fused node, the three layers of a block hand int8 to one another, every shortcut goes into an epilogue,
+    and the trunk's output equals the cpu device's bit for bit."""
+    path = os.path.join(ROOT, "tennis_b200", "libtennis_b200_workbench.so")
+    if not os.path.exists(path):
+        pytest.skip("tennis_b200/libtennis_b200_workbench.so was not built (needs the reference sources at build time)")
+    lib = ctypes.CDLL(path)
+    lib.tsb_workbench_resnet50.argtypes = [ctypes.c_int] * 4 + [ctypes.c_uint, ctypes.POINTER(ctypes.c_double), ctypes.c_char_p,
+                                           ctypes.c_int]
+    out = (ctypes.c_double * 6)()
+    msg = ctypes.create_string_buffer(512)
+    rc = lib.tsb_workbench_resnet50(2, 64, 1, 17, 3, out, msg, 512)
+    text = msg.value.decode(errors="replace")
+    assert rc == 0, text
+    assert "53 convolutions, trunk mismatches=0" in text
+    assert out[2] == 53 and out[3] == 32 and out[4] == 16, text
+    # 53 convolutions + the staging quantize of each layer that reads an fp32 tensor (53 - 32 hand-overs)
+    assert out[1] == 53 + 21, text
