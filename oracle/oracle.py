@@ -233,6 +233,23 @@ class Reference(Port):
                                             int(s.size), _ptr(y, ctypes.c_int8), self.threads))
         return y
 
+    def tensor_roundtrip(self, path_in, path_out=None):
+        """tensor::load of a .t file by the reference (and tensor::save of what it read, when path_out is given).
+        Returns (fields, dtype code of field 0, shape of field 0)."""
+        info = _ints([0] * 11)
+        self._check(self.ref.tsref_tensor_roundtrip(os.fsencode(path_in), os.fsencode(path_out) if path_out else None, info))
+        return info[0], info[1], tuple(info[3:3 + info[2]])
+
+    def run_module(self, path, x):
+        """Module::Load of a .tsm file, Workbench::Load on the cpu device, one fp32 input, the fp32 output."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        shape = _ints([0] * 9)
+        args = [os.fsencode(path), _ptr(x, ctypes.c_float), _ints(x.shape), x.ndim]
+        self._check(self.ref.tsref_run_module(*args, None, ctypes.c_long(0), shape, None, self.threads))
+        y = np.zeros(tuple(shape[1:1 + shape[0]]), dtype=np.float32)
+        self._check(self.ref.tsref_run_module(*args, _ptr(y, ctypes.c_float), ctypes.c_long(y.size), shape, None, self.threads))
+        return y
+
     def quantize_f64(self, x, scales):
         x = np.ascontiguousarray(x, dtype=np.float64)
         s = np.ascontiguousarray(scales, dtype=np.float32).reshape(-1)

@@ -11,6 +11,7 @@
 // Compiled against the reference headers where they lie; linked to _ref/libtennis_ref.so.
 #include <runtime/workbench.h>
 #include <module/bubble.h>
+#include <module/module.h>
 #include <core/tensor_builder.h>
 #include <backend/name.h>
 #include <utils/except.h>
@@ -239,6 +240,47 @@ int tsref_time_layer(const float *x, int images, int C, int H, int W,
     }
     *seconds_out = worst;
     if (quantize_seconds_out) *quantize_seconds_out = worst_q;
+    return 0;
+    TSREF_GUARD_END
+}
+
+// tensor::load + tensor::save (include/core/tensor_builder.h:153-159): reads a .t file with the reference and writes it
+// back with the reference, so a file written elsewhere can be compared byte for byte with the reference's own.
+// info receives {fields, dtype of field 0, dims of field 0, shape...} (up to 3 + 8 ints).
+__attribute__((visibility("default")))
+int tsref_tensor_roundtrip(const char *path_in, const char *path_out, int *info) {
+    TSREF_GUARD_BEGIN
+    Tensor t = tensor::load(path_in);
+    info[0] = int(t.fields_count());
+    info[1] = int(t.dtype());
+    info[2] = int(t.dims());
+    for (int i = 0; i < t.dims() && i < 8; ++i) info[3 + i] = t.size(i);
+    if (path_out) tensor::save(path_out, t);
+    return 0;
+    TSREF_GUARD_END
+}
+
+// Module::Load of a .tsm file (src/module/module.cpp:295-333), compiled for the cpu device with Workbench::Load and run
+// on one fp32 input.  out may be null to ask for the output's shape only (out_shape: dims, then the shape).
+__attribute__((visibility("default")))
+int tsref_run_module(const char *path, const float *x, const int *shape, int ndims, float *out, long out_capacity,
+                     int *out_shape, int *node_count, int threads) {
+    TSREF_GUARD_BEGIN
+    Module::shared module = Module::Load(path);
+    if (node_count) *node_count = 0;
+    ComputingDevice device(CPU, 0);
+    Workbench::shared bench = Workbench::Load(module, device);
+    bench->runtime().set_computing_thread_number(threads);
+    bench->input(0, make_tensor(FLOAT32, shape, ndims, x));
+    bench->run();
+    Tensor y = bench->output(0).view(MemoryDevice(CPU));
+    if (y.dtype() != FLOAT32) throw Exception("module output is not fp32");
+    out_shape[0] = y.dims();
+    for (int i = 0; i < y.dims() && i < 8; ++i) out_shape[1 + i] = y.size(i);
+    if (out) {
+        if (long(y.count()) > out_capacity) throw Exception("output buffer too small");
+        std::memcpy(out, y.data(), size_t(y.count()) * sizeof(float));
+    }
     return 0;
     TSREF_GUARD_END
 }

@@ -223,3 +223,44 @@ int tsb_workbench_resnet50(int batch, int image, int reps, int check, unsigned s
         return -1;
     }
 }
+
+// A module file (.tsm, Module::Load: src/module/module.cpp:295-333) compiled by Workbench::Load for `device` ("cpu" or
+// "gpu") and run on one fp32 input; the fp32 output is copied to `out` (null: only its shape is wanted).  out_shape
+// receives the number of dimensions, then the shape.  counters (may be null) receives what the pass ran of this library:
+// {fused nodes, int8 hand-overs, shortcuts folded, kernel launches}.
+extern "C" __attribute__((visibility("default")))
+int tsb_workbench_run_tsm(const char *path, const char *device, const float *x, const int *shape, int ndims, float *out,
+                          long out_capacity, int *out_shape, double *counters, char *msg, int msglen) {
+    try {
+        Module::shared module = Module::Load(path);
+        ComputingDevice where(device, 0);
+        Workbench::shared bench = Workbench::Load(module, where);
+        if (where.type() == CPU) bench->runtime().set_computing_thread_number(1);
+        Tensor input(FLOAT32, Shape(shape, shape + ndims));
+        std::memcpy(input.data(), x, size_t(input.count()) * sizeof(float));
+        bench->input(0, input);
+        bench->run();       // first run: plans, packed weights
+        const long fused0 = tsb_plugin_fused_runs(), hand0 = tsb_plugin_int8_handover_runs(), res0 = tsb_plugin_residual_runs();
+        const int64_t launches0 = tsb_kernel_launch_count();
+        bench->run();
+        Tensor y = bench->output(0).view(MemoryDevice(CPU));
+        if (counters) {
+            counters[0] = double(tsb_plugin_fused_runs() - fused0);
+            counters[1] = double(tsb_plugin_int8_handover_runs() - hand0);
+            counters[2] = double(tsb_plugin_residual_runs() - res0);
+            counters[3] = double(tsb_kernel_launch_count() - launches0);
+        }
+        if (y.dtype() != FLOAT32) throw Exception("the module's output is not fp32");
+        out_shape[0] = y.dims();
+        for (int i = 0; i < y.dims() && i < 8; ++i) out_shape[1 + i] = y.size(i);
+        if (out) {
+            if (long(y.count()) > out_capacity) throw Exception("output buffer too small");
+            std::memcpy(out, y.data(), size_t(y.count()) * sizeof(float));
+        }
+        std::snprintf(msg, msglen, "ok");
+        return 0;
+    } catch (const std::exception &e) {
+        std::snprintf(msg, msglen, "exception: %s", e.what());
+        return -1;
+    }
+}
