@@ -566,6 +566,35 @@ def run_elementwise(dev, peaks):
         del plan, xi
     return out
 
+def copy_rates(dev, barrier, megabytes=256, reps=4):
+    """Plain pinned-memory copies on this rank while every other rank does the same: GB/s of uploads alone, downloads alone,
+    and both directions at once on two streams.  The ceiling any end-to-end figure of this run sits under."""
+    import torch
+    n = megabytes << 20
+    h_up, h_down = torch.empty(n, dtype=torch.uint8).pin_memory(), torch.empty(n, dtype=torch.uint8).pin_memory()
+    h_up.zero_(); h_down.zero_()
+    d_up, d_down = torch.empty(n, dtype=torch.uint8, device=dev), torch.zeros(n, dtype=torch.uint8, device=dev)
+    s_up, s_down = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+
+    def timed(up, down):
+        torch.cuda.synchronize()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            if up:
+                with torch.cuda.stream(s_up):
+                    d_up.copy_(h_up, non_blocking=True)
+            if down:
+                with torch.cuda.stream(s_down):
+                    h_down.copy_(d_down, non_blocking=True)
+        s_up.synchronize(); s_down.synchronize()
+        return reps * n / (time.perf_counter() - t0) / 1e9
+
+    timed(True, True)
+    up, down, both = timed(True, False), timed(False, True), timed(True, True)
+    return [up, down, both, both]      # with both on, each direction moved reps * n bytes in the same time
+
+
 def run_ours(args):
     import numpy as np
     import torch
@@ -579,6 +608,14 @@ def run_ours(args):
         raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    # Before any pinned buffer exists: keep this rank on the CPUs next to its GPU, so that the host side of every
+    # upload and download (first touch) lies on the GPU's NUMA node.  Reads sysfs, changes this process's mask only.
+    props = torch.cuda.get_device_properties(dev)
+    try:
+        bus = "%04x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
+        locality = sharding.bind_to_gpu(bus)
+    except Exception as e:
+        locality = {"error": repr(e)[:100]}
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     lib = _lib.load()
@@ -818,6 +855,14 @@ def run_ours(args):
         s["plan"].set_weights(s["w"])
     h2d = sum(h["x"].numel() * 4 for h in host)
     d2h = sum(h["out"].numel() * 4 for h in host)
+    # what the host side of this machine gives every rank at this N: plain pinned copies, all ranks at once
+    try:
+        rates = sharding.gather_values(copy_rates(dev, barrier), dev)
+    except Exception as e:
+        rates = None
+    localities = sharding.gather_values([locality.get("numa_node", -1), locality.get("bound_cpus", 0),
+                                         locality.get("local_cpus", 0), locality.get("allowed_cpus", 0)], dev)
+    e2e_all = sharding.gather_values([e2e_s * 1e3], dev)
 
     # ---- secondary workload: the ResNet-50-shaped int8 network (configuration 2), batch 64 per GPU, one CUDA graph ----
     resnet = None
@@ -909,6 +954,25 @@ def run_ours(args):
             line["elementwise"] = elementwise
         line["e2e"]["h2d_bytes_per_step"] = h2d * world
         line["e2e"]["d2h_bytes_per_step"] = d2h * world
+        # per rank: the step's own transfer rates, the plain-copy rates of the same run, and the time the slower
+        # direction alone needs at the both-directions rate -- the floor the end-to-end step cannot go under
+        line["e2e"]["per_rank"] = []
+        for r in range(world):
+            ms_r = e2e_all[r][0]
+            rec = {"rank": r, "ms_per_step": ms_r, "h2d_gbs": h2d / ms_r / 1e6, "d2h_gbs": d2h / ms_r / 1e6,
+                   "numa_node": int(localities[r][0]), "cpus_bound": int(localities[r][1]), "cpus_local": int(localities[r][2]),
+                   "cpus_allowed": int(localities[r][3])}
+            if rates is not None:
+                up, down, both = rates[r][0], rates[r][1], rates[r][2]
+                rec.update({"copy_h2d_gbs": up, "copy_d2h_gbs": down, "copy_both_each_gbs": both,
+                            "transfer_floor_ms": max(h2d, d2h) / (both * 1e6)})
+            line["e2e"]["per_rank"].append(rec)
+        if rates is not None:
+            floor = max(rec["transfer_floor_ms"] for rec in line["e2e"]["per_rank"])
+            line["e2e"]["transfer_floor_ms"] = floor
+            line["e2e"]["frac_of_transfer_floor"] = floor / (e2e_s_max * 1e3)
+            line["e2e"]["transfer_floor_note"] = ("the larger of a step's upload and download bytes at the rate of plain pinned copies in "
+                                                  "both directions, measured on every rank at once in this run")
         if world == 1:
             try:
                 checker, cores, workers, images, ops_pass = cpu_arm(layers)

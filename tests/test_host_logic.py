@@ -236,3 +236,33 @@ def test_workload_arithmetic():
     assert all(np.array_equal(d[k], d2[k]) for k in d)
     assert abs(float(np.abs(d["x"]).max() * d["qscale"]) - 127.0) < 1e-3
     assert d["w"].min() >= -127 and d["dq"].shape == (4,)
+
+
+def test_gpu_locality_and_binding_from_a_fake_sysfs(tmp_path):
+    """The NUMA binding of a rank reads sysfs and changes only the process's own affinity mask."""
+    from tennis_b200 import sharding
+    assert sharding.parse_cpu_list("0-3,8,10-11\n") == [0, 1, 2, 3, 8, 10, 11]
+    assert sharding.parse_cpu_list("") == []
+    dev = tmp_path / "0000:1b:00.0"
+    dev.mkdir()
+    (dev / "numa_node").write_text("1\n")
+    (dev / "local_cpulist").write_text("4-7\n")
+    assert sharding.gpu_locality("0000:1B:00.0", str(tmp_path)) == (1, [4, 5, 6, 7])
+    calls = []
+    rec = sharding.bind_to_gpu("0000:1B:00.0", str(tmp_path), setaffinity=lambda pid, cpus: calls.append((pid, list(cpus))),
+                               getaffinity=lambda pid: set(range(8)))
+    assert calls == [(0, [4, 5, 6, 7])] and rec["numa_node"] == 1 and rec["bound_cpus"] == 4
+    # none of the local CPUs is in the process's mask (a container's cpuset): nothing is bound
+    calls.clear()
+    rec = sharding.bind_to_gpu("0000:1B:00.0", str(tmp_path), setaffinity=lambda pid, cpus: calls.append(1),
+                               getaffinity=lambda pid: {0, 1})
+    assert calls == [] and rec["bound_cpus"] == 0
+    # a platform that says nothing (no such device directory)
+    rec = sharding.bind_to_gpu("0000:ff:00.0", str(tmp_path), setaffinity=lambda pid, cpus: calls.append(1),
+                               getaffinity=lambda pid: {0, 1})
+    assert calls == [] and rec["numa_node"] == -1
+
+
+def test_gather_values_single_process():
+    from tennis_b200 import sharding
+    assert sharding.gather_values([1, 2.5]) == [[1.0, 2.5]]

@@ -46,8 +46,9 @@ def _worker(rank, world, port, out):
         elapsed_ms = 10.0 if rank == 0 else 25.0
         t, u = sharding.aggregate(elapsed_ms, count)
         tp = sharding.throughput(elapsed_ms, count)
+        rates = sharding.gather_values([50.0 + rank, 40.0 - rank])      # per-rank copy rates, as bench.py reports them
         dist.barrier()
-        out.put((rank, start, count, t, u, tp))
+        out.put((rank, start, count, t, u, tp, rates))
     finally:
         dist.destroy_process_group()
 
@@ -68,6 +69,7 @@ def test_two_replicas_aggregate_over_gloo():
     for r in results:
         assert r[3] == 25.0 and r[4] == 65.0            # max of the times, sum of the work, on every rank
         assert abs(r[5] - 65.0 / 0.025) < 1e-9
+        assert r[6] == [[50.0, 40.0], [51.0, 39.0]]      # every rank sees every rank's values, in rank order
 
 
 def test_single_process_needs_no_group():
