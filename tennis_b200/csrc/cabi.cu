@@ -244,6 +244,7 @@ int tsb_conv2d_i8_plan_describe(const tsb_conv_plan *plan, char *text, size_t te
         len = snprintf(text, text_bytes, "kernel=direct (%s)", plan->why_not_tc);
     } else {
         len = snprintf(text, text_bytes, "kernel=tcgen05 ");
+        if (plan->view.fold && len > 0 && (size_t)len < text_bytes) len += snprintf(text + len, text_bytes - len, "cpix=%d ", plan->view.cpix);
         if (len > 0 && (size_t)len < text_bytes) len += one(plan->cfg, text + len, text_bytes - len);
         if (plan->alt_valid && len > 0 && (size_t)len < text_bytes) {
             len += snprintf(text + len, text_bytes - len, " | alt: ");

@@ -26,24 +26,23 @@ maxpool_i8_nhwc_kernel(const int8_t *__restrict__ x, int8_t *__restrict__ y, int
         const int u = (int)(i % units);
         const int64_t pix = i / units;
         const int ow = (int)(pix % OW), oh = (int)((pix / OW) % OH), n = (int)(pix / ((int64_t)OW * OH));
-        int best[16];
-#pragma unroll
-        for (int b = 0; b < 16; ++b) best[b] = -128;
+        // four int8 lanes per 32-bit word, compared with the per-byte signed maximum
+        uint32_t w4[4] = {0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u};
         for (int kh = 0; kh < K; ++kh) {
             const int ih = oh * S - pad_t + kh;
             if ((unsigned)ih >= (unsigned)H) continue;
+            const int8_t *row = x + (((int64_t)n * H + ih) * W) * Cp + u * 16;
+#pragma unroll 3
             for (int kw = 0; kw < K; ++kw) {
                 const int iw = ow * S - pad_l + kw;
                 if ((unsigned)iw >= (unsigned)W) continue;
-                const int4 v = *reinterpret_cast<const int4 *>(x + (((int64_t)n * H + ih) * W + iw) * Cp + u * 16);
-                const int8_t *b8 = reinterpret_cast<const int8_t *>(&v);
-#pragma unroll
-                for (int b = 0; b < 16; ++b) best[b] = max(best[b], (int)b8[b]);
+                const int4 v = __ldg(reinterpret_cast<const int4 *>(row + (int64_t)iw * Cp));
+                w4[0] = __vmaxs4(w4[0], (uint32_t)v.x);
+                w4[1] = __vmaxs4(w4[1], (uint32_t)v.y);
+                w4[2] = __vmaxs4(w4[2], (uint32_t)v.z);
+                w4[3] = __vmaxs4(w4[3], (uint32_t)v.w);
             }
         }
-        uint32_t w4[4] = {0, 0, 0, 0};
-#pragma unroll
-        for (int b = 0; b < 16; ++b) w4[b >> 2] |= (uint32_t)(best[b] & 0xff) << (8 * (b & 3));
         *reinterpret_cast<int4 *>(y + pix * Cp + u * 16) = make_int4(w4[0], w4[1], w4[2], w4[3]);
     }
 }

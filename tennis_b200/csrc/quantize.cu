@@ -270,7 +270,7 @@ quantize_stage_kernel(const float *__restrict__ x, int8_t *__restrict__ y, Stage
 // consecutive output bytes -- four staged pixels of 8 bytes, or two of 16 -- from exactly the CC x pixels values that are
 // live, so no load is wasted on padding channels; loads of a warp cover consecutive pixels of each channel plane, stores are
 // two 16-byte vectors per thread, contiguous over the warp.  One scale per tensor or per sample (the host checks).
-template <int CC, int CPIX>
+template <int CC, int CPIX, bool VEC>
 __global__ void __launch_bounds__(kThreads)
 quantize_stage_small_kernel(const float *__restrict__ x, int8_t *__restrict__ y, StageDesc d, uint32_t units, QuantRule rule,
                             ScaleArg scales) {
@@ -288,12 +288,32 @@ quantize_stage_small_kernel(const float *__restrict__ x, int8_t *__restrict__ y,
         const int w0 = (int)(ur * PPT) - d.pad_l;
         const uint32_t base = (n * (uint32_t)CC * (uint32_t)d.H + h) * (uint32_t)d.W;
         float val[PPT][CC];
+        if (VEC) {
+            // W is a multiple of 4 and x is 16-byte aligned: the four pixels lie in two aligned groups of four, each wholly
+            // inside or wholly outside the row; every thread of the grid has the same offset into its first group
+            static_assert(!VEC || PPT == 4, "the 16-byte loads serve four pixels per thread");
+            const int g0 = (w0 + 4096) / 4 - 1024;           // floor(w0 / 4); w0 >= -pad_l > -4096
+            const int r = w0 - g0 * 4;                       // 0..3
+            const int groups = d.W >> 2;
 #pragma unroll
-        for (int p = 0; p < PPT; ++p) {
-            const int w = w0 + p;
-            const bool in = (unsigned)w < (unsigned)d.W;
+            for (int c = 0; c < CC; ++c) {
+                const float4 *src = reinterpret_cast<const float4 *>(x + base + (uint32_t)c * HW);
+                const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                const float4 a = (unsigned)g0 < (unsigned)groups ? __ldg(src + g0) : zero;
+                const float4 b = (r != 0 && (unsigned)(g0 + 1) < (unsigned)groups) ? __ldg(src + g0 + 1) : zero;
+                if (r == 0)      { val[0][c] = a.x; val[1][c] = a.y; val[2][c] = a.z; val[3][c] = a.w; }
+                else if (r == 1) { val[0][c] = a.y; val[1][c] = a.z; val[2][c] = a.w; val[3][c] = b.x; }
+                else if (r == 2) { val[0][c] = a.z; val[1][c] = a.w; val[2][c] = b.x; val[3][c] = b.y; }
+                else             { val[0][c] = a.w; val[1][c] = b.x; val[2][c] = b.y; val[3][c] = b.z; }
+            }
+        } else {
 #pragma unroll
-            for (int c = 0; c < CC; ++c) val[p][c] = in ? __ldg(x + base + (uint32_t)c * HW + (uint32_t)w) : 0.0f;
+            for (int p = 0; p < PPT; ++p) {
+                const int w = w0 + p;
+                const bool in = (unsigned)w < (unsigned)d.W;
+#pragma unroll
+                for (int c = 0; c < CC; ++c) val[p][c] = in ? __ldg(x + base + (uint32_t)c * HW + (uint32_t)w) : 0.0f;
+            }
         }
         const float s = scales.get(rule.nscales == 1 ? 0 : (int)n);
         uint32_t word[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -310,8 +330,8 @@ quantize_stage_small_kernel(const float *__restrict__ x, int8_t *__restrict__ y,
             }
         }
         int4 *dst = reinterpret_cast<int4 *>(y + (size_t)t * 32);
-        dst[0] = make_int4(word[0], word[1], word[2], word[3]);
-        dst[1] = make_int4(word[4], word[5], word[6], word[7]);
+        __stcs(dst, make_int4(word[0], word[1], word[2], word[3]));
+        __stcs(dst + 1, make_int4(word[4], word[5], word[6], word[7]));
     }
 }
 
@@ -479,11 +499,14 @@ int quantize_stage(const float *x, int8_t *y, int n, int c, int h, int w, int fo
         const uint32_t units32 = (uint32_t)((int64_t)n * h * (wp * cpix / 32));
         cudaError_t e = cudaSuccess;
         const dim3 small_grid((unsigned)ceil_div(wp * cpix / 32, 64), (unsigned)std::min(ceil_div(n * h, 4), 65535));
-#define TSB_STAGE_SMALL(CC_, CPIX_)                                                                                       \
-        if (c == CC_ && cpix == CPIX_)                                                                                    \
-            e = launch_pdl(quantize_stage_small_kernel<CC_, CPIX_>, small_grid, dim3(64, 4), 0, stream, x, y, d, units32, rule, arg)
-        TSB_STAGE_SMALL(1, 8); TSB_STAGE_SMALL(2, 8); TSB_STAGE_SMALL(3, 8); TSB_STAGE_SMALL(4, 8);
-        TSB_STAGE_SMALL(1, 16); TSB_STAGE_SMALL(2, 16); TSB_STAGE_SMALL(3, 16); TSB_STAGE_SMALL(4, 16);
+        // 16-byte loads where every row of every plane starts on a 16-byte boundary
+        const bool vec = cpix == 8 && w % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && pad_l < 4096;
+#define TSB_STAGE_SMALL(CC_, CPIX_, VEC_)                                                                                 \
+        if (c == CC_ && cpix == CPIX_ && vec == VEC_)                                                                     \
+            e = launch_pdl(quantize_stage_small_kernel<CC_, CPIX_, VEC_>, small_grid, dim3(64, 4), 0, stream, x, y, d, units32, rule, arg)
+        TSB_STAGE_SMALL(1, 8, true); TSB_STAGE_SMALL(2, 8, true); TSB_STAGE_SMALL(3, 8, true); TSB_STAGE_SMALL(4, 8, true);
+        TSB_STAGE_SMALL(1, 8, false); TSB_STAGE_SMALL(2, 8, false); TSB_STAGE_SMALL(3, 8, false); TSB_STAGE_SMALL(4, 8, false);
+        TSB_STAGE_SMALL(1, 16, false); TSB_STAGE_SMALL(2, 16, false); TSB_STAGE_SMALL(3, 16, false); TSB_STAGE_SMALL(4, 16, false);
 #undef TSB_STAGE_SMALL
         TSB_CUDA(e);
         TSB_LAUNCHED("quantize_stage_small_kernel");
