@@ -738,6 +738,49 @@ def run_ours(args):
     step_ms = [a.elapsed_time(b) for a, b in zip(starts, ends)]
     total_ms = sum(step_ms)
 
+    # ---- the same step with its five independent layers on five streams (one graph, fork / join): what a host that
+    # serves independent requests gets; a secondary figure, `value` stays the one-stream step ----
+    concurrent = None
+    try:
+        lanes = [torch.cuda.Stream(device=dev) for _ in state]
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream())
+
+        def forked_step():
+            cur = torch.cuda.current_stream()
+            for lane, st in zip(lanes, state):
+                lane.wait_stream(cur)
+                with torch.cuda.stream(lane):
+                    quantize(st)
+                    conv(st)
+            for lane in lanes:
+                cur.wait_stream(lane)
+
+        with torch.cuda.stream(side):
+            forked_step()
+            cgraph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(cgraph, stream=side):
+                forked_step()
+        torch.cuda.current_stream().wait_stream(side)
+        for _ in range(3):
+            cgraph.replay()
+        torch.cuda.synchronize()
+        for st in state:
+            st["plan"].status()
+        csteps = max(5, min(args.steps, 30))
+        cev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(csteps)]
+        for a, b in cev:
+            flush_l2()
+            a.record()
+            cgraph.replay()
+            b.record()
+        torch.cuda.synchronize()
+        cms = sum(a.elapsed_time(b) for a, b in cev) / csteps
+        concurrent = {"launch": "the five layers on five streams inside one CUDA graph", "ms_per_step": cms,
+                      "tops": sum(workloads.layer_ops(l) for l in layers) / cms / 1e9, "steps": csteps}
+    except Exception as e:
+        concurrent = {"error": repr(e)[:200]}
+
     # ---- per-kernel launch times (conv kernels only), for the roofline ----
     reps = max(10, min(args.steps, 50))
     per_layer = []
@@ -967,6 +1010,8 @@ def run_ours(args):
             "gpu_launches": int(launches), "wall_s_timed_region": wall,
             "clocks": sampler.summary(), "roofline": roofline, "layers": per_layer,
         }
+        if concurrent is not None:
+            line["layers_concurrent"] = concurrent
         if config0 is not None:
             line["config0"] = config0
         if resnet is not None:
