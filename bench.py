@@ -117,7 +117,7 @@ def cpu_arm(layers):
     # the reference's int8 GEMM is serial inside one Workbench; all host cores are used by running one
     # Workbench per core on its own samples.  The C port parallelises inside one call with OpenMP.
     workers = cores if checker.kind == "reference" else 1
-    images = 1
+    images = 4       # of each layer on each worker: about a second of wall clock, 10-20 core-seconds of CPU work
     ops_per_pass = sum(workloads.layer_ops(dict(l, n=images)) for l in layers) * workers
     return checker, cores, workers, images, ops_per_pass
 
@@ -806,7 +806,29 @@ def run_ours(args):
         per_layer.append(dict(name=l["name"], kernel="tcgen05" if s["tc"] else "direct", conv_ms=ms, quantize_ms=qms,
                               ops=workloads.layer_ops(l), tops=workloads.layer_ops(l) / ms / 1e9,
                               conv_bytes=workloads.layer_bytes(l), conv_gbs=workloads.layer_bytes(l) / ms / 1e6,
+                              written_bytes=4 * l["n"] * l["o"] * workloads.out_hw(l)[0] * workloads.out_hw(l)[1],
                               quantize_gbs=5 * n_in / qms / 1e6))
+
+    # ---- what this GPU takes as writes alone and reads alone (the copy bandwidth of the roofline is a half-and-half mix):
+    # a fill and a sum over 1 GiB, best of three ----
+    mem_rates = None
+    try:
+        big = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
+
+        def rate(fn):
+            fn()
+            best = None
+            for _ in range(3):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(); fn(); b.record()
+                torch.cuda.synchronize()
+                t = a.elapsed_time(b)
+                best = t if best is None or t < best else best
+            return big.numel() / best / 1e6
+        mem_rates = {"write_only_gbs": rate(lambda: big.fill_(3)), "read_only_gbs": rate(lambda: big.view(torch.float32).sum())}
+        del big
+    except Exception as e:
+        mem_rates = {"error": repr(e)[:200]}
 
     # ---- configuration 0: the single batch-1 layer the reference runs on its CPU today; latency of quantize + conv ----
     config0 = None
@@ -996,6 +1018,14 @@ def run_ours(args):
                     "algorithmic_bytes_per_launch": tc_bytes / n_tc, "algorithmic_ops_per_launch": tc_ops / n_tc,
                     "avg_launch_ms": tc_ms / n_tc,
                     "tensor_view": tensor_view, "hbm_view": hbm_view, "int8_gemm_probe": probe}
+        if mem_rates and "write_only_gbs" in mem_rates:
+            # the fp32 outputs are 92 % of the step's bytes and all of them are writes: against what this GPU takes as
+            # writes alone (measured just now), not against the half-read half-write copy figure
+            written = sum(p["written_bytes"] for p in tc_layers)
+            roofline["write_view"] = {"written_bytes_per_launch": written / n_tc, "achieved": written / tc_ms / 1e6,
+                                      "peak": mem_rates["write_only_gbs"], "unit": "GB/s", "frac": written / tc_ms / 1e6 / mem_rates["write_only_gbs"],
+                                      "min_ms": written / (mem_rates["write_only_gbs"] * 1e6), "read_only_gbs": mem_rates["read_only_gbs"],
+                                      "peak_source": "torch fill of 1 GiB timed in this run (reads alone: a sum over the same buffer)"}
         if probe and "tops" in probe:
             probe["frac_of_peak"] = probe["tops"] / int8_peak
             probe["frac_of_nominal_dense_int8"] = probe["tops"] / 4500.0   # NVIDIA's dense int8 figure for B200
@@ -1048,7 +1078,7 @@ def run_ours(args):
                 sec = cpu_sample(layers, images, workers, checker)
                 line["cpu_baseline"] = {
                     "value": ops_pass / sec / 1e12, "unit": UNIT, "cores": cores, "kind": checker.kind,
-                    "sample": "%d image of each of the 5 layers on each of %d worker(s); %.1f s" % (images, workers, time.perf_counter() - t0)}
+                    "sample": "%d images of each of the 5 layers on each of %d worker(s); %.1f s" % (images, workers, time.perf_counter() - t0)}
             except Exception as e:
                 line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": "failed: %r" % (e,)}
         print(json.dumps(line))
