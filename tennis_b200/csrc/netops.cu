@@ -20,12 +20,14 @@ __global__ void __launch_bounds__(kThreads)
 maxpool_i8_nhwc_kernel(const int8_t *__restrict__ x, int8_t *__restrict__ y, int N, int H, int W, int Cp, int OH, int OW,
                        int K, int S, int pad_t, int pad_l) {
     pdl_sync();
-    const int units = Cp / 16;
-    const int64_t total = (int64_t)N * OH * OW * units;
-    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < total; i += (int64_t)gridDim.x * kThreads) {
+    // (the host checks that the tensors have fewer than 2^31 16-byte units: 32-bit index arithmetic, no 64-bit divisions)
+    const uint32_t units = (uint32_t)Cp / 16u;
+    const uint32_t total = (uint32_t)N * (uint32_t)OH * (uint32_t)OW * units;
+    for (uint32_t i = blockIdx.x * kThreads + threadIdx.x; i < total; i += gridDim.x * kThreads) {
         const int u = (int)(i % units);
-        const int64_t pix = i / units;
-        const int ow = (int)(pix % OW), oh = (int)((pix / OW) % OH), n = (int)(pix / ((int64_t)OW * OH));
+        const uint32_t pix = i / units;
+        const uint32_t prow = pix / (uint32_t)OW;
+        const int ow = (int)(pix - prow * (uint32_t)OW), n = (int)(prow / (uint32_t)OH), oh = (int)(prow - (uint32_t)n * (uint32_t)OH);
         // four int8 lanes per 32-bit word, compared with the per-byte signed maximum
         uint32_t w4[4] = {0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u};
         for (int kh = 0; kh < K; ++kh) {
@@ -43,7 +45,7 @@ maxpool_i8_nhwc_kernel(const int8_t *__restrict__ x, int8_t *__restrict__ y, int
                 w4[3] = __vmaxs4(w4[3], (uint32_t)v.w);
             }
         }
-        *reinterpret_cast<int4 *>(y + pix * Cp + u * 16) = make_int4(w4[0], w4[1], w4[2], w4[3]);
+        *reinterpret_cast<int4 *>(y + (size_t)pix * Cp + u * 16) = make_int4(w4[0], w4[1], w4[2], w4[3]);
     }
 }
 
@@ -179,6 +181,7 @@ int maxpool_i8_nhwc(const int8_t *x, int8_t *y, int n, int h, int w, int channel
         return fail(TSB_ERR_UNSUPPORTED, "maxpool: a pooling window lies entirely in the padding (the reference's result there is undefined)");
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) % 16) return fail(TSB_ERR_INVALID_ARGUMENT, "maxpool: tensors must be 16-byte aligned");
     const int64_t items = (int64_t)n * oh * ow * (cp / 16);
+    if (items >= (int64_t)1 << 31 || (int64_t)n * h * w * (cp / 16) >= (int64_t)1 << 31) return fail(TSB_ERR_UNSUPPORTED, "maxpool: tensor too large");
     TSB_CUDA(launch_pdl(maxpool_i8_nhwc_kernel, dim3(grid_for(items, kThreads)), dim3(kThreads), 0, stream, x, y, n, h, w, cp, oh, ow, k, stride,
                         pad_top, pad_left));
     TSB_LAUNCHED("maxpool_i8_nhwc_kernel");
