@@ -266,6 +266,108 @@ quantize_stage_kernel(const float *__restrict__ x, int8_t *__restrict__ y, Stage
     }
 }
 
+// NHWC_PAD staging of tensors with 64-channel groups (Cp a multiple of 64), through a shared-memory tile of 32 pixels x 64
+// channels: warp w reads channels 8w .. 8w+7 of the tile's 32 consecutive pixels (every load instruction 128 contiguous
+// bytes of one channel plane), packs its 8 bytes per pixel into the pixel's row of the tile, and the tile leaves as 16-byte
+// units -- four lanes write the 64 contiguous bytes of a pixel, so every store fills whole sectors.  (The kernel above
+// writes a pixel's bytes 16 at a time from lanes that sit a whole pixel row apart.)  Two tiles alternate: one barrier per
+// tile.  Rounding and scale groups follow the NCHW element index.
+__global__ void __launch_bounds__(kThreads)
+quantize_stage_tile_kernel(const float *__restrict__ x, int8_t *__restrict__ y, StageDesc d, uint32_t tiles, QuantRule rule,
+                           ScaleArg scales) {
+    pdl_sync();
+    constexpr int kRow = 72;                                      // bytes per pixel row of the tile: 64 + 8 (bank spread)
+    __shared__ __align__(16) uint8_t tile[2][32 * kRow];
+    const uint32_t rne_limit = (uint32_t)rule.rne_limit;
+    const uint32_t group_len = (uint32_t)rule.group_len;
+    const uint32_t HW = (uint32_t)(d.H * d.W);
+    const uint32_t CHW = (uint32_t)d.C * HW;
+    const bool per_sample = rule.nscales > 1 && group_len == CHW;
+    const bool simple = rule.nscales == 1 || per_sample;
+    const uint32_t npix = (uint32_t)d.N * HW;
+    const uint32_t groups = (uint32_t)d.Cp / 64u;                 // channel groups per pixel tile
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    uint32_t buf = 0;
+    for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x, buf ^= 1u) {
+        const uint32_t ptile = t / groups, cg = t - ptile * groups;
+        const uint32_t pix = ptile * 32u + lane;
+        const bool live = pix < npix;
+        const uint32_t n = live ? pix / HW : 0u, p = live ? pix - n * HW : 0u;
+        const uint32_t c0 = cg * 64u + warp * 8u;
+        float val[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t c = c0 + (uint32_t)j;
+            val[j] = (live && c < (uint32_t)d.C) ? __ldg(x + (n * (uint32_t)d.C + c) * HW + p) : 0.0f;
+        }
+        const float sample_scale = scales.get(per_sample ? (int)n : 0);
+        uint32_t lo = 0, hi = 0;
+        // Fast forms for whole groups of eight live channels under one scale: the product, the rounding and a saturating
+        // conversion per value, one range test per eight (NaN and |v| >= 2^31 convert to -128 on the reference's CPU, not to
+        // what a saturating conversion gives: such a group falls through to the exact form below)
+        const uint32_t idx0 = (n * (uint32_t)d.C + c0) * HW + p;
+        const bool full = live && c0 + 8u <= (uint32_t)d.C && simple;
+        bool done = false;
+        if (full && (rne_limit == 0u || idx0 + 7u * HW < rne_limit)) {
+            const bool even = rne_limit != 0u;
+            float worst = 0.0f;
+            bool odd = false;
+            int q[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float v = __fmul_rn(val[j], sample_scale);
+                worst = fmaxf(worst, fabsf(v));     // (fmaxf drops a NaN operand: tested on its own)
+                odd = odd || (v != v);
+                if (even) {
+                    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q[j]) : "f"(v));
+                } else {
+                    const float mag = __fadd_rz(fabsf(v), 0.5f);
+                    const float sm = __int_as_float((__float_as_int(mag) & 0x7fffffff) | (__float_as_int(v) & 0x80000000));
+                    asm("cvt.rzi.sat.s8.f32 %0, %1;" : "=r"(q[j]) : "f"(sm));
+                }
+            }
+            odd = odd || !(worst < 2147483648.0f);
+            if (!odd) {
+                lo = (uint32_t)(q[0] & 0xff) | ((uint32_t)(q[1] & 0xff) << 8) | ((uint32_t)(q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
+                hi = (uint32_t)(q[4] & 0xff) | ((uint32_t)(q[5] & 0xff) << 8) | ((uint32_t)(q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);
+                done = true;
+            }
+        }
+        if (!done)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t c = c0 + (uint32_t)j;
+            int q = 0;
+            if (live && c < (uint32_t)d.C) {
+                const uint32_t idx = (n * (uint32_t)d.C + c) * HW + p;
+                float sc = sample_scale;
+                bool in_range = true;
+                if (!simple) {
+                    const uint32_t g = idx / group_len;
+                    in_range = g < (uint32_t)rule.nscales;
+                    sc = in_range ? scales.get((int)g) : 0.0f;
+                }
+                if (in_range) q = q8(val[j], sc, idx < rne_limit);
+            }
+            if (j < 4) lo |= (uint32_t)(q & 0xff) << (8 * j);
+            else hi |= (uint32_t)(q & 0xff) << (8 * (j - 4));
+        }
+        *reinterpret_cast<uint2 *>(&tile[buf][lane * kRow + warp * 8]) = make_uint2(lo, hi);
+        __syncthreads();
+        // 32 pixels x 4 units of 16 bytes: the first 128 threads carry one unit each
+        if (threadIdx.x < 128) {
+            const uint32_t pr = threadIdx.x >> 2, u = threadIdx.x & 3u;
+            const uint32_t opix = ptile * 32u + pr;
+            if (opix < npix) {
+                const uint2 a = *reinterpret_cast<const uint2 *>(&tile[buf][pr * kRow + u * 16]);
+                const uint2 b = *reinterpret_cast<const uint2 *>(&tile[buf][pr * kRow + u * 16 + 8]);
+                *reinterpret_cast<int4 *>(y + (size_t)opix * d.Cp + cg * 64u + u * 16u) = make_int4((int)a.x, (int)a.y, (int)b.x, (int)b.y);
+            }
+        }
+        // (the other tile is written next; this one is rewritten only after the next barrier)
+    }
+}
+
 // Folded staging of inputs with at most four channels (the RGB stems of the benchmark networks): a thread produces 32
 // consecutive output bytes -- four staged pixels of 8 bytes, or two of 16 -- from exactly the CC x pixels values that are
 // live, so no load is wasted on padding channels; loads of a warp cover consecutive pixels of each channel plane, stores are
@@ -512,6 +614,16 @@ int quantize_stage(const float *x, int8_t *y, int n, int c, int h, int w, int fo
         TSB_LAUNCHED("quantize_stage_small_kernel");
         if (tmp) TSB_CUDA(cudaFreeAsync(tmp, stream));
         return TSB_OK;
+    }
+    if (!folded && d.Cp % 64 == 0) {
+        const int64_t tiles = ceil_div64((int64_t)n * h * w, 32) * (d.Cp / 64);
+        if (tiles <= (int64_t)UINT32_MAX) {
+            const int blocks = (int)std::min<int64_t>(tiles, (int64_t)sm_count() * 8);
+            TSB_CUDA(launch_pdl(quantize_stage_tile_kernel, dim3(blocks), dim3(kThreads), 0, stream, x, y, d, (uint32_t)tiles, rule, arg));
+            TSB_LAUNCHED("quantize_stage_tile_kernel");
+            if (tmp) TSB_CUDA(cudaFreeAsync(tmp, stream));
+            return TSB_OK;
+        }
     }
     TSB_CUDA(launch_pdl(quantize_stage_kernel, dim3(grid_for(units)), dim3(kThreads), 0, stream, x, y, d, (uint32_t)units, rule, arg));
     TSB_LAUNCHED("quantize_stage_kernel");
