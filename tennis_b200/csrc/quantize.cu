@@ -87,11 +87,38 @@ quantize_vec16_kernel(const TIn *__restrict__ x, int8_t *__restrict__ y, uint32_
         } else {
             const float s = scales.get(g0);
             const bool he = i0 < rne_limit;
+            bool done = false;
+            if (sizeof(TIn) == 4) {
+                // fp32: product, rounding and ONE saturating conversion per value, one range test per sixteen (NaN and
+                // |v| >= 2^31 convert to -128 on the reference's CPU, which a saturating conversion does not give: such a
+                // vector takes the exact form below)
+                float worst = 0.0f;
+                bool odd = false;
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                int a = q8(f[4 * k + 0], s, he), b = q8(f[4 * k + 1], s, he);
-                int c = q8(f[4 * k + 2], s, he), d = q8(f[4 * k + 3], s, he);
-                packed[k] = (a & 0xff) | ((b & 0xff) << 8) | ((c & 0xff) << 16) | ((uint32_t)(d & 0xff) << 24);
+                for (int k = 0; k < 16; ++k) {
+                    const float v = __fmul_rn((float)f[k], s);
+                    worst = fmaxf(worst, fabsf(v));
+                    odd = odd || (v != v);
+                    int q;
+                    if (he) {
+                        asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q) : "f"(v));
+                    } else {
+                        const float mag = __fadd_rz(fabsf(v), 0.5f);
+                        const float sm = __int_as_float((__float_as_int(mag) & 0x7fffffff) | (__float_as_int(v) & 0x80000000));
+                        asm("cvt.rzi.sat.s8.f32 %0, %1;" : "=r"(q) : "f"(sm));
+                    }
+                    if ((k & 3) == 0) packed[k >> 2] = (uint32_t)(q & 0xff);
+                    else packed[k >> 2] |= (uint32_t)(q & 0xff) << (8 * (k & 3));
+                }
+                done = !(odd || !(worst < 2147483648.0f));
+            }
+            if (!done) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    int a = q8(f[4 * k + 0], s, he), b = q8(f[4 * k + 1], s, he);
+                    int c = q8(f[4 * k + 2], s, he), d = q8(f[4 * k + 3], s, he);
+                    packed[k] = (a & 0xff) | ((b & 0xff) << 8) | ((c & 0xff) << 16) | ((uint32_t)(d & 0xff) << 24);
+                }
             }
         }
         __stcs(reinterpret_cast<int4 *>(y + i0), make_int4(packed[0], packed[1], packed[2], packed[3]));
@@ -419,6 +446,34 @@ quantize_stage_small_kernel(const float *__restrict__ x, int8_t *__restrict__ y,
         }
         const float s = scales.get(rule.nscales == 1 ? 0 : (int)n);
         uint32_t word[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        bool done = false;
+        if (rne_limit == 0u) {
+            // everything rounds half away from zero (the multi-scale rule): product, rounding and a saturating conversion
+            // per value, one range test per thread (NaN and |v| >= 2^31 convert to -128 on the reference's CPU: the exact
+            // form below takes the thread then); values outside the row are zeros and stay zeros
+            float worst = 0.0f;
+            bool odd = false;
+#pragma unroll
+            for (int p = 0; p < PPT; ++p)
+#pragma unroll
+                for (int c = 0; c < CC; ++c) {
+                    const float v = __fmul_rn(val[p][c], s);
+                    worst = fmaxf(worst, fabsf(v));
+                    odd = odd || (v != v);
+                    const float mag = __fadd_rz(fabsf(v), 0.5f);
+                    const float sm = __int_as_float((__float_as_int(mag) & 0x7fffffff) | (__float_as_int(v) & 0x80000000));
+                    int q;
+                    asm("cvt.rzi.sat.s8.f32 %0, %1;" : "=r"(q) : "f"(sm));
+                    const bool in = (unsigned)(w0 + p) < (unsigned)d.W;
+                    word[(p * CPIX + c) >> 2] |= in ? (uint32_t)(q & 0xff) << (8 * (c & 3)) : 0u;
+                }
+            done = !(odd || !(worst < 2147483648.0f));
+            if (!done) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) word[k] = 0u;
+            }
+        }
+        if (!done)
 #pragma unroll
         for (int p = 0; p < PPT; ++p) {
             const int w = w0 + p;
