@@ -1094,15 +1094,24 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     // filter row kh reads the staged row (kh - kh_lo); rows outside [kh_lo, kh_hi] meet no input row
                     const uint32_t a16_0 = st16 + (uint32_t)(seg - rows_seg_first) * PIX - (uint32_t)kh_lo * row16;
                     if (kp.KH <= 8) {
+                        // straight-line code for the filter heights in use (a predicated-off MMA still costs the issuing
+                        // thread some 50 cycles, so the sequence is as long as the filter is high, not always eight)
+                        auto issue_rows = [&](auto height) {
+                            constexpr int kH = decltype(height)::value;
 #pragma unroll
-                        for (int kh = 0; kh < 8; ++kh) {
-                            const uint64_t da = dslide | (uint64_t)((a16_0 + (uint32_t)kh * row16) & 0x3FFFu);
-                            const uint64_t db = dhi | (uint64_t)(wres16 + (uint32_t)kh * kWgt16);
-                            const uint32_t on = (kh >= kh_lo && kh <= kh_hi) ? 1u : 0u;
+                            for (int kh = 0; kh < kH; ++kh) {
+                                const uint64_t da = dslide | (uint64_t)((a16_0 + (uint32_t)kh * row16) & 0x3FFFu);
+                                const uint64_t db = dhi | (uint64_t)(wres16 + (uint32_t)kh * kWgt16);
+                                const uint32_t on = (kh >= kh_lo && kh <= kh_hi && kh < kp.KH) ? 1u : 0u;
 #pragma unroll
-                            for (int k = 0; k < kMmaPerBlock; ++k)
-                                mma_i8_if(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kh > kh_lo || k > 0) ? 1u : 0u, on);
-                        }
+                                for (int k = 0; k < kMmaPerBlock; ++k)
+                                    mma_i8_if(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kh > kh_lo || k > 0) ? 1u : 0u, on);
+                            }
+                        };
+                        if (kp.KH <= 3) issue_rows(std::integral_constant<int, 3>());
+                        else if (kp.KH <= 5) issue_rows(std::integral_constant<int, 5>());
+                        else if (kp.KH <= 7) issue_rows(std::integral_constant<int, 7>());
+                        else issue_rows(std::integral_constant<int, 8>());
                     } else {
                         for (int kh = kh_lo; kh <= kh_hi; ++kh) {
                             const uint64_t da = dslide | (uint64_t)(a16_0 + (uint32_t)kh * row16);
