@@ -398,6 +398,11 @@ def test_quantize_into_the_plan_then_run_staged(checker, case):
     rng = np.random.default_rng(C + 17 * O)
     x = (rng.standard_normal((N, C, H, W)) * 50).astype(np.float32)
     x.reshape(-1)[::7] = np.round(x.reshape(-1)[::7]) + 0.5   # ties
+    # values the fast rounding forms must hand to the exact one: NaN, infinities, products beyond int32 (all -128 on the
+    # reference's CPU), and plain saturation
+    special = np.array([np.nan, np.inf, -np.inf, 3e9, -3e9, 300.0, -300.0, 127.5, -128.5], dtype=np.float32)
+    where = rng.permutation(x.size)[:special.size]
+    x.reshape(-1)[where] = special
     w = rng.integers(-127, 128, size=(O, C, KH, KW), dtype=np.int8)
     dq = rng.uniform(0.001, 0.01, size=O).astype(np.float32)
     bias = (rng.standard_normal(O) * 0.1).astype(np.float32)
