@@ -1098,6 +1098,19 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                         // thread some 50 cycles, so the sequence is as long as the filter is high, not always eight)
                         auto issue_rows = [&](auto height) {
                             constexpr int kH = decltype(height)::value;
+                            if (kh_lo == 0 && kh_hi == kH - 1) {
+                                // every filter row meets an input row (all output rows but those at the image's edge): no
+                                // predicates, accumulate flags known at compile time
+#pragma unroll
+                                for (int kh = 0; kh < kH; ++kh) {
+                                    const uint64_t da = dslide | (uint64_t)((a16_0 + (uint32_t)kh * row16) & 0x3FFFu);
+                                    const uint64_t db = dhi | (uint64_t)(wres16 + (uint32_t)kh * kWgt16);
+#pragma unroll
+                                    for (int k = 0; k < kMmaPerBlock; ++k)
+                                        mma_i8(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kh | k) ? 1u : 0u);
+                                }
+                                return;
+                            }
 #pragma unroll
                             for (int kh = 0; kh < kH; ++kh) {
                                 const uint64_t da = dslide | (uint64_t)((a16_0 + (uint32_t)kh * row16) & 0x3FFFu);
