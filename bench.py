@@ -272,18 +272,20 @@ def run_workbench_resnet(reps):
                     "inner_prod; built with the reference's graph API, compiled by Workbench::Load for device gpu",
            "timing": "wall clock around reps x (Workbench::input, Workbench::run, output view on the host), device idle at both ends"}
     for key, batch, mode in (("batch64_host_input", 64, 0), ("batch64_resident_input", 64, -1), ("batch1_resident_input", 1, -1)):
-        out = (ctypes.c_double * 6)()
+        out = (ctypes.c_double * 8)()
         msg = ctypes.create_string_buffer(512)
         rc = lib.tsb_workbench_resnet50(batch, 224, reps, mode, 3, out, msg, 512)
         if rc != 0:
             res[key] = {"error": msg.value.decode(errors="replace")[:300]}
             continue
         res[key] = {"ms_per_pass": out[0], "images_per_sec": batch / (out[0] / 1e3), "library_kernel_launches_per_pass": out[1],
-                    "fused_nodes_per_pass": out[2], "int8_handovers_per_pass": out[3], "shortcuts_in_epilogue_per_pass": out[4]}
+                    "fused_nodes_per_pass": out[2], "int8_handovers_per_pass": out[3], "shortcuts_in_epilogue_per_pass": out[4],
+                    "host_ms_inside_fused_operators": out[6]}
     one = res.get("batch1_resident_input", {})
     if "ms_per_pass" in one:
         # 53 fused nodes + pooling2d + global_pooling2d + flatten + inner_prod = 57 operator instructions per pass
         res["host_us_per_operator_upper_bound"] = one["ms_per_pass"] * 1e3 / 57
+        res["host_us_per_fused_operator_inside_plugin"] = one["host_ms_inside_fused_operators"] * 1e3 / 53
     return res
 
 

@@ -238,10 +238,16 @@ TSB_API int tsb_conv2d_i8_run(tsb_conv_plan *plan, const int8_t *x, int x_layout
  *  - tsb_conv2d_i8_status_async: only enqueues the 4-byte copy into `status_word_host` (pinned memory) on the
  *    stream -- no wait; the caller looks at the word once the stream has passed that point (an event, or its next
  *    synchronisation) and turns it into a status and message with tsb_conv2d_i8_status_decode.  This is how the
- *    TenniS operator checks without adding a synchronisation to the workbench's stream.
+ *  - tsb_conv2d_i8_set_status_word: the kernels of this plan report into `*device_visible_word` instead of the
+ *    workspace's first word (NULL: back to the workspace).  The word must be writable by the device for as long as the
+ *    plan runs: device memory, or -- what the TenniS operator does -- the device pointer of MAPPED pinned host memory
+ *    (cudaHostAlloc with cudaHostAllocMapped): nothing is written to it unless a wait gives up, and the host reads it as
+ *    plain memory, so checking costs neither a copy nor an event per run.  The caller zeroes the word before the first
+ *    run and after reporting a time-out; tsb_conv2d_i8_status / _status_async keep reading the workspace word.
  * tsb_conv2d_quantized_host (the waiting form) checks the word itself.
  */
 TSB_API int tsb_conv2d_i8_status(tsb_conv_plan *plan, void *workspace, void *stream);
+TSB_API int tsb_conv2d_i8_set_status_word(tsb_conv_plan *plan, int *device_visible_word);
 TSB_API int tsb_conv2d_i8_status_async(tsb_conv_plan *plan, void *workspace, int *status_word_host, void *stream);
 TSB_API int tsb_conv2d_i8_status_decode(int status_word);
 

@@ -75,6 +75,7 @@ SYMBOLS = {
     "tsb_conv2d_i8_run": (_i, [_vp, _vp, _i, ctypes.POINTER(ConvEpilogue), _vp, _sz, _vp]),
     "tsb_conv2d_i8_status": (_i, [_vp, _vp, _vp]),
     "tsb_conv2d_i8_status_async": (_i, [_vp, _vp, _vp, _vp]),
+    "tsb_conv2d_i8_set_status_word": (_i, [_vp, _vp]),
     "tsb_conv2d_i8_status_decode": (_i, [_i]),
     "tsb_conv2d_host_scratch_bytes": (_sz, [_vp]),
     "tsb_conv2d_quantized_host": (_i, [_vp, _vp, _fp, _i, _vp, _vp, _vp, _i, _f, _vp, _vp, _sz, _i, _vp]),

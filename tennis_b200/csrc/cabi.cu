@@ -51,6 +51,7 @@ struct tsb_conv_plan {
     int alt_valid;                   // staged configuration fits
     tsb::tc::Config cfg_stg[3];      // [1], [2]: configurations that set shared memory aside for the staged epilogue
     int stg_valid[3];
+    int *status_word = nullptr;      // where the kernels report a wait that gave up, when not the workspace's first word
     size_t off_weights, off_stage, ws_bytes;
     // state bound by set_weights / run
     const int8_t *weights_oihw;      // direct kernel reads the caller's tensor
@@ -382,7 +383,7 @@ int tsb_conv2d_i8_run(tsb_conv_plan *plan, const int8_t *x, int x_layout, const 
             plan->map_a_stg_ptr[level] = x_tc;
         }
         return tc::launch_conv_tc(plan->view, plan->cfg_stg[level], plan->map_a_stg[level], plan->map_b_stg[level], x_tc, epi,
-                                  static_cast<int *>(workspace), stream);
+                                  plan->status_word ? plan->status_word : static_cast<int *>(workspace), stream);
     }
     // Otherwise pixel-major fp32 tensors (a network's residuals and block outputs) are stored coalesced when a thread owns
     // a channel, i.e. in the swapped orientation; everything else follows the geometry heuristic.
@@ -396,14 +397,14 @@ int tsb_conv2d_i8_run(tsb_conv_plan *plan, const int8_t *x, int x_layout, const 
             if (st != TSB_OK) return st;
             plan->map_a_alt_ptr = x_tc;
         }
-        return tc::launch_conv_tc(plan->view, plan->cfg_alt, plan->map_a_alt, plan->map_b_alt, x_tc, epi, static_cast<int *>(workspace), stream);
+        return tc::launch_conv_tc(plan->view, plan->cfg_alt, plan->map_a_alt, plan->map_b_alt, x_tc, epi, plan->status_word ? plan->status_word : static_cast<int *>(workspace), stream);
     }
     if (plan->map_a_ptr != x_tc) {
         st = tc::encode_activation_map(plan->view, plan->cfg, x_tc, &plan->map_a);
         if (st != TSB_OK) return st;
         plan->map_a_ptr = x_tc;
     }
-    return tc::launch_conv_tc(plan->view, plan->cfg, plan->map_a, plan->map_b, x_tc, epi, static_cast<int *>(workspace), stream);
+    return tc::launch_conv_tc(plan->view, plan->cfg, plan->map_a, plan->map_b, x_tc, epi, plan->status_word ? plan->status_word : static_cast<int *>(workspace), stream);
 }
 
 // what each code of the status word means (the kernel's bounded waits, conv_tc.cu)
@@ -440,6 +441,12 @@ int tsb_conv2d_i8_status(tsb_conv_plan *plan, void *workspace, void *stream_) {
 int tsb_conv2d_i8_status_async(tsb_conv_plan *plan, void *workspace, int *status_word_host, void *stream_) {
     if (!plan || !workspace || !status_word_host) return fail(TSB_ERR_INVALID_ARGUMENT, "status_async: null pointer");
     TSB_CUDA(cudaMemcpyAsync(status_word_host, workspace, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream_));
+    return TSB_OK;
+}
+
+int tsb_conv2d_i8_set_status_word(tsb_conv_plan *plan, int *device_visible_word) {
+    if (!plan) return fail(TSB_ERR_INVALID_ARGUMENT, "set_status_word: null plan");
+    plan->status_word = device_visible_word;
     return TSB_OK;
 }
 

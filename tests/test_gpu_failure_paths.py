@@ -57,6 +57,42 @@ def test_a_timed_out_wait_is_reported_once_and_named():
     assert torch.equal(out, good)
 
 
+def test_status_word_can_live_in_mapped_host_memory():
+    """tsb_conv2d_i8_set_status_word: the plan's kernels report into a word the caller names.  With mapped pinned host
+    memory (what the TenniS operator uses) a healthy run leaves the word alone, and the host reads it as plain memory."""
+    from tennis_b200 import _lib
+    lib = _lib.load()
+    dev = torch.device("cuda")
+    plan, x, w, dq, out = small_plan(dev)
+    plan.run(x, _lib.LAYOUT_NCHW, dq, out_f32=out)
+    plan.status()
+    good = out.clone()
+    cudart = ctypes.CDLL("libcudart.so")
+    host = ctypes.c_void_p()
+    assert cudart.cudaHostAlloc(ctypes.byref(host), 4, 2) == 0              # 2 = cudaHostAllocMapped
+    try:
+        word = ctypes.cast(host, ctypes.POINTER(ctypes.c_int))
+        word[0] = 0
+        devptr = ctypes.c_void_p()
+        assert cudart.cudaHostGetDevicePointer(ctypes.byref(devptr), host, 0) == 0
+        _lib.check(lib.tsb_conv2d_i8_set_status_word(plan.handle, devptr))
+        plan.workspace[:4].copy_(torch.tensor([9, 0, 0, 0], dtype=torch.uint8))     # the workspace word is out of the loop now
+        out.zero_()
+        plan.run(x, _lib.LAYOUT_NCHW, dq, out_f32=out)
+        torch.cuda.synchronize()
+        assert word[0] == 0 and torch.equal(out, good)
+        assert int(plan.workspace[0]) == 9                                        # ... and untouched by the run
+        # what the host makes of a code found there
+        assert lib.tsb_conv2d_i8_status_decode(4) == _lib.ERR_DEVICE_TIMEOUT
+        _lib.check(lib.tsb_conv2d_i8_set_status_word(plan.handle, None))          # back to the workspace word
+        plan.workspace[:4].zero_()
+        plan.run(x, _lib.LAYOUT_NCHW, dq, out_f32=out)
+        plan.status()
+    finally:
+        torch.cuda.synchronize()
+        cudart.cudaFreeHost(host)
+
+
 def test_waiting_host_call_reports_the_status_word(checker):
     from tennis_b200 import _lib, workloads
     lib = _lib.load()

@@ -80,7 +80,7 @@ def test_resnet50_graph_on_gpu_device_equals_cpu_device():
     lib = ctypes.CDLL(path)
     lib.tsb_workbench_resnet50.argtypes = [ctypes.c_int] * 4 + [ctypes.c_uint, ctypes.POINTER(ctypes.c_double), ctypes.c_char_p,
                                            ctypes.c_int]
-    out = (ctypes.c_double * 6)()
+    out = (ctypes.c_double * 8)()
     msg = ctypes.create_string_buffer(512)
     rc = lib.tsb_workbench_resnet50(2, 64, 1, 17, 3, out, msg, 512)
     text = msg.value.decode(errors="replace")
