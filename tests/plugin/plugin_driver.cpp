@@ -285,3 +285,67 @@ int tsplug_selftest(int n, int c, int h, int w, int o, int k, int stride, int pa
         return -1;
     }
 }
+
+// The compile-time use of quantize (src/compiler/compiler.cpp:386-461: a node whose inputs are all constants is run once,
+// on the compiling workbench's device, and replaced by its result): a module that carries its convolution weights in fp32
+// with a quantize node behind them, one scale per output channel.  Compiled for the gpu device, that node runs through
+// this repo's quantize operator while the module is loaded; the graph's result must equal the cpu device's.
+extern "C" __attribute__((visibility("default")))
+int tsplug_const_weights(int n, int c, int h, int w, int o, int k, int stride, int pad, unsigned seed, char *msg, int msglen) {
+    try {
+        Case cs{n, c, h, w, o, k, stride, pad};
+        Data d = make_data(cs, seed);
+        std::mt19937 rng(seed + 7);
+        Tensor wf(FLOAT32, Shape({o, c, k, k}));
+        std::vector<float> wscales(o);
+        const int per_channel = c * k * k;
+        for (int oc = 0; oc < o; ++oc) {
+            float amax = 0;
+            for (int i = 0; i < per_channel; ++i) {
+                const float v = (float(rng() >> 8) / float(1 << 24) - 0.5f) * (0.2f + 0.01f * float(oc % 7));
+                wf.data<float>()[oc * per_channel + i] = v;
+                amax = std::max(amax, std::fabs(v));
+            }
+            wscales[oc] = 127.0f / amax;
+            d.dq[oc] = 1.0f / (wscales[oc] * d.qscales[0]);
+        }
+        auto run = [&](const std::string &device, int64_t *launches_at_load) {
+            Graph g;
+            ctx::bind<Graph> _graph(g);
+            auto x = bubble::param("x");
+            auto q = bubble::op("q", name::layer::quantize(), {x});
+            q.bubble().set(name::quantize_scale, float_vector(d.qscales));
+            auto wq = bubble::op("wq", name::layer::quantize(), {bubble::data("w32", wf)});
+            wq.bubble().set(name::quantize_scale, float_vector(wscales));
+            auto conv = bubble::op("conv", name::layer::conv2d_quantized(), {q, wq});
+            set_conv_params(conv.bubble(), cs, d);
+            auto biased = bubble::op("biased", name::layer::add_bias(), {conv, bubble::data("b", d.bias)});
+            biased.bubble().set(name::format, tensor::from("NCHW"));
+            auto y = bubble::op("y", name::layer::relu(), {biased});
+            std::shared_ptr<Module> m = std::make_shared<Module>();
+            m->load(g, {"y"});
+            ComputingDevice cd(device, 0);
+            const int64_t before = tsb_kernel_launch_count();
+            Workbench::shared bench = Workbench::Load(m, cd);
+            if (launches_at_load) *launches_at_load = tsb_kernel_launch_count() - before;
+            if (device == CPU) bench->runtime().set_computing_thread_number(1);
+            bench->input("x", d.x);
+            bench->run();
+            return bench->output("y").view(MemoryDevice(CPU)).clone();
+        };
+        Tensor y_cpu = run(CPU, nullptr);
+        int64_t at_load = 0;
+        const long fused0 = tsb_plugin_fused_runs();
+        Tensor y_gpu = run(GPU, &at_load);
+        const long fused = tsb_plugin_fused_runs() - fused0;
+        const long bad = mismatches_f32(y_cpu, y_gpu);
+        std::snprintf(msg, msglen, "constant weights: mismatches=%ld of %d; kernel launches while loading=%lld; fused operator runs=%ld",
+                      bad, y_cpu.count(), (long long) at_load, fused);
+        if (at_load < 1) return 2;       // the weights were not quantized by this library's operator at compile time
+        if (fused != 1) return 3;
+        return bad == 0 ? 0 : 1;
+    } catch (const std::exception &e) {
+        std::snprintf(msg, msglen, "exception: %s", e.what());
+        return -1;
+    }
+}

@@ -20,6 +20,7 @@ def driver():
     lib = ctypes.CDLL(DRIVER)
     lib.tsplug_selftest.argtypes = [ctypes.c_int] * 8 + [ctypes.c_uint, ctypes.c_char_p, ctypes.c_int]
     lib.tsplug_block.argtypes = [ctypes.c_int] * 6 + [ctypes.c_uint, ctypes.c_char_p, ctypes.c_int]
+    lib.tsplug_const_weights.argtypes = [ctypes.c_int] * 8 + [ctypes.c_uint, ctypes.c_char_p, ctypes.c_int]
     return lib
 
 
@@ -89,3 +90,17 @@ def test_resnet50_graph_on_gpu_device_equals_cpu_device():
     assert out[2] == 53 and out[3] == 32 and out[4] == 16, text
     # 53 convolutions + the staging quantize of each layer that reads an fp32 tensor (53 - 32 hand-overs)
     assert out[1] == 53 + 21, text
+
+
+@pytest.mark.parametrize("case", [
+    (2, 64, 14, 14, 96, 3, 1, 1),
+    (3, 40, 9, 9, 24, 1, 1, 0),       # 24 scales over 24 x 40 weights: groups of 40
+])
+def test_weights_quantized_at_compile_time_on_gpu(driver, case):
+    """A module that carries fp32 weights behind a quantize node (one scale per output channel): Workbench::Load folds
+    that node by running it once on the compiling device -- on gpu, through this repo's quantize operator."""
+    msg = ctypes.create_string_buffer(512)
+    rc = driver.tsplug_const_weights(*case, 9, msg, 512)
+    text = msg.value.decode(errors="replace")
+    assert rc == 0, text
+    assert "mismatches=0" in text and "fused operator runs=1" in text
