@@ -388,7 +388,7 @@ def run_resnet50(args, dev, rank, world, sharding, peaks):
             "images_per_sec": images / (ms_max / 1e3), "ms_per_batch": ms_max, "int8_conv_tops": ops_batch * world / (ms_max / 1e3) / 1e12,
             "e2e_images_per_sec": images / (e2e_max / 1e3), "e2e_ms_per_batch": e2e_max,
             "h2d_bytes_per_batch": hx.numel() * 4 * world, "d2h_bytes_per_batch": hout.numel() * 4 * world,
-            "kernels_per_pass": 53 + 4, "parity": parity,
+            "kernels_per_pass": 49 + 4, "projections_inside_conv3": 4, "parity": parity,
             "pass_roofline": pass_roofline(layer_times, ms_max, peaks, extra_bytes=glue_bytes) if layer_times else None,
             "layers": layer_table(layer_times, peaks),
             "config4": config4, "workbench": workbench}

@@ -228,6 +228,24 @@ TSB_API int tsb_conv2d_i8_quantize_input(tsb_conv_plan *plan, const float *x_f32
  */
 TSB_API int tsb_conv2d_i8_run(tsb_conv_plan *plan, const int8_t *x, int x_layout, const tsb_conv_epilogue *epilogue,
                       void *workspace, size_t workspace_bytes, void *stream);
+/*
+ * A residual block's expansion convolution and its projection shortcut in ONE launch.  In a TenniS graph the two are
+ *   add( add_bias(dequantize(conv2d_quantized(x, w))), add_bias(dequantize(conv2d_quantized(x_shortcut, w_shortcut))) )
+ * followed by the activation (src/kernels/cpu/math_cpu.cpp add; doc/zh_CN/operators.md conv2d_quantized): `shortcut` is
+ * the plan of the projection -- a 1x1 convolution of any stride without padding whose output shape equals `plan`'s --
+ * and its dequantized (+ shortcut_bias, may be NULL) fp32 result takes the place of epilogue->residual (which must be
+ * NULL; residual_after_activation keeps its meaning).  Every fp32 step is rounded separately, as when the projection is
+ * run on its own and handed over as a residual tensor, so the results are the same bits; the projection's fp32 output is
+ * never written to or read from global memory.  Both inputs are NHWC_PAD int8, 16-byte aligned; the outputs are
+ * pixel-major fp32 and / or NHWC_PAD int8 with half-away rounding (one requantize scale or one per image); both plans
+ * have had tsb_conv2d_i8_set_weights.  shortcut_dequantize_scales and shortcut_bias are device arrays of O floats.
+ * tile_channels: 0 = the library chooses, 128 or 256 = output channels per tile (a tuning override for tests).
+ * Returns TSB_ERR_UNSUPPORTED for anything else; the caller then runs the two convolutions one after the other.
+ */
+TSB_API int tsb_conv2d_i8_run_projected(tsb_conv_plan *plan, const int8_t *x, tsb_conv_plan *shortcut,
+                                        const int8_t *x_shortcut, const float *shortcut_dequantize_scales,
+                                        const float *shortcut_bias, const tsb_conv_epilogue *epilogue, int tile_channels,
+                                        void *workspace, size_t workspace_bytes, void *stream);
 
 /*
  * Failure detection.  Every wait inside the tensor-core kernel is bounded; a wait that runs out makes the kernel

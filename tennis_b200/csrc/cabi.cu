@@ -407,6 +407,46 @@ int tsb_conv2d_i8_run(tsb_conv_plan *plan, const int8_t *x, int x_layout, const 
     return tc::launch_conv_tc(plan->view, plan->cfg, plan->map_a, plan->map_b, x_tc, epi, plan->status_word ? plan->status_word : static_cast<int *>(workspace), stream);
 }
 
+int tsb_conv2d_i8_run_projected(tsb_conv_plan *plan, const int8_t *x, tsb_conv_plan *shortcut, const int8_t *x_shortcut,
+                                const float *shortcut_dequantize_scales, const float *shortcut_bias,
+                                const tsb_conv_epilogue *epilogue, int tile_channels, void *workspace, size_t workspace_bytes,
+                                void *stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (!plan || !shortcut || !x || !x_shortcut || !shortcut_dequantize_scales || !epilogue || !workspace)
+        return fail(TSB_ERR_INVALID_ARGUMENT, "run_projected: null pointer");
+    if (workspace_bytes < plan->ws_bytes) return fail(TSB_ERR_WORKSPACE_TOO_SMALL, "run_projected: workspace %zu < %zu", workspace_bytes, plan->ws_bytes);
+    if (plan->weights_ws != workspace || !plan->weights_oihw || !shortcut->weights_ws || !shortcut->weights_oihw)
+        return fail(TSB_ERR_INVALID_ARGUMENT, "run_projected: tsb_conv2d_i8_set_weights was not called on both plans");
+    if (tile_channels != 0 && tile_channels != 128 && tile_channels != 256) return fail(TSB_ERR_INVALID_ARGUMENT, "run_projected: tile_channels takes 0, 128 or 256");
+    if (plan->kernel != TSB_KERNEL_TCGEN05 || shortcut->kernel != TSB_KERNEL_TCGEN05)
+        return fail(TSB_ERR_UNSUPPORTED, "run_projected: both convolutions must run on the tcgen05 kernel");
+    if (epilogue->residual) return fail(TSB_ERR_INVALID_ARGUMENT, "run_projected: the projection is the residual; epilogue->residual must be null");
+    const char *why = "";
+    if (!tc::dual_supported(plan->view, shortcut->view, &why)) return fail(TSB_ERR_UNSUPPORTED, "run_projected: %s", why);
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(x_shortcut)) % 16) return fail(TSB_ERR_INVALID_ARGUMENT, "run_projected: inputs must be 16-byte aligned");
+    EpiParams epi;
+    int st = build_epilogue(plan, epilogue, &epi);
+    if (st != TSB_OK) return st;
+    epi.res_after = epilogue->residual_after_activation ? 1 : 0;
+    int sms = 148, dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+    const tc::Config cfg = tc::choose_config_dual(plan->view, shortcut->view, sms, tile_channels);
+    if (cfg.stages < 2 || cfg.dyn_smem > 227u * 1024u) return fail(TSB_ERR_UNSUPPORTED, "run_projected: the pair does not fit shared memory");
+    CUtensorMap map_a, map_b;
+    tc::DualArgs dual;
+    dual.view = &shortcut->view;
+    dual.dq = shortcut_dequantize_scales;
+    dual.bias = shortcut_bias;
+    const int8_t *wp = static_cast<const int8_t *>(workspace) + plan->off_weights;
+    const int8_t *wp2 = static_cast<const int8_t *>(shortcut->weights_ws) + shortcut->off_weights;
+    if ((st = tc::encode_activation_map(plan->view, cfg, x, &map_a)) != TSB_OK) return st;
+    if ((st = tc::encode_weight_map(plan->view, cfg, wp, &map_b)) != TSB_OK) return st;
+    if ((st = tc::encode_activation_map(shortcut->view, cfg, x_shortcut, &dual.map_a)) != TSB_OK) return st;
+    if ((st = tc::encode_weight_map(shortcut->view, cfg, wp2, &dual.map_b)) != TSB_OK) return st;
+    return tc::launch_conv_tc(plan->view, cfg, map_a, map_b, x, epi, plan->status_word ? plan->status_word : static_cast<int *>(workspace), stream, &dual);
+}
+
 // what each code of the status word means (the kernel's bounded waits, conv_tc.cu)
 static const char *wait_name(int code) {
     switch (code) {

@@ -40,16 +40,15 @@ struct EpiParams {
 };
 
 #ifdef __CUDACC__
-// One output element (image n, channel o, pixel p).
-__device__ __forceinline__ void epilogue_store_one(const EpiParams &e, int n, int o, int p, int acc) {
+// One output element (image n, channel o, pixel p) with the residual value handed in.
+__device__ __forceinline__ void epilogue_store_value(const EpiParams &e, int n, int o, int p, int acc, float res, bool has_res) {
     const uint32_t nchw = (uint32_t)(n * e.O + o) * (uint32_t)e.P + (uint32_t)p;
     const uint32_t nhwc = (uint32_t)(n * e.P + p) * (uint32_t)e.O + (uint32_t)o;
     if (e.out_acc) e.out_acc[nchw] = acc;
     if (!e.out_f32 && !e.out_i8) return;
     EpilogueMath math{e.activation, e.leaky};
     const uint32_t fidx = e.f32_nhwc ? nhwc : nchw;
-    const float v = math(acc, e.dq[o], e.bias ? e.bias[o] : 0.0f, e.bias != nullptr,
-                         e.residual ? e.residual[fidx] : 0.0f, e.residual != nullptr, e.res_after != 0);
+    const float v = math(acc, e.dq[o], e.bias ? e.bias[o] : 0.0f, e.bias != nullptr, res, has_res, e.res_after != 0);
     if (e.out_f32) e.out_f32[fidx] = v;
     if (e.out_i8) {
         const uint32_t g = e.nscales == 1 ? 0u : nchw / e.group_len;
@@ -59,6 +58,11 @@ __device__ __forceinline__ void epilogue_store_one(const EpiParams &e, int n, in
             e.out_i8[qidx] = (int8_t)q;
         }
     }
+}
+// One output element (image n, channel o, pixel p); the residual, if any, read from e.residual.
+__device__ __forceinline__ void epilogue_store_one(const EpiParams &e, int n, int o, int p, int acc) {
+    const uint32_t fidx = e.f32_nhwc ? (uint32_t)(n * e.P + p) * (uint32_t)e.O + (uint32_t)o : (uint32_t)(n * e.O + o) * (uint32_t)e.P + (uint32_t)p;
+    epilogue_store_value(e, n, o, p, acc, e.residual ? e.residual[fidx] : 0.0f, e.residual != nullptr);
 }
 #endif
 

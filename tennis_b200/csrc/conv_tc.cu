@@ -749,6 +749,18 @@ __device__ __forceinline__ void rows_span(const KernelParams &kp, int oh, int &k
 }
 
 constexpr int kModeGeneral = 0, kModeRows = 1, kModePatch = 2;
+
+// Projected-shortcut kernels (DUAL): a second, 1x1 convolution over the same output pixels (the projection shortcut of a
+// residual block: its own input, weights, dequantize scales and bias) runs in the same tile, into a second accumulator,
+// ahead of the main convolution; the epilogue dequantizes it (+ bias) and uses the result as the main convolution's
+// residual.  The projection's fp32 output never exists in global memory.
+struct alignas(64) DualParams {
+    CUtensorMap map_a2, map_b2;   // the projection's activations ([M][Cp2] tiles or a 1x1 im2col walk with its stride) and weights
+    const float *dq2, *bias2;     // its dequantize scales and (optional) bias, per output channel
+    int k2_iters;                 // its K blocks per tile: Cp2 / BK
+    int Cp2, a2_tiled, sh2, sw2;
+};
+struct NoDual {};
 constexpr int kMaxStages = 24;
 constexpr uint32_t kMaxDynamicSmem = 227 * 1024;
 
@@ -762,12 +774,14 @@ __host__ __device__ constexpr uint32_t num_barriers(int stages) { return 2u * (u
 // instruction where N = O would leave it half or three-quarters empty.
 // MODE: how activations reach shared memory -- kModeGeneral (im2col or plain 2-D tile loads), kModeRows (raw-row), kModePatch.
 // A compile-time parameter: the role loops of each mode stay short and keep their registers.
-template <int BN, int BK, bool SWAP, int MODE>
+template <int BN, int BK, bool SWAP, int MODE, bool DUAL = false>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_of,
                   const __grid_constant__ CUtensorMap map_oi, const __grid_constant__ KernelParams kp,
-                  const __grid_constant__ EpiParams epi) {
+                  const __grid_constant__ EpiParams epi,
+                  const __grid_constant__ std::conditional_t<DUAL, DualParams, NoDual> dual) {
+    static_assert(!DUAL || (!SWAP && MODE == kModeGeneral && BN >= 128), "projected-shortcut kernels: normal orientation, general mode");
     constexpr int PIX = SWAP ? BN : kBM;      // pixels per tile
     constexpr int CH = SWAP ? kBM : BN;       // output channels per tile
     constexpr uint32_t kPixBytes = PIX * BK, kWgtBytes = CH * BK;
@@ -797,6 +811,8 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_tiles = kp.num_m_tiles * kp.num_n_tiles;
     const int k_iters = kp.KH * kp.KW * (kp.Cp / BK);
+    int k_sc = 0;                              // K blocks of the projection, which come first in every tile
+    if constexpr (DUAL) k_sc = dual.k2_iters;
     // This CTA's tiles.  Streaming weights: tiles blockIdx.x, +gridDim.x, ... with the channel tile running fastest.
     // Resident weights: one contiguous range of the channel-major tile order, so the weight tile changes at most a
     // few times.
@@ -805,7 +821,8 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const int my_tiles = kp.b_resident ? tile_hi - tile_lo : (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
     // Accumulator buffers in use = epilogue groups: as many as tensor memory holds (kBufs), but no more than this CTA has
     // tiles -- a CTA with a single tile puts all sixteen epilogue warps on it.
-    const int nbuf = my_tiles >= 4 && kBufs >= 4 ? 4 : (my_tiles >= 2 ? 2 : 1);
+    // (a projected-shortcut tile holds two accumulators: buffers 2a and 2a+1 of logical buffer a)
+    const int nbuf = DUAL ? ((kBufs >= 4 && my_tiles >= 2) ? 2 : 1) : (my_tiles >= 4 && kBufs >= 4 ? 4 : (my_tiles >= 2 ? 2 : 1));
     auto decode = [&](int i, int &m_tile, int &n_tile) {   // m_tile: pixel tile, n_tile: channel tile
         if (kp.b_resident) {
             const int t = tile_lo + i;
@@ -863,9 +880,12 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                         if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 5); }
                         break;
                     }
-                    mbar_arrive_expect_tx(bar_bfull, (uint32_t)k_iters * kWgtBytes);
+                    mbar_arrive_expect_tx(bar_bfull, (uint32_t)(k_iters + k_sc) * kWgtBytes);
+                    if constexpr (DUAL)
+                        for (int it = 0; it < k_sc; ++it)
+                            tma_load_2d(w_res + (uint32_t)it * kWgtBytes, &dual.map_b2, bar_bfull, it * BK, n_tile * CH);
                     for (int it = 0; it < k_iters; ++it)
-                        tma_load_2d(w_res + (uint32_t)it * kWgtBytes, &map_b, bar_bfull, it * BK, n_tile * CH);
+                        tma_load_2d(w_res + (uint32_t)(k_sc + it) * kWgtBytes, &map_b, bar_bfull, it * BK, n_tile * CH);
                     cur_n = n_tile;
                     ++w_loads;
                 }
@@ -907,6 +927,27 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     }
                 } else {
                     int gk = 0;   // K block inside the current stage
+                    if constexpr (DUAL) {
+                        const int wc2 = ow * dual.sw2, hc2 = oh * dual.sh2;   // the projection: 1x1, no padding
+                        for (int cb = 0; cb < dual.Cp2; cb += BK) {
+                            if (gk == 0) {
+                                if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) {
+                                    if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 1); }
+                                    ok = false;
+                                    break;
+                                }
+                                mbar_arrive_expect_tx(bar_full + 8 * stage, (uint32_t)kp.kgroup * (kp.b_resident ? kPixBytes : kPixBytes + kWgtBytes));
+                            }
+                            const uint32_t sp = base + stage * kp.stage_bytes + (uint32_t)gk * kp.unit_bytes, sw = sp + kPixBytes;
+                            if (dual.a2_tiled) tma_load_2d(sp, &dual.map_a2, bar_full + 8 * stage, cb, m0);
+                            else tma_load_im2col_4d(sp, &dual.map_a2, bar_full + 8 * stage, cb, wc2, hc2, img, (uint16_t)0, (uint16_t)0);
+                            if (!kp.b_resident) tma_load_2d(sw, &dual.map_b2, bar_full + 8 * stage, cb, n_tile * CH);
+                            if (++gk == kp.kgroup) {
+                                gk = 0;
+                                if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                            }
+                        }
+                    }
                     for (int kh = 0; kh < kp.KH && ok; ++kh)
                         for (int kw = 0; kw < kp.KW && ok; ++kw)
                             for (int cb = 0; cb < kp.Cp; cb += BK) {
@@ -963,13 +1004,14 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             int first_m = 0, first_n = 0, last_m = 0, last_n = 0;
             if (my_tiles > 0) { decode(0, first_m, first_n); decode(my_tiles - 1, last_m, last_n); }
             // pipeline stages a tile consumes
-            const int spt = MODE == kModePatch ? kp.Cp / BK : (MODE == kModeRows ? 1 : k_iters / kp.kgroup);
+            const int spt = MODE == kModePatch ? kp.Cp / BK : (MODE == kModeRows ? 1 : (k_iters + k_sc) / kp.kgroup);
             // A barrier wait names a phase by its parity only, so a waiter must never be two rounds of the stage ring away
             // from the phase it means.  With several issuers that holds when the ring has room for one tile of each
             // (kStages >= issuers * spt): the round before the one an issuer waits for then lies in tiles that were
             // loaded before its own previous tile, whose loads it has seen complete.
             const bool shared_state = (MODE == kModeRows && kp.rows_segs > 1) || (resident && first_n != last_n);
-            const int issuers = (shared_state || kStages < kIssuers * spt) ? 1 : kIssuers;
+            // (an issuer must also own its accumulator buffers: with a single logical buffer one thread takes every tile)
+            const int issuers = (shared_state || kStages < kIssuers * spt || (DUAL && nbuf < kIssuers)) ? 1 : kIssuers;
             const int me = warp - 1;
             int stage = 0; uint32_t phase = 0;
             auto advance = [&](int n) {      // move n stages on (n >= 0)
@@ -1008,7 +1050,7 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 }
                 tc_fence_after();
                 if (me == 0) TSB_TRACE(local, 2);
-                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                uint32_t d_tmem = tmem_base + (uint32_t)(DUAL ? (2 * acc + 1) * BN : acc * BN);   // DUAL: the projection's accumulator first
                 uint32_t accumulate = 0;
                 if (MODE == kModePatch) {
                     const int n_cb = kp.Cp / BK;
@@ -1159,7 +1201,8 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                             }
                         }
                     };
-                    for (int it = 0; it < k_iters; it += G) {
+                    for (int it = 0; it < k_iters + k_sc; it += G) {
+                        if (DUAL && it == k_sc) { d_tmem -= BN; accumulate = 0u; }   // the main convolution's accumulator
                         TSB_CYC_START;
                         if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
                             if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 3); }
@@ -1223,7 +1266,8 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             int m_tile, n_tile;
             decode(local, m_tile, n_tile);
             const int o_base = n_tile * CH;
-            float *t_dq = table + acc * 2 * BN, *t_bias = t_dq + BN;
+            const int slot = DUAL ? 2 * acc : acc;          // first accumulator buffer (and table) of this tile
+            float *t_dq = table + slot * 2 * BN, *t_bias = t_dq + BN;
             if (!SWAP && n_tile != table_n) {
                 // this group's table of per-channel scales and biases: rebuilt only when the channel tile changes (never, for
                 // layers of at most BN channels), between two barriers of the group
@@ -1232,6 +1276,10 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     const int o = o_base + j;
                     t_dq[j] = o < epi.O ? epi.dq[o] : 0.0f;
                     t_bias[j] = (o < epi.O && epi.bias) ? epi.bias[o] : 0.0f;
+                    if constexpr (DUAL) {                   // the projection's table: the next slot
+                        t_dq[2 * BN + j] = o < epi.O ? dual.dq2[o] : 0.0f;
+                        t_dq[3 * BN + j] = (o < epi.O && dual.bias2) ? dual.bias2[o] : 0.0f;
+                    }
                 }
                 asm volatile("bar.sync %0, %1;" ::"r"(1 + group), "r"(group_threads) : "memory");
                 table_n = n_tile;
@@ -1249,7 +1297,7 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             // (outputs are then garbage) -- shows how fast the other two roles run when left alone
             if (kp.trace && kp.trace[255] != 0) { tc_fence_before(); mbar_arrive(bar_tempty + 8 * acc); continue; }
 #endif
-            const uint32_t taddr0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+            const uint32_t taddr0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(slot * BN);
             if (!SWAP) {
                 int m = m_tile * PIX + row;
                 bool live = m < kp.M_total;
@@ -1321,6 +1369,27 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                         const int col0 = c * 32;
                         const bool real = o_base + col0 < epi.O;      // false: nothing but the int8 output's channel padding
                         int v[32];
+                        if constexpr (DUAL) {
+                            // the projection's 32 channels of this pixel, dequantized (+ bias), into the thread's own row of
+                            // the fp32 tile -- where a tensor-map load would have put a residual
+                            if (real) {
+                                tmem_ld32(taddr0 + (uint32_t)(BN + col0), v);
+                                tmem_ld_wait();
+                                const bool bias2 = dual.bias2 != nullptr;
+#pragma unroll
+                                for (int j4 = 0; j4 < 8; ++j4) {
+                                    const float4 d4 = *reinterpret_cast<const float4 *>(t_dq + 2 * BN + col0 + 4 * j4);
+                                    const float4 b4 = *reinterpret_cast<const float4 *>(t_dq + 3 * BN + col0 + 4 * j4);
+                                    float4 f;
+                                    f.x = __fmul_rn(__int2float_rn(v[4 * j4 + 0]), d4.x);
+                                    f.y = __fmul_rn(__int2float_rn(v[4 * j4 + 1]), d4.y);
+                                    f.z = __fmul_rn(__int2float_rn(v[4 * j4 + 2]), d4.z);
+                                    f.w = __fmul_rn(__int2float_rn(v[4 * j4 + 3]), d4.w);
+                                    if (bias2) { f.x = __fadd_rn(f.x, b4.x); f.y = __fadd_rn(f.y, b4.y); f.z = __fadd_rn(f.z, b4.z); f.w = __fadd_rn(f.w, b4.w); }
+                                    r_row[j4 ^ key] = f;
+                                }
+                            }
+                        }
                         if (real) tmem_ld32(taddr0 + (uint32_t)col0, v);
                         else {
 #pragma unroll
@@ -1333,8 +1402,8 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                         if (real) tmem_ld_wait();
                         bool fine = true;
                         if (stg_ok) {
-                            if (epi.res_after) TSB_EPI_DISPATCH_W(fine =, staged_chunk_t, true, v, t_dq + col0, t_bias + col0, epi.leaky, r_row, key, real && has_res, has_f32, q_row, has_i8, rs);
-                            else TSB_EPI_DISPATCH_W(fine =, staged_chunk_t, false, v, t_dq + col0, t_bias + col0, epi.leaky, r_row, key, real && has_res, has_f32, q_row, has_i8, rs);
+                            if (epi.res_after) TSB_EPI_DISPATCH_W(fine =, staged_chunk_t, true, v, t_dq + col0, t_bias + col0, epi.leaky, r_row, key, real && (has_res || DUAL), has_f32, q_row, has_i8, rs);
+                            else TSB_EPI_DISPATCH_W(fine =, staged_chunk_t, false, v, t_dq + col0, t_bias + col0, epi.leaky, r_row, key, real && (has_res || DUAL), has_f32, q_row, has_i8, rs);
                         }
                         fence_async_smem();
                         // all four warps have written their rows; the OR says whether any value needs the exact slow path
@@ -1358,8 +1427,14 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                             for (int j = 0; j < 32; ++j) {
                                 const int o = o_base + col0 + j;
                                 const int a = real ? tmem_ld1(taddr0 + (uint32_t)(col0 + j)) : 0;
+                                int a2 = 0;
+                                if constexpr (DUAL) a2 = real ? tmem_ld1(taddr0 + (uint32_t)(BN + col0 + j)) : 0;
                                 if (!live) continue;
-                                if (o < epi.O) epilogue_store_one(epi, img, o, p, a);
+                                if (DUAL && o < epi.O) {
+                                    float r = __fmul_rn(__int2float_rn(a2), t_dq[2 * BN + col0 + j]);
+                                    if constexpr (DUAL) { if (dual.bias2) r = __fadd_rn(r, t_dq[3 * BN + col0 + j]); }
+                                    epilogue_store_value(epi, img, o, p, a, r, true);
+                                } else if (o < epi.O) epilogue_store_one(epi, img, o, p, a);
                                 else if (has_i8 && epi.i8_nhwc && o < epi.out_cp) epi.out_i8[(size_t)m * epi.out_cp + o] = 0;
                             }
                         }
@@ -1589,13 +1664,14 @@ CUtensorMapSwizzle swizzle_for(int bk) {
     return bk == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (bk == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
 }
 
-template <int BN, int BK, bool SWAP, int MODE>
+template <int BN, int BK, bool SWAP, int MODE, bool DUAL = false>
 int launch(const Config &cfg, const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mr, const CUtensorMap &mof,
-           const CUtensorMap &moi, const KernelParams &kp, const EpiParams &epi, cudaStream_t stream) {
+           const CUtensorMap &moi, const KernelParams &kp, const EpiParams &epi, cudaStream_t stream,
+           const std::conditional_t<DUAL, DualParams, NoDual> &dual = {}) {
     // The shared-memory limit of a kernel is a per-device attribute: one process may drive several GPUs (one TenniS
     // Workbench per device, each on its own thread), so the "already raised" note is kept per device.
     static std::atomic<uint64_t> configured{0};
-    auto kernel = conv_i8_tc_kernel<BN, BK, SWAP, MODE>;
+    auto kernel = conv_i8_tc_kernel<BN, BK, SWAP, MODE, DUAL>;
     int dev = 0;
     TSB_CUDA(cudaGetDevice(&dev));
     const uint64_t bit = dev >= 0 && dev < 64 ? 1ull << dev : 0;
@@ -1603,7 +1679,7 @@ int launch(const Config &cfg, const CUtensorMap &ma, const CUtensorMap &mb, cons
         TSB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynamicSmem));
         configured.fetch_or(bit, std::memory_order_release);
     }
-    TSB_CUDA(launch_pdl(kernel, dim3(cfg.grid), dim3(kThreads), cfg.dyn_smem, stream, ma, mb, mr, mof, moi, kp, epi));
+    TSB_CUDA(launch_pdl(kernel, dim3(cfg.grid), dim3(kThreads), cfg.dyn_smem, stream, ma, mb, mr, mof, moi, kp, epi, dual));
     TSB_LAUNCHED("conv_i8_tc_kernel");
     return TSB_OK;
 }
@@ -1816,6 +1892,68 @@ Config choose_config(const View &v, const Tuning &tune, int sm_count, int orient
     return c;
 }
 
+bool dual_supported(const View &v, const View &sc, const char **why) {
+    const ConvGeom &g = v.g, &s = sc.g;
+    *why = "";
+    if (v.fold || v.rows || sc.fold || sc.rows) { *why = "folded inputs (at most 16 channels)"; return false; }
+    if (s.KH != 1 || s.KW != 1 || s.pad_t != 0 || s.pad_l != 0) { *why = "the projection must be a 1x1 convolution without padding"; return false; }
+    if (s.N != g.N || s.O != g.O || s.OH != g.OH || s.OW != g.OW) { *why = "the projection's output shape differs"; return false; }
+    if ((s.H - 1) / s.sh + 1 != s.OH || (s.W - 1) / s.sw + 1 != s.OW) { *why = "the projection's padding is not zero on every side"; return false; }
+    if (g.O % 4 != 0) { *why = "output channels not a multiple of 4"; return false; }
+    return true;
+}
+
+Config choose_config_dual(const View &v, const View &sc, int sm_count, int bn) {
+    const ConvGeom &g = v.g, &s = sc.g;
+    Config c;
+    c.bk = (g.Cp % 128 == 0 && s.Cp % 128 == 0) ? 128 : 64;
+    c.swap = 0;
+    // 128 channels per tile: four accumulator buffers hold two tiles, so the MMAs of one tile run under the epilogue of
+    // the other (256 would fill tensor memory with a single tile; measured 10-25 % slower on the ResNet-50 shapes)
+    c.bn = bn == 128 || bn == 256 ? bn : 128;
+    c.pix = kBM;
+    c.ch = c.bn;
+    const int64_t M = (int64_t)g.N * g.OH * g.OW;
+    c.num_m_tiles = (int)ceil_div64(M, c.pix);
+    c.num_n_tiles = ceil_div(g.O, c.ch);
+    const int64_t tiles = (int64_t)c.num_m_tiles * c.num_n_tiles;
+    c.grid = (int)(tiles < sm_count ? tiles : sm_count);
+    const uint32_t stg_bytes = kQuads * (kStageF32Bytes + kStageI8Bytes);
+    const uint32_t budget = kSmemBudget - stg_bytes;
+    const uint32_t p_bytes = (uint32_t)c.pix * c.bk, w_bytes = (uint32_t)c.ch * c.bk;
+    const uint32_t k1 = (uint32_t)g.KH * g.KW * (g.Cp / c.bk), k2 = (uint32_t)(s.Cp / c.bk);
+    const uint32_t w_total = (k1 + k2) * w_bytes;
+    // K blocks per stage: a stage never mixes the two convolutions, so the group divides both block counts
+    auto group_for = [&](uint32_t unit, uint32_t room) {
+        for (int gsz = 4; gsz >= 2; gsz /= 2)
+            if (k1 % (uint32_t)gsz == 0 && k2 % (uint32_t)gsz == 0 && (uint32_t)gsz * unit <= 48 * 1024 && room / ((uint32_t)gsz * unit) >= 3) return gsz;
+        return 1;
+    };
+    if (tiles > c.grid && w_total <= 128 * 1024 && w_total < budget && (budget - w_total) / p_bytes >= 4) {
+        c.b_resident = 1;
+        c.unit_bytes = p_bytes;
+        c.kgroup = group_for(p_bytes, budget - w_total);
+        c.stage_bytes = (uint32_t)c.kgroup * p_bytes;
+        c.stages = std::min<int>(kMaxStages, (int)((budget - w_total) / c.stage_bytes));
+        c.b_off = (uint32_t)c.stages * c.stage_bytes;
+        c.bar_off = c.b_off + w_total;
+    } else {
+        c.b_resident = 0;
+        c.unit_bytes = p_bytes + w_bytes;
+        c.kgroup = group_for(c.unit_bytes, budget);
+        c.stage_bytes = (uint32_t)c.kgroup * c.unit_bytes;
+        c.stages = std::min<int>(kMaxStages, (int)(budget / c.stage_bytes));
+        c.b_off = 0;
+        c.bar_off = (uint32_t)c.stages * c.stage_bytes;
+    }
+    c.staging = 2;
+    c.stg_off = (c.bar_off + 1023u) & ~1023u;
+    c.bar_off = c.stg_off + stg_bytes;
+    const uint32_t tables = ((c.bar_off + 8 * num_barriers(c.stages) + 8 + 15) & ~15u) + kMaxAccBufs * 2 * (uint32_t)c.bn * 4;
+    c.dyn_smem = tables + 1024;
+    return c;
+}
+
 int encode_weight_map(const View &v, const Config &cfg, const int8_t *w_packed, CUtensorMap *map) {
     int st = load_driver();
     if (st != TSB_OK) return st;
@@ -1958,8 +2096,16 @@ int stage_folded(const View &v, const int8_t *x, int x_nhwc, int8_t *staged, cud
 }
 
 int launch_conv_tc(const View &v, const Config &cfg, const CUtensorMap &map_a, const CUtensorMap &map_b,
-                   const int8_t *x_staged, const EpiParams &epi, int *status_word, cudaStream_t stream) {
+                   const int8_t *x_staged, const EpiParams &epi, int *status_word, cudaStream_t stream, const DualArgs *dual) {
     const ConvGeom &g = v.g;
+    if (dual) {
+        // the projected-shortcut kernels exist for the staged block epilogue only
+        const bool i8_ok = !epi.out_i8 || (epi.i8_nhwc && epi.rne_limit == 0 && reinterpret_cast<uintptr_t>(epi.out_i8) % 16 == 0 &&
+                                           (epi.nscales == 1 || (epi.nscales == g.N && epi.group_len == (uint32_t)(g.O * g.OH * g.OW))));
+        const bool f32_ok = !epi.out_f32 || (epi.f32_nhwc && reinterpret_cast<uintptr_t>(epi.out_f32) % 16 == 0);
+        if (epi.out_acc || epi.residual || !i8_ok || !f32_ok || g.O % 4 != 0 || cfg.swap || cfg.patch || v.rows || v.fold || cfg.staging != 2)
+            return fail(TSB_ERR_UNSUPPORTED, "projected shortcut: needs pixel-major fp32 / NHWC_PAD int8 outputs with half-away rounding, no residual tensor, O %% 4 == 0");
+    }
     KernelParams kp;
     kp.M_total = g.N * g.OH * g.OW;
     kp.OW = g.OW;
@@ -2036,7 +2182,7 @@ int launch_conv_tc(const View &v, const Config &cfg, const CUtensorMap &map_a, c
     CUtensorMap map_of = map_b, map_oi = map_b;
     kp.stg_off = cfg.stg_off;
     kp.stg_f32 = cfg.staging == 2 ? 1 : 0;
-    const int want_staging = cfg.swap ? 0 : staging_level(v, epi);
+    const int want_staging = dual ? 2 : (cfg.swap ? 0 : staging_level(v, epi));
     if (want_staging != 0 && cfg.staging >= want_staging && load_driver() == TSB_OK) {
         const ConvGeom &r = v.real;
         auto encode = [&](CUtensorMap *map, const void *ptr, bool is_f32, uint64_t channels) -> bool {
@@ -2075,6 +2221,19 @@ int launch_conv_tc(const View &v, const Config &cfg, const CUtensorMap &map_a, c
             kp.res_prefetch = 0;
             kp.stg_f32 = cfg.staging == 2 ? 1 : 0;
         }
+    }
+    if (dual) {
+        if (kp.epi_mode != kEpiStaged) return fail(TSB_ERR_UNSUPPORTED, "projected shortcut: the output tensor maps could not be encoded");
+        const ConvGeom &s = dual->view->g;
+        DualParams dp;
+        dp.map_a2 = dual->map_a; dp.map_b2 = dual->map_b;
+        dp.dq2 = dual->dq; dp.bias2 = dual->bias;
+        dp.k2_iters = s.Cp / cfg.bk; dp.Cp2 = s.Cp; dp.a2_tiled = dual->view->a_tiled; dp.sh2 = s.sh; dp.sw2 = s.sw;
+        if (cfg.bn == 256 && cfg.bk == 64) return launch<256, 64, false, kModeGeneral, true>(cfg, map_a, map_b, map_r, map_of, map_oi, kp, epi, stream, dp);
+        if (cfg.bn == 256 && cfg.bk == 128) return launch<256, 128, false, kModeGeneral, true>(cfg, map_a, map_b, map_r, map_of, map_oi, kp, epi, stream, dp);
+        if (cfg.bn == 128 && cfg.bk == 64) return launch<128, 64, false, kModeGeneral, true>(cfg, map_a, map_b, map_r, map_of, map_oi, kp, epi, stream, dp);
+        if (cfg.bn == 128 && cfg.bk == 128) return launch<128, 128, false, kModeGeneral, true>(cfg, map_a, map_b, map_r, map_of, map_oi, kp, epi, stream, dp);
+        return fail(TSB_ERR_UNSUPPORTED, "no projected-shortcut kernel for tile %dx%d", cfg.bn, cfg.bk);
     }
 #define TSB_TC_CASE(BN_, BK_, SWAP_, MODE_) \
     if (cfg.bn == BN_ && cfg.bk == BK_ && (cfg.swap != 0) == SWAP_ && mode == MODE_) return launch<BN_, BK_, SWAP_, MODE_>(cfg, map_a, map_b, map_r, map_of, map_oi, kp, epi, stream)

@@ -85,9 +85,22 @@ int stage_folded(const View &v, const int8_t *x, int x_nhwc, int8_t *staged, cud
 // device buffer of 256 x 8 bytes; null switches it off.
 void set_trace_buffer(unsigned long long *device_buffer);
 #endif
+// A projection shortcut run inside the main convolution's kernel: a 1x1 convolution (any stride, no padding) over the
+// same output pixels, whose dequantized (+ bias) result is the main convolution's residual.  Both tensor maps are
+// encoded with the configuration of choose_config_dual.
+struct DualArgs {
+    const View *view;          // the projection
+    CUtensorMap map_a, map_b;  // its staged activations and packed weights
+    const float *dq, *bias;    // its dequantize scales and bias (may be null), per output channel, device pointers
+};
+// whether `shortcut` can run inside the kernel of `v`; *why names the reason when it cannot
+bool dual_supported(const View &v, const View &shortcut, const char **why);
+// one configuration for the pair: common K block, both weight tiles resident when they fit; bn: 0 = by output channels
+Config choose_config_dual(const View &v, const View &shortcut, int sm_count, int bn);
 // x_staged: the activations the map_a was encoded for (read directly in raw-row mode)
 int launch_conv_tc(const View &v, const Config &cfg, const CUtensorMap &map_a, const CUtensorMap &map_b,
-                   const int8_t *x_staged, const EpiParams &epi, int *status_word, cudaStream_t stream);
+                   const int8_t *x_staged, const EpiParams &epi, int *status_word, cudaStream_t stream,
+                   const DualArgs *dual = nullptr);
 
 }  // namespace tc
 }  // namespace tsb

@@ -80,8 +80,11 @@ class QuantResNet:
     """The network on one GPU: plans, weights and activation buffers are built once; forward() launches only kernels of
     libtennis_b200.so (quantize, convolutions with fused epilogues, max pool, average pool, inner product)."""
 
-    def __init__(self, spec, params, batch, device="cuda"):
+    def __init__(self, spec, params, batch, device="cuda", fuse_projection=True):
         self.spec, self.batch, self.dev = spec, batch, torch.device(device)
+        # the projection shortcut of a stage's first block runs inside the launch of the block's last convolution
+        # (tsb_conv2d_i8_run_projected); False: as a launch of its own whose fp32 output is that convolution's residual
+        self.fuse_projection = fuse_projection
         self.lib = _lib.load()
         dev = self.dev
         self.convs = []
@@ -133,6 +136,26 @@ class QuantResNet:
             self.launch_log.append(dict(name=c["name"], launch=launch, ops=2 * self.batch * c["o"] * c["oh"] * c["oh"] * c["c"] * c["k"] * c["k"],
                                         bytes=in_bytes + out_bytes, k=c["k"], c=c["c"], o=c["o"], size=c["oh"], stride=c["stride"],
                                         residual=residual is not None, fp32_out=bool(want_f32), int8_out=bool(want_i8)))
+        return out_i8, out_f32
+
+    def _conv_projected(self, idx, x_i8, idx_proj, x_proj, key, act):
+        """Convolution idx with the projection idx_proj (over x_proj) as its residual, one launch; int8 and fp32 out."""
+        L, S = self.convs[idx], self.convs[idx_proj]
+        c, cs = L["spec"], S["spec"]
+        out_i8 = self._i8(key + ".i8", c["oh"], c["o"])
+        out_f32 = self._f32(key + ".f32", c["oh"], c["o"])
+
+        def launch():
+            L["plan"].run_projected(x_i8, S["plan"], x_proj, L["dq"], S["dq"], bias=L["bias"], shortcut_bias=S["bias"],
+                                    activation=act, out_f32=out_f32, out_i8=out_i8, requant_scales=L["out_scale_arr"])
+        launch()
+        if self.launch_log is not None:
+            px = self.batch * c["oh"] * c["oh"]
+            in_bytes = (self.batch * c["h"] * c["h"] * ops.padded_channels(c["c"]) + c["o"] * c["c"] * c["k"] * c["k"] + 8 * c["o"] +
+                        self.batch * cs["h"] * cs["h"] * ops.padded_channels(cs["c"]) // (cs["stride"] ** 2) + c["o"] * cs["c"] + 8 * c["o"])
+            self.launch_log.append(dict(name=c["name"] + "+proj", launch=launch, ops=2 * px * c["o"] * (c["c"] * c["k"] * c["k"] + cs["c"]),
+                                        bytes=in_bytes + out_i8.numel() + 4 * px * c["o"], k=c["k"], c=c["c"] + cs["c"], o=c["o"],
+                                        size=c["oh"], stride=c["stride"], residual=False, fp32_out=True, int8_out=True))
         return out_i8, out_f32
 
     def _calibrate_conv(self, idx, x_i8, key, act, residual=None, staged=False, leaky=0.0, residual_after=False):
@@ -227,6 +250,9 @@ class QuantResNet:
             for b in stage:
                 a, _ = self._conv(b["conv1"], x_i8, b["name"] + ".a", ACT_RELU)
                 bb, _ = self._conv(b["conv2"], a, b["name"] + ".b", ACT_RELU)
+                if b["projection"] and self.fuse_projection:
+                    x_i8, x_f32 = self._conv_projected(b["conv3"], bb, b["proj"], x_i8, b["name"] + ".y", ACT_RELU)
+                    continue
                 if b["projection"]:
                     _, sc = self._conv(b["proj"], x_i8, b["name"] + ".sc", ACT_NONE, want_i8=False, want_f32=True)
                 else:

@@ -29,7 +29,9 @@ def reference_forward(spec, params, scales, x, chk):
     return chains.resnet_forward(spec, params, scales, x, chk)
 
 
-def test_small_resnet_matches_the_operator_chain(checker):
+@pytest.mark.parametrize("fuse_projection", [True, False])
+def test_small_resnet_matches_the_operator_chain(checker, fuse_projection):
+    """fuse_projection: the projection shortcuts inside the launch of the blocks' last convolution, or on their own."""
     from tennis_b200 import nets
     spec = nets.resnet_spec(image=64, widths=(64, 128), blocks=(2, 1), classes=10)
     assert len(spec["convs"]) == 1 + (2 * 3 + 1) + (3 + 1)
@@ -37,7 +39,7 @@ def test_small_resnet_matches_the_operator_chain(checker):
     n = 2
     rng = np.random.default_rng(0)
     x = rng.standard_normal((n, 3, 64, 64), dtype=np.float32)
-    net = nets.QuantResNet(spec, params, n)
+    net = nets.QuantResNet(spec, params, n, fuse_projection=fuse_projection)
     xd = torch.from_numpy(x).cuda()
     scales = net.calibrate(xd)
     logits = net.forward(xd).clone()
