@@ -447,6 +447,7 @@ def _main():
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--passes", type=int, default=3)
     args = ap.parse_args()
+    torch.manual_seed(0)
     if args.net == "resnet50":
         batch = args.batch or 64
         spec = resnet_spec()
