@@ -76,7 +76,9 @@ global_avgpool_f32_nhwc_kernel(const float *__restrict__ x, float *__restrict__ 
 // loads kIpN + kIpO values and does kIpN * kIpO multiply-adds, so every loaded value is used several times.  Each output
 // is summed in a fixed order (lane l takes k = l, l+32, ... in sequence, then a butterfly over the lanes), whatever the
 // block shape.
-constexpr int kIpN = 8, kIpO = 4;
+constexpr int kIpN = 8, kIpO = 8;
+// VEC = 4: every lane reads four consecutive k per step as one 16-byte load (rows 16-byte aligned, K a multiple of 4)
+template <int VEC>
 __global__ void __launch_bounds__(kThreads)
 inner_prod_f32_kernel(const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
                       float *__restrict__ y, int N, int K, int O) {
@@ -86,7 +88,8 @@ inner_prod_f32_kernel(const float *__restrict__ x, const float *__restrict__ w, 
     const int n_blocks = (N + kIpN - 1) / kIpN, o_blocks = (O + kIpO - 1) / kIpO;
     const int64_t total = (int64_t)n_blocks * o_blocks;
     for (int64_t i = (int64_t)blockIdx.x * warps_per_block + (threadIdx.x >> 5); i < total; i += (int64_t)gridDim.x * warps_per_block) {
-        const int ob = (int)(i % o_blocks), nb = (int)(i / o_blocks);
+        // neighbouring warps (of one block) take the same rows of w and different rows of x: w comes from HBM once
+        const int ob = (int)(i / n_blocks), nb = (int)(i % n_blocks);
         const float *xr[kIpN];
         const float *wr[kIpO];
 #pragma unroll
@@ -98,16 +101,37 @@ inner_prod_f32_kernel(const float *__restrict__ x, const float *__restrict__ w, 
         for (int a = 0; a < kIpN; ++a)
 #pragma unroll
             for (int b = 0; b < kIpO; ++b) s[a][b] = 0.0f;
-        for (int k = lane; k < K; k += 32) {
-            float xv[kIpN], wv[kIpO];
+        if (VEC == 4) {
+            for (int k = lane * 4; k < K; k += 128) {
+                float4 xv[kIpN], wv[kIpO];
 #pragma unroll
-            for (int a = 0; a < kIpN; ++a) xv[a] = __ldg(xr[a] + k);
+                for (int a = 0; a < kIpN; ++a) xv[a] = __ldg(reinterpret_cast<const float4 *>(xr[a] + k));
 #pragma unroll
-            for (int b = 0; b < kIpO; ++b) wv[b] = __ldg(wr[b] + k);
+                for (int b = 0; b < kIpO; ++b) wv[b] = __ldg(reinterpret_cast<const float4 *>(wr[b] + k));
 #pragma unroll
-            for (int a = 0; a < kIpN; ++a)
+                for (int a = 0; a < kIpN; ++a)
 #pragma unroll
-                for (int b = 0; b < kIpO; ++b) s[a][b] = fmaf(xv[a], wv[b], s[a][b]);
+                    for (int b = 0; b < kIpO; ++b) {
+                        float t = s[a][b];
+                        t = fmaf(xv[a].x, wv[b].x, t);
+                        t = fmaf(xv[a].y, wv[b].y, t);
+                        t = fmaf(xv[a].z, wv[b].z, t);
+                        t = fmaf(xv[a].w, wv[b].w, t);
+                        s[a][b] = t;
+                    }
+            }
+        } else {
+            for (int k = lane; k < K; k += 32) {
+                float xv[kIpN], wv[kIpO];
+#pragma unroll
+                for (int a = 0; a < kIpN; ++a) xv[a] = __ldg(xr[a] + k);
+#pragma unroll
+                for (int b = 0; b < kIpO; ++b) wv[b] = __ldg(wr[b] + k);
+#pragma unroll
+                for (int a = 0; a < kIpN; ++a)
+#pragma unroll
+                    for (int b = 0; b < kIpO; ++b) s[a][b] = fmaf(xv[a], wv[b], s[a][b]);
+            }
         }
 #pragma unroll
         for (int a = 0; a < kIpN; ++a)
@@ -199,7 +223,10 @@ int global_avgpool_f32_nhwc(const float *x, float *y, int n, int pixels, int cha
 int inner_prod_f32(const float *x, const float *w, const float *bias, float *y, int n, int k, int o, cudaStream_t stream) {
     if (!x || !w || !y) return fail(TSB_ERR_INVALID_ARGUMENT, "inner_prod: null pointer");
     if (n < 1 || k < 1 || o < 1) return fail(TSB_ERR_INVALID_ARGUMENT, "inner_prod: bad shape");
-    TSB_CUDA(launch_pdl(inner_prod_f32_kernel, dim3(grid_for((int64_t)((n + kIpN - 1) / kIpN) * ((o + kIpO - 1) / kIpO), kThreads / 32)), dim3(kThreads), 0, stream, x, w, bias, y, n, k, o));
+    const dim3 grid(grid_for((int64_t)((n + kIpN - 1) / kIpN) * ((o + kIpO - 1) / kIpO), kThreads / 32));
+    const bool vec = k % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) == 0;
+    if (vec) TSB_CUDA(launch_pdl(inner_prod_f32_kernel<4>, grid, dim3(kThreads), 0, stream, x, w, bias, y, n, k, o));
+    else TSB_CUDA(launch_pdl(inner_prod_f32_kernel<1>, grid, dim3(kThreads), 0, stream, x, w, bias, y, n, k, o));
     TSB_LAUNCHED("inner_prod_f32_kernel");
     return TSB_OK;
 }
