@@ -59,6 +59,16 @@ struct tsb_conv_plan {
     CUtensorMap map_b, map_b_alt, map_b_stg[3];
     const int8_t *map_a_ptr, *map_a_alt_ptr, *map_a_stg_ptr[3];
     CUtensorMap map_a, map_a_alt, map_a_stg[3];
+    // tsb_conv2d_i8_run_projected: configuration and tensor maps of the last pair, reused while the four pointers, the
+    // shortcut plan and the tile override stay the same
+    struct {
+        const void *x = nullptr, *x2 = nullptr, *w = nullptr, *w2 = nullptr;
+        const tsb_conv_plan *shortcut = nullptr;
+        tsb_conv_desc shortcut_desc;            // (a later plan at the same address may describe another convolution)
+        int tile = -1;
+        tsb::tc::Config cfg;
+        CUtensorMap map_a, map_b, map_a2, map_b2;
+    } pair;
 };
 
 using namespace tsb;
@@ -431,20 +441,28 @@ int tsb_conv2d_i8_run_projected(tsb_conv_plan *plan, const int8_t *x, tsb_conv_p
     int sms = 148, dev = 0;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (sms <= 0) sms = 148;
-    const tc::Config cfg = tc::choose_config_dual(plan->view, shortcut->view, sms, tile_channels);
-    if (cfg.stages < 2 || cfg.dyn_smem > 227u * 1024u) return fail(TSB_ERR_UNSUPPORTED, "run_projected: the pair does not fit shared memory");
-    CUtensorMap map_a, map_b;
-    tc::DualArgs dual;
-    dual.view = &shortcut->view;
-    dual.dq = shortcut_dequantize_scales;
-    dual.bias = shortcut_bias;
     const int8_t *wp = static_cast<const int8_t *>(workspace) + plan->off_weights;
     const int8_t *wp2 = static_cast<const int8_t *>(shortcut->weights_ws) + shortcut->off_weights;
-    if ((st = tc::encode_activation_map(plan->view, cfg, x, &map_a)) != TSB_OK) return st;
-    if ((st = tc::encode_weight_map(plan->view, cfg, wp, &map_b)) != TSB_OK) return st;
-    if ((st = tc::encode_activation_map(shortcut->view, cfg, x_shortcut, &dual.map_a)) != TSB_OK) return st;
-    if ((st = tc::encode_weight_map(shortcut->view, cfg, wp2, &dual.map_b)) != TSB_OK) return st;
-    return tc::launch_conv_tc(plan->view, cfg, map_a, map_b, x, epi, plan->status_word ? plan->status_word : static_cast<int *>(workspace), stream, &dual);
+    auto &pr = plan->pair;
+    if (pr.x != x || pr.x2 != x_shortcut || pr.w != wp || pr.w2 != wp2 || pr.shortcut != shortcut || pr.tile != tile_channels ||
+        memcmp(&pr.shortcut_desc, &shortcut->desc, sizeof(tsb_conv_desc)) != 0) {
+        pr.x = nullptr;     // invalid until every map is encoded
+        pr.cfg = tc::choose_config_dual(plan->view, shortcut->view, sms, tile_channels);
+        if (pr.cfg.stages < 2 || pr.cfg.dyn_smem > 227u * 1024u) return fail(TSB_ERR_UNSUPPORTED, "run_projected: the pair does not fit shared memory");
+        if ((st = tc::encode_activation_map(plan->view, pr.cfg, x, &pr.map_a)) != TSB_OK) return st;
+        if ((st = tc::encode_weight_map(plan->view, pr.cfg, wp, &pr.map_b)) != TSB_OK) return st;
+        if ((st = tc::encode_activation_map(shortcut->view, pr.cfg, x_shortcut, &pr.map_a2)) != TSB_OK) return st;
+        if ((st = tc::encode_weight_map(shortcut->view, pr.cfg, wp2, &pr.map_b2)) != TSB_OK) return st;
+        pr.x = x; pr.x2 = x_shortcut; pr.w = wp; pr.w2 = wp2; pr.shortcut = shortcut; pr.tile = tile_channels;
+        pr.shortcut_desc = shortcut->desc;
+    }
+    tc::DualArgs dual;
+    dual.view = &shortcut->view;
+    dual.map_a = pr.map_a2;
+    dual.map_b = pr.map_b2;
+    dual.dq = shortcut_dequantize_scales;
+    dual.bias = shortcut_bias;
+    return tc::launch_conv_tc(plan->view, pr.cfg, pr.map_a, pr.map_b, x, epi, plan->status_word ? plan->status_word : static_cast<int *>(workspace), stream, &dual);
 }
 
 // what each code of the status word means (the kernel's bounded waits, conv_tc.cu)
