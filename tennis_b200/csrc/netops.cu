@@ -5,6 +5,7 @@
 //   inner_prod             src/kernels/gpu/inner_prod.cu (cuBLAS SGEMM in the reference)
 #include "common.cuh"
 
+#include <algorithm>
 #include <cmath>
 
 namespace tsb {
@@ -15,7 +16,10 @@ constexpr int kThreads = 256;
 // int8 NHWC_PAD max pooling; a window is clipped to the image, as the reference's kernels clip it
 // (src/kernels/cpu/pooling2d_core.cpp:47-93, src/kernels/gpu/pooling2d_core.cu), so taps in the padding never count.
 // quantize is monotonic, so pooling the int8 tensor gives exactly quantize(pool(x)) for the same scale.  One thread
-// produces 16 channels of one output pixel.
+// produces 16 channels of one output pixel.  KFIX > 0: a KFIX x KFIX window as straight-line code -- every tap is loaded
+// (from a clamped address when it lies outside the image, and replaced by -128 afterwards), so all the loads of a thread
+// are in flight together; KFIX = 0: any window, taps outside the image skipped.
+template <int KFIX>
 __global__ void __launch_bounds__(kThreads)
 maxpool_i8_nhwc_kernel(const int8_t *__restrict__ x, int8_t *__restrict__ y, int N, int H, int W, int Cp, int OH, int OW,
                        int K, int S, int pad_t, int pad_l) {
@@ -30,6 +34,32 @@ maxpool_i8_nhwc_kernel(const int8_t *__restrict__ x, int8_t *__restrict__ y, int
         const int ow = (int)(pix - prow * (uint32_t)OW), n = (int)(prow / (uint32_t)OH), oh = (int)(prow - (uint32_t)n * (uint32_t)OH);
         // four int8 lanes per 32-bit word, compared with the per-byte signed maximum
         uint32_t w4[4] = {0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u};
+        if (KFIX > 0) {
+            const int8_t *img = x + (size_t)n * H * W * Cp + u * 16;
+            constexpr int kTaps = KFIX > 0 ? KFIX * KFIX : 1;
+            int4 v[kTaps];
+            bool ok[kTaps];
+#pragma unroll
+            for (int kh = 0; kh < KFIX; ++kh) {
+                const int ih = oh * S - pad_t + kh;
+                const int ihc = min(max(ih, 0), H - 1);
+#pragma unroll
+                for (int kw = 0; kw < KFIX; ++kw) {
+                    const int iw = ow * S - pad_l + kw;
+                    const int iwc = min(max(iw, 0), W - 1);
+                    ok[kh * KFIX + kw] = ih == ihc && iw == iwc;
+                    v[kh * KFIX + kw] = __ldg(reinterpret_cast<const int4 *>(img + ((uint32_t)ihc * (uint32_t)W + (uint32_t)iwc) * (uint32_t)Cp));
+                }
+            }
+#pragma unroll
+            for (int t = 0; t < KFIX * KFIX; ++t) {
+                if (!ok[t]) v[t] = make_int4((int)0x80808080u, (int)0x80808080u, (int)0x80808080u, (int)0x80808080u);
+                w4[0] = __vmaxs4(w4[0], (uint32_t)v[t].x);
+                w4[1] = __vmaxs4(w4[1], (uint32_t)v[t].y);
+                w4[2] = __vmaxs4(w4[2], (uint32_t)v[t].z);
+                w4[3] = __vmaxs4(w4[3], (uint32_t)v[t].w);
+            }
+        } else
         for (int kh = 0; kh < K; ++kh) {
             const int ih = oh * S - pad_t + kh;
             if ((unsigned)ih >= (unsigned)H) continue;
@@ -206,7 +236,10 @@ int maxpool_i8_nhwc(const int8_t *x, int8_t *y, int n, int h, int w, int channel
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) % 16) return fail(TSB_ERR_INVALID_ARGUMENT, "maxpool: tensors must be 16-byte aligned");
     const int64_t items = (int64_t)n * oh * ow * (cp / 16);
     if (items >= (int64_t)1 << 31 || (int64_t)n * h * w * (cp / 16) >= (int64_t)1 << 31) return fail(TSB_ERR_UNSUPPORTED, "maxpool: tensor too large");
-    TSB_CUDA(launch_pdl(maxpool_i8_nhwc_kernel, dim3(grid_for(items, kThreads)), dim3(kThreads), 0, stream, x, y, n, h, w, cp, oh, ow, k, stride,
+    auto kernel = k == 3 ? maxpool_i8_nhwc_kernel<3> : (k == 2 ? maxpool_i8_nhwc_kernel<2> : maxpool_i8_nhwc_kernel<0>);
+    // one item per thread (up to 148 x 64 blocks): the block scheduler evens out what a grid-stride loop of 1.3 rounds would not
+    const int blocks = (int)std::min<int64_t>((items + kThreads - 1) / kThreads, 148 * 64);
+    TSB_CUDA(launch_pdl(kernel, dim3(blocks), dim3(kThreads), 0, stream, x, y, n, h, w, cp, oh, ow, k, stride,
                         pad_top, pad_left));
     TSB_LAUNCHED("maxpool_i8_nhwc_kernel");
     return TSB_OK;
