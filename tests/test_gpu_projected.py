@@ -145,3 +145,23 @@ def test_projected_shortcut_refuses_what_it_cannot_run():
     with pytest.raises(TsbError) as e:
         main.run_projected(x, bad, x, dq, dq, out_f32=out)
     assert "1x1" in str(e.value)
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_projected_shortcut_random_geometry(checker, seed):
+    rng = np.random.default_rng(500 + seed)
+    N = int(rng.integers(2, 5))
+    C, Cs = int(rng.choice([64, 128, 192, 256])), int(rng.choice([64, 128, 192, 320]))
+    H, W = int(rng.integers(3, 21)), int(rng.integers(3, 21))
+    O = int(rng.choice([64, 100, 128, 256, 260, 512]))
+    stride = int(rng.integers(1, 4))
+    tile = int(rng.choice([0, 128, 256]))
+    x, w, xs, ws, dq, dqs, bias, bias_s = make(rng, N, C, Cs, H, W, O, stride)
+    if seed % 4 == 0:
+        bias_s = None
+    rq = (rng.random(N).astype(np.float32) + 0.5) * 25.0
+    act, leaky, after = [("relu", 0.0, False), ("leaky_relu", 0.1, True), ("none", 0.0, False)][seed % 3]
+    want_f, want_q = expected(checker, x, w, xs, ws, (stride, stride), dq, bias, dqs, bias_s, act, leaky, rq, after)
+    got = run_projected(x, w, xs, ws, (stride, stride), dq, bias, dqs, bias_s, act, leaky, rq, res_after=after, tile_channels=tile)
+    assert same_bits(got["f32"], want_f)
+    assert np.array_equal(got["i8"], want_q)
