@@ -552,7 +552,7 @@ def run_cspdarknet(args, dev, rank, world, sharding, peaks):
             "batch_per_gpu": batch, "images_per_sec": images / (ms_max / 1e3), "ms_per_batch": ms_max,
             "e2e_images_per_sec": images / (e2e_max / 1e3), "e2e_ms_per_batch": e2e_max,
             "h2d_bytes_per_batch": hx.numel() * 4 * world, "d2h_bytes_per_batch": houts[0].numel() * houts[0].element_size() * world,
-            "int8_conv_tops": ops_batch * world / (ms_max / 1e3) / 1e12, "kernels_per_pass": 72 + 1 + 5,
+            "int8_conv_tops": ops_batch * world / (ms_max / 1e3) / 1e12, "kernels_per_pass": 72 + 1, "concatenations_inside_transition": 5,
             "parity": parity, "pass_roofline": pass_roofline(layer_times, ms_max, peaks) if layer_times else None,
             "layers": layer_table(layer_times, peaks)}
 

@@ -246,6 +246,19 @@ TSB_API int tsb_conv2d_i8_run_projected(tsb_conv_plan *plan, const int8_t *x, ts
                                         const int8_t *x_shortcut, const float *shortcut_dequantize_scales,
                                         const float *shortcut_bias, const tsb_conv_epilogue *epilogue, int tile_channels,
                                         void *workspace, size_t workspace_bytes, void *stream);
+/*
+ * A convolution over the channel concatenation of two int8 tensors without materialising the concatenation
+ * (`concat` followed by `conv2d_quantized` in a graph: the transition of a cross-stage-partial block).  The weight tensor
+ * [O][C_first + C_rest][KH][KW] is split along its channel axis into two plans: `first` (a 1x1 convolution of any stride
+ * without padding over x_first, the leading C_first channels) and `plan` (over x, the remaining channels; its epilogue,
+ * dequantize scales and bias are those of the whole convolution).  Both parts sum into one int32 accumulator -- int32
+ * sums are exact in any order -- so the result is bit-identical to concatenating first.  Both inputs must have been
+ * quantized with the same scales (as a concatenated tensor would have been).  Layout rules, tile_channels and the
+ * TSB_ERR_UNSUPPORTED fallback are those of tsb_conv2d_i8_run_projected; epilogue->residual must be NULL.
+ */
+TSB_API int tsb_conv2d_i8_run_concat(tsb_conv_plan *plan, const int8_t *x, tsb_conv_plan *first, const int8_t *x_first,
+                                     const tsb_conv_epilogue *epilogue, int tile_channels, void *workspace,
+                                     size_t workspace_bytes, void *stream);
 
 /*
  * Failure detection.  Every wait inside the tensor-core kernel is bounded; a wait that runs out makes the kernel

@@ -74,6 +74,7 @@ SYMBOLS = {
     "tsb_conv2d_i8_quantize_input": (_i, [_vp, _vp, _fp, _i, _vp, _sz, _vp]),
     "tsb_conv2d_i8_run": (_i, [_vp, _vp, _i, ctypes.POINTER(ConvEpilogue), _vp, _sz, _vp]),
     "tsb_conv2d_i8_run_projected": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, ctypes.POINTER(ConvEpilogue), _i, _vp, _sz, _vp]),
+    "tsb_conv2d_i8_run_concat": (_i, [_vp, _vp, _vp, _vp, ctypes.POINTER(ConvEpilogue), _i, _vp, _sz, _vp]),
     "tsb_conv2d_i8_status": (_i, [_vp, _vp, _vp]),
     "tsb_conv2d_i8_status_async": (_i, [_vp, _vp, _vp, _vp]),
     "tsb_conv2d_i8_set_status_word": (_i, [_vp, _vp]),

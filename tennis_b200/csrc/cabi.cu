@@ -417,12 +417,14 @@ int tsb_conv2d_i8_run(tsb_conv_plan *plan, const int8_t *x, int x_layout, const 
     return tc::launch_conv_tc(plan->view, plan->cfg, plan->map_a, plan->map_b, x_tc, epi, plan->status_word ? plan->status_word : static_cast<int *>(workspace), stream);
 }
 
-int tsb_conv2d_i8_run_projected(tsb_conv_plan *plan, const int8_t *x, tsb_conv_plan *shortcut, const int8_t *x_shortcut,
-                                const float *shortcut_dequantize_scales, const float *shortcut_bias,
-                                const tsb_conv_epilogue *epilogue, int tile_channels, void *workspace, size_t workspace_bytes,
-                                void *stream_) {
+// Two convolutions in one launch (conv_tc.cu, DUAL instances).  concat == false: `shortcut` is a projection whose dequantized
+// (+ bias) result is the residual of `plan`.  concat == true: `shortcut` convolves the leading channels of a concatenated
+// input and `plan` the rest; both sum into one accumulator.
+static int run_pair(tsb_conv_plan *plan, const int8_t *x, tsb_conv_plan *shortcut, const int8_t *x_shortcut,
+                    const float *shortcut_dequantize_scales, const float *shortcut_bias, const tsb_conv_epilogue *epilogue,
+                    int tile_channels, void *workspace, size_t workspace_bytes, void *stream_, bool concat) {
     cudaStream_t stream = (cudaStream_t)stream_;
-    if (!plan || !shortcut || !x || !x_shortcut || !shortcut_dequantize_scales || !epilogue || !workspace)
+    if (!plan || !shortcut || !x || !x_shortcut || (!concat && !shortcut_dequantize_scales) || !epilogue || !workspace)
         return fail(TSB_ERR_INVALID_ARGUMENT, "run_projected: null pointer");
     if (workspace_bytes < plan->ws_bytes) return fail(TSB_ERR_WORKSPACE_TOO_SMALL, "run_projected: workspace %zu < %zu", workspace_bytes, plan->ws_bytes);
     if (plan->weights_ws != workspace || !plan->weights_oihw || !shortcut->weights_ws || !shortcut->weights_oihw)
@@ -437,32 +439,47 @@ int tsb_conv2d_i8_run_projected(tsb_conv_plan *plan, const int8_t *x, tsb_conv_p
     EpiParams epi;
     int st = build_epilogue(plan, epilogue, &epi);
     if (st != TSB_OK) return st;
-    epi.res_after = epilogue->residual_after_activation ? 1 : 0;
+    epi.res_after = (!concat && epilogue->residual_after_activation) ? 1 : 0;
     int sms = 148, dev = 0;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (sms <= 0) sms = 148;
     const int8_t *wp = static_cast<const int8_t *>(workspace) + plan->off_weights;
     const int8_t *wp2 = static_cast<const int8_t *>(shortcut->weights_ws) + shortcut->off_weights;
     auto &pr = plan->pair;
-    if (pr.x != x || pr.x2 != x_shortcut || pr.w != wp || pr.w2 != wp2 || pr.shortcut != shortcut || pr.tile != tile_channels ||
+    const int tile_key = tile_channels + (concat ? 1000 : 0);      // the two modes never share a configuration
+    if (pr.x != x || pr.x2 != x_shortcut || pr.w != wp || pr.w2 != wp2 || pr.shortcut != shortcut || pr.tile != tile_key ||
         memcmp(&pr.shortcut_desc, &shortcut->desc, sizeof(tsb_conv_desc)) != 0) {
         pr.x = nullptr;     // invalid until every map is encoded
-        pr.cfg = tc::choose_config_dual(plan->view, shortcut->view, sms, tile_channels);
+        pr.cfg = tc::choose_config_dual(plan->view, shortcut->view, sms, tile_channels, concat);
         if (pr.cfg.stages < 2 || pr.cfg.dyn_smem > 227u * 1024u) return fail(TSB_ERR_UNSUPPORTED, "run_projected: the pair does not fit shared memory");
         if ((st = tc::encode_activation_map(plan->view, pr.cfg, x, &pr.map_a)) != TSB_OK) return st;
         if ((st = tc::encode_weight_map(plan->view, pr.cfg, wp, &pr.map_b)) != TSB_OK) return st;
         if ((st = tc::encode_activation_map(shortcut->view, pr.cfg, x_shortcut, &pr.map_a2)) != TSB_OK) return st;
         if ((st = tc::encode_weight_map(shortcut->view, pr.cfg, wp2, &pr.map_b2)) != TSB_OK) return st;
-        pr.x = x; pr.x2 = x_shortcut; pr.w = wp; pr.w2 = wp2; pr.shortcut = shortcut; pr.tile = tile_channels;
+        pr.x = x; pr.x2 = x_shortcut; pr.w = wp; pr.w2 = wp2; pr.shortcut = shortcut; pr.tile = tile_key;
         pr.shortcut_desc = shortcut->desc;
     }
     tc::DualArgs dual;
     dual.view = &shortcut->view;
     dual.map_a = pr.map_a2;
     dual.map_b = pr.map_b2;
-    dual.dq = shortcut_dequantize_scales;
-    dual.bias = shortcut_bias;
+    dual.dq = concat ? nullptr : shortcut_dequantize_scales;
+    dual.bias = concat ? nullptr : shortcut_bias;
     return tc::launch_conv_tc(plan->view, pr.cfg, pr.map_a, pr.map_b, x, epi, plan->status_word ? plan->status_word : static_cast<int *>(workspace), stream, &dual);
+}
+
+int tsb_conv2d_i8_run_projected(tsb_conv_plan *plan, const int8_t *x, tsb_conv_plan *shortcut, const int8_t *x_shortcut,
+                                const float *shortcut_dequantize_scales, const float *shortcut_bias,
+                                const tsb_conv_epilogue *epilogue, int tile_channels, void *workspace, size_t workspace_bytes,
+                                void *stream) {
+    return run_pair(plan, x, shortcut, x_shortcut, shortcut_dequantize_scales, shortcut_bias, epilogue, tile_channels, workspace,
+                    workspace_bytes, stream, false);
+}
+
+int tsb_conv2d_i8_run_concat(tsb_conv_plan *plan, const int8_t *x, tsb_conv_plan *first, const int8_t *x_first,
+                             const tsb_conv_epilogue *epilogue, int tile_channels, void *workspace, size_t workspace_bytes,
+                             void *stream) {
+    return run_pair(plan, x, first, x_first, nullptr, nullptr, epilogue, tile_channels, workspace, workspace_bytes, stream, true);
 }
 
 // what each code of the status word means (the kernel's bounded waits, conv_tc.cu)

@@ -759,6 +759,9 @@ struct alignas(64) DualParams {
     const float *dq2, *bias2;     // its dequantize scales and (optional) bias, per output channel
     int k2_iters;                 // its K blocks per tile: Cp2 / BK
     int Cp2, a2_tiled, sh2, sw2;
+    int concat;                   // 1: no second accumulator and no residual -- the second convolution's K blocks are summed into
+                                  // the main accumulator, i.e. ONE convolution over the channel concatenation of the two inputs
+                                  // (int32 sums are exact in any order); dq2 / bias2 are unused
 };
 struct NoDual {};
 constexpr int kMaxStages = 24;
@@ -781,7 +784,7 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                   const __grid_constant__ CUtensorMap map_oi, const __grid_constant__ KernelParams kp,
                   const __grid_constant__ EpiParams epi,
                   const __grid_constant__ std::conditional_t<DUAL, DualParams, NoDual> dual) {
-    static_assert(!DUAL || (!SWAP && MODE == kModeGeneral && BN >= 128), "projected-shortcut kernels: normal orientation, general mode");
+    static_assert(!DUAL || (!SWAP && MODE == kModeGeneral), "projected-shortcut kernels: normal orientation, general mode");
     constexpr int PIX = SWAP ? BN : kBM;      // pixels per tile
     constexpr int CH = SWAP ? kBM : BN;       // output channels per tile
     constexpr uint32_t kPixBytes = PIX * BK, kWgtBytes = CH * BK;
@@ -812,7 +815,8 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const int total_tiles = kp.num_m_tiles * kp.num_n_tiles;
     const int k_iters = kp.KH * kp.KW * (kp.Cp / BK);
     int k_sc = 0;                              // K blocks of the projection, which come first in every tile
-    if constexpr (DUAL) k_sc = dual.k2_iters;
+    bool concat = false;
+    if constexpr (DUAL) { k_sc = dual.k2_iters; concat = dual.concat != 0; }
     // This CTA's tiles.  Streaming weights: tiles blockIdx.x, +gridDim.x, ... with the channel tile running fastest.
     // Resident weights: one contiguous range of the channel-major tile order, so the weight tile changes at most a
     // few times.
@@ -1050,7 +1054,7 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 }
                 tc_fence_after();
                 if (me == 0) TSB_TRACE(local, 2);
-                uint32_t d_tmem = tmem_base + (uint32_t)(DUAL ? (2 * acc + 1) * BN : acc * BN);   // DUAL: the projection's accumulator first
+                uint32_t d_tmem = tmem_base + (uint32_t)(DUAL ? (2 * acc + (concat ? 0 : 1)) * BN : acc * BN);   // DUAL: the projection's accumulator first
                 uint32_t accumulate = 0;
                 if (MODE == kModePatch) {
                     const int n_cb = kp.Cp / BK;
@@ -1202,7 +1206,7 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                         }
                     };
                     for (int it = 0; it < k_iters + k_sc; it += G) {
-                        if (DUAL && it == k_sc) { d_tmem -= BN; accumulate = 0u; }   // the main convolution's accumulator
+                        if (DUAL && it == k_sc && !concat) { d_tmem -= BN; accumulate = 0u; }   // the main convolution's accumulator
                         TSB_CYC_START;
                         if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
                             if (!*abort_flag) { *abort_flag = 1; atomicExch(kp.status, 3); }
@@ -1277,7 +1281,7 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     t_dq[j] = o < epi.O ? epi.dq[o] : 0.0f;
                     t_bias[j] = (o < epi.O && epi.bias) ? epi.bias[o] : 0.0f;
                     if constexpr (DUAL) {                   // the projection's table: the next slot
-                        t_dq[2 * BN + j] = o < epi.O ? dual.dq2[o] : 0.0f;
+                        t_dq[2 * BN + j] = (o < epi.O && dual.dq2) ? dual.dq2[o] : 0.0f;
                         t_dq[3 * BN + j] = (o < epi.O && dual.bias2) ? dual.bias2[o] : 0.0f;
                     }
                 }
@@ -1372,7 +1376,7 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                         if constexpr (DUAL) {
                             // the projection's 32 channels of this pixel, dequantized (+ bias), into the thread's own row of
                             // the fp32 tile -- where a tensor-map load would have put a residual
-                            if (real) {
+                            if (real && !concat) {
                                 tmem_ld32(taddr0 + (uint32_t)(BN + col0), v);
                                 tmem_ld_wait();
                                 const bool bias2 = dual.bias2 != nullptr;
@@ -1402,8 +1406,8 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                         if (real) tmem_ld_wait();
                         bool fine = true;
                         if (stg_ok) {
-                            if (epi.res_after) TSB_EPI_DISPATCH_W(fine =, staged_chunk_t, true, v, t_dq + col0, t_bias + col0, epi.leaky, r_row, key, real && (has_res || DUAL), has_f32, q_row, has_i8, rs);
-                            else TSB_EPI_DISPATCH_W(fine =, staged_chunk_t, false, v, t_dq + col0, t_bias + col0, epi.leaky, r_row, key, real && (has_res || DUAL), has_f32, q_row, has_i8, rs);
+                            if (epi.res_after) TSB_EPI_DISPATCH_W(fine =, staged_chunk_t, true, v, t_dq + col0, t_bias + col0, epi.leaky, r_row, key, real && (has_res || (DUAL && !concat)), has_f32, q_row, has_i8, rs);
+                            else TSB_EPI_DISPATCH_W(fine =, staged_chunk_t, false, v, t_dq + col0, t_bias + col0, epi.leaky, r_row, key, real && (has_res || (DUAL && !concat)), has_f32, q_row, has_i8, rs);
                         }
                         fence_async_smem();
                         // all four warps have written their rows; the OR says whether any value needs the exact slow path
@@ -1428,9 +1432,9 @@ conv_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                                 const int o = o_base + col0 + j;
                                 const int a = real ? tmem_ld1(taddr0 + (uint32_t)(col0 + j)) : 0;
                                 int a2 = 0;
-                                if constexpr (DUAL) a2 = real ? tmem_ld1(taddr0 + (uint32_t)(BN + col0 + j)) : 0;
+                                if constexpr (DUAL) a2 = (real && !concat) ? tmem_ld1(taddr0 + (uint32_t)(BN + col0 + j)) : 0;
                                 if (!live) continue;
-                                if (DUAL && o < epi.O) {
+                                if (DUAL && !concat && o < epi.O) {
                                     float r = __fmul_rn(__int2float_rn(a2), t_dq[2 * BN + col0 + j]);
                                     if constexpr (DUAL) { if (dual.bias2) r = __fadd_rn(r, t_dq[3 * BN + col0 + j]); }
                                     epilogue_store_value(epi, img, o, p, a, r, true);
@@ -1903,7 +1907,7 @@ bool dual_supported(const View &v, const View &sc, const char **why) {
     return true;
 }
 
-Config choose_config_dual(const View &v, const View &sc, int sm_count, int bn) {
+Config choose_config_dual(const View &v, const View &sc, int sm_count, int bn, bool concat) {
     const ConvGeom &g = v.g, &s = sc.g;
     Config c;
     c.bk = (g.Cp % 128 == 0 && s.Cp % 128 == 0) ? 128 : 64;
@@ -1911,6 +1915,7 @@ Config choose_config_dual(const View &v, const View &sc, int sm_count, int bn) {
     // 128 channels per tile: four accumulator buffers hold two tiles, so the MMAs of one tile run under the epilogue of
     // the other (256 would fill tensor memory with a single tile; measured 10-25 % slower on the ResNet-50 shapes)
     c.bn = bn == 128 || bn == 256 ? bn : 128;
+    if (concat && bn == 0 && g.O <= 64) c.bn = 64;      // one accumulator per tile: a narrow layer keeps its narrow tile
     c.pix = kBM;
     c.ch = c.bn;
     const int64_t M = (int64_t)g.N * g.OH * g.OW;
@@ -2182,7 +2187,10 @@ int launch_conv_tc(const View &v, const Config &cfg, const CUtensorMap &map_a, c
     CUtensorMap map_of = map_b, map_oi = map_b;
     kp.stg_off = cfg.stg_off;
     kp.stg_f32 = cfg.staging == 2 ? 1 : 0;
-    const int want_staging = dual ? 2 : (cfg.swap ? 0 : staging_level(v, epi));
+    // (a projection needs the staged epilogue, whose fp32 tile receives its result; a concatenation takes whatever epilogue
+    // its outputs would take in a plain run -- int8 alone goes out through the direct path, which is faster for it)
+    const bool dual_concat = dual && dual->dq == nullptr;
+    const int want_staging = (dual && !dual_concat) ? 2 : (cfg.swap ? 0 : staging_level(v, epi));
     if (want_staging != 0 && cfg.staging >= want_staging && load_driver() == TSB_OK) {
         const ConvGeom &r = v.real;
         auto encode = [&](CUtensorMap *map, const void *ptr, bool is_f32, uint64_t channels) -> bool {
@@ -2223,16 +2231,21 @@ int launch_conv_tc(const View &v, const Config &cfg, const CUtensorMap &map_a, c
         }
     }
     if (dual) {
-        if (kp.epi_mode != kEpiStaged) return fail(TSB_ERR_UNSUPPORTED, "projected shortcut: the output tensor maps could not be encoded");
+        if (!dual_concat && kp.epi_mode != kEpiStaged) return fail(TSB_ERR_UNSUPPORTED, "projected shortcut: the output tensor maps could not be encoded");
+        if (dual_concat && kp.epi_mode != kEpiStaged && kp.epi_mode != kEpiI8Nhwc && kp.epi_mode != kEpiNhwc)
+            return fail(TSB_ERR_UNSUPPORTED, "concatenated input: outputs must be pixel-major fp32 and / or NHWC_PAD int8 with half-away rounding");
         const ConvGeom &s = dual->view->g;
         DualParams dp;
         dp.map_a2 = dual->map_a; dp.map_b2 = dual->map_b;
         dp.dq2 = dual->dq; dp.bias2 = dual->bias;
+        dp.concat = dual->dq == nullptr ? 1 : 0;
         dp.k2_iters = s.Cp / cfg.bk; dp.Cp2 = s.Cp; dp.a2_tiled = dual->view->a_tiled; dp.sh2 = s.sh; dp.sw2 = s.sw;
         if (cfg.bn == 256 && cfg.bk == 64) return launch<256, 64, false, kModeGeneral, true>(cfg, map_a, map_b, map_r, map_of, map_oi, kp, epi, stream, dp);
         if (cfg.bn == 256 && cfg.bk == 128) return launch<256, 128, false, kModeGeneral, true>(cfg, map_a, map_b, map_r, map_of, map_oi, kp, epi, stream, dp);
         if (cfg.bn == 128 && cfg.bk == 64) return launch<128, 64, false, kModeGeneral, true>(cfg, map_a, map_b, map_r, map_of, map_oi, kp, epi, stream, dp);
         if (cfg.bn == 128 && cfg.bk == 128) return launch<128, 128, false, kModeGeneral, true>(cfg, map_a, map_b, map_r, map_of, map_oi, kp, epi, stream, dp);
+        if (cfg.bn == 64 && cfg.bk == 64 && dual_concat) return launch<64, 64, false, kModeGeneral, true>(cfg, map_a, map_b, map_r, map_of, map_oi, kp, epi, stream, dp);
+        if (cfg.bn == 64 && cfg.bk == 128 && dual_concat) return launch<64, 128, false, kModeGeneral, true>(cfg, map_a, map_b, map_r, map_of, map_oi, kp, epi, stream, dp);
         return fail(TSB_ERR_UNSUPPORTED, "no projected-shortcut kernel for tile %dx%d", cfg.bn, cfg.bk);
     }
 #define TSB_TC_CASE(BN_, BK_, SWAP_, MODE_) \

@@ -92,11 +92,13 @@ struct DualArgs {
     const View *view;          // the projection
     CUtensorMap map_a, map_b;  // its staged activations and packed weights
     const float *dq, *bias;    // its dequantize scales and bias (may be null), per output channel, device pointers
+                               // dq == null: channel concatenation -- `view` convolves the FIRST part of the concatenated input
+                               // and its K blocks are summed into the main convolution's accumulator; no residual
 };
 // whether `shortcut` can run inside the kernel of `v`; *why names the reason when it cannot
 bool dual_supported(const View &v, const View &shortcut, const char **why);
 // one configuration for the pair: common K block, both weight tiles resident when they fit; bn: 0 = by output channels
-Config choose_config_dual(const View &v, const View &shortcut, int sm_count, int bn);
+Config choose_config_dual(const View &v, const View &shortcut, int sm_count, int bn, bool concat = false);
 // x_staged: the activations the map_a was encoded for (read directly in raw-row mode)
 int launch_conv_tc(const View &v, const Config &cfg, const CUtensorMap &map_a, const CUtensorMap &map_b,
                    const int8_t *x_staged, const EpiParams &epi, int *status_word, cudaStream_t stream,

@@ -364,6 +364,41 @@ class QuantCSPDarknet(QuantResNet):
     ``quantize -> conv2d_quantized -> add_bias -> leaky_relu [-> add]``; the two routes of a stage are requantized with the
     same scale (that of the transition convolution's input) and joined by tsb_concat_i8_nhwc."""
 
+    def __init__(self, spec, params, batch, device="cuda", fuse_concat=True):
+        super().__init__(spec, params, batch, device)
+        # the transition convolution of a stage reads its two halves (post, route a) directly, each through a plan over
+        # its half of the weight columns (tsb_conv2d_i8_run_concat); False: an int8 concatenation kernel runs first
+        self.fuse_concat = fuse_concat
+        self.halves = {}
+        for st in spec["stages"]:
+            idx, half = st["transition"], st["half"]
+            c, w = spec["convs"][idx], params["convs"][idx]["w"]
+            shape = (batch, half, c["h"], c["h"])
+            pair = []
+            for part in (w[:, :half], w[:, half:]):
+                plan = ops.ConvPlan(shape, (c["o"], half, 1, 1), (0,) * 4, (1, 1), (1, 1), 0.0, _lib.KERNEL_AUTO, self.dev)
+                plan.set_weights(torch.from_numpy(np.ascontiguousarray(part)).to(self.dev))
+                pair.append(plan)
+            self.halves[idx] = pair
+
+    def _conv_concat(self, idx, first, rest, key, act, leaky):
+        """Transition idx over concat(first, rest) without the concatenation; int8 out."""
+        L = self.convs[idx]
+        c = L["spec"]
+        p_first, p_rest = self.halves[idx]
+        out_i8 = self._i8(key + ".i8", c["oh"], c["o"])
+
+        def launch():
+            p_rest.run_concat(rest, p_first, first, L["dq"], bias=L["bias"], activation=act, leaky=leaky, out_i8=out_i8,
+                              requant_scales=L["out_scale_arr"])
+        launch()
+        if self.launch_log is not None:
+            px = self.batch * c["oh"] * c["oh"]
+            self.launch_log.append(dict(name=c["name"] + "+concat", launch=launch, ops=2 * px * c["o"] * c["c"],
+                                        bytes=px * ops.padded_channels(c["c"]) + c["o"] * c["c"] + 8 * c["o"] + out_i8.numel(),
+                                        k=1, c=c["c"], o=c["o"], size=c["oh"], stride=1, residual=False, fp32_out=False, int8_out=True))
+        return out_i8
+
     def _concat(self, a, ca, b, cb, key, size):
         out = self._i8(key, size, ca + cb)
         check(self.lib.tsb_concat_i8_nhwc(a.data_ptr(), ca, b.data_ptr(), cb, out.data_ptr(), self.batch * size * size,
@@ -420,8 +455,11 @@ class QuantCSPDarknet(QuantResNet):
                 s_cat = None
             post, _ = run(st["post"], xb_i8, st["name"] + ".post", sb, out_scale=s_cat)
             ra, _ = run(st["route_a"], cur, st["name"] + ".ra", s_down, out_scale=s_cat)
-            cat = self._concat(post, half, ra, half, st["name"] + ".cat", size)
-            cur, _ = run(st["transition"], cat, st["name"] + ".out", self.convs[st["post"]]["out_scale"])
+            if self.fuse_concat and not calibrate:
+                cur = self._conv_concat(st["transition"], post, ra, st["name"] + ".out", act, LEAKY)
+            else:
+                cat = self._concat(post, half, ra, half, st["name"] + ".cat", size)
+                cur, _ = run(st["transition"], cat, st["name"] + ".out", self.convs[st["post"]]["out_scale"])
             cur_scale = self.convs[st["transition"]]["out_scale"]
         return cur
 

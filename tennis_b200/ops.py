@@ -219,6 +219,29 @@ class ConvPlan:
             _ptr(shortcut_bias) if shortcut_bias is not None else None, ctypes.byref(e), int(tile_channels),
             _ptr(self.workspace), self.ws_bytes, _stream_ptr(stream)))
 
+    def run_concat(self, x, first, x_first, dq, bias=None, activation=ACT_NONE, leaky=0.0, out_f32=None, out_i8=None,
+                   requant_scales=None, stream=None, tile_channels=0):
+        """The convolution over concat(x_first, x) along channels in one launch (tsb_conv2d_i8_run_concat): `first` holds the
+        weight columns of the leading channels (a 1x1 plan), this plan the rest; NHWC_PAD int8 inputs quantized with the
+        same scales, pixel-major fp32 / NHWC_PAD int8 outputs."""
+        e = ConvEpilogue()
+        e.dequantize_scales = dq.data_ptr()
+        e.bias = bias.data_ptr() if bias is not None else None
+        e.residual = None
+        e.activation = int(activation)
+        e.leaky_scale = float(leaky)
+        e.out_f32 = out_f32.data_ptr() if out_f32 is not None else None
+        e.out_f32_layout = LAYOUT_NHWC_PAD
+        e.out_i8 = out_i8.data_ptr() if out_i8 is not None else None
+        e.out_i8_layout = LAYOUT_NHWC_PAD
+        keep = None
+        if requant_scales is not None:
+            keep = requant_scales if isinstance(requant_scales, ctypes.Array) else float_array(requant_scales)
+            e.requant_scales_host = keep
+            e.n_requant_scales = len(requant_scales)
+        check(_lib.load().tsb_conv2d_i8_run_concat(self.handle, _ptr(x), first.handle, _ptr(x_first), ctypes.byref(e),
+                                                   int(tile_channels), _ptr(self.workspace), self.ws_bytes, _stream_ptr(stream)))
+
     def status(self, stream=None):
         check(_lib.load().tsb_conv2d_i8_status(self.handle, _ptr(self.workspace), _stream_ptr(stream)))
 

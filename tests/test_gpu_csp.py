@@ -14,7 +14,9 @@ def reference_forward(spec, params, scales, x, chk):
     return chains.cspdarknet_forward(spec, params, scales, x, chk, leaky=nets.LEAKY)
 
 
-def test_small_cspdarknet_matches_the_operator_chain(checker):
+@pytest.mark.parametrize("fuse_concat", [True, False])
+def test_small_cspdarknet_matches_the_operator_chain(checker, fuse_concat):
+    """fuse_concat: the transition convolutions read their two halves directly, or an int8 concatenation runs first."""
     from tennis_b200 import nets
     spec = nets.cspdarknet_spec(image=64, widths=(64, 128), blocks=(1, 2))
     assert len(spec["convs"]) == 1 + (5 + 2 * 1) + (5 + 2 * 2)
@@ -22,7 +24,7 @@ def test_small_cspdarknet_matches_the_operator_chain(checker):
     n = 2
     rng = np.random.default_rng(1)
     x = rng.random((n, 3, 64, 64), dtype=np.float32)
-    net = nets.QuantCSPDarknet(spec, params, n)
+    net = nets.QuantCSPDarknet(spec, params, n, fuse_concat=fuse_concat)
     xd = torch.from_numpy(x).cuda()
     scales = net.calibrate(xd)
     out = net.forward(xd).clone()

@@ -165,3 +165,48 @@ def test_projected_shortcut_random_geometry(checker, seed):
     got = run_projected(x, w, xs, ws, (stride, stride), dq, bias, dqs, bias_s, act, leaky, rq, res_after=after, tile_channels=tile)
     assert same_bits(got["f32"], want_f)
     assert np.array_equal(got["i8"], want_q)
+
+
+# N, C_first, C_rest, H, W, O, tile_channels
+CONCAT_CASES = [
+    (2, 64, 64, 12, 12, 64, 0),
+    (2, 64, 64, 12, 12, 128, 256),
+    (3, 128, 128, 9, 7, 256, 0),
+    (2, 256, 256, 6, 6, 512, 0),
+    (2, 64, 192, 5, 5, 200, 0),
+    (40, 64, 64, 28, 28, 128, 0),          # several tiles per CTA
+]
+
+
+@pytest.mark.parametrize("case", CONCAT_CASES)
+def test_convolution_over_a_concatenation_without_the_concatenation(checker, case):
+    """tsb_conv2d_i8_run_concat against concat -> conv2d_quantized -> add_bias -> leaky_relu -> quantize of the checker."""
+    from tennis_b200 import ops
+    N, C1, C2, H, W, O, tile = case
+    rng = np.random.default_rng(sum(case))
+    x1 = rng.integers(-128, 128, (N, C1, H, W), dtype=np.int8)
+    x2 = rng.integers(-128, 128, (N, C2, H, W), dtype=np.int8)
+    w = rng.integers(-127, 128, (O, C1 + C2, 1, 1), dtype=np.int8)
+    dq = (rng.random(O).astype(np.float32) + 0.5) * 1e-3
+    bias = rng.standard_normal(O).astype(np.float32)
+    rq = (rng.random(N).astype(np.float32) + 0.5) * 20.0
+    y = checker.conv2d_quantized(np.concatenate([x1, x2], axis=1), w, (0, 0, 0, 0), (1, 1), (1, 1), dq, 0.0)
+    y = checker.activation(checker.add_bias(y, bias), "leaky_relu", 0.1)
+    want_q = checker.quantize(y, rq)
+
+    dev = torch.device("cuda")
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    first = ops.ConvPlan(x1.shape, (O, C1, 1, 1), (0, 0, 0, 0), (1, 1), (1, 1), 0.0, 2, dev)
+    first.set_weights(t(w[:, :C1]))
+    rest = ops.ConvPlan(x2.shape, (O, C2, 1, 1), (0, 0, 0, 0), (1, 1), (1, 1), 0.0, 2, dev)
+    rest.set_weights(t(w[:, C1:]))
+    out_f32 = torch.full((N, H, W, O), float("nan"), dtype=torch.float32, device=dev)
+    out_i8 = torch.full((N, H, W, ops.padded_channels(O)), 99, dtype=torch.int8, device=dev)
+    rest.run_concat(ops.repack_nchw_to_nhwc(t(x2)), first, ops.repack_nchw_to_nhwc(t(x1)), t(dq), bias=t(bias), activation=2,
+                    leaky=0.1, out_f32=out_f32, out_i8=out_i8, requant_scales=list(rq), tile_channels=tile)
+    rest.status()
+    torch.cuda.synchronize()
+    assert same_bits(out_f32.cpu().numpy().transpose(0, 3, 1, 2), y)
+    q = out_i8.cpu().numpy()
+    assert not q[..., O:].any()
+    assert np.array_equal(q[..., :O].transpose(0, 3, 1, 2), want_q)
