@@ -104,75 +104,93 @@ global_avgpool_f32_nhwc_kernel(const float *__restrict__ x, float *__restrict__ 
 
 // y[n][o] = sum_k x[n][k] * w[o][k] + bias[o].  A warp owns a block of kIpN images x kIpO outputs: per step of 32 k's it
 // loads kIpN + kIpO values and does kIpN * kIpO multiply-adds, so every loaded value is used several times.  Each output
-// is summed in a fixed order (lane l takes k = l, l+32, ... in sequence, then a butterfly over the lanes), whatever the
-// block shape.
-constexpr int kIpN = 8, kIpO = 8;
+// is summed in a fixed order (lane l of K slice s takes its k's in sequence, then a butterfly over the lanes, then the
+// slices in order), whatever the block shape.
+constexpr int kIpN = 4, kIpO = 8;
 // VEC = 4: every lane reads four consecutive k per step as one 16-byte load (rows 16-byte aligned, K a multiple of 4)
+constexpr int kIpKS = 2;     // warps that share one block of outputs, each on every kIpKS-th step along K
 template <int VEC>
 __global__ void __launch_bounds__(kThreads)
 inner_prod_f32_kernel(const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
                       float *__restrict__ y, int N, int K, int O) {
+    static_assert(kIpN * kIpO == 32, "the final sum gives one output to every lane");
+    __shared__ float part[kThreads / 32][kIpN * kIpO];
     pdl_sync();
-    const int warps_per_block = kThreads / 32;
-    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int slots = kThreads / 32 / kIpKS;              // output blocks a thread block works on at a time
+    const int slot = warp / kIpKS, ks = warp % kIpKS;
     const int n_blocks = (N + kIpN - 1) / kIpN, o_blocks = (O + kIpO - 1) / kIpO;
     const int64_t total = (int64_t)n_blocks * o_blocks;
-    for (int64_t i = (int64_t)blockIdx.x * warps_per_block + (threadIdx.x >> 5); i < total; i += (int64_t)gridDim.x * warps_per_block) {
+    const int64_t per_round = (int64_t)gridDim.x * slots;
+    for (int64_t base = 0; base < total; base += per_round) {     // the same number of rounds for every thread (barriers inside)
+        const int64_t i = base + (int64_t)blockIdx.x * slots + slot;
+        const bool active = i < total;
         // neighbouring warps (of one block) take the same rows of w and different rows of x: w comes from HBM once
-        const int ob = (int)(i / n_blocks), nb = (int)(i % n_blocks);
-        const float *xr[kIpN];
-        const float *wr[kIpO];
+        const int ob = active ? (int)(i / n_blocks) : 0, nb = active ? (int)(i % n_blocks) : 0;
+        if (active) {
+            const float *xr[kIpN];
+            const float *wr[kIpO];
 #pragma unroll
-        for (int a = 0; a < kIpN; ++a) xr[a] = x + (int64_t)min(nb * kIpN + a, N - 1) * K;   // clamped: extra rows are not stored
+            for (int a = 0; a < kIpN; ++a) xr[a] = x + (int64_t)min(nb * kIpN + a, N - 1) * K;   // clamped: extra rows are not stored
 #pragma unroll
-        for (int b = 0; b < kIpO; ++b) wr[b] = w + (int64_t)min(ob * kIpO + b, O - 1) * K;
-        float s[kIpN][kIpO];
+            for (int b = 0; b < kIpO; ++b) wr[b] = w + (int64_t)min(ob * kIpO + b, O - 1) * K;
+            float s[kIpN][kIpO];
 #pragma unroll
-        for (int a = 0; a < kIpN; ++a)
+            for (int a = 0; a < kIpN; ++a)
 #pragma unroll
-            for (int b = 0; b < kIpO; ++b) s[a][b] = 0.0f;
-        if (VEC == 4) {
-            for (int k = lane * 4; k < K; k += 128) {
-                float4 xv[kIpN], wv[kIpO];
+                for (int b = 0; b < kIpO; ++b) s[a][b] = 0.0f;
+            if (VEC == 4) {
+                for (int k = (ks * 32 + lane) * 4; k < K; k += 128 * kIpKS) {
+                    float4 xv[kIpN], wv[kIpO];
 #pragma unroll
-                for (int a = 0; a < kIpN; ++a) xv[a] = __ldg(reinterpret_cast<const float4 *>(xr[a] + k));
+                    for (int a = 0; a < kIpN; ++a) xv[a] = __ldg(reinterpret_cast<const float4 *>(xr[a] + k));
 #pragma unroll
-                for (int b = 0; b < kIpO; ++b) wv[b] = __ldg(reinterpret_cast<const float4 *>(wr[b] + k));
+                    for (int b = 0; b < kIpO; ++b) wv[b] = __ldg(reinterpret_cast<const float4 *>(wr[b] + k));
 #pragma unroll
-                for (int a = 0; a < kIpN; ++a)
+                    for (int a = 0; a < kIpN; ++a)
 #pragma unroll
-                    for (int b = 0; b < kIpO; ++b) {
-                        float t = s[a][b];
-                        t = fmaf(xv[a].x, wv[b].x, t);
-                        t = fmaf(xv[a].y, wv[b].y, t);
-                        t = fmaf(xv[a].z, wv[b].z, t);
-                        t = fmaf(xv[a].w, wv[b].w, t);
-                        s[a][b] = t;
-                    }
+                        for (int b = 0; b < kIpO; ++b) {
+                            float t = s[a][b];
+                            t = fmaf(xv[a].x, wv[b].x, t);
+                            t = fmaf(xv[a].y, wv[b].y, t);
+                            t = fmaf(xv[a].z, wv[b].z, t);
+                            t = fmaf(xv[a].w, wv[b].w, t);
+                            s[a][b] = t;
+                        }
+                }
+            } else {
+                for (int k = ks * 32 + lane; k < K; k += 32 * kIpKS) {
+                    float xv[kIpN], wv[kIpO];
+#pragma unroll
+                    for (int a = 0; a < kIpN; ++a) xv[a] = __ldg(xr[a] + k);
+#pragma unroll
+                    for (int b = 0; b < kIpO; ++b) wv[b] = __ldg(wr[b] + k);
+#pragma unroll
+                    for (int a = 0; a < kIpN; ++a)
+#pragma unroll
+                        for (int b = 0; b < kIpO; ++b) s[a][b] = fmaf(xv[a], wv[b], s[a][b]);
+                }
             }
-        } else {
-            for (int k = lane; k < K; k += 32) {
-                float xv[kIpN], wv[kIpO];
 #pragma unroll
-                for (int a = 0; a < kIpN; ++a) xv[a] = __ldg(xr[a] + k);
+            for (int a = 0; a < kIpN; ++a)
 #pragma unroll
-                for (int b = 0; b < kIpO; ++b) wv[b] = __ldg(wr[b] + k);
+                for (int b = 0; b < kIpO; ++b) {
+                    float t = s[a][b];
 #pragma unroll
-                for (int a = 0; a < kIpN; ++a)
-#pragma unroll
-                    for (int b = 0; b < kIpO; ++b) s[a][b] = fmaf(xv[a], wv[b], s[a][b]);
-            }
+                    for (int off = 16; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
+                    if (lane == 0) part[warp][a * kIpO + b] = t;
+                }
         }
+        __syncthreads();
+        if (active && ks == 0) {
+            // lane l adds the K slices of output (l / kIpO, l % kIpO) in a fixed order
+            float t = part[warp][lane];
 #pragma unroll
-        for (int a = 0; a < kIpN; ++a)
-#pragma unroll
-            for (int b = 0; b < kIpO; ++b) {
-                float t = s[a][b];
-#pragma unroll
-                for (int off = 16; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
-                const int n = nb * kIpN + a, o = ob * kIpO + b;
-                if (lane == 0 && n < N && o < O) y[(int64_t)n * O + o] = bias ? t + bias[o] : t;
-            }
+            for (int q = 1; q < kIpKS; ++q) t += part[warp + q][lane];
+            const int n = nb * kIpN + lane / kIpO, o = ob * kIpO + lane % kIpO;
+            if (n < N && o < O) y[(int64_t)n * O + o] = bias ? t + bias[o] : t;
+        }
+        __syncthreads();
     }
 }
 
@@ -256,7 +274,7 @@ int global_avgpool_f32_nhwc(const float *x, float *y, int n, int pixels, int cha
 int inner_prod_f32(const float *x, const float *w, const float *bias, float *y, int n, int k, int o, cudaStream_t stream) {
     if (!x || !w || !y) return fail(TSB_ERR_INVALID_ARGUMENT, "inner_prod: null pointer");
     if (n < 1 || k < 1 || o < 1) return fail(TSB_ERR_INVALID_ARGUMENT, "inner_prod: bad shape");
-    const dim3 grid(grid_for((int64_t)((n + kIpN - 1) / kIpN) * ((o + kIpO - 1) / kIpO), kThreads / 32));
+    const dim3 grid(grid_for((int64_t)((n + kIpN - 1) / kIpN) * ((o + kIpO - 1) / kIpO), kThreads / 32 / kIpKS));
     const bool vec = k % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) == 0;
     if (vec) TSB_CUDA(launch_pdl(inner_prod_f32_kernel<4>, grid, dim3(kThreads), 0, stream, x, w, bias, y, n, k, o));
     else TSB_CUDA(launch_pdl(inner_prod_f32_kernel<1>, grid, dim3(kThreads), 0, stream, x, w, bias, y, n, k, o));
